@@ -1,0 +1,376 @@
+"""Drop-in for the reference's ``brt._C.router`` extension.
+
+Same function names, argument order, defaults, return shapes and error type
+(``RuntimeError``) as the pybind module defined in src/backend/torch/router.cc:479-513 of
+the reference.  Shape logic and output allocation live here (torch's caching allocator);
+all device work goes through the C ABI in ``include/brt_b200.h``.  Differences that are
+deliberate:
+
+* bf16 is accepted wherever fp16 is (the reference raises for bf16);
+* kernels are enqueued on the *current* stream (the reference uses the default stream;
+  identical when the current stream is the default one);
+* outputs are never pre-zeroed by a separate memset: the kernels write every byte.
+"""
+from typing import List, Optional
+
+import torch
+
+from .. import _lib
+
+_DT = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+
+
+def _check_cuda(t: torch.Tensor, name: str):
+    if not t.is_cuda:
+        # wording of CHECK_ON_CUDA, src/backend/torch/torch.h:20
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _int32c(t: torch.Tensor, name: str) -> torch.Tensor:
+    if t.dtype != torch.int32:
+        raise RuntimeError(f"{name} must be an int32 tensor, got {t.dtype}")
+    return t if t.is_contiguous() else t.contiguous()
+
+
+class _ScratchPool:
+    """One reusable scratch buffer per (device, purpose).  Reuse is safe for calls enqueued
+    on the same stream; a different stream gets its own buffer."""
+
+    def __init__(self):
+        self._bufs = {}
+
+    def get(self, purpose: str, device: torch.device, nbytes: int) -> torch.Tensor:
+        key = (purpose, device.index, torch.cuda.current_stream(device).cuda_stream)
+        buf = self._bufs.get(key)
+        if buf is None or buf.numel() < nbytes:
+            buf = torch.empty(max(nbytes, 1 << 16), dtype=torch.uint8, device=device)
+            self._bufs[key] = buf
+        return buf
+
+
+_scratch = _ScratchPool()
+
+
+def throttle_hotmask(hotmask: torch.Tensor, prefix: torch.Tensor, threshold: torch.Tensor):
+    """src/backend/torch/router.cc:15-31.  ``prefix`` is updated in place and returned."""
+    _check_cuda(hotmask, "hotmask")
+    _check_cuda(prefix, "prefix")
+    _check_cuda(threshold, "threshold")
+    if hotmask.size(1) != prefix.size(0) or hotmask.size(1) != threshold.size(0):
+        raise RuntimeError("CHECK_EQ fails.")
+    hotmask = _int32c(hotmask, "hotmask")
+    threshold = _int32c(threshold, "threshold")
+    if prefix.dtype != torch.int32 or not prefix.is_contiguous():
+        raise RuntimeError("prefix must be a contiguous int32 tensor (it is updated in place)")
+    T, E = hotmask.shape
+    with torch.cuda.device(hotmask.device):
+        out = torch.empty_like(hotmask)
+        nbytes = _lib.query("brt_index_scratch_bytes", T, E)
+        scratch = _scratch.get("index", hotmask.device, nbytes)
+        _lib.call("brt_throttle_hotmask", _ptr(hotmask), _ptr(out), _ptr(prefix),
+                  _ptr(threshold), T, E, _ptr(scratch), scratch.numel(),
+                  _stream(hotmask.device))
+    return out, prefix
+
+
+def generate_indices_and_loads(
+    hot_mask: torch.Tensor,
+    supported_capacities: Optional[torch.Tensor] = None,
+    capacity_padding: bool = False,
+    path_wise_padding: bool = False,
+    is_tag_index: bool = False,
+):
+    """src/backend/torch/router.cc:48-80."""
+    _check_cuda(hot_mask, "hot_mask")
+    hot_mask = _int32c(hot_mask, "hot_mask")
+    T, E = hot_mask.shape
+    with torch.cuda.device(hot_mask.device):
+        if hot_mask.numel() == 0:
+            return (torch.zeros((0, E), dtype=torch.int32, device=hot_mask.device),
+                    torch.zeros((E,), dtype=torch.int32, device=hot_mask.device))
+        caps = None
+        ncap = 0
+        if supported_capacities is not None:
+            _check_cuda(supported_capacities, "supported_capacities.value()")
+            caps = _int32c(supported_capacities, "supported_capacities")
+            ncap = caps.size(0)
+        indices = torch.empty_like(hot_mask)
+        loads = torch.empty((E,), dtype=torch.int32, device=hot_mask.device)
+        nbytes = _lib.query("brt_index_scratch_bytes", T, E)
+        scratch = _scratch.get("index", hot_mask.device, nbytes)
+        _lib.call("brt_generate_indices_and_loads", _ptr(hot_mask), _ptr(indices), _ptr(loads),
+                  T, E, _ptr(caps), ncap, int(bool(capacity_padding)),
+                  int(bool(path_wise_padding)), int(bool(is_tag_index)), _ptr(scratch),
+                  scratch.numel(), _stream(hot_mask.device))
+    return indices, loads
+
+
+def convert_index_format(origin_indices: torch.Tensor, loads: torch.Tensor, is_to_tag: bool):
+    """src/backend/torch/router.cc:90-110.  As in the reference, ``is_to_tag`` travels into
+    the launcher's ``tag_to_seat`` argument, so ``True`` converts tag indices to seat
+    indices."""
+    _check_cuda(origin_indices, "origin_indices")
+    origin = _int32c(origin_indices, "origin_indices")
+    T, E = origin.shape
+    with torch.cuda.device(origin.device):
+        cuda_loads = loads
+        if not loads.is_cuda:
+            if is_to_tag:
+                # the reference only moves CPU loads when is_to_tag is false and then hands a
+                # host pointer to the kernel; refuse instead of faulting
+                raise RuntimeError("loads must be a CUDA tensor")
+            cuda_loads = loads.to(origin.device, non_blocking=True)
+        cuda_loads = _int32c(cuda_loads, "loads")
+        out = torch.empty_like(origin)
+        _lib.call("brt_convert_index_format", _ptr(origin), _ptr(out), _ptr(cuda_loads), T, E,
+                  int(bool(is_to_tag)), _stream(origin.device))
+    return out
+
+
+def dispatch_with_indices_and_loads(
+    in_data: torch.Tensor,
+    route_indices: torch.Tensor,
+    loads: torch.Tensor,
+    gates: Optional[torch.Tensor] = None,
+    tag_generating: bool = False,
+    tags: Optional[torch.Tensor] = None,
+    max_path_padding: bool = False,
+    max_path_load: int = 0,
+    is_1d_routing: bool = True,
+    is_tag_index: bool = False,
+) -> List[torch.Tensor]:
+    """src/backend/torch/router.cc:131-273."""
+    _check_cuda(in_data, "in_data")
+    _check_cuda(route_indices, "route_indices")
+    dev = in_data.device
+    with torch.cuda.device(dev):
+        cell_num = in_data.size(0)
+        path_num = route_indices.size(1)
+        if cell_num == 0:
+            shape = list(in_data.shape)
+            if is_1d_routing:
+                shape[0] = 0
+            else:
+                if len(shape) == 2:
+                    shape.append(1)
+                shape[1] = 0
+                shape = shape[1:]
+            out = [torch.zeros(shape, dtype=in_data.dtype, device=dev)]
+            if tag_generating:
+                out.append(torch.zeros((0,), dtype=route_indices.dtype, device=dev))
+            return out
+        if in_data.dtype not in _DT:
+            raise NotImplementedError("data type is not supported")
+        cell_size = in_data.numel() // cell_num
+        if not is_1d_routing:
+            cell_size //= path_num
+        if in_data.dtype == torch.float16 and cell_size % 2 != 0:
+            raise RuntimeError("cell_size must be even when data type is float16")
+        route_indices = _int32c(route_indices, "route_indices")
+        cuda_loads = loads if loads.is_cuda else loads.to(dev, non_blocking=True)
+        cuda_loads = _int32c(cuda_loads, "loads")
+        # output size: the one host<->device sync of this op, as in the reference
+        if max_path_padding:
+            mpl = int(max_path_load) if max_path_load > 0 else int(loads.max().item())
+            total = mpl * path_num
+        else:
+            mpl = 0
+            total = int(loads.sum().item())
+        shape = list(in_data.shape)
+        if is_1d_routing:
+            shape[0] = total
+        else:
+            if len(shape) == 2:
+                shape.append(1)
+            shape[1] = total
+            shape = shape[1:]
+        src = in_data if in_data.is_contiguous() else in_data.contiguous()
+        out = torch.empty(shape, dtype=in_data.dtype, device=dev)
+        g = None
+        if gates is not None:
+            if not is_1d_routing:
+                raise RuntimeError("CHECK fails.")
+            _check_cuda(gates, "gates.value()")
+            if gates.dtype != in_data.dtype:
+                raise RuntimeError("CHECK_EQ fails.")
+            g = gates if gates.is_contiguous() else gates.contiguous()
+        old_tags = new_tags = None
+        if tag_generating:
+            if tags is None:
+                old_tags = torch.arange(1, cell_num + 1, dtype=route_indices.dtype, device=dev)
+            else:
+                _check_cuda(tags, "tags.value()")
+                if tags.dtype != route_indices.dtype:
+                    raise RuntimeError("CHECK_EQ fails.")
+                old_tags = tags if tags.is_contiguous() else tags.contiguous()
+            new_tags = torch.empty((total,), dtype=route_indices.dtype, device=dev)
+        nbytes = _lib.query("brt_dispatch_scratch_bytes", total, path_num)
+        scratch = _scratch.get("dispatch", dev, nbytes)
+        _lib.call("brt_dispatch_with_indices_and_loads", _ptr(src), _ptr(out), _ptr(g),
+                  _ptr(route_indices), _ptr(cuda_loads), _ptr(old_tags), _ptr(new_tags),
+                  cell_num, cell_size, path_num, mpl, total, int(bool(is_1d_routing)),
+                  int(bool(is_tag_index)), _DT[in_data.dtype], _ptr(scratch), scratch.numel(),
+                  _stream(dev))
+    if tag_generating:
+        return [out, new_tags]
+    return [out]
+
+
+def split_fused_cells_to_paths(
+    in_data: torch.Tensor,
+    loads: torch.Tensor,
+    max_path_padding: bool = False,
+    is_load_split: bool = False,
+    is_tag_split: bool = False,
+    tags: Optional[torch.Tensor] = None,
+):
+    """src/backend/torch/router.cc:285-335: per-path views of the fused tensor."""
+    path_num = loads.numel()
+    if is_tag_split:
+        is_load_split = True
+        if tags is None:
+            raise RuntimeError("CHECK fails.")
+    datas, loads_l, tags_l = [], [], []
+    if max_path_padding:
+        mpl = in_data.size(0) // path_num
+        for i in range(path_num):
+            datas.append(in_data.narrow(0, i * mpl, mpl))
+            if is_load_split:
+                loads_l.append(loads.narrow(0, i, 1))
+            if is_tag_split:
+                tags_l.append(tags.narrow(0, i * mpl, mpl))
+    else:
+        cpu_loads = loads.cpu().tolist()
+        start = 0
+        for i in range(path_num):
+            n = int(cpu_loads[i])
+            datas.append(in_data.narrow(0, start, n))
+            if is_load_split:
+                loads_l.append(loads.narrow(0, i, 1))
+            if is_tag_split:
+                tags_l.append(tags.narrow(0, start, n))
+            start += n
+    if is_tag_split:
+        return [datas, loads_l, tags_l]
+    if is_load_split:
+        return [datas, loads_l]
+    return [datas]
+
+
+def fuse_split_cells_from_paths(
+    in_data: List[torch.Tensor],
+    is_load_fuse: bool = False,
+    is_tag_fuse: bool = False,
+    loads: Optional[List[torch.Tensor]] = None,
+    tags: Optional[List[torch.Tensor]] = None,
+):
+    """src/backend/torch/router.cc:348-369."""
+    out = torch.cat(in_data, 0)
+    if is_load_fuse:
+        if loads is None:
+            raise RuntimeError("CHECK fails.")
+        return [out, torch.cat(loads, 0)]
+    if is_tag_fuse:
+        if tags is None:
+            raise RuntimeError("CHECK fails.")
+        all_tags = torch.cat(tags, 0)
+        new_tags, inverse = torch.unique(all_tags, sorted=True, return_inverse=True)
+        return [out, new_tags, inverse]
+    return [out]
+
+
+def combine_with_indices_and_loads(
+    in_data: torch.Tensor,
+    route_indices: torch.Tensor,
+    loads: Optional[torch.Tensor] = None,
+    gates: Optional[torch.Tensor] = None,
+    out_data: Optional[torch.Tensor] = None,
+    max_path_padding: bool = False,
+    ever_padded: bool = True,
+    is_tag_index: bool = False,
+    tags: Optional[torch.Tensor] = None,
+) -> List[torch.Tensor]:
+    """src/backend/torch/router.cc:372-473."""
+    _check_cuda(in_data, "in_data")
+    _check_cuda(route_indices, "route_indices")
+    dev = in_data.device
+    with torch.cuda.device(dev):
+        cell_num = route_indices.size(0)
+        if cell_num == 0:
+            if not is_tag_index:
+                return [out_data if out_data is not None else torch.empty_like(in_data)]
+            return [torch.empty_like(in_data), torch.empty_like(tags), torch.zeros_like(tags)]
+        if cell_num == 1:
+            # single-cell shortcut of the reference binding (router.cc:402-412)
+            if not is_tag_index:
+                return [out_data + in_data] if out_data is not None else [in_data]
+            return [in_data, tags, torch.ones_like(tags)]
+        if not is_tag_index:
+            if loads is None:
+                raise RuntimeError("CHECK fails.")
+            if in_data.dtype not in _DT:
+                raise NotImplementedError("data type is not supported")
+            cuda_loads = _int32c(loads.to(dev, non_blocking=True), "loads")
+            route_indices = _int32c(route_indices, "route_indices")
+            path_num = route_indices.size(1)
+            rows = in_data.size(0)
+            cell_size = in_data.numel() // rows if rows else 0
+            if rows == 0:
+                # nothing was routed anywhere; the shape of a cell is still known
+                cell_size = 1
+                for s in in_data.shape[1:]:
+                    cell_size *= s
+            g = None
+            gdt = 0
+            if gates is not None:
+                _check_cuda(gates, "gates.value()")
+                if gates.dtype not in (torch.float32, in_data.dtype):
+                    raise RuntimeError("gates must be float32 or match the data type")
+                g = gates if gates.is_contiguous() else gates.contiguous()
+                gdt = _DT[g.dtype]
+            mpl = rows // path_num if max_path_padding else 0
+            src = in_data if in_data.is_contiguous() else in_data.contiguous()
+            if out_data is not None:
+                _check_cuda(out_data, "out_data_t")
+                if not out_data.is_contiguous() or out_data.dtype != in_data.dtype:
+                    raise RuntimeError("out_data must be contiguous and match in_data's dtype")
+                out, residual = out_data, 1
+            else:
+                out = torch.empty((cell_num,) + tuple(in_data.shape[1:]), dtype=in_data.dtype,
+                                  device=dev)
+                residual = 0
+            _lib.call("brt_combine_with_indices_and_loads", _ptr(src), _ptr(out), _ptr(g),
+                      _ptr(route_indices), _ptr(cuda_loads), cell_num, cell_size, path_num, mpl,
+                      residual, _DT[in_data.dtype], gdt, _stream(dev))
+            return [out]
+        # tag branch (router.cc:449-472): sum of rows per unique tag
+        if tags is None:
+            raise RuntimeError("CHECK fails.")
+        cell_size = in_data.numel() // in_data.size(0)
+        n = tags.size(0)
+        tags_value = tags
+        if out_data is not None:
+            _check_cuda(out_data, "out_data_t")
+            if out_data.size(0) != n:
+                raise RuntimeError("CHECK_EQ fails.")
+            # the reference calls the functional scatter_reduce and drops its result, so the
+            # caller's tensor comes back unchanged
+            out = out_data
+        else:
+            flat = in_data.reshape(in_data.size(0), cell_size)
+            out = torch.zeros((n, cell_size), dtype=in_data.dtype, device=dev)
+            out.index_add_(0, route_indices.reshape(-1).to(torch.int64), flat)
+            out = out.reshape((n,) + tuple(in_data.shape[1:]))
+            if ever_padded and int(tags_value[0].item()) == 0:
+                out = out.narrow(0, 1, n - 1)
+                tags_value = tags_value.narrow(0, 1, n - 1)
+        out_loads = torch.tensor([tags_value.numel()], dtype=torch.int32, device=dev)
+        return [out, tags_value, out_loads]

@@ -1,0 +1,82 @@
+"""ctypes binding of ``libbrt_b200.so`` (the C ABI declared in ``include/brt_b200.h``).
+
+There is no fallback: if the library is missing or a call fails, a ``RuntimeError`` says
+so.  Pointers are passed as integers (``tensor.data_ptr()``), streams as
+``torch.cuda.current_stream().cuda_stream``.
+"""
+import ctypes
+from pathlib import Path
+
+_PKG = Path(__file__).resolve().parent
+LIB_PATH = _PKG / "libbrt_b200.so"
+
+_lib = None
+
+_vp = ctypes.c_void_p
+_i64 = ctypes.c_int64
+_i32 = ctypes.c_int32
+_int = ctypes.c_int
+_sz = ctypes.c_size_t
+
+# name -> (restype, argtypes); kept in step with include/brt_b200.h
+SIGNATURES = {
+    "brt_abi_version": (_int, []),
+    "brt_last_error": (ctypes.c_char_p, []),
+    "brt_index_scratch_bytes": (_sz, [_i64, _int]),
+    "brt_generate_indices_and_loads": (
+        _int, [_vp, _vp, _vp, _i64, _int, _vp, _int, _int, _int, _int, _vp, _sz, _vp]),
+    "brt_throttle_hotmask": (_int, [_vp, _vp, _vp, _vp, _i64, _int, _vp, _sz, _vp]),
+    "brt_convert_index_format": (_int, [_vp, _vp, _vp, _i64, _int, _int, _vp]),
+    "brt_dispatch_scratch_bytes": (_sz, [_i64, _int]),
+    "brt_dispatch_with_indices_and_loads": (
+        _int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _i32, _i64, _int, _int,
+               _int, _vp, _sz, _vp]),
+    "brt_combine_with_indices_and_loads": (
+        _int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _i32, _int, _int, _int, _vp]),
+}
+
+
+class BrtError(RuntimeError):
+    pass
+
+
+def load():
+    """Load the shared library once; raise if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise BrtError(
+            f"{LIB_PATH} is missing: build it with `python -m brainstorm_b200.build` "
+            "(there is no CPU or eager fallback)")
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name, (res, args) in SIGNATURES.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError:
+            continue  # reported by exported_symbols()/call()
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def exported(name: str) -> bool:
+    return hasattr(load(), name)
+
+
+def call(name: str, *args):
+    """Call a status-returning entry point; raise BrtError with the library's message."""
+    lib = load()
+    fn = getattr(lib, name, None)
+    if fn is None:
+        raise BrtError(f"libbrt_b200.so does not export {name}")
+    rc = fn(*args)
+    if rc != 0:
+        msg = lib.brt_last_error().decode("utf-8", "replace")
+        raise BrtError(f"{name} failed (status {rc}): {msg}")
+
+
+def query(name: str, *args):
+    """Call an entry point that returns a value rather than a status."""
+    return getattr(load(), name)(*args)

@@ -1,0 +1,148 @@
+/*
+ * brt_b200 — C ABI of the B200-native routing hot path.
+ *
+ * One shared library (libbrt_b200.so) exports these entry points.  They take raw
+ * device pointers, sizes and a CUDA stream; they never allocate device memory,
+ * never synchronise the host with the device and never touch a tensor library.
+ * Every function returns 0 on success or a brt_status code; the text of the last
+ * error on the calling thread is available from brt_last_error().
+ *
+ * Each entry point names the interface of the reference project
+ * (Raphael-Hao/brainstorm) that it stands in for, as path:line in that project.
+ *
+ * Conventions
+ *   - all index, load, tag and mask arrays are int32, row-major, device memory;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream);
+ *   - `dtype` is a brt_dtype; cell_size counts elements of that type per cell;
+ *   - scratch buffers are caller-owned device memory, at least as large as the
+ *     matching *_scratch_bytes() query says and 256-byte aligned; their contents
+ *     on entry are irrelevant and they may be reused by the next call on the
+ *     same stream.
+ */
+#ifndef BRT_B200_H_
+#define BRT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define BRT_API __attribute__((visibility("default")))
+#else
+#define BRT_API
+#endif
+
+typedef enum brt_status {
+  BRT_OK = 0,
+  BRT_ERR_INVALID_ARGUMENT = 1, /* bad size, null pointer, unsupported flag combination */
+  BRT_ERR_CUDA = 2,             /* a CUDA runtime call or launch failed */
+  BRT_ERR_SCRATCH_TOO_SMALL = 3,
+  BRT_ERR_UNSUPPORTED = 4,
+  BRT_ERR_NCCL = 5,
+  BRT_ERR_NOT_INITIALIZED = 6,
+  BRT_ERR_TIMEOUT = 7 /* a bounded device-side wait ran out */
+} brt_status;
+
+typedef enum brt_dtype { BRT_F32 = 0, BRT_F16 = 1, BRT_BF16 = 2 } brt_dtype;
+
+/* ABI revision; bumped on any signature change. */
+BRT_API int brt_abi_version(void);
+/* Message of the last failing call made by this thread ("" if none). */
+BRT_API const char* brt_last_error(void);
+
+/* ------------------------------------------------------------------ router: indices */
+
+/* Scratch needed by brt_generate_indices_and_loads / brt_throttle_hotmask. */
+BRT_API size_t brt_index_scratch_bytes(int64_t cell_num, int path_num);
+
+/*
+ * Replaces brt::router::GenerateIndicesAndLoads
+ * (include/brt/router/location.h:29-39, src/router/location.cu:335-379).
+ *
+ * hot_mask[cell_num, path_num] -> indices[cell_num, path_num], loads[path_num].
+ * Seat mode: indices[t,e] = mask[t,e] * (sum of mask[0..t, e]).  Tag mode:
+ * indices[r-1, e] = t+1 for the r-th routed cell of path e, 0 elsewhere.
+ * loads follow the reference's capacity rules (path_wise_padding only with
+ * capacity_padding; capacity_padding needs supported_capacity_num >= 1).
+ * `indices` is fully written (it does not have to be zeroed by the caller).
+ */
+BRT_API int brt_generate_indices_and_loads(const int32_t* hot_mask, int32_t* indices,
+                                           int32_t* loads, int64_t cell_num, int path_num,
+                                           const int32_t* supported_capacities,
+                                           int supported_capacity_num, int capacity_padding,
+                                           int path_wise_padding, int is_tag_index,
+                                           void* scratch, size_t scratch_bytes, void* stream);
+
+/*
+ * Replaces brt::router::ThrottleHotmask
+ * (include/brt/router/location.h:13-19, src/router/location.cu:59-130,304-315).
+ *
+ * throttled[t,e] = (hotmask[t,e] == 1 && prefix[e] + sum(hotmask[0..t, e]) <= threshold[e]);
+ * prefix[e] <- min(prefix[e] + sum(hotmask[:, e]), threshold[e]) in place (untouched when
+ * cell_num == 0).  `throttled` is fully written.
+ */
+BRT_API int brt_throttle_hotmask(const int32_t* hotmask, int32_t* throttled, int32_t* prefix,
+                                 const int32_t* threshold, int64_t cell_num, int path_num,
+                                 void* scratch, size_t scratch_bytes, void* stream);
+
+/*
+ * Replaces brt::router::ConvertIndexFormat
+ * (include/brt/router/location.h:21-27, src/router/location.cu:259-333).
+ * tag_to_seat != 0: new[tag-1, e] = r+1 for rows r < loads[e] with a non-zero tag;
+ * tag_to_seat == 0: new[seat-1, e] = t+1 for non-zero seats.  `new_indices` is
+ * fully written.  Entries that would land outside [0, cell_num) are ignored.
+ */
+BRT_API int brt_convert_index_format(const int32_t* origin_indices, int32_t* new_indices,
+                                     const int32_t* loads, int64_t cell_num, int path_num,
+                                     int tag_to_seat, void* stream);
+
+/* ------------------------------------------------------------------ router: data movement */
+
+/* Scratch needed by brt_dispatch_with_indices_and_loads for `total_rows` output rows. */
+BRT_API size_t brt_dispatch_scratch_bytes(int64_t total_rows, int path_num);
+
+/*
+ * Replaces brt::router::DispatchWithIndicesAndLoads<T>
+ * (include/brt/router/route.h:14-28, src/router/route.cu:13-206,284-465).
+ *
+ * 1-D routing: src[cell_num, cell_size]; 2-D routing: src[cell_num, path_num, cell_size]
+ * (path e takes element e of each cell; no gates).  dst has `total_rows` rows:
+ * path e starts at row e*max_path_load when max_path_load != 0, otherwise at
+ * sum(loads[0..e)).  A cell goes to row base(e)+seat-1 when 0 < seat <= loads[e].
+ * Rows of dst (and of new_tags) that no kept cell lands on are written as zero by
+ * this call: the caller does not pre-zero anything.  gates (optional, 1-D only) has
+ * the data's dtype and scales the copied row; old_tags/new_tags (optional, both or
+ * neither) carry the cell tags.  is_tag_index != 0 reads route_indices as tag indices
+ * (row i < loads[e] of path e pulls cell tag-1; a zero tag leaves the row zero).
+ */
+BRT_API int brt_dispatch_with_indices_and_loads(
+    const void* src_data, void* dst_data, const void* gates, const int32_t* route_indices,
+    const int32_t* loads, const int32_t* old_tags, int32_t* new_tags, int64_t cell_num,
+    int64_t cell_size, int path_num, int32_t max_path_load, int64_t total_rows,
+    int is_1d_routing, int is_tag_index, int dtype, void* scratch, size_t scratch_bytes,
+    void* stream);
+
+/*
+ * Replaces brt::router::CombineWithIndicesAndLoads<T>
+ * (include/brt/router/route.h:30-44, src/router/route.cu:208-282,467-522).
+ *
+ * dst[t, :] = sum over paths e in ascending order with 0 < seat <= loads[e] of
+ * src[base(e)+seat-1, :] (* gates[t,e]); every product and every add is rounded to
+ * fp32 separately, the sum starts from +0.  is_residual == 0: every row of dst is
+ * written (zero when the cell has no kept route).  is_residual != 0: only rows
+ * with at least one kept route are replaced, the others keep the caller's data.
+ * dtype is the element type of src/dst (16-bit types accumulate in fp32 and round
+ * once on store); gates_dtype is BRT_F32 or equal to dtype.
+ */
+BRT_API int brt_combine_with_indices_and_loads(
+    const void* src_data, void* dst_data, const void* gates, const int32_t* route_indices,
+    const int32_t* loads, int64_t cell_num, int64_t cell_size, int path_num,
+    int32_t max_path_load, int is_residual, int dtype, int gates_dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BRT_B200_H_ */

@@ -1,0 +1,328 @@
+"""Parity of the CUDA router ops (through the C ABI) with the CPU checker.
+
+Integer outputs (indices, loads, masks, tags) and unweighted dispatch are compared bit for
+bit; weighted dispatch and combine are compared bit for bit too (the kernels keep the
+checker's operation order), which is tighter than the 1e-6 (fp32) / 1e-2 (bf16) relative
+tolerance the path is specified with.
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
+
+
+@pytest.fixture(scope="module")
+def R():
+    from brainstorm_b200._C import router
+
+    return router
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a))
+    if dtype in ("f16", "bf16"):
+        t = t.view(torch.int16).view(DTYPES[dtype])
+    return t.cuda()
+
+
+def host(t):
+    if t.dtype in (torch.float16, torch.bfloat16):
+        return t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+    return t.cpu().numpy()
+
+
+def rand_mask(rng, T, E, k):
+    return oracle.topk_hot_mask(rng.standard_normal((T, E)).astype(np.float32), k)
+
+
+INDEX_CASES = [
+    # T, E, k
+    (16, 4, 2), (1, 1, 1), (31, 2, 1), (33, 3, 2), (1037, 5, 2), (4096, 8, 1), (512, 16, 4),
+    (4096, 16, 4), (777, 12, 3), (2048, 32, 2), (1500, 64, 2), (3000, 128, 1), (260, 260, 3),
+    (70, 1028, 5), (100000, 8, 1),
+]
+
+
+@pytest.mark.parametrize("T,E,k", INDEX_CASES)
+@pytest.mark.parametrize("tag", [False, True])
+def test_generate_indices(R, T, E, k, tag):
+    rng = np.random.default_rng(T * 131 + E)
+    mask = rand_mask(rng, T, E, k)
+    exp_i, exp_l = oracle.generate_indices_and_loads(mask, is_tag_index=tag)
+    got_i, got_l = R.generate_indices_and_loads(dev(mask), is_tag_index=tag)
+    assert np.array_equal(host(got_l), exp_l)
+    assert np.array_equal(host(got_i), exp_i)
+
+
+@pytest.mark.parametrize("caps,cpad,pwise", [
+    ([1, 2, 4, 8, 16, 32, 64, 128, 256, 512], False, False),
+    ([1, 2, 4, 8, 16, 32, 64, 128], False, False),
+    ([1, 2, 4, 8, 16, 32, 64, 128, 256, 512], True, False),
+    ([16, 32, 100], True, False),
+    ([2, 4, 8, 16, 32, 64, 128, 256], True, True),
+    ([2, 4, 8, 16, 32, 64, 128, 256], False, True),
+])
+def test_generate_indices_capacities(R, caps, cpad, pwise):
+    rng = np.random.default_rng(len(caps) * 7 + cpad)
+    mask = rand_mask(rng, 600, 8, 3)
+    mask[:, 5] = 0  # an empty path
+    for tag in (False, True):
+        exp_i, exp_l = oracle.generate_indices_and_loads(mask, caps, cpad, pwise, tag)
+        got_i, got_l = R.generate_indices_and_loads(
+            dev(mask), dev(np.array(caps, dtype=np.int32)), cpad, pwise, tag)
+        assert np.array_equal(host(got_l), exp_l)
+        assert np.array_equal(host(got_i), exp_i)
+
+
+def test_generate_indices_golden(R, golden_dir):
+    z = np.load(golden_dir / "ref_python_vectors.npz")
+    names = sorted({k.split("/")[1] for k in z.files if k.startswith("idx/")})
+    for name in names:
+        caps = z[f"idx/{name}/caps"]
+        cpad, pwise = (bool(x) for x in z[f"idx/{name}/flags"])
+        for kind in ("seat", "tag"):
+            got_i, got_l = R.generate_indices_and_loads(
+                dev(z[f"idx/{name}/mask"]), dev(caps) if caps.size else None, cpad, pwise,
+                kind == "tag")
+            assert np.array_equal(host(got_i), z[f"idx/{name}/{kind}_indices"]), (name, kind)
+            assert np.array_equal(host(got_l), z[f"idx/{name}/{kind}_loads"]), (name, kind)
+
+
+def test_generate_indices_errors_and_empty(R):
+    i, l = R.generate_indices_and_loads(torch.zeros((0, 4), dtype=torch.int32, device="cuda"))
+    assert i.shape == (0, 4) and l.tolist() == [0, 0, 0, 0]
+    with pytest.raises(RuntimeError):
+        R.generate_indices_and_loads(torch.zeros((4, 4), dtype=torch.int32))  # CPU tensor
+    with pytest.raises(RuntimeError):
+        R.generate_indices_and_loads(torch.ones((4, 4), dtype=torch.int32, device="cuda"),
+                                     None, True)
+
+
+def test_generate_indices_general_integers(R):
+    """Masks holding values other than 0/1 follow index = running sum * value
+    (src/router/location.cu:176-178)."""
+    rng = np.random.default_rng(5)
+    mask = rng.integers(0, 4, size=(900, 8)).astype(np.int32)
+    exp_i, exp_l = oracle.generate_indices_and_loads(mask)
+    got_i, got_l = R.generate_indices_and_loads(dev(mask))
+    assert np.array_equal(host(got_i), exp_i) and np.array_equal(host(got_l), exp_l)
+    # the binary path must come back on the next call through the same scratch
+    mask = rand_mask(rng, 900, 8, 2)
+    exp_i, exp_l = oracle.generate_indices_and_loads(mask)
+    got_i, got_l = R.generate_indices_and_loads(dev(mask))
+    assert np.array_equal(host(got_i), exp_i) and np.array_equal(host(got_l), exp_l)
+
+
+def test_generate_indices_unaligned_view(R):
+    """A mask whose storage offset breaks 16-byte alignment takes the narrow-vector path."""
+    rng = np.random.default_rng(9)
+    mask = rand_mask(rng, 500, 8, 2)
+    flat = torch.zeros(500 * 8 + 1, dtype=torch.int32, device="cuda")
+    view = flat[1:].view(500, 8)
+    view.copy_(dev(mask))
+    exp_i, exp_l = oracle.generate_indices_and_loads(mask)
+    got_i, got_l = R.generate_indices_and_loads(view)
+    assert np.array_equal(host(got_i), exp_i) and np.array_equal(host(got_l), exp_l)
+
+
+def test_throttle_golden(R, golden_dir):
+    import json
+
+    v = json.load(open(golden_dir / "notebook_vectors.json"))["throttle"]
+    prefix = dev(np.array(v["prefix_in"], dtype=np.int32))
+    out, p2 = R.throttle_hotmask(dev(np.array(v["hot_mask"], dtype=np.int32)), prefix,
+                                 dev(np.array(v["threshold"], dtype=np.int32)))
+    assert p2 is prefix
+    assert host(out).tolist() == v["throttled_mask"]
+    assert host(prefix).tolist() == v["prefix_out"]
+
+
+@pytest.mark.parametrize("T,E,k", [(16, 4, 2), (1037, 5, 2), (5000, 32, 2), (3000, 128, 1),
+                                   (40000, 8, 2)])
+def test_throttle(R, T, E, k):
+    rng = np.random.default_rng(T + E)
+    mask = rand_mask(rng, T, E, k)
+    prefix = rng.integers(0, 20, size=E).astype(np.int32)
+    thr = rng.integers(0, max(2, 2 * T * k // E), size=E).astype(np.int32)
+    exp_p = prefix.copy()
+    exp_m, _ = oracle.throttle_hotmask(mask, exp_p, thr)
+    p = dev(prefix)
+    got_m, got_p = R.throttle_hotmask(dev(mask), p, dev(thr))
+    assert np.array_equal(host(got_m), exp_m)
+    assert np.array_equal(host(got_p), exp_p)
+
+
+def test_convert_index_format(R):
+    rng = np.random.default_rng(11)
+    mask = rand_mask(rng, 3000, 6, 2)
+    seat, loads = oracle.generate_indices_and_loads(mask)
+    tag, _ = oracle.generate_indices_and_loads(mask, is_tag_index=True)
+    # flag forwarded inverted, as in the reference: False = seat -> tag
+    got_tag = R.convert_index_format(dev(seat), dev(loads), False)
+    assert np.array_equal(host(got_tag), tag)
+    got_seat = R.convert_index_format(dev(tag), dev(loads), True)
+    assert np.array_equal(host(got_seat), seat)
+    assert np.array_equal(host(got_seat), oracle.convert_index_format(tag, loads, True))
+
+
+def make_data(rng, shape, dtype):
+    return oracle.to_bits(rng.standard_normal(shape).astype(np.float32), dtype)
+
+
+DISPATCH_CASES = [
+    # T, E, k, cell shape
+    (16, 4, 2, (8,)), (300, 8, 1, (768,)), (257, 5, 2, (3,)), (200, 8, 2, (4, 3, 2, 3)),
+    (128, 16, 2, (1024,)), (64, 4, 2, (2050,)), (37, 3, 1, (1,)), (50, 130, 3, (64,)),
+]
+
+
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("T,E,k,cell", DISPATCH_CASES)
+@pytest.mark.parametrize("variant", ["plain", "padded", "capacity", "weighted", "tags"])
+def test_dispatch_and_combine(R, dtype, T, E, k, cell, variant):
+    if dtype == "f16" and int(np.prod(cell)) % 2:
+        pytest.skip("the reference requires an even cell size for fp16")
+    rng = np.random.default_rng(T * 7 + E + len(variant))
+    mask = rand_mask(rng, T, E, k)
+    caps, cpad = None, False
+    kw = {}
+    if variant == "capacity":
+        caps, cpad = [max(1, T * k // E // 2)], True  # forces drops and padding
+    idx, loads = oracle.generate_indices_and_loads(mask, caps, cpad)
+    if variant == "padded":
+        kw = dict(max_path_padding=True, max_path_load=int(loads.max()) + 3)
+    x = make_data(rng, (T,) + cell, dtype)
+    gates = make_data(rng, (T, E), dtype) if variant == "weighted" else None
+    tagging = variant == "tags"
+    exp = oracle.dispatch_with_indices_and_loads(x, idx, loads, gates, tagging, None,
+                                                 dtype=dtype, **kw)
+    got = R.dispatch_with_indices_and_loads(
+        dev(x, dtype), dev(idx), dev(loads), None if gates is None else dev(gates, dtype),
+        tagging, None, **kw)
+    assert len(got) == len(exp)
+    assert got[0].shape == exp[0].shape
+    assert np.array_equal(host(got[0]), exp[0])
+    if tagging:
+        assert np.array_equal(host(got[1]), exp[1])
+    # combine what was dispatched, with fp32 gates, with and without a residual
+    g32 = rng.standard_normal((T, E)).astype(np.float32)
+    ckw = dict(max_path_padding=kw.get("max_path_padding", False))
+    for use_gates in (False, True):
+        (exp_c,) = oracle.combine_with_indices_and_loads(
+            exp[0], idx, loads, g32 if use_gates else None, dtype=dtype, **ckw)
+        (got_c,) = R.combine_with_indices_and_loads(
+            got[0], dev(idx), dev(loads), dev(g32) if use_gates else None, **ckw)
+        assert np.array_equal(host(got_c), exp_c)
+    res = make_data(rng, (T,) + cell, dtype)
+    exp_res = res.copy()
+    oracle.combine_with_indices_and_loads(exp[0], idx, loads, g32, out_data=exp_res, dtype=dtype,
+                                          **ckw)
+    res_d = dev(res, dtype)
+    (got_res,) = R.combine_with_indices_and_loads(got[0], dev(idx), dev(loads), dev(g32), res_d,
+                                                  **ckw)
+    assert got_res is res_d
+    assert np.array_equal(host(res_d), exp_res)
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_combine_gates_in_data_dtype(R, dtype):
+    rng = np.random.default_rng(2)
+    T, E = 500, 8
+    idx, loads = oracle.generate_indices_and_loads(rand_mask(rng, T, E, 2))
+    x = make_data(rng, (int(loads.sum()), 96), dtype)
+    g = make_data(rng, (T, E), dtype)
+    (exp,) = oracle.combine_with_indices_and_loads(x, idx, loads, g, dtype=dtype,
+                                                   gates_dtype=dtype)
+    (got,) = R.combine_with_indices_and_loads(dev(x, dtype), dev(idx), dev(loads), dev(g, dtype))
+    assert np.array_equal(host(got), exp)
+
+
+def test_dispatch_2d_scores(R):
+    rng = np.random.default_rng(4)
+    T, E = 700, 8
+    idx, loads = oracle.generate_indices_and_loads(rand_mask(rng, T, E, 2))
+    score = rng.standard_normal((T, E)).astype(np.float32)
+    (exp,) = oracle.dispatch_with_indices_and_loads(score, idx, loads, is_1d_routing=False)
+    (got,) = R.dispatch_with_indices_and_loads(dev(score), dev(idx), dev(loads),
+                                               is_1d_routing=False)
+    assert got.shape == exp.shape == (int(loads.sum()), 1)
+    assert np.array_equal(host(got), exp)
+    x3 = rng.standard_normal((T, E, 6)).astype(np.float32)
+    exp = oracle.dispatch_with_indices_and_loads(x3, idx, loads, tag_generating=True,
+                                                 is_1d_routing=False)
+    got = R.dispatch_with_indices_and_loads(dev(x3), dev(idx), dev(loads), None, True, None,
+                                            False, 0, False)
+    assert np.array_equal(host(got[0]), exp[0]) and np.array_equal(host(got[1]), exp[1])
+
+
+@pytest.mark.parametrize("weighted", [False, True])
+def test_dispatch_with_tag_indices(R, weighted):
+    rng = np.random.default_rng(6)
+    T, E = 900, 6
+    mask = rand_mask(rng, T, E, 2)
+    tag, loads = oracle.generate_indices_and_loads(mask, [64, 128, 256, 512], True, False, True)
+    x = rng.standard_normal((T, 40)).astype(np.float32)
+    g = rng.standard_normal((T, E)).astype(np.float32) if weighted else None
+    for kw in ({}, dict(max_path_padding=True, max_path_load=600)):
+        exp = oracle.dispatch_with_indices_and_loads(x, tag, loads, g, True, None,
+                                                     is_tag_index=True, **kw)
+        got = R.dispatch_with_indices_and_loads(
+            dev(x), dev(tag), dev(loads), None if g is None else dev(g), True, None,
+            kw.get("max_path_padding", False), kw.get("max_path_load", 0), True, True)
+        assert np.array_equal(host(got[0]), exp[0]) and np.array_equal(host(got[1]), exp[1])
+
+
+def test_dispatch_empty_and_single(R):
+    x = torch.zeros((0, 5), device="cuda")
+    idx = torch.zeros((0, 3), dtype=torch.int32, device="cuda")
+    loads = torch.zeros((3,), dtype=torch.int32, device="cuda")
+    (o,) = R.dispatch_with_indices_and_loads(x, idx, loads)
+    assert o.shape == (0, 5)
+    o, t = R.dispatch_with_indices_and_loads(x, idx, loads, None, True)
+    assert o.shape == (0, 5) and t.shape == (0,)
+    (o,) = R.combine_with_indices_and_loads(x, idx, loads)
+    assert o.shape == (0, 5)
+    # single-cell shortcut: data returned as is / added to the residual
+    one = torch.randn((1, 5), device="cuda")
+    idx1 = torch.ones((1, 3), dtype=torch.int32, device="cuda")
+    (o,) = R.combine_with_indices_and_loads(one, idx1, loads)
+    assert o is one
+    res = torch.ones((1, 5), device="cuda")
+    (o,) = R.combine_with_indices_and_loads(one, idx1, loads, None, res)
+    assert torch.equal(o, res + one)
+
+
+def test_path_wise_padding_with_no_cells_routed(R):
+    """Every output row is padding: the whole output must come back zero."""
+    mask = np.zeros((10, 4), dtype=np.int32)
+    caps = np.array([3, 0, 2, 5], dtype=np.int32)
+    idx, loads = oracle.generate_indices_and_loads(mask, caps, True, True)
+    x = np.ones((10, 7), dtype=np.float32)
+    (exp,) = oracle.dispatch_with_indices_and_loads(x, idx, loads)
+    (got,) = R.dispatch_with_indices_and_loads(dev(x), dev(idx), dev(loads))
+    assert got.shape == (10, 7) and np.array_equal(host(got), exp) and not host(got).any()
+
+
+def test_notebook_round_trip(R):
+    """sample/cpp/dispatch.ipynb: both combine paths return 2*x for a top-2 mask."""
+    rng = np.random.default_rng(1)
+    T, E = 2048, 4
+    mask = dev(rand_mask(rng, T, E, 2))
+    caps = torch.tensor([64, 128, 256, 512, 1024, 2048], dtype=torch.int32, device="cuda")
+    idx, loads = R.generate_indices_and_loads(mask, caps, capacity_padding=True)
+    x = torch.randn((T, 4, 3, 2, 3), device="cuda")
+    out, tags = R.dispatch_with_indices_and_loads(x, idx, loads, tag_generating=True)
+    datas, sloads, stags = R.split_fused_cells_to_paths(out, loads, is_load_split=True,
+                                                        is_tag_split=True, tags=tags)
+    fused, new_tags, inverse = R.fuse_split_cells_from_paths(datas, is_tag_fuse=True, tags=stags)
+    final, ftags, n = R.combine_with_indices_and_loads(fused, inverse, loads, tags=new_tags,
+                                                       is_tag_index=True)
+    assert n.item() == T and torch.equal(final, 2 * x)
+    fused2, floads = R.fuse_split_cells_from_paths(datas, is_load_fuse=True, loads=sloads)
+    (final2,) = R.combine_with_indices_and_loads(fused2, idx, floads)
+    assert torch.equal(final2, 2 * x)
