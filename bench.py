@@ -1,0 +1,488 @@
+"""Benchmark of the routing hot path (mask -> throttle -> seat indices/loads -> dispatch ->
+combine, plus the expert-parallel exchange when run on more than one GPU).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2] [--impl reference]
+
+Prints ONE JSON line (rank 0).  Inputs are seeded synthetic tensors with the shapes and value
+distributions of the named workload; nothing is read from disk.  With ``--impl reference``
+the CPU restatement of the reference's router (``oracle/``) is timed on the host cores
+instead, on the same workload.
+"""
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+METRIC = "routed tokens/sec (dispatch+combine)"
+UNIT = "tokens/s"
+
+WORKLOADS = {
+    # name: T, d, E, top_k, dtype, bias_std, capacity rule
+    "cfg1": dict(T=4096, d=768, E=8, k=1, dtype="f32", seed=0, bias="none", cap="ceil1.25",
+                 desc="Switch top-1, T=4096 d=768 E=8 fp32, capacity ceil(1.25*T/E), drop"),
+    "cfg2": dict(T=32768, d=1024, E=32, k=2, dtype="bf16", seed=2, bias="normal0.5",
+                 cap="swin1.0",
+                 desc="top-2 MoE route bf16, T=32768 d=1024 E=32, biased logits, renormalised "
+                      "gates, capacity factor 1.0 with drop"),
+    "cfg3": dict(T=262144, d=768, E=128, k=1, dtype="bf16", seed=3, bias="zipf", cap="ceil2.0",
+                 desc="Switch-Base-128-like top-1 bf16, T=262144 d=768 E=128, Zipf-biased "
+                      "logits, capacity factor 2.0 with drop"),
+    "cfg4": dict(T=65536, d=2048, E=64, k=2, dtype="bf16", seed=4, bias="normal1.0", cap="none",
+                 desc="expert-parallel top-2 bf16 per GPU T=65536 d=2048 E=64, no capacity"),
+}
+
+TORCH_DT = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
+
+
+# --------------------------------------------------------------------------------- workloads
+def capacity_of(w) -> int:
+    T, E, k = w["T"], w["E"], w["k"]
+    rule = w["cap"]
+    if rule == "ceil1.25":
+        return math.ceil(1.25 * T / E)
+    if rule == "ceil2.0":
+        return math.ceil(2.0 * T / E)
+    if rule == "swin1.0":
+        return k * int(1.0 * math.ceil(T / E))
+    return 0
+
+
+def make_workload(name: str, rank: int = 0, local_bias: float = 0.0, world: int = 1):
+    """Host (CPU) tensors of one workload: activations, fp32 logits, softmax scores, top-k hot
+    mask, combine gates.  Generated on CPU in fp32 so that the CPU checker and the GPU see the
+    same bits."""
+    w = WORKLOADS[name]
+    T, d, E, k = w["T"], w["d"], w["E"], w["k"]
+    g = torch.Generator(device="cpu").manual_seed(w["seed"] * 1000 + rank)
+    gb = torch.Generator(device="cpu").manual_seed(w["seed"] * 1000 + 999)  # shared by all ranks
+    x = torch.randn((T, d), generator=g, dtype=torch.float32).to(TORCH_DT[w["dtype"]])
+    logits = torch.randn((T, E), generator=g, dtype=torch.float32)
+    if w["bias"].startswith("normal"):
+        logits = logits + float(w["bias"][6:]) * torch.randn((E,), generator=gb)
+    elif w["bias"] == "zipf":
+        ranks = torch.randperm(E, generator=gb).to(torch.float32) + 1.0
+        z = ranks.pow(-1.1)
+        logits = logits + 4.0 * z / z.max()
+    if local_bias and world > 1:
+        G = E // world
+        logits[:, rank * G:(rank + 1) * G] += local_bias
+    score = torch.softmax(logits, dim=1)
+    vals, picks = torch.topk(score, k, dim=1)
+    mask = torch.zeros((T, E), dtype=torch.int32).scatter_(1, picks, 1)
+    if k > 1:
+        denom = torch.clamp(vals.sum(dim=1, keepdim=True), min=torch.finfo(torch.float32).eps)
+        gates = torch.zeros_like(score).scatter_(1, picks, vals / denom)
+    else:
+        gates = score
+    return dict(name=name, spec=w, x=x, logits=logits, score=score, mask=mask, gates=gates,
+                cap=capacity_of(w))
+
+
+def algorithmic_bytes(w, idx: np.ndarray, loads: np.ndarray, total_rows: int):
+    """Minimum HBM bytes of each op for this routing: R kept routes, T_r cells
+    with at least one kept route, L output rows."""
+    T, d, E = w["T"], w["d"], w["E"]
+    s = 4 if w["dtype"] == "f32" else 2
+    kept = (idx > 0) & (idx <= loads[None, :])
+    R = int(kept.sum())
+    Tr = int(kept.any(axis=1).sum())
+    return {
+        "throttle": 8 * T * E + 12 * E,
+        "indices": 8 * T * E + 4 * E,
+        "dispatch": Tr * d * s + total_rows * d * s + 4 * T * E,
+        "combine": R * d * s + T * d * s + 8 * T * E,
+        "R": R, "T_r": Tr, "L": total_rows,
+    }
+
+
+# --------------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100", "-i", str(self.gpu_index)],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                f = [c.strip() for c in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6),
+                                  ("sw_thermal_slowdown", 7), ("sw_power_cap", 8)):
+                    if f[col].lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), samples=len(sm),
+                       reasons=sorted(reasons))
+        return out
+
+
+# --------------------------------------------------------------------------------- GPU arm
+def run_gpu(args):
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group(backend="nccl", device_id=dev)
+    from brainstorm_b200._C import router as R
+    from brainstorm_b200.router import GatherRouter, ScatterRouter
+    from brainstorm_b200.runtime import distributed as brt_dist
+
+    wl = make_workload(args.workload, rank=rank, world=world)
+    w = wl["spec"]
+    T, d, E = w["T"], w["d"], w["E"]
+    cap = wl["cap"]
+    padded = cap > 0
+    x = wl["x"].to(dev)
+    mask = wl["mask"].to(dev)
+    gates = wl["gates"].to(dev)
+    caps = torch.full((E,), cap, dtype=torch.int32, device=dev) if padded else None
+    zeros_e = torch.zeros((E,), dtype=torch.int32, device=dev)
+    distributed = world > 1
+    if distributed:
+        assert E % world == 0
+        brt_dist.is_nccl_activated()
+
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(8)] for _ in range(args.steps)]
+    a2a_bytes = [0]
+
+    def step(i=None):
+        rec = (lambda j: ev[i][j].record()) if i is not None else (lambda j: None)
+        rec(0)
+        m = mask
+        if padded:
+            prefix = zeros_e.clone()
+            m, _ = R.throttle_hotmask(mask, prefix, caps)
+        rec(1)
+        idx, loads = R.generate_indices_and_loads(m, caps)
+        rec(2)
+        (routed,) = R.dispatch_with_indices_and_loads(x, idx, loads, None, False, None, padded,
+                                                      cap)
+        rec(3)
+        if distributed:
+            recv, out_loads, in_loads = brt_dist.group_sparse_a2a(routed, loads, padded, cap)
+            rec(4)
+            routed = brt_dist.size_known_group_sparse_a2a(recv, out_loads, in_loads, padded)
+            rec(5)
+            a2a_bytes[0] = int(in_loads.sum()) * d * x.element_size() if not padded else \
+                int(routed.numel() * x.element_size())
+        else:
+            rec(4)
+            rec(5)
+        (out,) = R.combine_with_indices_and_loads(routed, idx, loads, gates, None, padded)
+        rec(6)
+        return out, idx, loads, routed
+
+    def barrier():
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        out, idx, loads, routed = step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    t_start = torch.cuda.Event(enable_timing=True)
+    t_end = torch.cuda.Event(enable_timing=True)
+    t_start.record()
+    for i in range(args.steps):
+        out, idx, loads, routed = step(i)
+    t_end.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = t_start.elapsed_time(t_end)
+    if distributed:
+        t = torch.tensor([total_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+
+    names = ["throttle", "indices", "dispatch", "a2a_forward", "a2a_backward", "combine"]
+    op_ms = {n: statistics.mean(ev[i][j].elapsed_time(ev[i][j + 1]) for i in range(args.steps))
+             for j, n in enumerate(names)}
+    ab = algorithmic_bytes(w, idx.cpu().numpy(), loads.cpu().numpy(), routed.size(0))
+    peaks = {}
+    try:
+        peaks = json.load(open(ROOT / "MEASURED_PEAKS.json"))
+    except Exception:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    peak_kind = "measured" if "hbm_gbs" in peaks else "fallback"
+    kernels = {}
+    for n in ("throttle", "indices", "dispatch", "combine"):
+        if op_ms[n] > 0 and (n != "throttle" or padded):
+            gbs = ab[n] / (op_ms[n] * 1e-3) / 1e9
+            kernels[n] = {"ms": round(op_ms[n], 5), "algorithmic_bytes": ab[n],
+                          "achieved_gbs": round(gbs, 1), "frac": round(gbs / peak, 4)}
+    dominant = max(kernels, key=lambda n: kernels[n]["ms"])
+    dc_ms = op_ms["dispatch"] + op_ms["combine"]
+
+    # ---- end to end through the router API with host buffers
+    e2e = measure_e2e(wl, dev, args, ScatterRouter, GatherRouter, distributed, world)
+
+    result = {
+        "metric": METRIC, "value": world * T / (ms_per_step * 1e-3), "unit": UNIT,
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {w['desc']}",
+                   "step": "throttle + seat indices/loads + dispatch + "
+                           + ("sparse all-to-all forward and back + " if distributed else "")
+                           + "weighted combine",
+                   "l2": "inputs and outputs of a step exceed the 126 MB L2"
+                         if (T * d * x.element_size() * 3) > 126e6 else
+                         "working set fits in L2; numbers are L2-assisted",
+                   "parallelism": f"ep{world}" if distributed else "single"},
+        "dispatch_combine_only": {"tokens_per_s": world * T / (dc_ms * 1e-3), "ms": dc_ms},
+        "roofline": {"bound": "hbm", "kernel": dominant,
+                     "achieved": kernels[dominant]["achieved_gbs"], "peak": peak, "unit": "GB/s",
+                     "frac": kernels[dominant]["frac"], "traffic": None,
+                     "peak_kind": f"{peak_kind} copy bandwidth",
+                     "nominal_frac_of_8000": round(kernels[dominant]["achieved_gbs"] / 8000, 4)},
+        "kernels": kernels,
+        "routing": {"kept_routes": ab["R"], "cells_routed": ab["T_r"], "output_rows": ab["L"]},
+        "gpu_launches": args.steps * ((3 if padded else 0) + 3 + 2 + 1),
+        "clocks": clocks, "e2e": e2e,
+    }
+    if distributed:
+        fwd = a2a_bytes[0] * (world - 1) / world
+        result["a2a"] = {
+            "forward_ms": op_ms["a2a_forward"], "backward_ms": op_ms["a2a_backward"],
+            "bytes_per_rank_per_direction": a2a_bytes[0],
+            "bus_gbs_forward": fwd / (op_ms["a2a_forward"] * 1e-3) / 1e9,
+            "bus_gbs_backward": fwd / (op_ms["a2a_backward"] * 1e-3) / 1e9,
+            "nvlink_peak_gbs_per_direction": 900.0, "transport": "nccl send/recv",
+        }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        result["cpu_baseline"] = cpu_baseline(wl, budget_s=args.cpu_seconds)
+    if rank == 0:
+        print(json.dumps(result))
+    if distributed:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def measure_e2e(wl, dev, args, ScatterRouter, GatherRouter, distributed, world):
+    """Same routing through ScatterRouter / GatherRouter, inputs in pinned host memory, the
+    combined result copied back to the host, all inside the timed region."""
+    import torch.distributed as dist
+
+    w = wl["spec"]
+    T, E = w["T"], w["E"]
+    cap = wl["cap"]
+    padded = cap > 0
+    kind = "distributed_fused" if distributed else "fused"
+    fkw = {"max_path_padding": padded, "max_path_load": cap}
+    if padded:
+        fkw["supported_capacities"] = [cap]
+    scatter = ScatterRouter(protocol_type="topk", fabric_type=f"{kind}_dispatch",
+                            protocol_kwargs={"top_k": w["k"]}, fabric_kwargs=fkw).to(dev)
+    gather = GatherRouter(fabric_type=f"{kind}_combine",
+                          fabric_kwargs={"transform": True, "max_path_padding": padded}).to(dev)
+    x_h = wl["x"].pin_memory()
+    score_h = wl["score"].pin_memory()
+    gates_h = wl["gates"].pin_memory()
+    out_h = torch.empty_like(wl["x"]).pin_memory()
+    from brainstorm_b200.runtime.grid_tensor import init_grid_tensor
+
+    def step():
+        x = init_grid_tensor(x_h.to(dev, non_blocking=True), [None], [None])
+        score = score_h.to(dev, non_blocking=True)
+        gates = gates_h.to(dev, non_blocking=True)
+        routed = scatter(x, score)
+        out = gather(routed, None, gates)
+        out_h.copy_(out, non_blocking=True)
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    if distributed:
+        dist.barrier()
+    steps = max(3, min(args.steps, 20))
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        step()
+    t1.record()
+    torch.cuda.synchronize()
+    ms = t0.elapsed_time(t1) / steps
+    if distributed:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    h2d = sum(t.numel() * t.element_size() for t in (x_h, score_h, gates_h))
+    d2h = out_h.numel() * out_h.element_size()
+    return {"value": world * T / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms,
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "api": "ScatterRouter(topk, fused_dispatch) -> GatherRouter(fused_combine)"}
+
+
+# --------------------------------------------------------------------------------- CPU arm
+def cpu_pass(wl, oracle):
+    w = wl["spec"]
+    cap = wl["cap"]
+    padded = cap > 0
+    dt = w["dtype"]
+    x = wl["x_bits"]
+    mask = wl["mask_np"]
+    caps = [cap] * w["E"] if padded else None
+    m = mask
+    if padded:
+        m, _ = oracle.throttle_hotmask(mask, np.zeros(w["E"], dtype=np.int32),
+                                       np.full(w["E"], cap, dtype=np.int32))
+    idx, loads = oracle.generate_indices_and_loads(m, caps)
+    (routed,) = oracle.dispatch_with_indices_and_loads(x, idx, loads, max_path_padding=padded,
+                                                       max_path_load=cap, dtype=dt)
+    (out,) = oracle.combine_with_indices_and_loads(routed, idx, loads, wl["gates_np"],
+                                                   max_path_padding=padded, dtype=dt)
+    return out
+
+
+def cpu_baseline(wl, budget_s: float = 15.0, min_passes: int = 2):
+    """The reference has no CPU implementation of the fused router ops; the baseline is the
+    CPU restatement in oracle/ (C + OpenMP) on all host cores."""
+    import oracle
+
+    w = wl["spec"]
+    cores = os.cpu_count() or 1
+    oracle.set_threads(cores)
+    if "x_bits" not in wl:
+        xt = wl["x"]
+        wl["x_bits"] = xt.numpy() if w["dtype"] == "f32" else \
+            xt.view(torch.int16).numpy().view(np.uint16)
+        wl["mask_np"] = wl["mask"].numpy()
+        wl["gates_np"] = wl["gates"].numpy()
+    cpu_pass(wl, oracle)  # warm-up
+    times = []
+    t_all = time.perf_counter()
+    while len(times) < min_passes or (time.perf_counter() - t_all < budget_s):
+        t0 = time.perf_counter()
+        cpu_pass(wl, oracle)
+        times.append(time.perf_counter() - t0)
+    best = min(times)
+    return {"value": w["T"] / best, "unit": UNIT, "cores": min(cores, oracle.max_threads()),
+            "kind": "port",
+            "sample": f"whole batch of {w['T']} tokens, best of {len(times)} passes "
+                      f"({sum(times):.1f} s of CPU work)",
+            "ms_per_step": best * 1e3}
+
+
+def run_reference(args):
+    """Reference arm: the CPU restatement of the reference's router on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    wl = make_workload(args.workload)
+    w = wl["spec"]
+    import oracle
+
+    cores = os.cpu_count() or 1
+    oracle.set_threads(cores)
+    xt = wl["x"]
+    wl["x_bits"] = xt.numpy() if w["dtype"] == "f32" else \
+        xt.view(torch.int16).numpy().view(np.uint16)
+    wl["mask_np"] = wl["mask"].numpy()
+    wl["gates_np"] = wl["gates"].numpy()
+    warm = max(1, min(args.warmup, 3))
+    for _ in range(warm):
+        cpu_pass(wl, oracle)
+    steps = max(1, min(args.steps, 20))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_pass(wl, oracle)
+    ms = (time.perf_counter() - t0) / steps * 1e3
+    value = w["T"] / (ms * 1e-3)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT,
+        "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"],
+        "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {w['desc']}",
+                   "step": "throttle + seat indices/loads + dispatch + weighted combine",
+                   "note": "the reference has no CPU implementation of its fused router ops "
+                           "(every op asserts CUDA tensors); this is its algorithm restated in "
+                           "C + OpenMP (oracle/), on all host cores"},
+        "cpu_baseline": {"value": value, "unit": UNIT,
+                         "cores": min(cores, oracle.max_threads()), "kind": "port",
+                         "sample": f"whole batch of {w['T']} tokens per step, {steps} steps"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

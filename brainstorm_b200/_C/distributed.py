@@ -1,0 +1,309 @@
+"""Drop-in for the reference's ``brt._C.distributed`` extension
+(src/backend/torch/distributed.cc:903-949): same 15 functions, argument names and return
+shapes.  The exchange runs over the library's own NCCL communicator through the C ABI in
+``include/brt_b200.h``; torch only allocates the outputs.
+
+Deliberate differences from the reference:
+
+* collectives are enqueued on the current stream instead of a private side stream fenced by
+  events (the reference waits for them at once, so nothing overlapped there either);
+* byte counts are 64-bit (the reference's ``int`` byte counts overflow past 2 GiB);
+* sizes reach the host through one copy and one sync per call, not two;
+* a second ``init_nccl`` raises ``RuntimeError`` instead of printing a warning.
+"""
+import ctypes
+from typing import List
+
+import numpy as np
+import torch
+
+from .. import _lib
+from ..runtime import a2a_plan
+
+_state = {"rank": None, "size": None}
+
+
+def _check_cuda(t: torch.Tensor, name: str):
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _world():
+    if _state["size"] is None:
+        r, s = ctypes.c_int(0), ctypes.c_int(0)
+        _lib.call("brt_nccl_world", ctypes.byref(r), ctypes.byref(s))
+        _state["rank"], _state["size"] = r.value, s.value
+    return _state["rank"], _state["size"]
+
+
+def _host_sizes(*tensors: torch.Tensor) -> List[np.ndarray]:
+    """int32 size vectors -> host arrays with a single device->host copy and sync."""
+    if all(not t.is_cuda for t in tensors):
+        return [t.to(torch.int32).contiguous().numpy() for t in tensors]
+    dev = next(t.device for t in tensors if t.is_cuda)
+    flat = torch.cat([t.to(dev, torch.int32).reshape(-1) for t in tensors]).cpu().numpy()
+    out, at = [], 0
+    for t in tensors:
+        out.append(np.ascontiguousarray(flat[at:at + t.numel()]))
+        at += t.numel()
+    return out
+
+
+def _np_ptr(a: np.ndarray):
+    assert a.dtype == np.int32 and a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data
+
+
+def _contig(t: torch.Tensor) -> torch.Tensor:
+    return t if t.is_contiguous() else t.contiguous()
+
+
+# ----------------------------------------------------------------------------- bootstrap
+
+
+def make_nccl_unique_id(world_rank: int) -> torch.Tensor:
+    """int8 tensor of 128 bytes on the GPU; only rank 0's content is meaningful.  The caller
+    broadcasts it (python/brt/runtime/distributed.py:30-32 in the reference)."""
+    t = torch.zeros(128, dtype=torch.int8)
+    if world_rank == 0:
+        _lib.call("brt_nccl_get_unique_id", t.data_ptr())
+    return t.cuda()
+
+
+def init_nccl(unique_id: torch.Tensor, world_rank: int, world_size: int) -> None:
+    cpu = unique_id.to("cpu").contiguous()
+    if cpu.numel() != 128:
+        raise RuntimeError("unique_id must hold 128 bytes")
+    _lib.call("brt_nccl_init", cpu.data_ptr(), int(world_rank), int(world_size))
+    _state["rank"], _state["size"] = int(world_rank), int(world_size)
+
+
+# ----------------------------------------------------------------------------- reorder
+
+
+def locality_reorder(loads: torch.Tensor, wolrd_size: int):
+    """(reordered_loads, reorder_indices); the argument keeps the reference's spelling."""
+    return group_locality_reorder(loads, wolrd_size, 1)
+
+
+def group_locality_reorder(loads: torch.Tensor, wolrd_size: int, group_size: int = 1):
+    _check_cuda(loads, "loads")
+    if loads.dtype != torch.int32:
+        raise RuntimeError("loads must be an int32 tensor")
+    W = int(wolrd_size)
+    if loads.numel() != W * W * group_size:
+        raise RuntimeError(f"loads must hold world_size^2 * group_size = {W * W * group_size} "
+                           f"entries, got {loads.numel()}")
+    src = _contig(loads)
+    with torch.cuda.device(loads.device):
+        out = torch.empty_like(src)
+        idx = torch.empty(W, dtype=torch.int32, device=loads.device)
+        _lib.call("brt_group_locality_reorder", src.data_ptr(), int(group_size), W,
+                  idx.data_ptr(), out.data_ptr(), _stream(loads.device))
+    return out, idx
+
+
+def _exchange_one(in_data, dst, src):
+    _check_cuda(in_data, "in_data")
+    x = _contig(in_data)
+    out = torch.empty_like(x)
+    _lib.call("brt_exchange", x.data_ptr(), out.data_ptr(), x.numel() * x.element_size(), dst,
+              src, _stream(x.device))
+    return out
+
+
+def exchange(in_data: torch.Tensor, reorder_indices: torch.Tensor) -> torch.Tensor:
+    rank, _ = _world()
+    dst, src = a2a_plan.exchange_partners(reorder_indices.cpu().tolist(), rank)
+    return _exchange_one(in_data, dst, src)
+
+
+def batched_exchange(in_datas: List[torch.Tensor], reorder_indices: torch.Tensor):
+    rank, _ = _world()
+    dst, src = a2a_plan.exchange_partners(reorder_indices.cpu().tolist(), rank)
+    return [_exchange_one(x, dst, src) for x in in_datas]
+
+
+def reverse_exchange(in_data: torch.Tensor, reorder_indices: torch.Tensor) -> torch.Tensor:
+    rank, _ = _world()
+    dst, src = a2a_plan.exchange_partners(reorder_indices.cpu().tolist(), rank)
+    return _exchange_one(in_data, src, dst)
+
+
+def batched_reverse_exchange(in_datas: List[torch.Tensor], reorder_indices: torch.Tensor):
+    _check_cuda(reorder_indices, "reorder_indices")
+    rank, _ = _world()
+    dst, src = a2a_plan.exchange_partners(reorder_indices.cpu().tolist(), rank)
+    return [_exchange_one(x, src, dst) for x in in_datas]
+
+
+# ----------------------------------------------------------------------------- padded slots
+
+
+def _exchange_sizes(send_sizes: torch.Tensor) -> torch.Tensor:
+    """Sizes all-to-all: slice i of send_sizes goes to rank i (device tensors)."""
+    _, W = _world()
+    s = _contig(send_sizes)
+    recv = torch.empty_like(s)
+    _lib.call("brt_all_to_all", s.data_ptr(), recv.data_ptr(),
+              s.numel() * s.element_size() // W, _stream(s.device))
+    return recv
+
+
+def _slot_a2a(in_data, send_np, recv_np, group_size, zero_fill):
+    x = _contig(in_data)
+    out = torch.zeros_like(x) if zero_fill else torch.empty_like(x)
+    total = x.numel() * x.element_size()
+    grain = total // x.size(0) if x.size(0) else 0
+    slot = total // send_np.size
+    _lib.call("brt_group_asymmetry_all_to_all", x.data_ptr(), out.data_ptr(), _np_ptr(send_np),
+              _np_ptr(recv_np), grain, slot, group_size, _stream(x.device))
+    return out
+
+
+def _locality_tail(recv_sizes: torch.Tensor, group_size: int):
+    """Gather every rank's received sizes on rank 0, match there, scatter the reordered
+    loads and broadcast the permutation (src/backend/torch/distributed.cc:246-330)."""
+    rank, W = _world()
+    dev = recv_sizes.device
+    st = _stream(dev)
+    recv_sizes = _contig(recv_sizes)
+    nbytes = recv_sizes.numel() * 4
+    all_sizes = torch.empty(recv_sizes.numel() * W, dtype=torch.int32, device=dev) \
+        if rank == 0 else None
+    _lib.call("brt_gather", recv_sizes.data_ptr(),
+              all_sizes.data_ptr() if rank == 0 else None, nbytes, 0, st)
+    reordered = torch.empty_like(recv_sizes)
+    if rank == 0:
+        all_reordered, reorder_indices = group_locality_reorder(all_sizes, W, group_size)
+    else:
+        all_reordered = None
+        reorder_indices = torch.empty(W, dtype=torch.int32, device=dev)
+    _lib.call("brt_scatter", all_reordered.data_ptr() if rank == 0 else None,
+              reordered.data_ptr(), nbytes, 0, st)
+    _lib.call("brt_broadcast", reorder_indices.data_ptr(), reorder_indices.data_ptr(), W * 4, 0,
+              st)
+    return reordered, reorder_indices
+
+
+def _asymmetry(in_data, send_sizes, locality_aware, zero_fill=False):
+    _check_cuda(in_data, "in_data")
+    _check_cuda(send_sizes, "send_sizes")
+    _, W = _world()
+    group_size = send_sizes.numel() // W
+    with torch.cuda.device(in_data.device):
+        recv_sizes = _exchange_sizes(send_sizes)
+        send_np, recv_np = _host_sizes(send_sizes, recv_sizes)
+        out = _slot_a2a(in_data, send_np, recv_np, group_size, zero_fill)
+        if locality_aware:
+            reordered, reorder_indices = _locality_tail(recv_sizes, group_size)
+            return [out, reordered, reorder_indices]
+    return [out, recv_sizes]
+
+
+def asymmetry_all_to_all(in_data: torch.Tensor, send_sizes: torch.Tensor,
+                         locality_aware: bool = False):
+    return _asymmetry(in_data, send_sizes, locality_aware)
+
+
+def group_asymmetry_all_to_all(in_data: torch.Tensor, send_sizes: torch.Tensor,
+                               locality_aware: bool = False):
+    return _asymmetry(in_data, send_sizes, locality_aware)
+
+
+def batched_group_asymmetry_all_to_all(in_datas: List[torch.Tensor], send_sizes: torch.Tensor,
+                                       locality_aware: bool = False):
+    _check_cuda(send_sizes, "send_sizes")
+    _, W = _world()
+    group_size = send_sizes.numel() // W
+    with torch.cuda.device(send_sizes.device):
+        recv_sizes = _exchange_sizes(send_sizes)
+        send_np, recv_np = _host_sizes(send_sizes, recv_sizes)
+        outs = []
+        for x in in_datas:
+            _check_cuda(x, "in_data")
+            outs.append(_slot_a2a(x, send_np, recv_np, group_size, False))
+        if locality_aware:
+            reordered, reorder_indices = _locality_tail(recv_sizes, group_size)
+            return outs, reordered, reorder_indices
+    return outs, recv_sizes, recv_sizes
+
+
+def size_known_group_asymmetry_all_to_all(in_data: torch.Tensor, send_sizes: torch.Tensor,
+                                          recv_sizes: torch.Tensor) -> torch.Tensor:
+    _check_cuda(in_data, "in_data")
+    _, W = _world()
+    send_np, recv_np = _host_sizes(send_sizes, recv_sizes)
+    with torch.cuda.device(in_data.device):
+        return _slot_a2a(in_data, send_np, recv_np, send_sizes.numel() // W, True)
+
+
+def batched_size_known_group_asymmetry_all_to_all(in_datas: List[torch.Tensor],
+                                                  send_sizes: torch.Tensor,
+                                                  recv_sizes: torch.Tensor):
+    _, W = _world()
+    send_np, recv_np = _host_sizes(send_sizes, recv_sizes)
+    outs = []
+    for x in in_datas:
+        _check_cuda(x, "in_data")
+        with torch.cuda.device(x.device):
+            outs.append(_slot_a2a(x, send_np, recv_np, send_sizes.numel() // W, False))
+    return outs
+
+
+# ----------------------------------------------------------------------------- packed buckets
+
+
+def _sparse_a2a(x, send_np, recv_np, stride_rows, out_rows, group_size, forward):
+    shape = list(x.shape)
+    shape[0] = out_rows
+    out = torch.empty(shape, dtype=x.dtype, device=x.device)
+    grain = (x.numel() * x.element_size()) // x.size(0) if x.size(0) else \
+        int(np.prod(shape[1:])) * x.element_size()
+    _lib.call("brt_group_sparse_all_to_all", x.data_ptr(), out.data_ptr(), _np_ptr(send_np),
+              _np_ptr(recv_np), grain, stride_rows, group_size, int(forward),
+              _stream(x.device))
+    return out
+
+
+def group_sparse_all_to_all(in_data: torch.Tensor, send_sizes: torch.Tensor,
+                            max_path_padding: bool = False, max_path_load: int = 0):
+    """(out_data, recv_sizes [G, W] on CPU, send_sizes [W, G] on CPU)."""
+    _check_cuda(in_data, "in_data")
+    _check_cuda(send_sizes, "send_sizes")
+    _, W = _world()
+    group_size = send_sizes.numel() // W
+    with torch.cuda.device(in_data.device):
+        recv_dev = _exchange_sizes(send_sizes.to(torch.int32))
+        send_np, recv_np = _host_sizes(send_sizes, recv_dev)
+        recv_np = a2a_plan.to_expert_major(recv_np, W)
+        if max_path_padding:
+            stride = int(max_path_load) if max_path_load else int(recv_np.max())
+        else:
+            stride = 0
+        rows = a2a_plan.total_rows(recv_np, stride)
+        out = _sparse_a2a(_contig(in_data), send_np, recv_np, stride, rows, group_size, True)
+    return [out, torch.from_numpy(recv_np.copy()), torch.from_numpy(send_np.copy())]
+
+
+def size_known_group_sparse_all_to_all(in_data: torch.Tensor, send_sizes: torch.Tensor,
+                                       recv_sizes: torch.Tensor,
+                                       max_path_padding: bool = False) -> torch.Tensor:
+    """Inverse of ``group_sparse_all_to_all``: ``send_sizes`` is that call's second output
+    ([G, W]), ``recv_sizes`` its third ([W, G])."""
+    _check_cuda(in_data, "in_data")
+    _, W = _world()
+    group_size = send_sizes.numel() // W
+    send_np, recv_np = _host_sizes(send_sizes, recv_sizes)
+    if max_path_padding:
+        rows = in_data.size(0)
+        stride = rows // send_np.size
+    else:
+        stride = 0
+        rows = a2a_plan.total_rows(recv_np)
+    with torch.cuda.device(in_data.device):
+        return _sparse_a2a(_contig(in_data), send_np, recv_np, stride, rows, group_size, False)

@@ -16,6 +16,9 @@ import sys
 
 __version__ = "0.1.0"
 
+from .runtime.annotate import Annotator  # noqa: E402,F401
+from .runtime.grid_tensor import GridTensor, to_grid_tensor, to_torch_tensor  # noqa: E402,F401
+
 _ALIASES = (
     "", "_C", "_C.router", "_C.distributed", "router", "router.base", "router.scatter",
     "router.gather", "router.utils", "router.protocol", "router.protocol.base",

@@ -33,6 +33,20 @@ SIGNATURES = {
                _int, _vp, _sz, _vp]),
     "brt_combine_with_indices_and_loads": (
         _int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _i32, _int, _int, _int, _vp]),
+    "brt_locality_reorder": (_int, [_vp, _int, _vp, _vp, _vp]),
+    "brt_group_locality_reorder": (_int, [_vp, _int, _int, _vp, _vp, _vp]),
+    "brt_nccl_get_unique_id": (_int, [_vp]),
+    "brt_nccl_init": (_int, [_vp, _int, _int]),
+    "brt_nccl_is_initialized": (_int, []),
+    "brt_nccl_world": (_int, [ctypes.POINTER(_int), ctypes.POINTER(_int)]),
+    "brt_nccl_destroy": (_int, []),
+    "brt_broadcast": (_int, [_vp, _vp, _i64, _int, _vp]),
+    "brt_exchange": (_int, [_vp, _vp, _i64, _int, _int, _vp]),
+    "brt_scatter": (_int, [_vp, _vp, _i64, _int, _vp]),
+    "brt_gather": (_int, [_vp, _vp, _i64, _int, _vp]),
+    "brt_all_to_all": (_int, [_vp, _vp, _i64, _vp]),
+    "brt_group_asymmetry_all_to_all": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _int, _vp]),
+    "brt_group_sparse_all_to_all": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _int, _int, _vp]),
 }
 
 

@@ -1,0 +1,81 @@
+"""Expert-parallel fused fabrics (counterpart of python/brt/router/fabric/distributed.py:14-158).
+
+Dispatch: local fused dispatch in global-expert order, then the packed variable-size
+all-to-all that regroups rows as [local expert][source rank].  Combine: the inverse exchange,
+then the local weighted combine.  Without an initialised process group both exchanges are the
+identity, which is how single-GPU runs use these fabrics.
+"""
+from typing import List, Tuple, Union
+
+import torch
+import torch.distributed as dist
+
+from ..._C import router as c_router
+from ...runtime import distributed as brt_dist
+from ...runtime.grid_tensor import GridTensor, init_grid_tensor, to_torch_tensor
+from .base import register_fabric
+from .fused import FusedCombineFabric, FusedDispatchFabric
+
+__all__ = ["DistributedFusedDispatchFabric", "DistributedFusedCombineFabric"]
+
+
+@register_fabric("distributed_fused_dispatch")
+class DistributedFusedDispatchFabric(FusedDispatchFabric):
+    def __init__(self, flow_num: int, capacity_padding=False,
+                 route_logic: Union[str, List[str]] = "1d",
+                 transform: Union[bool, List[bool]] = False, task_locality: bool = False,
+                 **kwargs):
+        self.task_locality = task_locality
+        super().__init__(flow_num=flow_num, capacity_padding=capacity_padding,
+                         route_logic=route_logic, transform=transform, **kwargs)
+
+    def dispatch(self, in_flows: List[GridTensor], route_indices: torch.Tensor,
+                 loads: torch.Tensor, score: torch.Tensor) -> Tuple[List[GridTensor], torch.Tensor]:
+        all_out_flows = []
+        for flow_idx in range(self.flow_num):
+            data, tag_stack, load_stack, extra = to_torch_tensor(in_flows[flow_idx],
+                                                                 retrieve_attr=True)
+            (routed,) = self._route(data, route_indices, loads, score, flow_idx, None)
+            out_data, out_loads, in_loads = brt_dist.group_sparse_a2a(
+                routed, loads, self.max_path_padding, self.max_path_load)
+            if self.task_locality:
+                # hand back, per received row, the global id of the local expert ("task") it
+                # belongs to, in place of the score
+                world_size = dist.get_world_size() if dist.is_initialized() else 1
+                world_rank = dist.get_rank() if dist.is_initialized() else 0
+                local_tasks = out_loads.numel() // world_size
+                per_task = out_loads.reshape(local_tasks, world_size).sum(dim=1).to(
+                    out_data.device)
+                ids = torch.arange(local_tasks, device=out_data.device) + world_rank * local_tasks
+                score = torch.repeat_interleave(ids, per_task.to(torch.int64),
+                                                output_size=out_data.size(0))
+                all_out_flows.append(out_data)
+                continue
+            out_flow = init_grid_tensor(out_data, tag_stack, load_stack, extra)
+            out_flow.pack(route_indices, out_loads, in_loads=in_loads)
+            all_out_flows.append(out_flow)
+        return all_out_flows, score
+
+
+@register_fabric("distributed_fused_combine")
+class DistributedFusedCombineFabric(FusedCombineFabric):
+    def __init__(self, flow_num, reduction="add", transform=False, task_locality: bool = False,
+                 **kwargs) -> None:
+        self.task_locality = task_locality
+        super().__init__(flow_num=flow_num, reduction=reduction, transform=transform, **kwargs)
+
+    def combine(self, in_flows: List[GridTensor], residual_flows: List[GridTensor],
+                score: torch.Tensor) -> List[GridTensor]:
+        out_flows = []
+        for idx, flow in enumerate(in_flows):
+            flow, route_indices, in_loads, popped = flow.unpack("in_loads")
+            out_loads = popped["in_loads"]
+            data, tag_stack, load_stack, extra = to_torch_tensor(flow, retrieve_attr=True)
+            residual = residual_flows[idx] if residual_flows is not None else None
+            data = brt_dist.size_known_group_sparse_a2a(data, in_loads, out_loads,
+                                                        self.max_path_padding)
+            (out,) = c_router.combine_with_indices_and_loads(
+                data, route_indices, out_loads, score if self.transform else None, residual,
+                max_path_padding=self.max_path_padding, ever_padded=self.ever_padded)
+            out_flows.append(init_grid_tensor(out, tag_stack, load_stack, extra))
+        return out_flows

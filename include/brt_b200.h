@@ -142,6 +142,94 @@ BRT_API int brt_combine_with_indices_and_loads(
     const int32_t* loads, int64_t cell_num, int64_t cell_size, int path_num,
     int32_t max_path_load, int is_residual, int dtype, int gates_dtype, void* stream);
 
+/* ------------------------------------------------------------------ distributed: rank reorder */
+
+/*
+ * Replaces brt::distributed::LocalityReorder
+ * (include/brt/distributed/local_reorder.h:11-12, src/distributed/local_reorder.cu:15-63,143-149).
+ * loads[c * world_size + o] = rows rank c received from rank o.  world_size rounds of
+ * arg-max over the entries whose row and column are still free (ties: smallest flat index);
+ * reorder_indices[c] = o; reordered_loads[r, c] = loads[r, reorder_indices[c]].
+ * world_size <= 32.  All arrays are device memory; reordered_loads must not alias loads.
+ */
+BRT_API int brt_locality_reorder(const int32_t* loads, int world_size, int32_t* reorder_indices,
+                                 int32_t* reordered_loads, void* stream);
+
+/*
+ * Replaces brt::distributed::GroupLocalityReorder
+ * (include/brt/distributed/local_reorder.h:13-14, src/distributed/local_reorder.cu:65-141,151-159).
+ * loads[(c * world_size + o) * group_size + g]; the matching runs on the sums over g (any
+ * group_size; the reference's tree sum is only exact for powers of two and needs
+ * group_size * world_size^2 <= 1024), and the o axis of the output is permuted:
+ * reordered_loads[r, c, :] = loads[r, reorder_indices[c], :].
+ */
+BRT_API int brt_group_locality_reorder(const int32_t* loads, int group_size, int world_size,
+                                       int32_t* reorder_indices, int32_t* reordered_loads,
+                                       void* stream);
+
+/* ------------------------------------------------------------------ distributed: NCCL exchange */
+
+#define BRT_NCCL_UNIQUE_ID_BYTES 128
+
+/*
+ * Communicator bootstrap; replaces make_nccl_unique_id / init_nccl and NcclManager::Init
+ * (src/backend/torch/distributed.cc:16-41, src/backend/torch/nccl_manager.cc:19-30).
+ * Rank 0 fills a 128-byte id, the caller moves it to every rank, every rank calls
+ * brt_nccl_init with the current CUDA device set.  A second brt_nccl_init is refused
+ * (BRT_ERR_INVALID_ARGUMENT) and leaves the first communicator in place.
+ */
+BRT_API int brt_nccl_get_unique_id(void* out_id /* BRT_NCCL_UNIQUE_ID_BYTES, host */);
+BRT_API int brt_nccl_init(const void* unique_id, int world_rank, int world_size);
+BRT_API int brt_nccl_is_initialized(void);
+BRT_API int brt_nccl_world(int* world_rank, int* world_size);
+BRT_API int brt_nccl_destroy(void);
+
+/*
+ * Replace brt::distributed::BroadCast / Exchange / Scatter / Gather / AllToAll
+ * (include/brt/distributed/collective.h:18-56, src/distributed/collective.cc:13-88): grouped
+ * ncclSend/ncclRecv of raw bytes on the library's communicator.  Sizes are int64 bytes.
+ * brt_scatter / brt_gather: `bytes` is the per-rank piece; the root's buffer holds
+ * world_size pieces.  brt_all_to_all: piece i of send goes to rank i, piece i of recv comes
+ * from rank i.
+ */
+BRT_API int brt_broadcast(const void* send_buffer, void* recv_buffer, int64_t bytes, int root,
+                          void* stream);
+BRT_API int brt_exchange(const void* send_buffer, void* recv_buffer, int64_t bytes, int dest,
+                         int source, void* stream);
+BRT_API int brt_scatter(const void* send_buffer, void* recv_buffer, int64_t bytes, int root,
+                        void* stream);
+BRT_API int brt_gather(const void* send_buffer, void* recv_buffer, int64_t bytes, int root,
+                       void* stream);
+BRT_API int brt_all_to_all(const void* send_buffer, void* recv_buffer, int64_t slice_bytes,
+                           void* stream);
+
+/*
+ * Replaces brt::distributed::AsymmetryAllToAll and GroupAsymmetryAllToAll
+ * (include/brt/distributed/collective.h:57-74, src/distributed/collective.cc:90-140).
+ * Both buffers are world_size * group_size slots of slot_bytes; slot (i, j) sends its first
+ * send_sizes[i*G+j] grains to rank i and receives recv_sizes[i*G+j] grains from rank i.
+ * group_size == 1 is the ungrouped form.  send_sizes / recv_sizes are HOST arrays.
+ */
+BRT_API int brt_group_asymmetry_all_to_all(const void* send_buffer, void* recv_buffer,
+                                           const int32_t* send_sizes, const int32_t* recv_sizes,
+                                           int64_t grain_bytes, int64_t slot_bytes,
+                                           int group_size, void* stream);
+
+/*
+ * Replaces brt::distributed::GroupSparseAllToAllForward (forward != 0) and
+ * GroupSparseAllToAllBackward (forward == 0)
+ * (include/brt/distributed/collective.h:75-93, src/distributed/collective.cc:142-224).
+ * Forward: the send buffer is packed in [rank i][local expert j] order with
+ * send_sizes[i*G+j] rows per bucket; the receive buffer is filled in [local expert j][rank i]
+ * order with recv_sizes[j*W+i] rows per bucket.  Backward swaps the two walks.
+ * stride_rows != 0 places buckets stride_rows rows apart (max_path_padding) instead of back
+ * to back.  Row size is grain_bytes.  send_sizes / recv_sizes are HOST arrays.
+ */
+BRT_API int brt_group_sparse_all_to_all(const void* send_buffer, void* recv_buffer,
+                                        const int32_t* send_sizes, const int32_t* recv_sizes,
+                                        int64_t grain_bytes, int64_t stride_rows, int group_size,
+                                        int forward, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
