@@ -19,6 +19,19 @@
 // waits on another CTA.  Masks holding values other than 0/1 are detected during `pack`
 // and make `expand` re-read the mask instead of the bit words, so the integer semantics
 // of the reference (index = running sum * mask value) hold for any int32 mask.
+//
+// Two implementations of pack/expand share that plan:
+//   * the tiled path (path_num % 4 == 0, 16-byte aligned arrays): a CTA stages a
+//     [32*k cells, <=256 paths] tile in shared memory with fully coalesced 16-byte loads
+//     (every load of the tile is in flight at once), each warp turns a 32x32 block into
+//     column bit words with a 5-step shuffle transpose, and `expand` is one popcount per
+//     output element with coalesced 16-byte stores;
+//   * the strip path (any path_num / alignment): a thread walks 32 cells of V paths.
+#include <cooperative_groups.h>
+
+#include <map>
+#include <utility>
+
 #include "common.cuh"
 
 namespace brt_b200 {
@@ -63,6 +76,8 @@ struct Scratch {
   uint32_t* bits;
 };
 
+size_t tiled_scratch_bytes(int64_t cell_num, int path_num);
+
 size_t scratch_bytes_for(int64_t cell_num, int path_num) {
   // Sized for the smallest tile (vec = 1 gives the same group count; slices is smallest when
   // cgb is largest), so any alignment of the caller's pointers fits.
@@ -75,7 +90,8 @@ size_t scratch_bytes_for(int64_t cell_num, int path_num) {
   size_t bytes = 256;
   bytes += round_up((size_t)tiles_max * (size_t)path_num * 4, 256);
   bytes += round_up((size_t)(groups + 1) * (size_t)path_num * 4, 256);
-  return bytes;
+  const size_t tiled = tiled_scratch_bytes(cell_num, path_num);
+  return bytes > tiled ? bytes : tiled;
 }
 
 Scratch carve(void* base, const Tiling& t, int path_num) {
@@ -428,6 +444,616 @@ tag_to_seat_kernel(const int* __restrict__ tag, int* __restrict__ seat,
   }
 }
 
+// ================================================================================ tiled path
+constexpr int kTileThreads = 256;
+constexpr int kTileWarps = kTileThreads / 32;
+
+struct TileGeom {
+  int ec;          // paths per CTA (multiple of 4, <= 256)
+  int col_chunks;  // CTAs along the path axis
+  int rg;          // 32-cell groups per CTA
+  int pitch;       // shared-memory row pitch in ints (ec + 4: conflict-free 16-byte rows)
+  int64_t num_groups;
+  int64_t num_tiles;
+};
+
+int max_row_groups(int ec) {
+  const int col_blocks = (ec + 31) / 32;
+  const int rg = kTileWarps / col_blocks;  // one 32x32 block per warp
+  return rg < 1 ? 1 : rg;
+}
+
+// rg == 0: pick the tile height that yields at least two CTAs per SM when possible.
+TileGeom make_tile_geom(int64_t cell_num, int path_num, int rg = 0) {
+  TileGeom g;
+  g.ec = path_num < 256 ? path_num : 256;
+  g.col_chunks = (path_num + g.ec - 1) / g.ec;
+  g.pitch = g.ec + 4;
+  g.num_groups = (cell_num + kGroupRows - 1) / kGroupRows;
+  if (rg == 0) {
+    rg = max_row_groups(g.ec);
+    const int64_t want = (int64_t)sm_count() * 2;
+    while (rg > 1 && (g.num_groups + rg - 1) / rg * g.col_chunks < want) rg >>= 1;
+  }
+  g.rg = rg;
+  g.num_tiles = (g.num_groups + rg - 1) / rg;
+  return g;
+}
+
+// Shared-memory carve-up of one CTA (ints): staged tile | column sums | extra sums | flag |
+// bit words | base seats | thresholds.  The staged tile is only needed by pack.
+struct TileSmem {
+  int* tile;
+  int* sum;
+  int* extra;
+  int* flag;
+  int* bits;
+  int* base;
+  int* thr;
+};
+
+__host__ __device__ inline size_t tile_smem_ints(int ec, int rg, int pitch, bool with_tile) {
+  return (with_tile ? (size_t)rg * kGroupRows * pitch : 0) + 2 * (size_t)ec + 8 +
+         2 * (size_t)rg * ec + ec;
+}
+
+__device__ __forceinline__ TileSmem carve_tile_smem(int* s, int ec, int rg, int pitch,
+                                                    bool with_tile) {
+  TileSmem t;
+  t.tile = s;
+  s += with_tile ? (size_t)rg * kGroupRows * pitch : 0;
+  t.sum = s;
+  t.extra = s + ec;
+  t.flag = s + 2 * ec;
+  s += 2 * ec + 8;
+  t.bits = s;
+  t.base = s + rg * ec;
+  t.thr = s + 2 * rg * ec;
+  return t;
+}
+
+struct TileCtx {
+  int64_t cell_num;
+  int path_num;
+  int ec, rg, pitch;
+  int64_t tile;  // tile index along the cell axis
+  int chunk;     // chunk index along the path axis
+  int chunks;
+};
+
+// 32x32 bit transpose across a warp: lane r enters with row word a (bit c = element (r, c))
+// and leaves with the column word of column r (bit k = element (k, r)).
+__device__ __forceinline__ uint32_t warp_transpose32(uint32_t a, int lane) {
+  uint32_t m = 0x0000ffffu;
+#pragma unroll
+  for (int j = 16; j != 0; j >>= 1) {
+    const uint32_t other = __shfl_xor_sync(0xffffffffu, a, j);
+    if ((lane & j) == 0)
+      a = (a & m) | ((other & m) << j);
+    else
+      a = ((other >> j) & m) | (a & ~m);
+    m ^= (m << (j >> 1));
+  }
+  return a;
+}
+
+// Stage one tile of the mask, turn it into column bit words (kept in shared memory, and
+// written to `bits_out` when that is not null) and publish the tile's column sums and its
+// "value other than 0/1 seen" flag.  Ends with a CTA barrier.
+__device__ __forceinline__ void pack_tile(const TileCtx& x, const TileSmem& sm,
+                                          const int* __restrict__ mask,
+                                          uint32_t* __restrict__ bits_out,
+                                          int* __restrict__ tile_sums,
+                                          int* __restrict__ tile_flags) {
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int col0 = x.chunk * x.ec;
+  const int cols = (x.path_num - col0) < x.ec ? (x.path_num - col0) : x.ec;  // multiple of 4
+  const int64_t row0 = x.tile * x.rg * kGroupRows;
+  const int tile_rows = x.rg * kGroupRows;
+  const int vec_per_row = cols >> 2;
+  const int total_vecs = tile_rows * vec_per_row;
+
+  for (int i = tid; i < 2 * x.ec + 1; i += kTileThreads) sm.sum[i] = 0;
+  for (int i = tid; i < x.rg * x.ec; i += kTileThreads) sm.bits[i] = 0;
+
+  // stage the tile: every 16-byte load of a batch is issued before its first store
+  constexpr int kBatch = 9;  // a whole tile (<= 36.9 KB) in one batch of loads
+  for (int base = tid; base < total_vecs; base += kTileThreads * kBatch) {
+    int4 v[kBatch];
+#pragma unroll
+    for (int k = 0; k < kBatch; k++) {
+      const int idx = base + k * kTileThreads;
+      v[k] = make_int4(0, 0, 0, 0);
+      if (idx < total_vecs) {
+        const int r = idx / vec_per_row;
+        const int q = idx - r * vec_per_row;
+        if (row0 + r < x.cell_num)
+          v[k] = __ldcs(reinterpret_cast<const int4*>(mask + (row0 + r) * x.path_num + col0 +
+                                                       4 * q));
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < kBatch; k++) {
+      const int idx = base + k * kTileThreads;
+      if (idx < total_vecs) {
+        const int r = idx / vec_per_row;
+        const int q = idx - r * vec_per_row;
+        *reinterpret_cast<int4*>(sm.tile + r * x.pitch + 4 * q) = v[k];
+      }
+    }
+  }
+  __syncthreads();
+
+  const int col_blocks = (cols + 31) >> 5;
+  const int blocks = x.rg * col_blocks;
+  bool nonbinary = false;
+  for (int b = warp; b < blocks; b += kTileWarps) {
+    const int g = b / col_blocks;
+    const int cb = b - g * col_blocks;
+    const int64_t group = x.tile * x.rg + g;
+    if (group * kGroupRows >= x.cell_num) continue;  // warp-uniform
+    const int c_begin = cb * 32;
+    const int c_count = (cols - c_begin) < 32 ? (cols - c_begin) : 32;  // multiple of 4
+    const int* rowp = sm.tile + (g * kGroupRows + lane) * x.pitch + c_begin;
+    uint32_t roww = 0;
+#pragma unroll
+    for (int q = 0; q < 8; q++) {
+      if (4 * q < c_count) {
+        const int4 v = *reinterpret_cast<const int4*>(rowp + 4 * q);
+        const int e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          roww |= (e[j] != 0 ? 1u : 0u) << (4 * q + j);
+          if (static_cast<unsigned>(e[j]) > 1u) {
+            nonbinary = true;
+            atomicAdd(&sm.extra[c_begin + 4 * q + j], e[j] - 1);
+          }
+        }
+      }
+    }
+    const uint32_t colw = warp_transpose32(roww, lane);
+    if (lane < c_count) {
+      sm.bits[g * x.ec + c_begin + lane] = static_cast<int>(colw);
+      if (bits_out != nullptr) bits_out[group * x.path_num + col0 + c_begin + lane] = colw;
+      const int n = __popc(colw);
+      if (n != 0) atomicAdd(&sm.sum[c_begin + lane], n);
+    }
+  }
+  if (nonbinary) atomicOr(sm.flag, 1);
+  __syncthreads();
+  for (int c = tid; c < cols; c += kTileThreads)
+    tile_sums[x.tile * x.path_num + col0 + c] = sm.sum[c] + sm.extra[c];
+  if (tid == 0) tile_flags[x.tile * x.chunks + x.chunk] = *sm.flag;
+}
+
+// Exclusive prefix of the per-tile sums along the tile axis, in place, for the 4 paths
+// starting at 4 * col_block; THREADS / 4 tile segments are scanned in parallel.  The CTA
+// with col_block == 0 also folds the per-tile flags into flags[0].  The thread that owns
+// the last segment applies the capacity / throttle rules to the column total.
+template <bool THROTTLE, int THREADS>
+__device__ __forceinline__ void scan_tiles(int col_block, int* __restrict__ tile_sums,
+                                           int64_t num_tiles, int path_num,
+                                           const int* __restrict__ tile_flags,
+                                           int64_t num_flags, int* __restrict__ flags,
+                                           int* __restrict__ loads,
+                                           const int* __restrict__ caps, int ncap,
+                                           int capacity_padding, int path_wise,
+                                           int* __restrict__ prefix,
+                                           const int* __restrict__ threshold,
+                                           int (*s_warp)[4]) {
+  constexpr int kSegs = THREADS / 4;
+  constexpr int kWarpsHere = THREADS / 32;
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int cw = tid & 3;
+  const int seg = tid >> 2;
+  const int col = col_block * 4 + cw;
+  const bool valid = col < path_num;
+  const int64_t len = (num_tiles + kSegs - 1) / kSegs;
+  const int64_t t0 = seg * len;
+  const int64_t t1 = (t0 + len) < num_tiles ? (t0 + len) : num_tiles;
+
+  // The segment is read once into registers when it is short enough (the common case),
+  // so that the prefix pass needs no second, serialised trip to memory.
+  constexpr int kKeep = 16;
+  int kept[kKeep];
+  const bool short_seg = len <= kKeep;
+  int own = 0;
+  if (valid) {
+    if (short_seg) {
+#pragma unroll
+      for (int i = 0; i < kKeep; i++) {
+        const int64_t t = t0 + i;
+        kept[i] = t < t1 ? tile_sums[t * path_num + col] : 0;
+      }
+#pragma unroll
+      for (int i = 0; i < kKeep; i++) own += kept[i];
+    } else {
+      for (int64_t tb = t0; tb < t1; tb += kKeep) {
+#pragma unroll
+        for (int i = 0; i < kKeep; i++) {
+          const int64_t t = tb + i;
+          kept[i] = t < t1 ? tile_sums[t * path_num + col] : 0;
+        }
+#pragma unroll
+        for (int i = 0; i < kKeep; i++) own += kept[i];
+      }
+    }
+  }
+  int incl = own;
+#pragma unroll
+  for (int d = 4; d < 32; d <<= 1) {
+    const int n = __shfl_up_sync(0xffffffffu, incl, d);
+    if (lane >= d) incl += n;
+  }
+  if (lane >= 28) s_warp[warp][cw] = incl;
+  int start = 0;
+  if (THROTTLE && valid) start = prefix[col];  // read before anyone overwrites it below
+  int any_flag = 0;
+  if (col_block == 0)
+    for (int64_t i = tid; i < num_flags; i += THREADS) any_flag |= tile_flags[i];
+  any_flag = __syncthreads_or(any_flag);
+  if (col_block == 0 && tid == 0) flags[0] = any_flag;
+
+  int run = incl - own;
+  for (int w = 0; w < warp && w < kWarpsHere; w++) run += s_warp[w][cw];
+  if (valid) {
+    int acc = run + start;
+    if (short_seg) {
+#pragma unroll
+      for (int i = 0; i < kKeep; i++) {
+        const int64_t t = t0 + i;
+        if (t < t1) tile_sums[t * path_num + col] = acc;
+        acc += kept[i];
+      }
+    } else {
+      for (int64_t tb = t0; tb < t1; tb += kKeep) {
+#pragma unroll
+        for (int i = 0; i < kKeep; i++) {
+          const int64_t t = tb + i;
+          kept[i] = t < t1 ? tile_sums[t * path_num + col] : 0;
+        }
+#pragma unroll
+        for (int i = 0; i < kKeep; i++) {
+          const int64_t t = tb + i;
+          if (t < t1) tile_sums[t * path_num + col] = acc;
+          acc += kept[i];
+        }
+      }
+    }
+    if (seg == kSegs - 1) {
+      const int total = run + own;
+      if (THROTTLE) {
+        const int thr = threshold[col];
+        const int p = start + total;
+        prefix[col] = p >= thr ? thr : p;
+      } else {
+        loads[col] = map_load(total, col, caps, ncap, capacity_padding != 0, path_wise != 0);
+      }
+    }
+  }
+}
+
+// Write the indices (or the throttled mask) of one tile from its bit words in shared
+// memory and the tile's exclusive prefix.  `bits_in` != null: the words are first fetched
+// from global memory (separate-launch path); null: pack left them in shared memory.
+template <Mode MODE>
+__device__ __forceinline__ void expand_tile(const TileCtx& x, const TileSmem& sm,
+                                            const int* __restrict__ mask,
+                                            const uint32_t* __restrict__ bits_in,
+                                            const int* __restrict__ tile_prefix,
+                                            const int* __restrict__ flags,
+                                            int* __restrict__ out,
+                                            const int* __restrict__ threshold) {
+  const int tid = threadIdx.x;
+  const int col0 = x.chunk * x.ec;
+  const int cols = (x.path_num - col0) < x.ec ? (x.path_num - col0) : x.ec;
+  const int64_t row0 = x.tile * x.rg * kGroupRows;
+  const int64_t num_groups = (x.cell_num + kGroupRows - 1) / kGroupRows;
+  const bool general = (flags[0] & 1) != 0;
+
+  if (general) {
+    // Masks with values other than 0/1: one thread walks one path of the tile serially
+    // through the mask itself (integer semantics: index = running sum * value).
+    for (int c = tid; c < cols; c += kTileThreads) {
+      int run = tile_prefix[x.tile * x.path_num + col0 + c];
+      const int thr = MODE == Mode::kThrottle ? threshold[col0 + c] : 0;
+      for (int r = 0; r < x.rg * kGroupRows; r++) {
+        const int64_t row = row0 + r;
+        if (row >= x.cell_num) break;
+        const int64_t at = row * x.path_num + col0 + c;
+        const int m = mask[at];
+        run += m;
+        if constexpr (MODE == Mode::kThrottle) {
+          out[at] = (m == 1 && run <= thr) ? 1 : 0;
+        } else if constexpr (MODE == Mode::kSeat) {
+          out[at] = run * m;
+        } else {
+          const int64_t dst_row = (int64_t)run * m - 1;
+          if (run * m != 0 && dst_row >= 0 && dst_row < x.cell_num)
+            out[dst_row * x.path_num + col0 + c] = (int)(row + 1);
+        }
+      }
+    }
+    return;
+  }
+
+  if (bits_in != nullptr) {
+    for (int i = tid; i < x.rg * cols; i += kTileThreads) {
+      const int g = i / cols;
+      const int c = i - g * cols;
+      const int64_t group = x.tile * x.rg + g;
+      sm.bits[g * x.ec + c] =
+          group < num_groups ? static_cast<int>(bits_in[group * x.path_num + col0 + c]) : 0;
+    }
+  }
+  if constexpr (MODE == Mode::kThrottle)
+    for (int c = tid; c < cols; c += kTileThreads) sm.thr[c] = threshold[col0 + c];
+  // cols <= 256 = kTileThreads: one path per thread; fetched before the barrier so that
+  // the global reads of the prologue overlap
+  const int my_prefix = tid < cols ? tile_prefix[x.tile * x.path_num + col0 + tid] : 0;
+  __syncthreads();
+  if (tid < cols) {
+    int run = my_prefix;
+    for (int g = 0; g < x.rg; g++) {
+      sm.base[g * x.ec + tid] = run;
+      run += __popc(static_cast<uint32_t>(sm.bits[g * x.ec + tid]));
+    }
+  }
+  __syncthreads();
+
+  const int vec_per_row = cols >> 2;
+  const int total_vecs = x.rg * kGroupRows * vec_per_row;
+  for (int idx = tid; idx < total_vecs; idx += kTileThreads) {
+    const int r = idx / vec_per_row;
+    const int q = idx - r * vec_per_row;
+    const int64_t row = row0 + r;
+    if (row >= x.cell_num) break;
+    const int g = r >> 5;
+    const int rr = r & 31;
+    const uint32_t low = 0xffffffffu >> (31 - rr);  // bits 0..rr
+    const int4 w4 = *reinterpret_cast<const int4*>(sm.bits + g * x.ec + 4 * q);
+    const int4 b4 = *reinterpret_cast<const int4*>(sm.base + g * x.ec + 4 * q);
+    const uint32_t w[4] = {(uint32_t)w4.x, (uint32_t)w4.y, (uint32_t)w4.z, (uint32_t)w4.w};
+    const int b[4] = {b4.x, b4.y, b4.z, b4.w};
+    int v[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int bit = (w[j] >> rr) & 1u;
+      const int seat = b[j] + __popc(w[j] & low);
+      if constexpr (MODE == Mode::kThrottle)
+        v[j] = (bit && seat <= sm.thr[4 * q + j]) ? 1 : 0;
+      else
+        v[j] = bit ? seat : 0;
+    }
+    if constexpr (MODE == Mode::kTag) {
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const int64_t dst_row = (int64_t)v[j] - 1;
+        if (v[j] != 0 && dst_row < x.cell_num)
+          out[dst_row * x.path_num + col0 + 4 * q + j] = (int)(row + 1);
+      }
+    } else {
+      __stcs(reinterpret_cast<int4*>(out + row * x.path_num + col0 + 4 * q),
+             make_int4(v[0], v[1], v[2], v[3]));
+    }
+  }
+}
+
+struct TiledArgs {
+  const int* mask;
+  int* out;
+  uint32_t* bits;
+  int* tile_sums;
+  int* tile_flags;
+  int* flags;
+  int* loads;
+  const int* caps;
+  int ncap;
+  int capacity_padding;
+  int path_wise;
+  int* prefix;
+  const int* threshold;
+  int64_t cell_num;
+  int path_num;
+  int ec, rg, pitch;
+  int64_t num_tiles;
+  int chunks;
+};
+
+__device__ __forceinline__ TileCtx ctx_of(const TiledArgs& a) {
+  TileCtx x;
+  x.cell_num = a.cell_num;
+  x.path_num = a.path_num;
+  x.ec = a.ec;
+  x.rg = a.rg;
+  x.pitch = a.pitch;
+  x.tile = blockIdx.x;
+  x.chunk = blockIdx.y;
+  x.chunks = a.chunks;
+  return x;
+}
+
+__global__ void __launch_bounds__(kTileThreads) mask_pack_tiled_kernel(const TiledArgs a) {
+  extern __shared__ __align__(16) int s_dyn[];
+  const TileSmem sm = carve_tile_smem(s_dyn, a.ec, a.rg, a.pitch, true);
+  pack_tile(ctx_of(a), sm, a.mask, a.bits, a.tile_sums, a.tile_flags);
+}
+
+template <bool THROTTLE>
+__global__ void __launch_bounds__(1024) tile_scan_wide_kernel(const TiledArgs a) {
+  __shared__ int s_warp[32][4];
+  scan_tiles<THROTTLE, 1024>(blockIdx.x, a.tile_sums, a.num_tiles, a.path_num, a.tile_flags,
+                             a.num_tiles * a.chunks, a.flags, a.loads, a.caps, a.ncap,
+                             a.capacity_padding, a.path_wise, a.prefix, a.threshold, s_warp);
+}
+
+template <Mode MODE>
+__global__ void __launch_bounds__(kTileThreads) index_expand_tiled_kernel(const TiledArgs a) {
+  extern __shared__ __align__(16) int s_dyn[];
+  const TileSmem sm = carve_tile_smem(s_dyn, a.ec, a.rg, a.pitch, false);
+  expand_tile<MODE>(ctx_of(a), sm, a.mask, a.bits, a.tile_sums, a.flags, a.out, a.threshold);
+}
+
+// Small masks: the whole grid is resident at once, so pack, scan and expand run as one
+// cooperative launch with two grid-wide barriers; the bit words never leave shared memory
+// and two launch boundaries disappear.
+template <Mode MODE>
+__global__ void __launch_bounds__(kTileThreads, 3) index_fused_kernel(const TiledArgs a) {
+  extern __shared__ __align__(16) int s_dyn[];
+  __shared__ int s_warp[kTileWarps][4];
+  cooperative_groups::grid_group grid = cooperative_groups::this_grid();
+  const TileSmem sm = carve_tile_smem(s_dyn, a.ec, a.rg, a.pitch, true);
+  const TileCtx x = ctx_of(a);
+  pack_tile(x, sm, a.mask, nullptr, a.tile_sums, a.tile_flags);
+  grid.sync();
+  const int linear = blockIdx.y * gridDim.x + blockIdx.x;
+  const int scan_blocks = (a.path_num + 3) / 4;
+  const int total_blocks = gridDim.x * gridDim.y;
+  for (int cb = linear; cb < scan_blocks; cb += total_blocks) {
+    scan_tiles<MODE == Mode::kThrottle, kTileThreads>(
+        cb, a.tile_sums, a.num_tiles, a.path_num, a.tile_flags, a.num_tiles * a.chunks, a.flags,
+        a.loads, a.caps, a.ncap, a.capacity_padding, a.path_wise, a.prefix, a.threshold, s_warp);
+    __syncthreads();
+  }
+  grid.sync();
+  expand_tile<MODE>(x, sm, a.mask, nullptr, a.tile_sums, a.flags, a.out, a.threshold);
+}
+
+size_t tiled_scratch_bytes(int64_t cell_num, int path_num) {
+  // bounded for the smallest tile (one 32-cell group per tile)
+  const size_t groups = (size_t)((cell_num + kGroupRows - 1) / kGroupRows);
+  const size_t chunks = (size_t)(path_num + 255) / 256;
+  return 256 + round_up(groups * chunks * 4 + 4, 256) + 2 * round_up(groups * path_num * 4 + 4, 256);
+}
+
+// Resident-CTA capacity of the fused kernel per mode (cached per device and shared-memory
+// size by the caller's thread).
+template <Mode MODE>
+int fused_capacity(size_t smem) {
+  static thread_local std::map<std::pair<int, size_t>, int> cache;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  const auto key = std::make_pair(dev, smem);
+  const auto hit = cache.find(key);
+  if (hit != cache.end()) return hit->second;
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, index_fused_kernel<MODE>,
+                                                    kTileThreads, smem) != cudaSuccess)
+    per_sm = 0;
+  const int capacity = per_sm * sm_count();
+  cache[key] = capacity;
+  return capacity;
+}
+
+template <Mode MODE>
+int launch_fused(const TiledArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
+  void* params[] = {const_cast<TiledArgs*>(&a)};
+  BRT_CUDA_TRY(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(index_fused_kernel<MODE>),
+                                           grid, dim3(kTileThreads), params, smem, stream));
+  return BRT_OK;
+}
+
+int fused_capacity_for(Mode mode, size_t smem) {
+  switch (mode) {
+    case Mode::kSeat: return fused_capacity<Mode::kSeat>(smem);
+    case Mode::kTag: return fused_capacity<Mode::kTag>(smem);
+    default: return fused_capacity<Mode::kThrottle>(smem);
+  }
+}
+
+int launch_tiled(Mode mode, const int32_t* mask, int32_t* out, int32_t* loads, int64_t cell_num,
+                 int path_num, const int32_t* caps, int ncap, int capacity_padding,
+                 int path_wise, int32_t* prefix, const int32_t* threshold, void* scratch,
+                 cudaStream_t stream) {
+  TileGeom g = make_tile_geom(cell_num, path_num);
+  BRT_REQUIRE(g.num_tiles <= 0x7fffffffLL && g.col_chunks <= 65535,
+              "mask of %lld x %d cells is too large for one launch", (long long)cell_num,
+              path_num);
+  // Fused single launch when some tile height lets the whole grid be resident at once:
+  // take the smallest such height (most CTAs).
+  bool fused = false;
+  {
+    const int rg_max = max_row_groups(g.ec);
+    const int64_t groups = g.num_groups * g.col_chunks;
+    if ((groups + rg_max - 1) / rg_max <= 4096) {  // cheap pre-filter
+      for (int rg = 1; rg <= rg_max; rg <<= 1) {
+        const TileGeom t = make_tile_geom(cell_num, path_num, rg);
+        const size_t smem = tile_smem_ints(t.ec, t.rg, t.pitch, true) * sizeof(int);
+        if (t.num_tiles * t.col_chunks <= fused_capacity_for(mode, smem)) {
+          g = t;
+          fused = true;
+          break;
+        }
+      }
+    }
+  }
+  TiledArgs a;
+  char* p = static_cast<char*>(scratch);
+  a.flags = reinterpret_cast<int*>(p);
+  p += 256;
+  a.tile_flags = reinterpret_cast<int*>(p);
+  p += round_up((size_t)g.num_tiles * g.col_chunks * 4 + 4, 256);
+  a.tile_sums = reinterpret_cast<int*>(p);
+  p += round_up((size_t)g.num_tiles * path_num * 4 + 4, 256);
+  a.bits = reinterpret_cast<uint32_t*>(p);
+  a.mask = mask;
+  a.out = out;
+  a.loads = loads;
+  a.caps = caps;
+  a.ncap = ncap;
+  a.capacity_padding = capacity_padding;
+  a.path_wise = path_wise;
+  a.prefix = prefix;
+  a.threshold = threshold;
+  a.cell_num = cell_num;
+  a.path_num = path_num;
+  a.ec = g.ec;
+  a.rg = g.rg;
+  a.pitch = g.pitch;
+  a.num_tiles = g.num_tiles;
+  a.chunks = g.col_chunks;
+
+  const dim3 grid((unsigned)g.num_tiles, (unsigned)g.col_chunks);
+  const size_t smem_full = tile_smem_ints(g.ec, g.rg, g.pitch, true) * sizeof(int);
+  const size_t smem_expand = tile_smem_ints(g.ec, g.rg, g.pitch, false) * sizeof(int);
+  if (mode == Mode::kTag)
+    BRT_CUDA_TRY(cudaMemsetAsync(out, 0, (size_t)cell_num * path_num * 4, stream));
+  if (fused) {
+    switch (mode) {
+      case Mode::kSeat: return launch_fused<Mode::kSeat>(a, grid, smem_full, stream);
+      case Mode::kTag: return launch_fused<Mode::kTag>(a, grid, smem_full, stream);
+      default: return launch_fused<Mode::kThrottle>(a, grid, smem_full, stream);
+    }
+  }
+
+  mask_pack_tiled_kernel<<<grid, kTileThreads, smem_full, stream>>>(a);
+  BRT_LAUNCH_CHECK("mask_pack_tiled_kernel");
+  const unsigned scan_grid = (unsigned)((path_num + 3) / 4);
+  if (mode == Mode::kThrottle)
+    tile_scan_wide_kernel<true><<<scan_grid, 1024, 0, stream>>>(a);
+  else
+    tile_scan_wide_kernel<false><<<scan_grid, 1024, 0, stream>>>(a);
+  BRT_LAUNCH_CHECK("tile_scan_wide_kernel");
+  switch (mode) {
+    case Mode::kSeat:
+      index_expand_tiled_kernel<Mode::kSeat><<<grid, kTileThreads, smem_expand, stream>>>(a);
+      break;
+    case Mode::kTag:
+      index_expand_tiled_kernel<Mode::kTag><<<grid, kTileThreads, smem_expand, stream>>>(a);
+      break;
+    case Mode::kThrottle:
+      index_expand_tiled_kernel<Mode::kThrottle><<<grid, kTileThreads, smem_expand, stream>>>(a);
+      break;
+  }
+  BRT_LAUNCH_CHECK("index_expand_tiled_kernel");
+  return BRT_OK;
+}
+
+// ================================================================================ strip path
 template <int V>
 int launch_scan(Mode mode, const Tiling& tl, const Scratch& sc, const int32_t* mask,
                 int32_t* out, int32_t* loads, int64_t cell_num, int path_num,
@@ -480,6 +1106,9 @@ int run_scan(Mode mode, const int32_t* mask, int32_t* out, int32_t* loads, int64
   if (scratch_bytes < need)
     return set_error(BRT_ERR_SCRATCH_TOO_SMALL, "scratch holds %zu bytes, %zu needed",
                      scratch_bytes, need);
+  if (path_num % 4 == 0 && aligned_to(mask, 16) && aligned_to(out, 16))
+    return launch_tiled(mode, mask, out, loads, cell_num, path_num, caps, ncap,
+                        capacity_padding, path_wise, prefix, threshold, scratch, stream);
   const bool a16 = aligned_to(mask, 16) && aligned_to(out, 16) &&
                    (threshold == nullptr || aligned_to(threshold, 16));
   const bool a8 = aligned_to(mask, 8) && aligned_to(out, 8) &&

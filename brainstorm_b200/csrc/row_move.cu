@@ -1,23 +1,30 @@
 // Token dispatch and weighted combine for sm_100a.
 //
-// Both are pure data movement, so the design goal is HBM traffic equal to the
-// algorithmic minimum:
+// Both are pure data movement, so the design goal is HBM traffic equal to the algorithmic
+// minimum and enough independent 16-byte accesses in flight to cover HBM latency.
 //
-//   dispatch : source-major.  One warp owns (cell, 2 KB piece of the row): it reads the
-//              cell's index row once, keeps the piece in registers and stores it to every
-//              path that kept the cell, so a source row crosses HBM once however many
-//              copies are made.  All accesses are 16 bytes per lane (narrower only when the
-//              row size or a pointer is not 16-byte aligned).  Rows of the output that no
-//              cell lands on (capacity padding, dropped seats) are found through a byte map
-//              that the copy pass marks, and are written as zeros by a second launch: the
-//              output is never memset as a whole and no row is written twice.
-//   combine  : destination-major.  One warp owns (cell, piece): it walks the cell's kept
-//              routes in ascending path order, accumulates in fp32 registers with separate
-//              multiply and add roundings (the order and rounding of the reference's
-//              atomicAdd sequence, without atomics) and writes the row once.
+//   dispatch : source-major.  One warp owns (cell, 2 KB piece of its row): it scans the
+//              cell's index row with one coalesced 16-byte load per lane (128 paths per
+//              load), keeps the piece in registers and stores it to every path that kept
+//              the cell (times the gate when weighted), so a source row crosses HBM once
+//              however many copies are made.  The index row of the warp's next item is
+//              fetched before the current one is moved.  Rows of the output that no cell
+//              lands on (capacity padding, dropped seats) are found through a byte map that
+//              the move pass marks, and are written as zeros by a second launch: the output
+//              is never memset as a whole and no row is written twice.
+//   combine  : destination-major.  One warp owns (cell, 1 KB piece).  The rows of the
+//              cell's kept routes are brought into shared memory with asynchronous 16-byte
+//              copies (cp.async) - the copies of the warp's NEXT item are issued before
+//              the current item is folded, so every warp keeps two items of row traffic in
+//              flight without spending registers on it.  The fold walks the routes in
+//              ascending path order with separate fp32 multiply and add roundings (the
+//              order and rounding of the reference's atomicAdd sequence, without atomics)
+//              and writes the row once.  Rows that are not 16-byte aligned take a simpler
+//              register-only kernel.
 //
-// Per-path base rows (prefix sum of loads, or e * max_path_load) are computed once per
-// CTA into shared memory instead of once per thread.
+// Per-path base rows (prefix sum of loads, or e * max_path_load) are computed once per CTA
+// into shared memory.  Cells with more routes than the staging buffers hold (4) finish
+// through a slower serial walk of the index row, so any number of routes is correct.
 #include "common.cuh"
 
 #include <initializer_list>
@@ -27,9 +34,71 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
-constexpr int kUnroll = 4;                 // vectors per lane per piece
-constexpr int kPieceVecs = 32 * kUnroll;   // vectors per piece
 constexpr int kMaxPaths = 4096;
+constexpr int kPieceVecs = 128;    // vectors per dispatch item (2 KB at 16 bytes)
+constexpr int kCopyUnroll = kPieceVecs / 32;
+constexpr int kMaxRoutes = 4;      // routes per combine item staged in shared memory
+constexpr int kFoldVecs = 64;      // vectors per combine item (1 KB at 16 bytes)
+constexpr int kFoldUnroll = kFoldVecs / 32;
+constexpr int kStages = 2;
+
+struct RouteSlot {
+  int row;     // output row (dispatch) / input row (combine)
+  float gate;  // gate as fp32; for 2-D dispatch the path id, bit-cast
+};
+
+// The index row of one cell is scanned IV paths per lane: one coalesced 16-byte load per
+// lane covers 128 paths when the row is 16-byte aligned (IV = 4), otherwise one path per
+// lane (IV = 1).
+template <int IV>
+__device__ __forceinline__ void load_index_chunk(const int* __restrict__ indices, int64_t cell,
+                                                 int path_num, int chunk, int lane,
+                                                 int (&v)[IV]) {
+  const int e0 = (chunk * 32 + lane) * IV;
+  if constexpr (IV == 4) {
+    if (e0 < path_num) {
+      const int4 q = *reinterpret_cast<const int4*>(indices + cell * path_num + e0);
+      v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+    } else {
+      v[0] = v[1] = v[2] = v[3] = 0;
+    }
+  } else {
+    v[0] = e0 < path_num ? indices[cell * path_num + e0] : 0;
+  }
+}
+
+// Gate rows travel with the index rows.  GK: 0 = no gates, 1 = fp32, 2 = stored as DT.
+template <int IV, int GK, int DT>
+__device__ __forceinline__ void load_gate_chunk(const void* __restrict__ gates, int64_t cell,
+                                                int path_num, int chunk, int lane,
+                                                float (&g)[IV]) {
+#pragma unroll
+  for (int j = 0; j < IV; j++) g[j] = 1.f;
+  if constexpr (GK == 0) return;
+  const int e0 = (chunk * 32 + lane) * IV;
+  if (e0 >= path_num) return;
+  if constexpr (GK == 1) {
+    const float* p = static_cast<const float*>(gates) + cell * path_num + e0;
+    if constexpr (IV == 4) {
+      const float4 q = *reinterpret_cast<const float4*>(p);
+      g[0] = q.x; g[1] = q.y; g[2] = q.z; g[3] = q.w;
+    } else {
+      g[0] = *p;
+    }
+  } else {
+    using E = typename Elem<DT>::type;
+    const E* p = static_cast<const E*>(gates) + cell * path_num + e0;
+    if constexpr (IV == 4 && sizeof(E) == 2) {
+      alignas(8) E e[4];
+      *reinterpret_cast<uint2*>(e) = *reinterpret_cast<const uint2*>(p);
+#pragma unroll
+      for (int j = 0; j < 4; j++) g[j] = Elem<DT>::to_f32(e[j]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < IV; j++) g[j] = Elem<DT>::to_f32(p[j]);
+    }
+  }
+}
 
 // s_loads[e], s_base[e] for every path; called by all threads of the CTA.
 __device__ __forceinline__ void setup_paths(const int* __restrict__ loads, int path_num,
@@ -76,27 +145,116 @@ __device__ __forceinline__ typename Chunk<VB>::type scale_chunk(typename Chunk<V
   return *reinterpret_cast<typename L::V*>(e);
 }
 
-struct DispatchArgs {
+struct MoveArgs {
   const void* src;
   void* dst;
   const void* gates;
   const int* indices;
   const int* loads;
-  const int* old_tags;
-  int* new_tags;
-  unsigned char* row_marks;
+  const int* old_tags;       // dispatch only
+  int* new_tags;             // dispatch only
+  unsigned char* row_marks;  // dispatch only
   int64_t cell_num;
-  int64_t row_vecs;       // vectors per row
+  int64_t row_vecs;  // vectors per row
   int64_t pieces_per_row;
   int path_num;
   int max_path_load;
-  int64_t total_rows;
+  int64_t total_rows;  // dispatch: output rows
+  int is_residual;     // combine only
 };
 
+// Position of a warp in the (cell, piece) item space.  Items are visited with a fixed
+// stride, so the position advances by a precomputed (cells, pieces) step with one carry
+// instead of a 64-bit division per item.
+struct ItemCursor {
+  int64_t cell;
+  int piece;
+};
+struct ItemStep {
+  int64_t cells;
+  int pieces;
+  int pieces_per_row;
+};
+__device__ __forceinline__ ItemCursor cursor_at(int64_t item, int64_t pieces_per_row) {
+  ItemCursor c;
+  c.cell = item / pieces_per_row;
+  c.piece = (int)(item - c.cell * pieces_per_row);
+  return c;
+}
+__device__ __forceinline__ ItemStep step_of(int64_t stride, int64_t pieces_per_row) {
+  ItemStep s;
+  s.cells = stride / pieces_per_row;
+  s.pieces = (int)(stride - s.cells * pieces_per_row);
+  s.pieces_per_row = (int)pieces_per_row;
+  return s;
+}
+__device__ __forceinline__ ItemCursor advance(ItemCursor c, const ItemStep& s) {
+  c.cell += s.cells;
+  c.piece += s.pieces;
+  if (c.piece >= s.pieces_per_row) {
+    c.piece -= s.pieces_per_row;
+    c.cell += 1;
+  }
+  return c;
+}
+
+// Scan the index row of `cell` (first chunk already in seat/gate registers) and write its
+// kept routes to slots[0..kMaxRoutes) in ascending path order; returns their total count.
+// kStorePath: keep the path id in the slot's gate field (2-D dispatch needs it).
+template <int IV, int GK, int DT, bool kStorePath>
+__device__ __forceinline__ int build_routes(const MoveArgs& a, int64_t cell,
+                                            const int (&first_seat)[IV],
+                                            const float (&first_gate)[IV], const int* s_loads,
+                                            const int* s_base, RouteSlot* slots, int lane) {
+  const int E = a.path_num;
+  const int chunks = (E + 32 * IV - 1) / (32 * IV);
+  int count = 0;
+  for (int c = 0; c < chunks; c++) {
+    int seat[IV];
+    float gate[IV];
+    if (c == 0) {
+#pragma unroll
+      for (int j = 0; j < IV; j++) { seat[j] = first_seat[j]; gate[j] = first_gate[j]; }
+    } else {
+      load_index_chunk<IV>(a.indices, cell, E, c, lane, seat);
+      load_gate_chunk<IV, GK, DT>(a.gates, cell, E, c, lane, gate);
+    }
+    unsigned mine = 0;
+#pragma unroll
+    for (int j = 0; j < IV; j++) {
+      const int e = (c * 32 + lane) * IV + j;
+      const bool keep = e < E && seat[j] > 0 && seat[j] <= s_loads[e];
+      mine |= (keep ? 1u : 0u) << j;
+    }
+    unsigned any = __ballot_sync(0xffffffffu, mine != 0);
+    while (any) {  // lanes, then paths within a lane: ascending path order
+      const int l = __ffs(any) - 1;
+      any &= any - 1;
+      const unsigned theirs = __shfl_sync(0xffffffffu, mine, l);
+#pragma unroll
+      for (int j = 0; j < IV; j++) {
+        if ((theirs >> j) & 1u) {  // warp-uniform
+          const int e = (c * 32 + l) * IV + j;
+          const int seat_b = __shfl_sync(0xffffffffu, seat[j], l);
+          const float g = __shfl_sync(0xffffffffu, gate[j], l);
+          if (count < kMaxRoutes && lane == 0) {
+            slots[count].row = s_base[e] + seat_b - 1;
+            slots[count].gate = kStorePath ? __int_as_float(e) : g;
+          }
+          count++;
+        }
+      }
+    }
+  }
+  return count;
+}
+
 // ---------------------------------------------------------------------------------- dispatch
-template <int VB, int DT, bool WEIGHTED, bool IS_1D>
-__global__ void __launch_bounds__(kThreads) dispatch_seat_kernel(const DispatchArgs a) {
+template <int VB, int DT, bool WEIGHTED, bool IS_1D, int IV>
+__global__ void __launch_bounds__(kThreads, 4) dispatch_seat_kernel(const MoveArgs a) {
   using V = typename Chunk<VB>::type;
+  constexpr int U = kCopyUnroll;
+  constexpr int GK = WEIGHTED ? 2 : 0;
   extern __shared__ int s_mem[];
   int* s_loads = s_mem;
   int* s_base = s_mem + a.path_num;
@@ -109,81 +267,120 @@ __global__ void __launch_bounds__(kThreads) dispatch_seat_kernel(const DispatchA
   const V* __restrict__ src = static_cast<const V*>(a.src);
   V* __restrict__ dst = static_cast<V*>(a.dst);
   const int E = a.path_num;
+  const int chunks = (E + 32 * IV - 1) / (32 * IV);
 
-  for (int64_t item = warp; item < items; item += warps) {
-    const int64_t cell = item / a.pieces_per_row;
-    const int64_t piece = item - cell * a.pieces_per_row;
-    const int64_t v0 = piece * kPieceVecs + lane;
-    V regs[kUnroll];
+  const ItemStep step = step_of(warps, a.pieces_per_row);
+  ItemCursor at = cursor_at(warp < items ? warp : 0, a.pieces_per_row);
+  if (warp >= items) at.cell = a.cell_num;
+  ItemCursor ahead = advance(at, step);
+  int cur[IV];
+#pragma unroll
+  for (int j = 0; j < IV; j++) cur[j] = 0;
+  if (at.cell < a.cell_num) load_index_chunk<IV>(a.indices, at.cell, E, 0, lane, cur);
+  while (at.cell < a.cell_num) {
+    int nxt[IV];
+#pragma unroll
+    for (int j = 0; j < IV; j++) nxt[j] = 0;
+    if (ahead.cell < a.cell_num) load_index_chunk<IV>(a.indices, ahead.cell, E, 0, lane, nxt);
+
+    const int64_t cell = at.cell;
+    const int piece = at.piece;
+    const int64_t v0 = (int64_t)piece * kPieceVecs + lane;
+    V regs[U];
     bool loaded = false;
-    for (int p = 0; p < E; p += 32) {
-      const int e_lane = p + lane;
-      int seat = 0;
-      if (e_lane < E) seat = a.indices[cell * E + e_lane];
-      const bool keep = e_lane < E && seat > 0 && seat <= s_loads[e_lane];
-      float gate = 0.f;
-      if constexpr (WEIGHTED) {
-        if (keep)
-          gate = Elem<DT>::to_f32(
-              static_cast<const typename Elem<DT>::type*>(a.gates)[cell * E + e_lane]);
+    for (int c = 0; c < chunks; c++) {
+      int seat[IV];
+      if (c == 0) {
+#pragma unroll
+        for (int j = 0; j < IV; j++) seat[j] = cur[j];
+      } else {
+        load_index_chunk<IV>(a.indices, cell, E, c, lane, seat);
       }
-      unsigned ballot = __ballot_sync(0xffffffffu, keep);
-      while (ballot) {
-        const int b = __ffs(ballot) - 1;
-        ballot &= ballot - 1;
-        const int e = p + b;
-        const int seat_b = __shfl_sync(0xffffffffu, seat, b);
-        const int64_t row = (int64_t)s_base[e] + seat_b - 1;
-        if (!IS_1D || !loaded) {
-          const int64_t src_row = IS_1D ? cell : cell * E + e;
-          const V* sp = src + src_row * a.row_vecs;
+      unsigned mine = 0;
 #pragma unroll
-          for (int u = 0; u < kUnroll; u++) {
-            const int64_t v = v0 + u * 32;
-            if (v < a.row_vecs) regs[u] = load_stream(sp + v);
-          }
-          loaded = true;
-        }
-        V* dp = dst + row * a.row_vecs;
-        if constexpr (WEIGHTED) {
-          const float g = __shfl_sync(0xffffffffu, gate, b);
+      for (int j = 0; j < IV; j++) {
+        const int e = (c * 32 + lane) * IV + j;
+        const bool keep = e < E && seat[j] > 0 && seat[j] <= s_loads[e];
+        mine |= (keep ? 1u : 0u) << j;
+      }
+      float gate[IV];
+      if (mine != 0)
+        load_gate_chunk<IV, GK, DT>(a.gates, cell, E, c, lane, gate);
+      else {
 #pragma unroll
-          for (int u = 0; u < kUnroll; u++) {
-            const int64_t v = v0 + u * 32;
-            if (v < a.row_vecs) store_stream(dp + v, scale_chunk<VB, DT>(regs[u], g));
-          }
-        } else {
+        for (int j = 0; j < IV; j++) gate[j] = 1.f;
+      }
+      unsigned any = __ballot_sync(0xffffffffu, mine != 0);
+      while (any) {
+        const int l = __ffs(any) - 1;
+        any &= any - 1;
+        const unsigned theirs = __shfl_sync(0xffffffffu, mine, l);
 #pragma unroll
-          for (int u = 0; u < kUnroll; u++) {
-            const int64_t v = v0 + u * 32;
-            if (v < a.row_vecs) store_stream(dp + v, regs[u]);
+        for (int j = 0; j < IV; j++) {
+          if ((theirs >> j) & 1u) {  // warp-uniform
+            const int e = (c * 32 + l) * IV + j;
+            const int seat_b = __shfl_sync(0xffffffffu, seat[j], l);
+            const int64_t row = (int64_t)s_base[e] + seat_b - 1;
+            if (!IS_1D || !loaded) {
+              const int64_t src_row = IS_1D ? cell : cell * E + e;
+              const V* sp = src + src_row * a.row_vecs;
+#pragma unroll
+              for (int u = 0; u < U; u++) {
+                const int64_t v = v0 + u * 32;
+                if (v < a.row_vecs) regs[u] = load_stream(sp + v);
+              }
+              loaded = true;
+            }
+            V* dp = dst + row * a.row_vecs;
+            if constexpr (WEIGHTED) {
+              const float g = __shfl_sync(0xffffffffu, gate[j], l);
+#pragma unroll
+              for (int u = 0; u < U; u++) {
+                const int64_t v = v0 + u * 32;
+                if (v < a.row_vecs) store_stream(dp + v, scale_chunk<VB, DT>(regs[u], g));
+              }
+            } else {
+#pragma unroll
+              for (int u = 0; u < U; u++) {
+                const int64_t v = v0 + u * 32;
+                if (v < a.row_vecs) store_stream(dp + v, regs[u]);
+              }
+            }
+            if (piece == 0 && lane == 0) {
+              a.row_marks[row] = 1;
+              if (a.new_tags != nullptr) a.new_tags[row] = a.old_tags[cell];
+            }
           }
-        }
-        if (piece == 0 && lane == 0) {
-          a.row_marks[row] = 1;
-          if (a.new_tags != nullptr) a.new_tags[row] = a.old_tags[cell];
         }
       }
     }
+#pragma unroll
+    for (int j = 0; j < IV; j++) cur[j] = nxt[j];
+    at = ahead;
+    ahead = advance(ahead, step);
   }
 }
 
-// Writes zeros to every row (and tag) the copy pass did not mark.
+// Writes zeros to every row (and tag) the move pass did not mark.
 template <int VB>
-__global__ void __launch_bounds__(kThreads) dispatch_zero_fill_kernel(const DispatchArgs a) {
+__global__ void __launch_bounds__(kThreads) dispatch_zero_fill_kernel(const MoveArgs a) {
   using V = typename Chunk<VB>::type;
+  constexpr int kUnroll = kCopyUnroll;
   const int lane = threadIdx.x & 31;
   const int64_t warp = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
   const int64_t warps = (int64_t)gridDim.x * kWarps;
   const int64_t items = a.total_rows * a.pieces_per_row;
   V* __restrict__ dst = static_cast<V*>(a.dst);
   const V zero = zero_chunk<V>();
-  for (int64_t item = warp; item < items; item += warps) {
-    const int64_t row = item / a.pieces_per_row;
-    const int64_t piece = item - row * a.pieces_per_row;
+  const ItemStep step = step_of(warps, a.pieces_per_row);
+  ItemCursor at = cursor_at(warp < items ? warp : 0, a.pieces_per_row);
+  if (warp >= items) at.cell = a.total_rows;
+  for (; at.cell < a.total_rows; at = advance(at, step)) {
+    const int64_t row = at.cell;
+    const int piece = at.piece;
     if (a.row_marks[row] != 0) continue;
     V* dp = dst + row * a.row_vecs;
-    const int64_t v0 = piece * kPieceVecs + lane;
+    const int64_t v0 = (int64_t)piece * kPieceVecs + lane;
 #pragma unroll
     for (int u = 0; u < kUnroll; u++) {
       const int64_t v = v0 + u * 32;
@@ -196,8 +393,9 @@ __global__ void __launch_bounds__(kThreads) dispatch_zero_fill_kernel(const Disp
 // Tag-index dispatch: output-major.  One warp owns (output row, piece); row i of path e
 // pulls cell tag-1 when i < loads[e] and the tag is non-zero, otherwise it is zeroed.
 template <int VB, int DT, bool WEIGHTED, bool IS_1D>
-__global__ void __launch_bounds__(kThreads) dispatch_tag_kernel(const DispatchArgs a) {
+__global__ void __launch_bounds__(kThreads) dispatch_tag_kernel(const MoveArgs a) {
   using V = typename Chunk<VB>::type;
+  constexpr int kUnroll = kCopyUnroll;
   extern __shared__ int s_mem[];
   int* s_loads = s_mem;
   int* s_base = s_mem + a.path_num;
@@ -265,23 +463,164 @@ __global__ void __launch_bounds__(kThreads) dispatch_tag_kernel(const DispatchAr
 }
 
 // ---------------------------------------------------------------------------------- combine
-struct CombineArgs {
-  const void* src;
-  void* dst;
-  const void* gates;
-  const int* indices;
-  const int* loads;
-  int64_t cell_num;
-  int64_t row_vecs;
-  int64_t pieces_per_row;
-  int path_num;
-  int max_path_load;
-  int is_residual;
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
+  const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() {
+  asm volatile("cp.async.commit_group;\n" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+template <int VB, int DT, int GMODE>
+__device__ __forceinline__ void fold_chunk(float (&acc)[Lanes<VB, DT>::N],
+                                           const typename Chunk<VB>::type& row, float g) {
+  using L = Lanes<VB, DT>;
+  alignas(VB) typename L::E el[L::N];
+  *reinterpret_cast<typename L::V*>(el) = row;
+#pragma unroll
+  for (int i = 0; i < L::N; i++) {
+    float x = Elem<DT>::to_f32(el[i]);
+    if constexpr (GMODE != 0) x = __fmul_rn(x, g);
+    acc[i] = __fadd_rn(acc[i], x);
+  }
+}
+
+template <int DT, int GMODE>
+__device__ __forceinline__ float gate_at(const void* gates, int64_t at) {
+  if constexpr (GMODE == 1) return static_cast<const float*>(gates)[at];
+  if constexpr (GMODE == 2)
+    return Elem<DT>::to_f32(static_cast<const typename Elem<DT>::type*>(gates)[at]);
+  return 1.f;
+}
+
+// Per-warp staging area: kStages x (route table + kMaxRoutes row pieces of 1 KB).
+struct alignas(16) FoldStage {
+  uint4 rows[kMaxRoutes][kFoldVecs];
+  RouteSlot route[kMaxRoutes];
+  int count;
+  int pad[3];
 };
 
 // GMODE: 0 = no gates, 1 = fp32 gates, 2 = gates stored in the data type.
+// 16-byte rows only (VB == 16).
+template <int DT, int GMODE, int IV>
+__global__ void __launch_bounds__(kThreads, 3) combine_seat_async_kernel(const MoveArgs a) {
+  constexpr int VB = 16;
+  using L = Lanes<VB, DT>;
+  using V = typename L::V;
+  extern __shared__ __align__(16) unsigned char s_raw[];
+  FoldStage* s_stage = reinterpret_cast<FoldStage*>(s_raw);  // [kWarps][kStages]
+  int* s_loads = reinterpret_cast<int*>(s_raw + sizeof(FoldStage) * kWarps * kStages);
+  int* s_base = s_loads + a.path_num;
+  setup_paths(a.loads, a.path_num, a.max_path_load, s_loads, s_base);
+
+  const int lane = threadIdx.x & 31;
+  const int warp_in_cta = threadIdx.x >> 5;
+  const int64_t warp = (int64_t)blockIdx.x * kWarps + warp_in_cta;
+  const int64_t warps = (int64_t)gridDim.x * kWarps;
+  const int64_t items = a.cell_num * a.pieces_per_row;
+  const V* __restrict__ src = static_cast<const V*>(a.src);
+  V* __restrict__ dst = static_cast<V*>(a.dst);
+  const int E = a.path_num;
+  FoldStage* my = s_stage + warp_in_cta * kStages;
+
+  int seat[IV];
+  float gate[IV];
+  auto fetch = [&](const ItemCursor& c) {
+#pragma unroll
+    for (int j = 0; j < IV; j++) { seat[j] = 0; gate[j] = 1.f; }
+    if (c.cell < a.cell_num) {
+      load_index_chunk<IV>(a.indices, c.cell, E, 0, lane, seat);
+      load_gate_chunk<IV, GMODE, DT>(a.gates, c.cell, E, 0, lane, gate);
+    }
+  };
+  // Build the route table of an item from the registers fetched for it and start the
+  // asynchronous copies of its rows; always closes exactly one copy group.
+  auto issue = [&](FoldStage& st, const ItemCursor& c) {
+    if (c.cell < a.cell_num) {
+      const int count = build_routes<IV, GMODE, DT, false>(a, c.cell, seat, gate, s_loads,
+                                                           s_base, st.route, lane);
+      if (lane == 0) st.count = count;
+      __syncwarp();
+      const int staged = count < kMaxRoutes ? count : kMaxRoutes;
+      const int64_t first = (int64_t)c.piece * kFoldVecs;
+      for (int r = 0; r < staged; r++) {
+        const V* sp = src + (int64_t)st.route[r].row * a.row_vecs + first;
+#pragma unroll
+        for (int u = 0; u < kFoldUnroll; u++) {
+          const int v = u * 32 + lane;
+          if (first + v < a.row_vecs) cp_async_16(&st.rows[r][v], sp + v);
+        }
+      }
+    }
+    cp_async_commit();
+  };
+
+  const ItemStep step = step_of(warps, a.pieces_per_row);
+  ItemCursor at = cursor_at(warp < items ? warp : 0, a.pieces_per_row);
+  if (warp >= items) at.cell = a.cell_num;
+  ItemCursor ahead = advance(at, step);
+  ItemCursor ahead2 = advance(ahead, step);
+  int stage = 0;
+  fetch(at);
+  issue(my[0], at);
+  fetch(ahead);
+  while (at.cell < a.cell_num) {
+    issue(my[stage ^ 1], ahead);
+    fetch(ahead2);
+    cp_async_wait<1>();
+    __syncwarp();
+
+    const FoldStage& st = my[stage];
+    const int64_t cell = at.cell;
+    const int64_t first = (int64_t)at.piece * kFoldVecs;
+    const int count = st.count;
+    const int staged = count < kMaxRoutes ? count : kMaxRoutes;
+    V* dp = dst + cell * a.row_vecs + first;
+#pragma unroll
+    for (int u = 0; u < kFoldUnroll; u++) {
+      const int v = u * 32 + lane;
+      if (first + v >= a.row_vecs) continue;
+      float acc[L::N];
+#pragma unroll
+      for (int n = 0; n < L::N; n++) acc[n] = 0.f;
+      for (int r = 0; r < staged; r++)
+        fold_chunk<VB, DT, GMODE>(acc, st.rows[r][v], st.route[r].gate);
+      if (count > kMaxRoutes) {
+        // more routes than the staging area holds: walk the index row for the rest
+        int seen = 0;
+        for (int e = 0; e < E; e++) {
+          const int s = a.indices[cell * E + e];
+          if (s <= 0 || s > s_loads[e]) continue;
+          if (seen++ < kMaxRoutes) continue;
+          const V row =
+              load_stream(src + ((int64_t)s_base[e] + s - 1) * a.row_vecs + first + v);
+          fold_chunk<VB, DT, GMODE>(acc, row, gate_at<DT, GMODE>(a.gates, cell * E + e));
+        }
+      }
+      if (count > 0 || !a.is_residual) {
+        alignas(VB) typename L::E el[L::N];
+#pragma unroll
+        for (int n = 0; n < L::N; n++) el[n] = Elem<DT>::from_f32(acc[n]);
+        store_stream(dp + v, *reinterpret_cast<V*>(el));
+      }
+    }
+    __syncwarp();
+    at = ahead;
+    ahead = ahead2;
+    ahead2 = advance(ahead2, step);
+    stage ^= 1;
+  }
+  cp_async_wait<0>();
+}
+
+// Register-only combine for rows that cannot be moved 16 bytes at a time.
 template <int VB, int DT, int GMODE>
-__global__ void __launch_bounds__(kThreads) combine_seat_kernel(const CombineArgs a) {
+__global__ void __launch_bounds__(kThreads) combine_seat_kernel(const MoveArgs a) {
   using L = Lanes<VB, DT>;
   using V = typename L::V;
   extern __shared__ int s_mem[];
@@ -300,12 +639,11 @@ __global__ void __launch_bounds__(kThreads) combine_seat_kernel(const CombineArg
   for (int64_t item = warp; item < items; item += warps) {
     const int64_t cell = item / a.pieces_per_row;
     const int64_t piece = item - cell * a.pieces_per_row;
-    const int64_t v0 = piece * kPieceVecs + lane;
-    float acc[kUnroll][L::N];
+    float acc[kFoldUnroll][L::N];
 #pragma unroll
-    for (int u = 0; u < kUnroll; u++)
+    for (int u = 0; u < kFoldUnroll; u++)
 #pragma unroll
-      for (int i = 0; i < L::N; i++) acc[u][i] = 0.f;
+      for (int n = 0; n < L::N; n++) acc[u][n] = 0.f;
     bool routed = false;
     for (int p = 0; p < E; p += 32) {
       const int e_lane = p + lane;
@@ -313,55 +651,31 @@ __global__ void __launch_bounds__(kThreads) combine_seat_kernel(const CombineArg
       if (e_lane < E) seat = a.indices[cell * E + e_lane];
       const bool keep = e_lane < E && seat > 0 && seat <= s_loads[e_lane];
       float gate = 1.f;
-      if constexpr (GMODE == 1) {
-        if (keep) gate = static_cast<const float*>(a.gates)[cell * E + e_lane];
-      } else if constexpr (GMODE == 2) {
-        if (keep)
-          gate = Elem<DT>::to_f32(
-              static_cast<const typename Elem<DT>::type*>(a.gates)[cell * E + e_lane]);
-      }
+      if (keep) gate = gate_at<DT, GMODE>(a.gates, cell * E + e_lane);
       unsigned ballot = __ballot_sync(0xffffffffu, keep);
       while (ballot) {
         const int b = __ffs(ballot) - 1;
         ballot &= ballot - 1;
-        const int e = p + b;
         const int seat_b = __shfl_sync(0xffffffffu, seat, b);
         const float g = __shfl_sync(0xffffffffu, gate, b);
-        const int64_t row = (int64_t)s_base[e] + seat_b - 1;
-        const V* sp = src + row * a.row_vecs;
-        V regs[kUnroll];
+        const V* sp = src + ((int64_t)s_base[p + b] + seat_b - 1) * a.row_vecs;
 #pragma unroll
-        for (int u = 0; u < kUnroll; u++) {
-          const int64_t v = v0 + u * 32;
-          if (v < a.row_vecs) regs[u] = load_stream(sp + v);
-        }
-#pragma unroll
-        for (int u = 0; u < kUnroll; u++) {
-          const int64_t v = v0 + u * 32;
-          if (v < a.row_vecs) {
-            alignas(VB) typename L::E el[L::N];
-            *reinterpret_cast<V*>(el) = regs[u];
-#pragma unroll
-            for (int i = 0; i < L::N; i++) {
-              float x = Elem<DT>::to_f32(el[i]);
-              if constexpr (GMODE != 0) x = __fmul_rn(x, g);
-              acc[u][i] = __fadd_rn(acc[u][i], x);
-            }
-          }
+        for (int u = 0; u < kFoldUnroll; u++) {
+          const int64_t vec = piece * kFoldVecs + u * 32 + lane;
+          if (vec < a.row_vecs) fold_chunk<VB, DT, GMODE>(acc[u], load_stream(sp + vec), g);
         }
         routed = true;
       }
     }
     if (routed || !a.is_residual) {
-      V* dp = dst + cell * a.row_vecs;
 #pragma unroll
-      for (int u = 0; u < kUnroll; u++) {
-        const int64_t v = v0 + u * 32;
-        if (v < a.row_vecs) {
+      for (int u = 0; u < kFoldUnroll; u++) {
+        const int64_t vec = piece * kFoldVecs + u * 32 + lane;
+        if (vec < a.row_vecs) {
           alignas(VB) typename L::E el[L::N];
 #pragma unroll
-          for (int i = 0; i < L::N; i++) el[i] = Elem<DT>::from_f32(acc[u][i]);
-          store_stream(dp + v, *reinterpret_cast<V*>(el));
+          for (int n = 0; n < L::N; n++) el[n] = Elem<DT>::from_f32(acc[u][n]);
+          store_stream(dst + cell * a.row_vecs + vec, *reinterpret_cast<V*>(el));
         }
       }
     }
@@ -381,7 +695,8 @@ int pick_vec_bytes(int64_t row_bytes, std::initializer_list<const void*> ptrs, i
   return 0;
 }
 
-unsigned grid_for(int64_t items) {
+// warp-per-item kernels
+unsigned grid_for_items(int64_t items) {
   int64_t blocks = (items + kWarps - 1) / kWarps;
   const int64_t cap = (int64_t)sm_count() * 8;
   if (blocks > cap) blocks = cap;
@@ -389,20 +704,38 @@ unsigned grid_for(int64_t items) {
   return (unsigned)blocks;
 }
 
+unsigned grid_for_resident(int64_t items, int ctas_per_sm) {
+  int64_t blocks = (items + kWarps - 1) / kWarps;
+  const int64_t cap = (int64_t)sm_count() * ctas_per_sm;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (unsigned)blocks;
+}
+
+// 16-byte scans of index (and gate) rows need path_num % 4 == 0 and aligned arrays.
+bool wide_rows(const int* indices, const void* gates, int gate_elem_bytes, int path_num) {
+  if (path_num % 4 != 0 || !aligned_to(indices, 16)) return false;
+  if (gates != nullptr && !aligned_to(gates, (size_t)4 * gate_elem_bytes)) return false;
+  return true;
+}
+
 template <int VB, int DT, bool WEIGHTED, bool IS_1D>
-void launch_dispatch(const DispatchArgs& a, bool is_tag, cudaStream_t st) {
+void launch_dispatch(const MoveArgs& a, bool is_tag, cudaStream_t st) {
   const size_t smem = (size_t)a.path_num * 2 * sizeof(int);
   if (is_tag) {
     dispatch_tag_kernel<VB, DT, WEIGHTED, IS_1D>
-        <<<grid_for(a.total_rows * a.pieces_per_row), kThreads, smem, st>>>(a);
+        <<<grid_for_items(a.total_rows * a.pieces_per_row), kThreads, smem, st>>>(a);
+  } else if (wide_rows(a.indices, a.gates, dtype_size(DT), a.path_num)) {
+    dispatch_seat_kernel<VB, DT, WEIGHTED, IS_1D, 4>
+        <<<grid_for_items(a.cell_num * a.pieces_per_row), kThreads, smem, st>>>(a);
   } else {
-    dispatch_seat_kernel<VB, DT, WEIGHTED, IS_1D>
-        <<<grid_for(a.cell_num * a.pieces_per_row), kThreads, smem, st>>>(a);
+    dispatch_seat_kernel<VB, DT, WEIGHTED, IS_1D, 1>
+        <<<grid_for_items(a.cell_num * a.pieces_per_row), kThreads, smem, st>>>(a);
   }
 }
 
 template <int VB>
-int dispatch_by_flags(const DispatchArgs& a, int dtype, bool weighted, bool is_1d, bool is_tag,
+int dispatch_by_flags(const MoveArgs& a, int dtype, bool weighted, bool is_1d, bool is_tag,
                       cudaStream_t st) {
   if (!weighted) {
     // an unweighted move is a byte copy: the element type does not matter
@@ -427,34 +760,53 @@ int dispatch_by_flags(const DispatchArgs& a, int dtype, bool weighted, bool is_1
 }
 
 template <int VB>
-void launch_zero_fill(const DispatchArgs& a, cudaStream_t st) {
+void launch_zero_fill(const MoveArgs& a, cudaStream_t st) {
   dispatch_zero_fill_kernel<VB>
-      <<<grid_for(a.total_rows * a.pieces_per_row), kThreads, 0, st>>>(a);
+      <<<grid_for_items(a.total_rows * a.pieces_per_row), kThreads, 0, st>>>(a);
 }
 
-template <int VB, int DT>
-int combine_by_gates(const CombineArgs& a, int gmode, cudaStream_t st) {
-  const size_t smem = (size_t)a.path_num * 2 * sizeof(int);
-  const unsigned grid = grid_for(a.cell_num * a.pieces_per_row);
-  switch (gmode) {
-    case 0:
-      combine_seat_kernel<VB, DT, 0><<<grid, kThreads, smem, st>>>(a);
-      break;
-    case 1:
-      combine_seat_kernel<VB, DT, 1><<<grid, kThreads, smem, st>>>(a);
-      break;
-    default:
-      if constexpr (DT == BRT_F32)
-        combine_seat_kernel<VB, DT, 1><<<grid, kThreads, smem, st>>>(a);
-      else
-        combine_seat_kernel<VB, DT, 2><<<grid, kThreads, smem, st>>>(a);
-      break;
+template <int DT, int GMODE, int IV>
+int launch_combine_async(const MoveArgs& a, cudaStream_t st) {
+  const size_t smem = sizeof(FoldStage) * kWarps * kStages + (size_t)a.path_num * 2 * sizeof(int);
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  BRT_CUDA_TRY(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    BRT_CUDA_TRY(cudaFuncSetAttribute(combine_seat_async_kernel<DT, GMODE, IV>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)(sizeof(FoldStage) * kWarps * kStages +
+                                            (size_t)kMaxPaths * 2 * sizeof(int))));
+    configured_device = dev;
   }
+  combine_seat_async_kernel<DT, GMODE, IV>
+      <<<grid_for_resident(a.cell_num * a.pieces_per_row, 3), kThreads, smem, st>>>(a);
   return BRT_OK;
 }
 
+template <int VB, int DT, int GMODE>
+int launch_combine(const MoveArgs& a, cudaStream_t st) {
+  if constexpr (VB == 16) {
+    const int gate_bytes = GMODE == 1 ? 4 : dtype_size(DT);
+    if (wide_rows(a.indices, a.gates, gate_bytes, a.path_num))
+      return launch_combine_async<DT, GMODE, 4>(a, st);
+    return launch_combine_async<DT, GMODE, 1>(a, st);
+  } else {
+    const size_t smem = (size_t)a.path_num * 2 * sizeof(int);
+    combine_seat_kernel<VB, DT, GMODE>
+        <<<grid_for_items(a.cell_num * a.pieces_per_row), kThreads, smem, st>>>(a);
+    return BRT_OK;
+  }
+}
+
+template <int VB, int DT>
+int combine_by_gates(const MoveArgs& a, int gmode, cudaStream_t st) {
+  if (gmode == 0) return launch_combine<VB, DT, 0>(a, st);
+  if (gmode == 1 || DT == BRT_F32) return launch_combine<VB, DT, 1>(a, st);
+  return launch_combine<VB, DT, 2>(a, st);
+}
+
 template <int VB>
-int combine_by_dtype(const CombineArgs& a, int dtype, int gmode, cudaStream_t st) {
+int combine_by_dtype(const MoveArgs& a, int dtype, int gmode, cudaStream_t st) {
   if (dtype == BRT_F32) {
     if constexpr (VB >= 4) return combine_by_gates<VB, BRT_F32>(a, gmode, st);
     return set_error(BRT_ERR_INVALID_ARGUMENT, "fp32 rows must be 4-byte aligned");
@@ -504,7 +856,7 @@ BRT_API int brt_dispatch_with_indices_and_loads(
   BRT_REQUIRE(vb != 0, "rows of %lld bytes cannot be moved: misaligned pointers",
               (long long)row_bytes);
 
-  DispatchArgs a;
+  MoveArgs a;
   a.src = src_data;
   a.dst = dst_data;
   a.gates = gates;
@@ -519,6 +871,7 @@ BRT_API int brt_dispatch_with_indices_and_loads(
   a.path_num = path_num;
   a.max_path_load = max_path_load;
   a.total_rows = total_rows;
+  a.is_residual = 0;
 
   const bool is_tag = is_tag_index != 0;
   if (!is_tag) {
@@ -573,17 +926,21 @@ BRT_API int brt_combine_with_indices_and_loads(
   const int vb = pick_vec_bytes(row_bytes, {src_data, dst_data}, es);
   BRT_REQUIRE(vb != 0, "rows of %lld bytes cannot be moved: misaligned pointers",
               (long long)row_bytes);
-  CombineArgs a;
+  MoveArgs a;
   a.src = src_data;
   a.dst = dst_data;
   a.gates = gates;
   a.indices = route_indices;
   a.loads = loads;
+  a.old_tags = nullptr;
+  a.new_tags = nullptr;
+  a.row_marks = nullptr;
   a.cell_num = cell_num;
   a.row_vecs = row_bytes / vb;
-  a.pieces_per_row = (a.row_vecs + kPieceVecs - 1) / kPieceVecs;
+  a.pieces_per_row = (a.row_vecs + kFoldVecs - 1) / kFoldVecs;
   a.path_num = path_num;
   a.max_path_load = max_path_load;
+  a.total_rows = 0;
   a.is_residual = is_residual;
   const int gmode = gates == nullptr ? 0 : (gates_dtype == BRT_F32 ? 1 : 2);
   int rc;
