@@ -12,7 +12,7 @@
 //              lands on (capacity padding, dropped seats) are found through a byte map that
 //              the move pass marks, and are written as zeros by a second launch: the output
 //              is never memset as a whole and no row is written twice.
-//   combine  : destination-major.  One warp owns (cell, 1 KB piece).  The rows of the
+//   combine  : destination-major.  One warp owns (cell, 2 KB piece).  The rows of the
 //              cell's kept routes are brought into shared memory with asynchronous 16-byte
 //              copies (cp.async) - the copies of the warp's NEXT item are issued before
 //              the current item is folded, so every warp keeps two items of row traffic in
@@ -23,7 +23,7 @@
 //              register-only kernel.
 //
 // Per-path base rows (prefix sum of loads, or e * max_path_load) are computed once per CTA
-// into shared memory.  Cells with more routes than the staging buffers hold (4) finish
+// into shared memory.  Cells with more routes than the staging buffers hold (2) finish
 // through a slower serial walk of the index row, so any number of routes is correct.
 #include "common.cuh"
 
@@ -37,8 +37,8 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kMaxPaths = 4096;
 constexpr int kPieceVecs = 128;    // vectors per dispatch item (2 KB at 16 bytes)
 constexpr int kCopyUnroll = kPieceVecs / 32;
-constexpr int kMaxRoutes = 4;      // routes per combine item staged in shared memory
-constexpr int kFoldVecs = 64;      // vectors per combine item (1 KB at 16 bytes)
+constexpr int kMaxRoutes = 2;      // routes per combine item staged in shared memory
+constexpr int kFoldVecs = 128;     // vectors per combine item (2 KB at 16 bytes)
 constexpr int kFoldUnroll = kFoldVecs / 32;
 constexpr int kStages = 2;
 
@@ -132,17 +132,72 @@ struct Lanes {
   static constexpr int N = VB / (int)sizeof(E);
 };
 
+// 16-byte chunk <-> fp32 lanes.  16-bit types convert two at a time (the scalar
+// float -> bf16/half conversions run at a quarter of the packed rate).
+template <int VB, int DT>
+__device__ __forceinline__ void unpack_chunk(const typename Chunk<VB>::type& row,
+                                             float (&f)[Lanes<VB, DT>::N]) {
+  using L = Lanes<VB, DT>;
+  if constexpr (VB == 16 && DT == BRT_BF16) {
+    const uint32_t w[4] = {row.x, row.y, row.z, row.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  } else if constexpr (VB == 16 && DT == BRT_F16) {
+    const uint32_t w[4] = {row.x, row.y, row.z, row.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const float2 p = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      f[2 * i] = p.x;
+      f[2 * i + 1] = p.y;
+    }
+  } else {
+    alignas(VB) typename L::E el[L::N];
+    *reinterpret_cast<typename L::V*>(el) = row;
+#pragma unroll
+    for (int i = 0; i < L::N; i++) f[i] = Elem<DT>::to_f32(el[i]);
+  }
+}
+
+template <int VB, int DT>
+__device__ __forceinline__ typename Chunk<VB>::type pack_chunk(
+    const float (&f)[Lanes<VB, DT>::N]) {
+  using L = Lanes<VB, DT>;
+  if constexpr (VB == 16 && DT == BRT_BF16) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const __nv_bfloat162 p = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<const uint32_t*>(&p);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  } else if constexpr (VB == 16 && DT == BRT_F16) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const __half2 p = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<const uint32_t*>(&p);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  } else {
+    alignas(VB) typename L::E el[L::N];
+#pragma unroll
+    for (int i = 0; i < L::N; i++) el[i] = Elem<DT>::from_f32(f[i]);
+    return *reinterpret_cast<typename L::V*>(el);
+  }
+}
+
 // x * g element-wise in the storage type: exact product in fp32, one rounding.
 template <int VB, int DT>
 __device__ __forceinline__ typename Chunk<VB>::type scale_chunk(typename Chunk<VB>::type x,
                                                                 float g) {
-  using L = Lanes<VB, DT>;
-  alignas(VB) typename L::E e[L::N];
-  *reinterpret_cast<typename L::V*>(e) = x;
+  float f[Lanes<VB, DT>::N];
+  unpack_chunk<VB, DT>(x, f);
 #pragma unroll
-  for (int i = 0; i < L::N; i++)
-    e[i] = Elem<DT>::from_f32(__fmul_rn(Elem<DT>::to_f32(e[i]), g));
-  return *reinterpret_cast<typename L::V*>(e);
+  for (int i = 0; i < Lanes<VB, DT>::N; i++) f[i] = __fmul_rn(f[i], g);
+  return pack_chunk<VB, DT>(f);
 }
 
 struct MoveArgs {
@@ -479,13 +534,12 @@ template <int VB, int DT, int GMODE>
 __device__ __forceinline__ void fold_chunk(float (&acc)[Lanes<VB, DT>::N],
                                            const typename Chunk<VB>::type& row, float g) {
   using L = Lanes<VB, DT>;
-  alignas(VB) typename L::E el[L::N];
-  *reinterpret_cast<typename L::V*>(el) = row;
+  float x[L::N];
+  unpack_chunk<VB, DT>(row, x);
 #pragma unroll
   for (int i = 0; i < L::N; i++) {
-    float x = Elem<DT>::to_f32(el[i]);
-    if constexpr (GMODE != 0) x = __fmul_rn(x, g);
-    acc[i] = __fadd_rn(acc[i], x);
+    if constexpr (GMODE != 0) x[i] = __fmul_rn(x[i], g);
+    acc[i] = __fadd_rn(acc[i], x[i]);
   }
 }
 
@@ -497,7 +551,7 @@ __device__ __forceinline__ float gate_at(const void* gates, int64_t at) {
   return 1.f;
 }
 
-// Per-warp staging area: kStages x (route table + kMaxRoutes row pieces of 1 KB).
+// Per-warp staging area: kStages x (route table + kMaxRoutes row pieces of 2 KB).
 struct alignas(16) FoldStage {
   uint4 rows[kMaxRoutes][kFoldVecs];
   RouteSlot route[kMaxRoutes];
@@ -602,12 +656,7 @@ __global__ void __launch_bounds__(kThreads, 3) combine_seat_async_kernel(const M
           fold_chunk<VB, DT, GMODE>(acc, row, gate_at<DT, GMODE>(a.gates, cell * E + e));
         }
       }
-      if (count > 0 || !a.is_residual) {
-        alignas(VB) typename L::E el[L::N];
-#pragma unroll
-        for (int n = 0; n < L::N; n++) el[n] = Elem<DT>::from_f32(acc[n]);
-        store_stream(dp + v, *reinterpret_cast<V*>(el));
-      }
+      if (count > 0 || !a.is_residual) store_stream(dp + v, pack_chunk<VB, DT>(acc));
     }
     __syncwarp();
     at = ahead;
@@ -671,12 +720,8 @@ __global__ void __launch_bounds__(kThreads) combine_seat_kernel(const MoveArgs a
 #pragma unroll
       for (int u = 0; u < kFoldUnroll; u++) {
         const int64_t vec = piece * kFoldVecs + u * 32 + lane;
-        if (vec < a.row_vecs) {
-          alignas(VB) typename L::E el[L::N];
-#pragma unroll
-          for (int n = 0; n < L::N; n++) el[n] = Elem<DT>::from_f32(acc[u][n]);
-          store_stream(dst + cell * a.row_vecs + vec, *reinterpret_cast<V*>(el));
-        }
+        if (vec < a.row_vecs)
+          store_stream(dst + cell * a.row_vecs + vec, pack_chunk<VB, DT>(acc[u]));
       }
     }
   }
