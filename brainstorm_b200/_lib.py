@@ -25,6 +25,9 @@ SIGNATURES = {
     "brt_index_scratch_bytes": (_sz, [_i64, _int]),
     "brt_generate_indices_and_loads": (
         _int, [_vp, _vp, _vp, _i64, _int, _vp, _int, _int, _int, _int, _vp, _sz, _vp]),
+    "brt_static_index_scratch_bytes": (_sz, []),
+    "brt_generate_indices_and_loads_static": (
+        _int, [_vp, _vp, _vp, _i64, _int, _vp, _int, _int, _int, _int, _vp]),
     "brt_throttle_hotmask": (_int, [_vp, _vp, _vp, _vp, _i64, _int, _vp, _sz, _vp]),
     "brt_convert_index_format": (_int, [_vp, _vp, _vp, _i64, _int, _int, _vp]),
     "brt_dispatch_scratch_bytes": (_sz, [_i64, _int]),

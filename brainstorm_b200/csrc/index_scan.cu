@@ -30,6 +30,7 @@
 #include <cooperative_groups.h>
 
 #include <map>
+#include <mutex>
 #include <utility>
 
 #include "common.cuh"
@@ -1131,6 +1132,33 @@ int run_scan(Mode mode, const int32_t* mask, int32_t* out, int32_t* loads, int64
   }
 }
 
+// ------------------------------------------------------------------------ fixed scratch
+// Scratch for the entry point that must not allocate: lives in the library's image on
+// every GPU that loads it, until the process exits.
+constexpr size_t kStaticScratchBytes = 2u << 20;
+static __device__ __align__(256) unsigned char g_static_index_scratch[kStaticScratchBytes];
+
+// Device address of the array above for the current device.  The name of a __device__
+// array is only a host-side handle; the address a kernel can use comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+int static_scratch_address(void** out) {
+  constexpr int kMaxDevices = 64;
+  static void* cached[kMaxDevices] = {nullptr};
+  static std::mutex mu;
+  int dev = 0;
+  BRT_CUDA_TRY(cudaGetDevice(&dev));
+  BRT_REQUIRE(dev >= 0 && dev < kMaxDevices, "device ordinal %d is not supported", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == nullptr) {
+    void* ptr = nullptr;
+    BRT_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_index_scratch));
+    BRT_REQUIRE(ptr != nullptr, "cudaGetSymbolAddress returned a null address");
+    cached[dev] = ptr;
+  }
+  *out = cached[dev];
+  return BRT_OK;
+}
+
 }  // namespace
 }  // namespace brt_b200
 
@@ -1214,6 +1242,33 @@ BRT_API int brt_convert_index_format(const int32_t* origin_indices, int32_t* new
   }
   BRT_LAUNCH_CHECK("convert_index_format");
   return BRT_OK;
+}
+
+BRT_API size_t brt_static_index_scratch_bytes(void) { return kStaticScratchBytes; }
+
+BRT_API int brt_generate_indices_and_loads_static(const int32_t* hot_mask, int32_t* indices,
+                                                  int32_t* loads, int64_t cell_num, int path_num,
+                                                  const int32_t* supported_capacities,
+                                                  int supported_capacity_num,
+                                                  int capacity_padding, int path_wise_padding,
+                                                  int is_tag_index, void* stream) {
+  clear_error();
+  BRT_REQUIRE(cell_num >= 0 && path_num > 0, "bad shape: cell_num=%lld path_num=%d",
+              (long long)cell_num, path_num);
+  const size_t need = scratch_bytes_for(cell_num, path_num);
+  if (need > kStaticScratchBytes)
+    return set_error(BRT_ERR_SCRATCH_TOO_SMALL,
+                     "a %lld x %d mask needs %zu bytes of scratch; the built-in scratch of "
+                     "this entry point holds %zu bytes (use brt_generate_indices_and_loads "
+                     "with caller-provided scratch for larger masks)",
+                     (long long)cell_num, path_num, need, kStaticScratchBytes);
+  void* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc != BRT_OK) return rc;
+  return brt_generate_indices_and_loads(hot_mask, indices, loads, cell_num, path_num,
+                                        supported_capacities, supported_capacity_num,
+                                        capacity_padding, path_wise_padding, is_tag_index,
+                                        scratch, kStaticScratchBytes, stream);
 }
 
 }  // extern "C"

@@ -77,6 +77,36 @@ BRT_API int brt_generate_indices_and_loads(const int32_t* hot_mask, int32_t* ind
                                            void* scratch, size_t scratch_bytes, void* stream);
 
 /*
+ * No counterpart in the reference.
+ *
+ * Same result as brt_generate_indices_and_loads, for callers that are not allowed to
+ * obtain device memory themselves and therefore cannot supply the scratch buffer: code
+ * running under a memory planner that owns the whole device heap, or a plugin host that
+ * hands out only the input and output tensors.  The scratch lives in a fixed array inside the
+ * library image (brt_static_index_scratch_bytes() bytes, 2 MiB, held on every GPU that
+ * loads the library until the process exits), so this call performs no device allocation
+ * of any kind.
+ *
+ * Limits and rules:
+ *   - masks whose scratch need exceeds the built-in array are refused with
+ *     BRT_ERR_SCRATCH_TOO_SMALL and a message that states both sizes (roughly
+ *     cell_num * path_num up to 7 million entries); nothing is launched in that case;
+ *   - the first call on each device looks up the device address of the array (once, with
+ *     that device current); make that first call before starting any stream capture;
+ *   - all calls on a device share the one array: two calls whose kernels can overlap on
+ *     the GPU (different streams without an ordering between them) race; calls ordered on
+ *     one stream are safe, and nothing has to be cleared between them.
+ */
+BRT_API size_t brt_static_index_scratch_bytes(void);
+BRT_API int brt_generate_indices_and_loads_static(const int32_t* hot_mask, int32_t* indices,
+                                                  int32_t* loads, int64_t cell_num,
+                                                  int path_num,
+                                                  const int32_t* supported_capacities,
+                                                  int supported_capacity_num,
+                                                  int capacity_padding, int path_wise_padding,
+                                                  int is_tag_index, void* stream);
+
+/*
  * Replaces brt::router::ThrottleHotmask
  * (include/brt/router/location.h:13-19, src/router/location.cu:59-130,304-315).
  *
