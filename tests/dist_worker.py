@@ -1,0 +1,130 @@
+"""Per-rank body of the multi-GPU tests; launched by tests/test_distributed_gpu.py through
+torch.distributed.run, one process per GPU.  Every rank can rebuild every other rank's
+seeded inputs, so each one checks its own outputs against the CPU restatement of the
+reference's exchange semantics."""
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+import oracle  # noqa: E402
+
+
+def rank_inputs(rank, W, G, d, hi, stride=0):
+    rng = np.random.default_rng(1000 + rank)
+    sizes = rng.integers(0, hi, size=W * G).astype(np.int32)
+    rows = stride * W * G if stride else int(sizes.sum())
+    x = rng.standard_normal((rows, d)).astype(np.float32)
+    return x, sizes
+
+
+def main():
+    rank = int(os.environ["RANK"])
+    W = int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    import brainstorm_b200.runtime.distributed as brt_dist
+    from brainstorm_b200._C import distributed as C_dist
+
+    assert brt_dist.is_nccl_activated()
+    try:
+        C_dist.init_nccl(torch.zeros(128, dtype=torch.int8), rank, W)
+        raise AssertionError("second init_nccl must be refused")
+    except RuntimeError:
+        pass
+
+    # ---- packed (sparse) exchange, forward and back, for G local experts
+    for G, d, hi in ((1, 8, 40), (2, 16, 30), (4, 5, 12)):
+        all_in = [rank_inputs(r, W, G, d, hi) for r in range(W)]
+        fwd = oracle.sim_group_sparse_all_to_all([a[0] for a in all_in], [a[1] for a in all_in])
+        x, sizes = all_in[rank]
+        out, out_loads, in_loads = brt_dist.group_sparse_a2a(
+            torch.from_numpy(x).to(dev), torch.from_numpy(sizes).to(dev))
+        assert not out_loads.is_cuda and not in_loads.is_cuda
+        assert np.array_equal(out_loads.numpy(), fwd[rank][1])
+        assert np.array_equal(in_loads.numpy(), sizes)
+        assert np.array_equal(out.cpu().numpy(), fwd[rank][0]), f"rank {rank} forward G={G}"
+        back = brt_dist.size_known_group_sparse_a2a(out, out_loads, in_loads)
+        assert np.array_equal(back.cpu().numpy(), x), f"rank {rank} round trip G={G}"
+    # padded buckets
+    G, d, stride = 2, 4, 16
+    all_in = [rank_inputs(r, W, G, d, stride + 1, stride) for r in range(W)]
+    x, sizes = all_in[rank]
+    out, out_loads, in_loads = brt_dist.group_sparse_a2a(
+        torch.from_numpy(x).to(dev), torch.from_numpy(sizes).to(dev), True, stride)
+    fwd = oracle.sim_group_sparse_all_to_all([a[0] for a in all_in], [a[1] for a in all_in],
+                                             True, stride)
+    o = out.cpu().numpy()
+    for b, n in enumerate(out_loads.numpy()):
+        assert np.array_equal(o[b * stride:b * stride + n], fwd[rank][0][b * stride:b * stride + n])
+    back = brt_dist.size_known_group_sparse_a2a(out, out_loads, in_loads, True).cpu().numpy()
+    for b, n in enumerate(sizes):
+        assert np.array_equal(back[b * stride:b * stride + n], x[b * stride:b * stride + n])
+
+    # ---- padded-slot exchange with the locality tail
+    for G in (1, 2):
+        slot, d = 12, 6
+        all_in = []
+        for r in range(W):
+            rng = np.random.default_rng(2000 + r + 10 * G)
+            s = rng.integers(0, slot + 1, size=W * G).astype(np.int32)
+            all_in.append((rng.standard_normal((slot * W * G, d)).astype(np.float32), s))
+        sim = oracle.sim_group_asymmetry_all_to_all([a[0] for a in all_in],
+                                                    [a[1] for a in all_in])
+        x, s = all_in[rank]
+        xt, st = torch.from_numpy(x).to(dev), torch.from_numpy(s).to(dev)
+        out, recv = brt_dist.group_asymmetry_a2a(xt, st, False)
+        assert np.array_equal(recv.cpu().numpy(), sim[rank][1])
+        o = out.cpu().numpy()
+        for k, n in enumerate(sim[rank][1]):
+            assert np.array_equal(o[k * slot:k * slot + n], sim[rank][0][k * slot:k * slot + n])
+        back = C_dist.size_known_group_asymmetry_all_to_all(out, recv, st)
+        b = back.cpu().numpy()
+        for k, n in enumerate(s):
+            assert np.array_equal(b[k * slot:k * slot + n], x[k * slot:k * slot + n])
+            assert not b[k * slot + n:(k + 1) * slot].any()
+        out2, reordered, reorder = brt_dist.group_asymmetry_a2a(xt, st, True)
+        m = np.stack([sim[r][1] for r in range(W)]).reshape(W, W, G)
+        exp_loads, exp_idx = oracle.group_locality_reorder(m, W, G)
+        assert np.array_equal(reorder.cpu().numpy(), exp_idx)
+        assert np.array_equal(reordered.cpu().numpy(), exp_loads[rank].reshape(-1))
+        # exchange along the permutation and back
+        mine = torch.full((7, 3), float(rank), device=dev)
+        got = brt_dist.exchange(mine, reorder)
+        assert torch.all(got == float(exp_idx[rank]))
+        assert torch.equal(brt_dist.reverse_exchange(got, reorder), mine)
+        outs = brt_dist.batched_exchange([mine, mine * 2], reorder)
+        assert torch.all(outs[1] == 2.0 * exp_idx[rank])
+
+    # ---- routers: the distributed fused fabrics equal the local fused fabrics (identity expert)
+    from brainstorm_b200 import Annotator
+    from brainstorm_b200.router import GatherRouter, ScatterRouter
+
+    g = torch.Generator().manual_seed(rank)
+    T, E, d = 512, 4 * W, 64
+    x = torch.randn((T, d), generator=g).to(dev)
+    score = torch.softmax(torch.randn((T, E), generator=g), dim=1).to(dev)
+    local = GatherRouter("fused_combine", {"transform": True})(
+        ScatterRouter(protocol_type="topk", fabric_type="fused_dispatch",
+                      protocol_kwargs={"top_k": 2})(Annotator([0])(x), score), None, score)
+    routed = ScatterRouter(protocol_type="topk", fabric_type="distributed_fused_dispatch",
+                           protocol_kwargs={"top_k": 2})(Annotator([0])(x), score)
+    ep = GatherRouter("distributed_fused_combine", {"transform": True})(routed, None, score)
+    assert torch.equal(ep.data, local.data), f"rank {rank}: expert-parallel route differs"
+
+    dist.barrier()
+    if rank == 0:
+        print("DIST_OK", W)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
