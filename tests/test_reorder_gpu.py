@@ -63,7 +63,12 @@ def test_against_reference_kernel(D):
             b = D.locality_reorder(m.view(-1), W)
             torch.cuda.synchronize()
             assert torch.equal(a[1], b[1]) and torch.equal(a[0], b[0])
-        for G in (2, 4):  # powers of two with G*W*W <= 1024: the range the reference handles
+        for G in (2, 4):
+            # The reference sums the G loads of a pair in place and then compacts the sums
+            # inside the same shared array without a barrier (local_reorder.cu:83-102);
+            # that is only race-free while all W*W*G threads sit in one warp.
+            if W * W * G > 32:
+                continue
             m = torch.from_numpy(rng.integers(0, 1024, size=(W * W * G,)).astype(np.int32)).cuda()
             a = ref.group_locality_reorder(m, W, G)
             b = D.group_locality_reorder(m, W, G)
