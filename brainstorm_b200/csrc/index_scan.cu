@@ -559,31 +559,32 @@ __device__ __forceinline__ void pack_tile(const TileCtx& x, const TileSmem& sm,
   for (int i = tid; i < 2 * x.ec + 1; i += kTileThreads) sm.sum[i] = 0;
   for (int i = tid; i < x.rg * x.ec; i += kTileThreads) sm.bits[i] = 0;
 
-  // stage the tile: every 16-byte load of a batch is issued before its first store
-  constexpr int kBatch = 9;  // a whole tile (<= 36.9 KB) in one batch of loads
-  for (int base = tid; base < total_vecs; base += kTileThreads * kBatch) {
+  // Stage the tile: every 16-byte load is issued before the first store.  A tile holds at
+  // most 2048 vectors (8 per thread).  (row, vector) of a thread's k-th element advance by a
+  // fixed step with one carry, so the loop has no integer division.
+  constexpr int kBatch = 8;
+  {
+    const int step_r = kTileThreads / vec_per_row;
+    const int step_q = kTileThreads - step_r * vec_per_row;
+    int r = tid / vec_per_row;
+    int q = tid - r * vec_per_row;
     int4 v[kBatch];
+    int soff[kBatch];
 #pragma unroll
     for (int k = 0; k < kBatch; k++) {
-      const int idx = base + k * kTileThreads;
       v[k] = make_int4(0, 0, 0, 0);
-      if (idx < total_vecs) {
-        const int r = idx / vec_per_row;
-        const int q = idx - r * vec_per_row;
-        if (row0 + r < x.cell_num)
-          v[k] = __ldcs(reinterpret_cast<const int4*>(mask + (row0 + r) * x.path_num + col0 +
-                                                       4 * q));
-      }
+      soff[k] = r * x.pitch + 4 * q;
+      if (r < tile_rows && row0 + r < x.cell_num)
+        v[k] = __ldcs(reinterpret_cast<const int4*>(mask + (row0 + r) * x.path_num + col0 +
+                                                     4 * q));
+      r += step_r;
+      q += step_q;
+      if (q >= vec_per_row) { q -= vec_per_row; r += 1; }
     }
 #pragma unroll
-    for (int k = 0; k < kBatch; k++) {
-      const int idx = base + k * kTileThreads;
-      if (idx < total_vecs) {
-        const int r = idx / vec_per_row;
-        const int q = idx - r * vec_per_row;
-        *reinterpret_cast<int4*>(sm.tile + r * x.pitch + 4 * q) = v[k];
-      }
-    }
+    for (int k = 0; k < kBatch; k++)
+      if (tid + k * kTileThreads < total_vecs)
+        *reinterpret_cast<int4*>(sm.tile + soff[k]) = v[k];
   }
   __syncthreads();
 
@@ -808,9 +809,11 @@ __device__ __forceinline__ void expand_tile(const TileCtx& x, const TileSmem& sm
 
   const int vec_per_row = cols >> 2;
   const int total_vecs = x.rg * kGroupRows * vec_per_row;
+  const int step_r = kTileThreads / vec_per_row;
+  const int step_q = kTileThreads - step_r * vec_per_row;
+  int r = tid / vec_per_row;
+  int q = tid - r * vec_per_row;
   for (int idx = tid; idx < total_vecs; idx += kTileThreads) {
-    const int r = idx / vec_per_row;
-    const int q = idx - r * vec_per_row;
     const int64_t row = row0 + r;
     if (row >= x.cell_num) break;
     const int g = r >> 5;
@@ -841,6 +844,9 @@ __device__ __forceinline__ void expand_tile(const TileCtx& x, const TileSmem& sm
       __stcs(reinterpret_cast<int4*>(out + row * x.path_num + col0 + 4 * q),
              make_int4(v[0], v[1], v[2], v[3]));
     }
+    r += step_r;
+    q += step_q;
+    if (q >= vec_per_row) { q -= vec_per_row; r += 1; }
   }
 }
 

@@ -37,7 +37,8 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kMaxPaths = 4096;
 constexpr int kPieceVecs = 128;    // vectors per dispatch item (2 KB at 16 bytes)
 constexpr int kCopyUnroll = kPieceVecs / 32;
-constexpr int kMaxRoutes = 2;      // routes per combine item staged in shared memory
+constexpr int kMaxRoutes = 2;      // routes per combine item staged in shared memory (the
+                                   // fold below is written out for exactly two)
 constexpr int kFoldVecs = 128;     // vectors per combine item (2 KB at 16 bytes)
 constexpr int kFoldUnroll = kFoldVecs / 32;
 constexpr int kStages = 2;
@@ -633,19 +634,35 @@ __global__ void __launch_bounds__(kThreads, 3) combine_seat_async_kernel(const M
     const int64_t cell = at.cell;
     const int64_t first = (int64_t)at.piece * kFoldVecs;
     const int count = st.count;
-    const int staged = count < kMaxRoutes ? count : kMaxRoutes;
-    V* dp = dst + cell * a.row_vecs + first;
+    V* dp = dst + cell * a.row_vecs + first + lane;
+    const uint4* r0 = &st.rows[0][lane];
+    const uint4* r1 = &st.rows[1][lane];
+    const float g0 = st.route[0].gate;
+    const float g1 = st.route[1].gate;
+    const bool full = first + kFoldVecs <= a.row_vecs;
+    if (count <= kMaxRoutes && (count > 0 || !a.is_residual)) {
+      // common case: every route of the cell is staged
 #pragma unroll
-    for (int u = 0; u < kFoldUnroll; u++) {
-      const int v = u * 32 + lane;
-      if (first + v >= a.row_vecs) continue;
-      float acc[L::N];
+      for (int u = 0; u < kFoldUnroll; u++) {
+        if (!full && first + u * 32 + lane >= a.row_vecs) continue;
+        float acc[L::N];
 #pragma unroll
-      for (int n = 0; n < L::N; n++) acc[n] = 0.f;
-      for (int r = 0; r < staged; r++)
-        fold_chunk<VB, DT, GMODE>(acc, st.rows[r][v], st.route[r].gate);
-      if (count > kMaxRoutes) {
-        // more routes than the staging area holds: walk the index row for the rest
+        for (int n = 0; n < L::N; n++) acc[n] = 0.f;
+        if (count >= 1) fold_chunk<VB, DT, GMODE>(acc, r0[u * 32], g0);
+        if (count >= 2) fold_chunk<VB, DT, GMODE>(acc, r1[u * 32], g1);
+        store_stream(dp + u * 32, pack_chunk<VB, DT>(acc));
+      }
+    } else if (count > kMaxRoutes) {
+      // more routes than the staging area holds: walk the index row for the rest
+#pragma unroll 1
+      for (int u = 0; u < kFoldUnroll; u++) {
+        const int v = u * 32 + lane;
+        if (first + v >= a.row_vecs) continue;
+        float acc[L::N];
+#pragma unroll
+        for (int n = 0; n < L::N; n++) acc[n] = 0.f;
+        fold_chunk<VB, DT, GMODE>(acc, r0[u * 32], g0);
+        fold_chunk<VB, DT, GMODE>(acc, r1[u * 32], g1);
         int seen = 0;
         for (int e = 0; e < E; e++) {
           const int s = a.indices[cell * E + e];
@@ -655,8 +672,8 @@ __global__ void __launch_bounds__(kThreads, 3) combine_seat_async_kernel(const M
               load_stream(src + ((int64_t)s_base[e] + s - 1) * a.row_vecs + first + v);
           fold_chunk<VB, DT, GMODE>(acc, row, gate_at<DT, GMODE>(a.gates, cell * E + e));
         }
+        store_stream(dp + u * 32, pack_chunk<VB, DT>(acc));
       }
-      if (count > 0 || !a.is_residual) store_stream(dp + v, pack_chunk<VB, DT>(acc));
     }
     __syncwarp();
     at = ahead;
