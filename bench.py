@@ -361,7 +361,10 @@ def run_gpu(args):
             "bytes_per_rank_per_direction": a2a_bytes[0],
             "bus_gbs_forward": fwd / (op_ms["a2a_forward"] * 1e-3) / 1e9,
             "bus_gbs_backward": fwd / (op_ms["a2a_backward"] * 1e-3) / 1e9,
-            "nvlink_peak_gbs_per_direction": 900.0, "transport": "nccl send/recv",
+            "nvlink_peak_gbs_per_direction": 900.0,
+            "transport": "peer-memory push kernels over NVLink"
+                         if __import__("brainstorm_b200.runtime.p2p", fromlist=["arena"]).arena()
+                         is not None else "nccl send/recv",
         }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         result["cpu_baseline"] = cpu_baseline(wl, budget_s=args.cpu_seconds)

@@ -18,7 +18,7 @@ import numpy as np
 import torch
 
 from .. import _lib
-from ..runtime import a2a_plan
+from ..runtime import a2a_plan, p2p
 
 _state = {"rank": None, "size": None}
 
@@ -270,6 +270,111 @@ def _sparse_a2a(x, send_np, recv_np, stride_rows, out_rows, group_size, forward)
     return out
 
 
+_matrix_cache = {}
+
+
+def _p2p_usable(x: torch.Tensor, world: int, group_size: int) -> bool:
+    a = p2p.arena()
+    if a is None or world * group_size > p2p.MAX_COPIES or x.dim() < 1:
+        return False
+    row_bytes = (x.numel() // x.size(0)) * x.element_size() if x.size(0) else 0
+    return row_bytes % 16 == 0 and x.data_ptr() % 16 == 0
+
+
+def _copy_out_remote(arena, epoch, out, starts, rows, sources, rank, grain):
+    """Bring the ranges that peers pushed into my arena half to the same offsets of ``out``
+    (ranges from this rank were written to ``out`` directly).  Adjacent ranges are merged."""
+    src_off, dst_ptr, nbytes = [], [], []
+    base = out.data_ptr()
+    half = arena.half_offset(epoch)
+    run_start, run_len = None, 0
+    for st, n, srcr in zip(starts, rows, sources):
+        if srcr != rank and n > 0 and run_start is not None and run_start + run_len == st:
+            run_len += n
+            continue
+        if run_start is not None and run_len > 0:
+            src_off.append(half + run_start * grain)
+            dst_ptr.append(base + run_start * grain)
+            nbytes.append(run_len * grain)
+        run_start, run_len = (st, n) if (srcr != rank and n > 0) else (None, 0)
+    if run_start is not None and run_len > 0:
+        src_off.append(half + run_start * grain)
+        dst_ptr.append(base + run_start * grain)
+        nbytes.append(run_len * grain)
+    arena.copy_ranges(arena.base, src_off, dst_ptr, nbytes, _stream(out.device))
+
+
+def _sparse_forward_p2p(x, send_sizes, stride, group_size):
+    """Forward packed exchange over peer memory.  Every rank sees the whole size matrix, so
+    every rank computes the same placement (and takes the same fallback decision)."""
+    rank, W = _world()
+    G = group_size
+    dev = x.device
+    arena = p2p.arena()
+    sizes32 = send_sizes.to(torch.int32).contiguous()
+    S = arena.gather_sizes(sizes32, _stream(dev)).reshape(W, W, G).astype(np.int64)
+    grain = (x.numel() // x.size(0)) * x.element_size() if x.size(0) else 0
+    send_np = np.ascontiguousarray(S[rank].reshape(-1).astype(np.int32))
+    recv_np = np.ascontiguousarray(S[:, rank, :].T.reshape(-1).astype(np.int32))  # [G, W]
+    rows_out = np.full(W, stride * W * G, dtype=np.int64) if stride else S.sum(axis=(0, 2))
+    if grain == 0 or int(rows_out.max()) * grain > arena.half_bytes:
+        return None, send_np, recv_np                          # same answer on every rank
+    # start row of bucket (expert j, source s) in every destination rank's output
+    per = np.transpose(S, (1, 2, 0)).reshape(W, G * W)          # [dst, (j, src)]
+    if stride:
+        starts = np.broadcast_to(np.arange(G * W, dtype=np.int64) * stride, (W, G * W))
+    else:
+        starts = np.cumsum(per, axis=1) - per
+    mine = S[rank].reshape(-1)                                  # rank-major [i*G + j]
+    src_rows = (np.arange(W * G, dtype=np.int64) * stride) if stride else \
+        (np.cumsum(mine) - mine)
+    dst_rank = np.repeat(np.arange(W), G)
+    dst_rows = starts.reshape(W, G, W)[:, :, rank].reshape(-1)
+    out_rows = int(rows_out[rank])
+    shape = list(x.shape)
+    shape[0] = out_rows
+    out = torch.empty(shape, dtype=x.dtype, device=dev)
+    epoch = arena.exchange(x, src_rows * grain, dst_rank, dst_rows * grain, mine * grain,
+                           _stream(dev), local_out=out.data_ptr())
+    _copy_out_remote(arena, epoch, out, starts[rank].tolist(), per[rank].tolist(),
+                     np.tile(np.arange(W), G).tolist(), rank, grain)
+    _matrix_cache[send_np.tobytes()] = S
+    return out, send_np, recv_np
+
+
+def _sparse_backward_p2p(x, send_np, recv_np, stride, group_size):
+    """Inverse exchange; the size matrix of the matching forward call is reused, so nothing
+    is exchanged or synchronised before the data moves."""
+    rank, W = _world()
+    G = group_size
+    S = _matrix_cache.get(recv_np.tobytes())
+    if S is None or not np.array_equal(S[:, rank, :].T.reshape(-1), send_np):
+        return None
+    arena = p2p.arena()
+    grain = (x.numel() // x.size(0)) * x.element_size() if x.size(0) else 0
+    rows_out = np.full(W, stride * W * G, dtype=np.int64) if stride else S.sum(axis=(1, 2))
+    if grain == 0 or int(rows_out.max()) * grain > arena.half_bytes:
+        return None
+    held = S[:, rank, :].T.reshape(-1)                          # expert-major [j*W + i]
+    src_rows = (np.arange(G * W, dtype=np.int64) * stride) if stride else \
+        (np.cumsum(held) - held)
+    flat = S.reshape(W, W * G)                                  # every rank's rank-major sizes
+    rank_major_starts = (np.broadcast_to(np.arange(W * G, dtype=np.int64) * stride, (W, W * G))
+                         if stride else np.cumsum(flat, axis=1) - flat)
+    dst_rank = np.tile(np.arange(W), G)
+    # bucket (j, i) returns to rank i at the start of its bucket (me, j)
+    dst_rows = rank_major_starts[:, rank * G:(rank + 1) * G].T.reshape(-1)
+    out_rows = int(rows_out[rank])
+    shape = list(x.shape)
+    shape[0] = out_rows
+    out = torch.empty(shape, dtype=x.dtype, device=x.device)
+    epoch = arena.exchange(x, src_rows * grain, dst_rank, dst_rows * grain, held * grain,
+                           _stream(x.device), local_out=out.data_ptr())
+    _copy_out_remote(arena, epoch, out, rank_major_starts[rank].tolist(), flat[rank].tolist(),
+                     np.repeat(np.arange(W), G).tolist(), rank, grain)
+    return out
+
+
 def group_sparse_all_to_all(in_data: torch.Tensor, send_sizes: torch.Tensor,
                             max_path_padding: bool = False, max_path_load: int = 0):
     """(out_data, recv_sizes [G, W] on CPU, send_sizes [W, G] on CPU)."""
@@ -278,6 +383,14 @@ def group_sparse_all_to_all(in_data: torch.Tensor, send_sizes: torch.Tensor,
     _, W = _world()
     group_size = send_sizes.numel() // W
     with torch.cuda.device(in_data.device):
+        x = _contig(in_data)
+        if _p2p_usable(x, W, group_size) and not (max_path_padding and not max_path_load):
+            stride = int(max_path_load) if max_path_padding else 0
+            out, send_np, recv_np = _sparse_forward_p2p(x, send_sizes, stride, group_size)
+            if out is None:  # does not fit the arena: NCCL, sizes already known
+                rows = a2a_plan.total_rows(recv_np, stride)
+                out = _sparse_a2a(x, send_np, recv_np, stride, rows, group_size, True)
+            return [out, torch.from_numpy(recv_np.copy()), torch.from_numpy(send_np.copy())]
         recv_dev = _exchange_sizes(send_sizes.to(torch.int32))
         send_np, recv_np = _host_sizes(send_sizes, recv_dev)
         recv_np = a2a_plan.to_expert_major(recv_np, W)
@@ -286,7 +399,7 @@ def group_sparse_all_to_all(in_data: torch.Tensor, send_sizes: torch.Tensor,
         else:
             stride = 0
         rows = a2a_plan.total_rows(recv_np, stride)
-        out = _sparse_a2a(_contig(in_data), send_np, recv_np, stride, rows, group_size, True)
+        out = _sparse_a2a(x, send_np, recv_np, stride, rows, group_size, True)
     return [out, torch.from_numpy(recv_np.copy()), torch.from_numpy(send_np.copy())]
 
 
@@ -306,4 +419,9 @@ def size_known_group_sparse_all_to_all(in_data: torch.Tensor, send_sizes: torch.
         stride = 0
         rows = a2a_plan.total_rows(recv_np)
     with torch.cuda.device(in_data.device):
-        return _sparse_a2a(_contig(in_data), send_np, recv_np, stride, rows, group_size, False)
+        x = _contig(in_data)
+        if _p2p_usable(x, W, group_size):
+            out = _sparse_backward_p2p(x, send_np, recv_np, stride, group_size)
+            if out is not None:
+                return out
+        return _sparse_a2a(x, send_np, recv_np, stride, rows, group_size, False)

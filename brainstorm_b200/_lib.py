@@ -50,6 +50,14 @@ SIGNATURES = {
     "brt_all_to_all": (_int, [_vp, _vp, _i64, _vp]),
     "brt_group_asymmetry_all_to_all": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _int, _vp]),
     "brt_group_sparse_all_to_all": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _int, _int, _vp]),
+    "brt_p2p_alloc": (_int, [_sz, ctypes.POINTER(_vp), _vp]),
+    "brt_p2p_open": (_int, [_vp, ctypes.POINTER(_vp)]),
+    "brt_p2p_close": (_int, [_vp]),
+    "brt_p2p_free": (_int, [_vp]),
+    "brt_p2p_push": (_int, [_vp, _int, _vp, _vp, _vp, _int, _int, ctypes.c_uint64, _vp, _vp,
+                            _vp]),
+    "brt_p2p_post": (_int, [_vp, _int, _int, _int, ctypes.c_uint64, _vp, _vp, _vp]),
+    "brt_p2p_wait": (_int, [_vp, _int, ctypes.c_uint64, _vp, _vp]),
 }
 
 

@@ -1,0 +1,264 @@
+// Expert-parallel exchange over NVLink peer memory.
+//
+// Every rank owns one "arena": device memory it allocates here and exports to the other
+// ranks of the box through CUDA IPC.  A variable-size all-to-all is then
+//
+//   push    : one kernel copies each of my buckets with 16-byte stores straight to its final
+//             row offset inside the destination rank's arena (plain peer stores; no TMA, no
+//             multicast), my own bucket included;
+//   arrive  : when the last CTA of the push has finished, the kernel raises my flag in every
+//             peer's arena (system-scope release);
+//   wait    : a second, tiny kernel waits until all peers have raised theirs.  The wait is
+//             bounded: after the limit it records a timeout in a status word and returns,
+//             it never hangs the GPU.
+//
+// The arena is used in two halves that alternate from one exchange to the next, which is
+// what makes a single arrive/wait per exchange sufficient: a peer can only start writing a
+// half again after I have signalled the exchange in between, and that signal is enqueued on
+// my stream behind my copy out of that half.
+#include "common.cuh"
+
+namespace brt_b200 {
+namespace {
+
+constexpr int kMaxRanks = 32;
+constexpr int kMaxCopies = 96;
+constexpr int kThreads = 256;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
+
+struct CopyList {
+  int count;
+  long long src_offset[kMaxCopies];  // bytes from `src`
+  char* dst[kMaxCopies];             // absolute destination address (peer or local arena)
+  long long bytes[kMaxCopies];       // multiple of 16
+  long long first_chunk[kMaxCopies + 1];
+};
+
+struct SignalList {
+  int world_size;
+  int my_rank;
+  unsigned long long epoch;
+  unsigned long long* peer_flags[kMaxRanks];  // flag array of every rank (index: who raised it)
+  unsigned int* done_counter;                 // in my control block
+};
+
+constexpr long long kChunkBytes = 32768;
+
+__device__ __forceinline__ void store_release_sys(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long load_acquire_sys(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(kThreads)
+p2p_push_kernel(const char* __restrict__ src, const __grid_constant__ CopyList list,
+                const __grid_constant__ SignalList sig) {
+  const long long total_chunks = list.first_chunk[list.count];
+  for (long long chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
+    // which copy does this chunk belong to (count <= 96: linear scan from a hint is cheap)
+    int c = 0;
+    while (c + 1 < list.count && list.first_chunk[c + 1] <= chunk) c++;
+    const long long at = (chunk - list.first_chunk[c]) * kChunkBytes;
+    long long n = list.bytes[c] - at;
+    if (n > kChunkBytes) n = kChunkBytes;
+    const uint4* s = reinterpret_cast<const uint4*>(src + list.src_offset[c] + at);
+    uint4* d = reinterpret_cast<uint4*>(list.dst[c] + at);
+    const int vecs = (int)(n >> 4);
+    for (int v = threadIdx.x; v < vecs; v += kThreads * 4) {
+      uint4 r[4];
+#pragma unroll
+      for (int k = 0; k < 4; k++)
+        if (v + k * kThreads < vecs) r[k] = __ldcs(s + v + k * kThreads);
+#pragma unroll
+      for (int k = 0; k < 4; k++)
+        if (v + k * kThreads < vecs) d[v + k * kThreads] = r[k];
+    }
+  }
+  if (sig.world_size == 0) return;  // plain multi-range copy, nobody to tell
+  // arrive: the last CTA to finish raises my flag at every rank
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(sig.done_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *sig.done_counter = 0;  // ready for the next exchange (stream-ordered)
+      __threadfence_system();
+      for (int r = 0; r < sig.world_size; r++)
+        store_release_sys(sig.peer_flags[r] + sig.my_rank, sig.epoch);
+    }
+  }
+}
+
+// Post `n` int32 values (my bucket sizes) into row `my_rank` of every rank's size board and
+// raise my flag there.  One CTA.
+struct PostList {
+  int world_size;
+  int my_rank;
+  int n;
+  unsigned long long epoch;
+  int* peer_board[kMaxRanks];
+  unsigned long long* peer_flags[kMaxRanks];
+};
+
+__global__ void __launch_bounds__(kThreads)
+p2p_post_kernel(const int* __restrict__ values, const __grid_constant__ PostList post) {
+  for (int r = 0; r < post.world_size; r++)
+    for (int t = threadIdx.x; t < post.n; t += kThreads)
+      post.peer_board[r][post.my_rank * post.n + t] = values[t];
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0)
+    for (int r = 0; r < post.world_size; r++)
+      store_release_sys(post.peer_flags[r] + post.my_rank, post.epoch);
+}
+
+__global__ void p2p_wait_kernel(const unsigned long long* __restrict__ my_flags, int world_size,
+                                unsigned long long epoch, int* __restrict__ status) {
+  const int r = threadIdx.x;
+  if (r >= world_size) return;
+  unsigned long long start = 0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
+  unsigned int spins = 0;
+  while (load_acquire_sys(my_flags + r) < epoch) {
+    __nanosleep(200);
+    if ((++spins & 255u) == 0) {
+      unsigned long long now = 0;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (now - start > kWaitLimitNs) {
+        atomicExch(status, BRT_ERR_TIMEOUT);
+        return;
+      }
+    }
+  }
+}
+
+}  // namespace
+}  // namespace brt_b200
+
+using namespace brt_b200;
+
+extern "C" {
+
+BRT_API int brt_p2p_alloc(size_t bytes, void** dev_ptr, void* ipc_handle_out) {
+  clear_error();
+  BRT_REQUIRE(dev_ptr != nullptr && ipc_handle_out != nullptr && bytes > 0, "bad arguments");
+  static_assert(sizeof(cudaIpcMemHandle_t) == BRT_P2P_HANDLE_BYTES, "handle size");
+  void* p = nullptr;
+  BRT_CUDA_TRY(cudaMalloc(&p, bytes));
+  cudaError_t e = cudaMemset(p, 0, bytes);
+  if (e == cudaSuccess) {
+    cudaIpcMemHandle_t h;
+    e = cudaIpcGetMemHandle(&h, p);
+    if (e == cudaSuccess) memcpy(ipc_handle_out, &h, sizeof(h));
+  }
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return set_error(BRT_ERR_CUDA, "exporting the arena failed: %s", cudaGetErrorString(e));
+  }
+  *dev_ptr = p;
+  return BRT_OK;
+}
+
+BRT_API int brt_p2p_open(const void* ipc_handle, void** peer_ptr) {
+  clear_error();
+  BRT_REQUIRE(ipc_handle != nullptr && peer_ptr != nullptr, "bad arguments");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, ipc_handle, sizeof(h));
+  BRT_CUDA_TRY(cudaIpcOpenMemHandle(peer_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return BRT_OK;
+}
+
+BRT_API int brt_p2p_close(void* peer_ptr) {
+  clear_error();
+  BRT_CUDA_TRY(cudaIpcCloseMemHandle(peer_ptr));
+  return BRT_OK;
+}
+
+BRT_API int brt_p2p_free(void* dev_ptr) {
+  clear_error();
+  BRT_CUDA_TRY(cudaFree(dev_ptr));
+  return BRT_OK;
+}
+
+BRT_API int brt_p2p_push(const void* src, int copy_count, const int64_t* src_offsets,
+                         void* const* dst_ptrs, const int64_t* bytes, int world_size,
+                         int my_rank, uint64_t epoch, void* const* peer_flag_arrays,
+                         void* my_done_counter, void* stream) {
+  clear_error();
+  BRT_REQUIRE(copy_count >= 0 && copy_count <= kMaxCopies, "at most %d copies per push",
+              kMaxCopies);
+  BRT_REQUIRE(world_size >= 0 && world_size <= kMaxRanks &&
+                  (world_size == 0 || (my_rank >= 0 && my_rank < world_size)),
+              "bad rank %d of %d", my_rank, world_size);
+  BRT_REQUIRE(world_size == 0 || (peer_flag_arrays != nullptr && my_done_counter != nullptr),
+              "null control pointers");
+  CopyList list;
+  list.count = copy_count;
+  long long chunks = 0;
+  for (int i = 0; i < copy_count; i++) {
+    BRT_REQUIRE(bytes[i] >= 0 && bytes[i] % 16 == 0 && src_offsets[i] % 16 == 0 &&
+                    aligned_to(dst_ptrs[i], 16),
+                "copy %d is not 16-byte aligned", i);
+    list.src_offset[i] = src_offsets[i];
+    list.dst[i] = static_cast<char*>(dst_ptrs[i]);
+    list.bytes[i] = bytes[i];
+    list.first_chunk[i] = chunks;
+    chunks += (bytes[i] + kChunkBytes - 1) / kChunkBytes;
+  }
+  list.first_chunk[copy_count] = chunks;
+  BRT_REQUIRE(copy_count == 0 || aligned_to(src, 16), "source is not 16-byte aligned");
+  SignalList sig;
+  sig.world_size = world_size;
+  sig.my_rank = my_rank;
+  sig.epoch = epoch;
+  for (int r = 0; r < world_size; r++)
+    sig.peer_flags[r] = static_cast<unsigned long long*>(peer_flag_arrays[r]);
+  sig.done_counter = static_cast<unsigned int*>(my_done_counter);
+  long long grid = chunks;
+  const long long cap = (long long)sm_count() * 4;
+  if (grid > cap) grid = cap;
+  if (grid < 1) grid = 1;
+  p2p_push_kernel<<<(unsigned)grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const char*>(src), list, sig);
+  BRT_LAUNCH_CHECK("p2p_push_kernel");
+  return BRT_OK;
+}
+
+BRT_API int brt_p2p_post(const int32_t* values, int n, int world_size, int my_rank,
+                         uint64_t epoch, void* const* peer_boards, void* const* peer_flag_arrays,
+                         void* stream) {
+  clear_error();
+  BRT_REQUIRE(values != nullptr && n > 0 && peer_boards != nullptr && peer_flag_arrays != nullptr,
+              "bad arguments");
+  BRT_REQUIRE(world_size >= 1 && world_size <= kMaxRanks && my_rank >= 0 && my_rank < world_size,
+              "bad rank %d of %d", my_rank, world_size);
+  PostList post;
+  post.world_size = world_size;
+  post.my_rank = my_rank;
+  post.n = n;
+  post.epoch = epoch;
+  for (int r = 0; r < world_size; r++) {
+    post.peer_board[r] = static_cast<int*>(peer_boards[r]);
+    post.peer_flags[r] = static_cast<unsigned long long*>(peer_flag_arrays[r]);
+  }
+  p2p_post_kernel<<<1, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(values, post);
+  BRT_LAUNCH_CHECK("p2p_post_kernel");
+  return BRT_OK;
+}
+
+BRT_API int brt_p2p_wait(const void* my_flag_array, int world_size, uint64_t epoch,
+                         void* status_word, void* stream) {
+  clear_error();
+  BRT_REQUIRE(my_flag_array != nullptr && status_word != nullptr, "null control pointers");
+  BRT_REQUIRE(world_size >= 1 && world_size <= kMaxRanks, "bad world size %d", world_size);
+  p2p_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const unsigned long long*>(my_flag_array), world_size, epoch,
+      static_cast<int*>(status_word));
+  BRT_LAUNCH_CHECK("p2p_wait_kernel");
+  return BRT_OK;
+}
+
+}  // extern "C"

@@ -12,6 +12,7 @@ import torch
 import torch.distributed as dist
 
 from .._C import distributed as C_dist
+from . import p2p
 
 
 class global_info:
@@ -36,6 +37,8 @@ def is_nccl_activated(group: dist.ProcessGroup = None) -> bool:
         unique_id = C_dist.make_nccl_unique_id(global_info.world_rank)
         dist.broadcast(unique_id, 0, global_info.group)
         C_dist.init_nccl(unique_id, global_info.world_rank, global_info.world_size)
+        # NVLink peer arena for the packed exchange (all ranks or none; BRT_P2P=0 disables)
+        p2p.setup(global_info.group, global_info.world_rank, global_info.world_size)
         global_info.initialized = True
     return True
 

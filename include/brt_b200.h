@@ -260,6 +260,50 @@ BRT_API int brt_group_sparse_all_to_all(const void* send_buffer, void* recv_buff
                                         int64_t grain_bytes, int64_t stride_rows, int group_size,
                                         int forward, void* stream);
 
+/* ------------------------------------------------------------------ distributed: NVLink peer exchange */
+
+#define BRT_P2P_HANDLE_BYTES 64
+
+/*
+ * Same exchange patterns as brt_group_sparse_all_to_all / brt_group_asymmetry_all_to_all
+ * (src/distributed/collective.cc:90-224 in the reference), moved by this library's own
+ * kernels over NVLink peer memory instead of NCCL send/recv.  No counterpart in the
+ * reference for the mechanism.
+ *
+ * brt_p2p_alloc   allocates an arena on the current device, zero-fills it and exports it as a
+ *                 CUDA IPC handle (BRT_P2P_HANDLE_BYTES bytes) that the caller moves to the
+ *                 other ranks of the box.  Setup-time call (this one does allocate).
+ * brt_p2p_open    maps another rank's arena into this process; brt_p2p_close unmaps it;
+ *                 brt_p2p_free releases an arena made by brt_p2p_alloc.
+ * brt_p2p_push    copies `copy_count` (<= 96) byte ranges of `src` to absolute destination
+ *                 addresses (inside peers' arenas or local memory; all 16-byte aligned and
+ *                 sized) and then stores `epoch` into slot `my_rank` of every rank's flag
+ *                 array.  `my_done_counter` is a zero-initialised 4-byte word in local memory.
+ *                 world_size == 0: no flag is raised (a plain multi-range copy).
+ * brt_p2p_post    writes `n` int32 values (this rank's bucket sizes) into row `my_rank` of the
+ *                 size board in every rank's arena and raises slot `my_rank` of the given flag
+ *                 arrays; together with brt_p2p_wait this is the size exchange that precedes
+ *                 a data exchange (the reference does it with an NCCL all-to-all,
+ *                 src/backend/torch/distributed.cc:777-783).
+ * brt_p2p_wait    enqueues a kernel that returns once every slot of `my_flag_array` holds a
+ *                 value >= epoch.  The wait is bounded (2 s): on expiry it writes
+ *                 BRT_ERR_TIMEOUT into `status_word` (a 4-byte device word the caller reads
+ *                 back when convenient) and returns; it never blocks the GPU indefinitely.
+ */
+BRT_API int brt_p2p_alloc(size_t bytes, void** dev_ptr, void* ipc_handle_out);
+BRT_API int brt_p2p_open(const void* ipc_handle, void** peer_ptr);
+BRT_API int brt_p2p_close(void* peer_ptr);
+BRT_API int brt_p2p_free(void* dev_ptr);
+BRT_API int brt_p2p_push(const void* src, int copy_count, const int64_t* src_offsets,
+                         void* const* dst_ptrs, const int64_t* bytes, int world_size,
+                         int my_rank, uint64_t epoch, void* const* peer_flag_arrays,
+                         void* my_done_counter, void* stream);
+BRT_API int brt_p2p_post(const int32_t* values, int n, int world_size, int my_rank,
+                         uint64_t epoch, void* const* peer_boards, void* const* peer_flag_arrays,
+                         void* stream);
+BRT_API int brt_p2p_wait(const void* my_flag_array, int world_size, uint64_t epoch,
+                         void* status_word, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -35,6 +35,10 @@ def main():
     from brainstorm_b200._C import distributed as C_dist
 
     assert brt_dist.is_nccl_activated()
+    from brainstorm_b200.runtime import p2p
+
+    want_p2p = os.environ.get("BRT_P2P", "1") != "0"
+    assert (p2p.arena() is not None) == want_p2p, p2p._disabled_reason
     try:
         C_dist.init_nccl(torch.zeros(128, dtype=torch.int8), rank, W)
         raise AssertionError("second init_nccl must be refused")
@@ -120,6 +124,7 @@ def main():
     ep = GatherRouter("distributed_fused_combine", {"transform": True})(routed, None, score)
     assert torch.equal(ep.data, local.data), f"rank {rank}: expert-parallel route differs"
 
+    p2p.check_status()
     dist.barrier()
     if rank == 0:
         print("DIST_OK", W)
