@@ -283,25 +283,11 @@ def _p2p_usable(x: torch.Tensor, world: int, group_size: int) -> bool:
 
 def _copy_out_remote(arena, epoch, out, starts, rows, sources, rank, grain):
     """Bring the ranges that peers pushed into my arena half to the same offsets of ``out``
-    (ranges from this rank were written to ``out`` directly).  Adjacent ranges are merged."""
-    src_off, dst_ptr, nbytes = [], [], []
-    base = out.data_ptr()
-    half = arena.half_offset(epoch)
-    run_start, run_len = None, 0
-    for st, n, srcr in zip(starts, rows, sources):
-        if srcr != rank and n > 0 and run_start is not None and run_start + run_len == st:
-            run_len += n
-            continue
-        if run_start is not None and run_len > 0:
-            src_off.append(half + run_start * grain)
-            dst_ptr.append(base + run_start * grain)
-            nbytes.append(run_len * grain)
-        run_start, run_len = (st, n) if (srcr != rank and n > 0) else (None, 0)
-    if run_start is not None and run_len > 0:
-        src_off.append(half + run_start * grain)
-        dst_ptr.append(base + run_start * grain)
-        nbytes.append(run_len * grain)
-    arena.copy_ranges(arena.base, src_off, dst_ptr, nbytes, _stream(out.device))
+    (ranges from this rank were written to ``out`` directly)."""
+    starts = np.asarray(starts, dtype=np.int64)
+    nbytes = np.where(np.asarray(sources) != rank, np.asarray(rows, dtype=np.int64), 0) * grain
+    arena.copy_ranges(arena.base, arena.half_offset(epoch) + starts * grain,
+                      out.data_ptr() + starts * grain, nbytes, _stream(out.device))
 
 
 def _sparse_forward_p2p(x, send_sizes, stride, group_size):
@@ -336,8 +322,8 @@ def _sparse_forward_p2p(x, send_sizes, stride, group_size):
     out = torch.empty(shape, dtype=x.dtype, device=dev)
     epoch = arena.exchange(x, src_rows * grain, dst_rank, dst_rows * grain, mine * grain,
                            _stream(dev), local_out=out.data_ptr())
-    _copy_out_remote(arena, epoch, out, starts[rank].tolist(), per[rank].tolist(),
-                     np.tile(np.arange(W), G).tolist(), rank, grain)
+    _copy_out_remote(arena, epoch, out, starts[rank], per[rank], np.tile(np.arange(W), G), rank,
+                     grain)
     _matrix_cache[send_np.tobytes()] = S
     return out, send_np, recv_np
 
@@ -370,8 +356,8 @@ def _sparse_backward_p2p(x, send_np, recv_np, stride, group_size):
     out = torch.empty(shape, dtype=x.dtype, device=x.device)
     epoch = arena.exchange(x, src_rows * grain, dst_rank, dst_rows * grain, held * grain,
                            _stream(x.device), local_out=out.data_ptr())
-    _copy_out_remote(arena, epoch, out, rank_major_starts[rank].tolist(), flat[rank].tolist(),
-                     np.repeat(np.arange(W), G).tolist(), rank, grain)
+    _copy_out_remote(arena, epoch, out, rank_major_starts[rank], flat[rank],
+                     np.repeat(np.arange(W), G), rank, grain)
     return out
 
 

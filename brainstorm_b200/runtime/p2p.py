@@ -54,6 +54,7 @@ class PeerArena:
             self.peer_base.append(p.value)
         self.epoch = 0
         self.size_epoch = 0
+        self._peer_base_np = np.array(self.peer_base, dtype=np.int64)
         self._size_flag_ptrs = (ctypes.c_void_p * world)(
             *[b + SIZE_FLAGS_OFFSET for b in self.peer_base])
         self._board_ptrs = (ctypes.c_void_p * world)(*[b + BOARD_OFFSET for b in self.peer_base])
@@ -86,18 +87,21 @@ class PeerArena:
                                "(brt_p2p_wait, 2 s limit)")
         return host[1:].reshape(self.world, n)
 
+    @staticmethod
+    def _i64(a) -> np.ndarray:
+        return np.ascontiguousarray(a, dtype=np.int64)
+
     def copy_ranges(self, src_base: int, src_offsets, dst_ptrs, nbytes, stream: int) -> None:
         """Local multi-range copy with the push kernel (no flags involved)."""
-        keep = [i for i, n in enumerate(nbytes) if n > 0]
-        if not keep:
+        nb = self._i64(nbytes)
+        keep = nb > 0
+        if not keep.any():
             return
-        for at in range(0, len(keep), MAX_COPIES):
-            part = keep[at:at + MAX_COPIES]
-            n = len(part)
-            so = (ctypes.c_int64 * n)(*[int(src_offsets[i]) for i in part])
-            dp = (ctypes.c_void_p * n)(*[int(dst_ptrs[i]) for i in part])
-            nb = (ctypes.c_int64 * n)(*[int(nbytes[i]) for i in part])
-            _lib.call("brt_p2p_push", src_base, n, so, dp, nb, 0, 0, 0, None, None, stream)
+        so, dp, nb = self._i64(src_offsets)[keep], self._i64(dst_ptrs)[keep], nb[keep]
+        for at in range(0, nb.size, MAX_COPIES):
+            a, b, c = (np.ascontiguousarray(v[at:at + MAX_COPIES]) for v in (so, dp, nb))
+            _lib.call("brt_p2p_push", src_base, int(c.size), a.ctypes.data, b.ctypes.data,
+                      c.ctypes.data, 0, 0, 0, None, None, stream)
 
     def exchange(self, src: torch.Tensor, src_offsets, dst_ranks, dst_offsets, nbytes,
                  stream: int, local_out: int = 0) -> int:
@@ -107,16 +111,21 @@ class PeerArena:
         Returns the epoch whose half now holds the data that peers sent to this rank."""
         self.epoch += 1
         e = self.epoch
-        keep = [i for i, n in enumerate(nbytes) if n > 0]
-        n = len(keep)
         half = self.half_offset(e)
-        so = (ctypes.c_int64 * max(n, 1))(*[int(src_offsets[i]) for i in keep])
-        dp = (ctypes.c_void_p * max(n, 1))(
-            *[(local_out + int(dst_offsets[i])) if (local_out and int(dst_ranks[i]) == self.rank)
-              else self.peer_base[int(dst_ranks[i])] + half + int(dst_offsets[i]) for i in keep])
-        nb = (ctypes.c_int64 * max(n, 1))(*[int(nbytes[i]) for i in keep])
-        _lib.call("brt_p2p_push", src.data_ptr(), n, so, dp, nb, self.world, self.rank, e,
-                  self._flag_ptrs, self.base + COUNTER_OFFSET, stream)
+        nb = self._i64(nbytes)
+        ranks = self._i64(dst_ranks)
+        dp = self._peer_base_np[ranks] + half + self._i64(dst_offsets)
+        if local_out:
+            dp = np.where(ranks == self.rank, local_out + self._i64(dst_offsets), dp)
+        keep = nb > 0
+        so = np.ascontiguousarray(self._i64(src_offsets)[keep])
+        dp = np.ascontiguousarray(dp[keep])
+        nb = np.ascontiguousarray(nb[keep])
+        if nb.size > MAX_COPIES:
+            raise RuntimeError("too many buckets for one peer push")
+        _lib.call("brt_p2p_push", src.data_ptr(), int(nb.size), so.ctypes.data, dp.ctypes.data,
+                  nb.ctypes.data, self.world, self.rank, e, self._flag_ptrs,
+                  self.base + COUNTER_OFFSET, stream)
         _lib.call("brt_p2p_wait", self.base + FLAGS_OFFSET, self.world, e,
                   self.base + STATUS_OFFSET, stream)
         return e
@@ -139,7 +148,7 @@ def setup(group, rank: int, world: int) -> Optional[PeerArena]:
     if os.environ.get("BRT_P2P", "1") == "0":
         _disabled_reason = "BRT_P2P=0"
         return None
-    half = int(os.environ.get("BRT_P2P_ARENA_MB", "768")) << 20
+    half = int(os.environ.get("BRT_P2P_ARENA_MB", "2048")) << 20
     ok, made, err = 1, None, ""
     try:
         if dist.get_world_size(group) != torch.cuda.device_count() and \
