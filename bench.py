@@ -238,11 +238,12 @@ def run_gpu(args):
         out, idx, loads, routed = step()
     barrier()
 
-    # The single-GPU step has no host synchronisation, so it is captured once into a CUDA
-    # graph and the timed region replays it: launch latency of the Python wrappers is not
-    # part of the device-side number (the eager number is reported next to it).
+    # The padded single-GPU step has no host synchronisation, so it is captured once into a
+    # CUDA graph and the timed region replays it: launch latency of the Python wrappers is
+    # not part of the device-side number (the eager number is reported next to it).  The
+    # un-padded step reads loads.sum() on the host to size its output and stays eager.
     graph = None
-    if not distributed and not args.no_graph:
+    if not distributed and not args.no_graph and padded:
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -277,13 +278,18 @@ def run_gpu(args):
     ms_per_step = total_ms / args.steps
 
     # Host-inclusive time of the eager Python API, for reference.
+    # The library counts its own kernel launches; the eager steps give launches per step
+    # (a graph replay issues the same kernels without passing through the entry points).
+    from brainstorm_b200 import _lib
     h0 = torch.cuda.Event(enable_timing=True)
     h1 = torch.cuda.Event(enable_timing=True)
+    launches_before = _lib.query("brt_kernel_launch_count")
     h0.record()
     for _ in range(args.steps):
         step()
     h1.record()
     barrier()
+    launches_per_step = (_lib.query("brt_kernel_launch_count") - launches_before) / args.steps
     eager_host_ms = h0.elapsed_time(h1) / args.steps
 
     # Per-op device times: the same steps, eagerly, with events between the ops.  A spin
@@ -348,7 +354,8 @@ def run_gpu(args):
                      "nominal_frac_of_8000": round(kernels[dominant]["achieved_gbs"] / 8000, 4)},
         "kernels": kernels,
         "routing": {"kept_routes": ab["R"], "cells_routed": ab["T_r"], "output_rows": ab["L"]},
-        "gpu_launches": args.steps * ((3 if padded else 0) + 3 + 2 + 1),
+        "gpu_launches": int(round(args.steps * launches_per_step)),
+        "gpu_launches_per_step": launches_per_step,
         "clocks": clocks, "e2e": e2e,
         "timed_region": "CUDA graph replay of the step" if graph is not None
                         else "eager launches of the step",
@@ -406,28 +413,75 @@ def measure_e2e(wl, dev, args, ScatterRouter, GatherRouter, distributed, world):
         out = gather(routed, None, gates)
         out_h.copy_(out, non_blocking=True)
 
+    def timed(run_steps, steps):
+        torch.cuda.synchronize()
+        if distributed:
+            dist.barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        run_steps(steps)
+        t1.record()
+        torch.cuda.synchronize()
+        ms = t0.elapsed_time(t1) / steps
+        if distributed:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
     for _ in range(3):
         step()
-    torch.cuda.synchronize()
-    if distributed:
-        dist.barrier()
     steps = max(3, min(args.steps, 20))
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for _ in range(steps):
-        step()
-    t1.record()
-    torch.cuda.synchronize()
-    ms = t0.elapsed_time(t1) / steps
-    if distributed:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    serial_ms = timed(lambda n: [step() for _ in range(n)], steps)
+
+    # The same steps as a three-stage pipeline, the way a serving loop feeds a GPU: step i+1's
+    # inputs go up on a copy stream and step i-1's result comes down on another while step i
+    # routes.  Every step still copies its own inputs in and its own result out; two device
+    # input slots and two pinned output slots are reused in turn.
+    main = torch.cuda.current_stream()
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    slots = [{"x": torch.empty_like(wl["x"], device=dev),
+              "score": torch.empty_like(wl["score"], device=dev),
+              "gates": torch.empty_like(wl["gates"], device=dev),
+              "out_h": torch.empty_like(wl["x"]).pin_memory(),
+              "loaded": torch.cuda.Event(), "consumed": torch.cuda.Event(),
+              "drained": torch.cuda.Event()} for _ in range(2)]
+
+    def pipelined(n):
+        for i in range(n):
+            sl = slots[i % 2]
+            with torch.cuda.stream(s_in):
+                if i >= 2:
+                    s_in.wait_event(sl["consumed"])
+                sl["x"].copy_(x_h, non_blocking=True)
+                sl["score"].copy_(score_h, non_blocking=True)
+                sl["gates"].copy_(gates_h, non_blocking=True)
+                sl["loaded"].record(s_in)
+            main.wait_event(sl["loaded"])
+            x = init_grid_tensor(sl["x"], [None], [None])
+            routed = scatter(x, sl["score"])
+            out = gather(routed, None, sl["gates"])
+            sl["consumed"].record(main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(sl["consumed"])
+                if i >= 2:
+                    s_out.wait_event(sl["drained"])
+                out.record_stream(s_out)
+                sl["out_h"].copy_(out, non_blocking=True)
+                sl["drained"].record(s_out)
+        main.wait_stream(s_out)
+        main.wait_stream(s_in)
+
+    pipelined(4)
+    ms = timed(pipelined, steps)
     h2d = sum(t.numel() * t.element_size() for t in (x_h, score_h, gates_h))
     d2h = out_h.numel() * out_h.element_size()
     return {"value": world * T / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms,
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-            "api": "ScatterRouter(topk, fused_dispatch) -> GatherRouter(fused_combine)"}
+            "api": "ScatterRouter(topk, fused_dispatch) -> GatherRouter(fused_combine)",
+            "schedule": "copy-in, route and copy-out of consecutive steps overlap (2 slots)",
+            "serial_ms_per_step": serial_ms,
+            "serial_value": world * T / (serial_ms * 1e-3)}
 
 
 # --------------------------------------------------------------------------------- CPU arm

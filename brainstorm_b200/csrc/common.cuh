@@ -19,6 +19,10 @@ char* error_buffer();
 int set_error(int code, const char* fmt, ...);
 void clear_error();
 
+// Counts a kernel launch made by this library (process-wide; read by
+// brt_kernel_launch_count()).
+void note_launch();
+
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
@@ -48,6 +52,20 @@ inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintp
 inline size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 inline int dtype_size(int dtype) { return dtype == BRT_F32 ? 4 : 2; }
+
+// ---- asynchronous 16-byte copies from global to shared memory (bypassing L1) ----------------
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
+  const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() {
+  asm volatile("cp.async.commit_group;\n" ::: "memory");
+}
+// Waits until at most N of this thread's committed groups are still in flight.
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
 
 // ---- device-side conversion between storage types and fp32 ---------------------------------
 

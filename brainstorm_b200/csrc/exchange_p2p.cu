@@ -222,7 +222,7 @@ BRT_API int brt_p2p_push(const void* src, int copy_count, const int64_t* src_off
   if (grid > cap) grid = cap;
   if (grid < 1) grid = 1;
   p2p_push_kernel<<<(unsigned)grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const char*>(src), list, sig);
+      static_cast<const char*>(src), list, sig), note_launch();
   BRT_LAUNCH_CHECK("p2p_push_kernel");
   return BRT_OK;
 }
@@ -244,7 +244,7 @@ BRT_API int brt_p2p_post(const int32_t* values, int n, int world_size, int my_ra
     post.peer_board[r] = static_cast<int*>(peer_boards[r]);
     post.peer_flags[r] = static_cast<unsigned long long*>(peer_flag_arrays[r]);
   }
-  p2p_post_kernel<<<1, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(values, post);
+  p2p_post_kernel<<<1, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(values, post), note_launch();
   BRT_LAUNCH_CHECK("p2p_post_kernel");
   return BRT_OK;
 }
@@ -256,7 +256,7 @@ BRT_API int brt_p2p_wait(const void* my_flag_array, int world_size, uint64_t epo
   BRT_REQUIRE(world_size >= 1 && world_size <= kMaxRanks, "bad world size %d", world_size);
   p2p_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const unsigned long long*>(my_flag_array), world_size, epoch,
-      static_cast<int*>(status_word));
+      static_cast<int*>(status_word)), note_launch();
   BRT_LAUNCH_CHECK("p2p_wait_kernel");
   return BRT_OK;
 }

@@ -15,20 +15,25 @@
 //   expand : each thread re-reads its word from L2, finds its offset inside the tile with
 //            one block-level scan of the popcounts, and writes 32 rows of V indices.
 //
-// HBM traffic is one read of the mask and one write of the indices; nothing spins or
-// waits on another CTA.  Masks holding values other than 0/1 are detected during `pack`
-// and make `expand` re-read the mask instead of the bit words, so the integer semantics
-// of the reference (index = running sum * mask value) hold for any int32 mask.
+// HBM traffic is one read of the mask and one write of the indices.  Masks holding values
+// other than 0/1 are detected during `pack` and make `expand` re-read the mask instead of
+// the bit words, so the integer semantics of the reference (index = running sum * mask
+// value) hold for any int32 mask.
 //
 // Two implementations of pack/expand share that plan:
 //   * the tiled path (path_num % 4 == 0, 16-byte aligned arrays): a CTA stages a
 //     [32*k cells, <=256 paths] tile in shared memory with fully coalesced 16-byte loads
 //     (every load of the tile is in flight at once), each warp turns a 32x32 block into
 //     column bit words with a 5-step shuffle transpose, and `expand` is one popcount per
-//     output element with coalesced 16-byte stores;
+//     output element with coalesced 16-byte stores.  Whenever the bit words of a CTA's
+//     share of the mask fit in shared memory the three steps run as ONE launch (the
+//     chained path): a CTA packs a run of consecutive tiles, publishes the run's column
+//     sums, adds up the sums of the runs before it (a bounded wait on CTAs that started
+//     earlier) and expands its tiles from shared memory;
 //   * the strip path (any path_num / alignment): a thread walks 32 cells of V paths.
-#include <cooperative_groups.h>
 
+#include <cstdlib>
+#include <cstring>
 #include <map>
 #include <mutex>
 #include <utility>
@@ -538,56 +543,17 @@ __device__ __forceinline__ uint32_t warp_transpose32(uint32_t a, int lane) {
   return a;
 }
 
-// Stage one tile of the mask, turn it into column bit words (kept in shared memory, and
-// written to `bits_out` when that is not null) and publish the tile's column sums and its
-// "value other than 0/1 seen" flag.  Ends with a CTA barrier.
-__device__ __forceinline__ void pack_tile(const TileCtx& x, const TileSmem& sm,
-                                          const int* __restrict__ mask,
-                                          uint32_t* __restrict__ bits_out,
-                                          int* __restrict__ tile_sums,
-                                          int* __restrict__ tile_flags) {
+// Turn the tile staged at sm.tile into column bit words at sm.bits (zeroed by the caller
+// before the barrier that made the staged tile visible; also written to `bits_out` when that
+// is not null).  The tile's column sums are ADDED to sm.sum / sm.extra and a value other
+// than 0/1 sets sm.flag.  Ends with a CTA barrier.
+__device__ __forceinline__ void pack_staged(const TileCtx& x, const TileSmem& sm,
+                                            uint32_t* __restrict__ bits_out) {
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
   const int col0 = x.chunk * x.ec;
   const int cols = (x.path_num - col0) < x.ec ? (x.path_num - col0) : x.ec;  // multiple of 4
-  const int64_t row0 = x.tile * x.rg * kGroupRows;
-  const int tile_rows = x.rg * kGroupRows;
-  const int vec_per_row = cols >> 2;
-  const int total_vecs = tile_rows * vec_per_row;
-
-  for (int i = tid; i < 2 * x.ec + 1; i += kTileThreads) sm.sum[i] = 0;
-  for (int i = tid; i < x.rg * x.ec; i += kTileThreads) sm.bits[i] = 0;
-
-  // Stage the tile: every 16-byte load is issued before the first store.  A tile holds at
-  // most 2048 vectors (8 per thread).  (row, vector) of a thread's k-th element advance by a
-  // fixed step with one carry, so the loop has no integer division.
-  constexpr int kBatch = 8;
-  {
-    const int step_r = kTileThreads / vec_per_row;
-    const int step_q = kTileThreads - step_r * vec_per_row;
-    int r = tid / vec_per_row;
-    int q = tid - r * vec_per_row;
-    int4 v[kBatch];
-    int soff[kBatch];
-#pragma unroll
-    for (int k = 0; k < kBatch; k++) {
-      v[k] = make_int4(0, 0, 0, 0);
-      soff[k] = r * x.pitch + 4 * q;
-      if (r < tile_rows && row0 + r < x.cell_num)
-        v[k] = __ldcs(reinterpret_cast<const int4*>(mask + (row0 + r) * x.path_num + col0 +
-                                                     4 * q));
-      r += step_r;
-      q += step_q;
-      if (q >= vec_per_row) { q -= vec_per_row; r += 1; }
-    }
-#pragma unroll
-    for (int k = 0; k < kBatch; k++)
-      if (tid + k * kTileThreads < total_vecs)
-        *reinterpret_cast<int4*>(sm.tile + soff[k]) = v[k];
-  }
-  __syncthreads();
-
   const int col_blocks = (cols + 31) >> 5;
   const int blocks = x.rg * col_blocks;
   bool nonbinary = false;
@@ -625,6 +591,99 @@ __device__ __forceinline__ void pack_tile(const TileCtx& x, const TileSmem& sm,
   }
   if (nonbinary) atomicOr(sm.flag, 1);
   __syncthreads();
+}
+
+// Start the asynchronous copy of one tile of the mask into `stage` (rows beyond the mask
+// are zero-filled with plain stores) and zero the tile's bit words.  The caller commits the
+// group, waits for it and passes a CTA barrier before pack_staged.
+__device__ __forceinline__ void stage_tile_async(const TileCtx& x, int* stage, int* bits,
+                                                 const int* __restrict__ mask) {
+  const int tid = threadIdx.x;
+  const int col0 = x.chunk * x.ec;
+  const int cols = (x.path_num - col0) < x.ec ? (x.path_num - col0) : x.ec;
+  const int64_t row0 = x.tile * x.rg * kGroupRows;
+  const int tile_rows = x.rg * kGroupRows;
+  const int vec_per_row = cols >> 2;
+  const int total_vecs = tile_rows * vec_per_row;
+  for (int i = tid; i < x.rg * x.ec; i += kTileThreads) bits[i] = 0;
+  const int step_r = kTileThreads / vec_per_row;
+  const int step_q = kTileThreads - step_r * vec_per_row;
+  int r = tid / vec_per_row;
+  int q = tid - r * vec_per_row;
+  for (int idx = tid; idx < total_vecs; idx += kTileThreads) {
+    int* dst = stage + r * x.pitch + 4 * q;
+    if (row0 + r < x.cell_num)
+      cp_async_16(dst, mask + (row0 + r) * x.path_num + col0 + 4 * q);
+    else
+      *reinterpret_cast<int4*>(dst) = make_int4(0, 0, 0, 0);
+    r += step_r;
+    q += step_q;
+    if (q >= vec_per_row) { q -= vec_per_row; r += 1; }
+  }
+}
+
+// Stage one tile of the mask and turn it into column bit words (kept in shared memory at
+// sm.bits, and written to `bits_out` when that is not null).  The tile's column sums are
+// ADDED to sm.sum / sm.extra and a value other than 0/1 sets sm.flag: the caller zeroes the
+// three before its first tile.  Ends with a CTA barrier.
+__device__ __forceinline__ void pack_tile_body(const TileCtx& x, const TileSmem& sm,
+                                               const int* __restrict__ mask,
+                                               uint32_t* __restrict__ bits_out) {
+  const int tid = threadIdx.x;
+  const int col0 = x.chunk * x.ec;
+  const int cols = (x.path_num - col0) < x.ec ? (x.path_num - col0) : x.ec;  // multiple of 4
+  const int64_t row0 = x.tile * x.rg * kGroupRows;
+  const int tile_rows = x.rg * kGroupRows;
+  const int vec_per_row = cols >> 2;
+  const int total_vecs = tile_rows * vec_per_row;
+
+  for (int i = tid; i < x.rg * x.ec; i += kTileThreads) sm.bits[i] = 0;
+
+  // Stage the tile: every 16-byte load is issued before the first store.  A tile holds at
+  // most 2048 vectors (8 per thread).  (row, vector) of a thread's k-th element advance by a
+  // fixed step with one carry, so the loop has no integer division.
+  constexpr int kBatch = 8;
+  {
+    const int step_r = kTileThreads / vec_per_row;
+    const int step_q = kTileThreads - step_r * vec_per_row;
+    int r = tid / vec_per_row;
+    int q = tid - r * vec_per_row;
+    int4 v[kBatch];
+    int soff[kBatch];
+#pragma unroll
+    for (int k = 0; k < kBatch; k++) {
+      v[k] = make_int4(0, 0, 0, 0);
+      soff[k] = r * x.pitch + 4 * q;
+      if (r < tile_rows && row0 + r < x.cell_num)
+        v[k] = __ldcs(reinterpret_cast<const int4*>(mask + (row0 + r) * x.path_num + col0 +
+                                                     4 * q));
+      r += step_r;
+      q += step_q;
+      if (q >= vec_per_row) { q -= vec_per_row; r += 1; }
+    }
+#pragma unroll
+    for (int k = 0; k < kBatch; k++)
+      if (tid + k * kTileThreads < total_vecs)
+        *reinterpret_cast<int4*>(sm.tile + soff[k]) = v[k];
+  }
+  __syncthreads();
+
+  pack_staged(x, sm, bits_out);
+}
+
+// One tile per CTA: pack it and publish its column sums and its "value other than 0/1
+// seen" flag to global memory.
+__device__ __forceinline__ void pack_tile(const TileCtx& x, const TileSmem& sm,
+                                          const int* __restrict__ mask,
+                                          uint32_t* __restrict__ bits_out,
+                                          int* __restrict__ tile_sums,
+                                          int* __restrict__ tile_flags) {
+  const int tid = threadIdx.x;
+  const int col0 = x.chunk * x.ec;
+  const int cols = (x.path_num - col0) < x.ec ? (x.path_num - col0) : x.ec;
+  // zeroed before the barrier inside the body that precedes its first atomic
+  for (int i = tid; i < 2 * x.ec + 1; i += kTileThreads) sm.sum[i] = 0;
+  pack_tile_body(x, sm, mask, bits_out);
   for (int c = tid; c < cols; c += kTileThreads)
     tile_sums[x.tile * x.path_num + col0 + c] = sm.sum[c] + sm.extra[c];
   if (tid == 0) tile_flags[x.tile * x.chunks + x.chunk] = *sm.flag;
@@ -739,67 +798,50 @@ __device__ __forceinline__ void scan_tiles(int col_block, int* __restrict__ tile
   }
 }
 
-// Write the indices (or the throttled mask) of one tile from its bit words in shared
-// memory and the tile's exclusive prefix.  `bits_in` != null: the words are first fetched
-// from global memory (separate-launch path); null: pack left them in shared memory.
+// Masks with values other than 0/1: thread c walks path c of the tile serially through the
+// mask itself (integer semantics: index = running sum * value).  `run` enters as the
+// column's sum over all earlier cells and leaves advanced by this tile.
 template <Mode MODE>
-__device__ __forceinline__ void expand_tile(const TileCtx& x, const TileSmem& sm,
-                                            const int* __restrict__ mask,
-                                            const uint32_t* __restrict__ bits_in,
-                                            const int* __restrict__ tile_prefix,
-                                            const int* __restrict__ flags,
-                                            int* __restrict__ out,
-                                            const int* __restrict__ threshold) {
+__device__ __forceinline__ void expand_general(const TileCtx& x, const int* __restrict__ mask,
+                                               int& run, int* __restrict__ out,
+                                               const int* __restrict__ threshold) {
   const int tid = threadIdx.x;
   const int col0 = x.chunk * x.ec;
   const int cols = (x.path_num - col0) < x.ec ? (x.path_num - col0) : x.ec;
   const int64_t row0 = x.tile * x.rg * kGroupRows;
-  const int64_t num_groups = (x.cell_num + kGroupRows - 1) / kGroupRows;
-  const bool general = (flags[0] & 1) != 0;
-
-  if (general) {
-    // Masks with values other than 0/1: one thread walks one path of the tile serially
-    // through the mask itself (integer semantics: index = running sum * value).
-    for (int c = tid; c < cols; c += kTileThreads) {
-      int run = tile_prefix[x.tile * x.path_num + col0 + c];
-      const int thr = MODE == Mode::kThrottle ? threshold[col0 + c] : 0;
-      for (int r = 0; r < x.rg * kGroupRows; r++) {
-        const int64_t row = row0 + r;
-        if (row >= x.cell_num) break;
-        const int64_t at = row * x.path_num + col0 + c;
-        const int m = mask[at];
-        run += m;
-        if constexpr (MODE == Mode::kThrottle) {
-          out[at] = (m == 1 && run <= thr) ? 1 : 0;
-        } else if constexpr (MODE == Mode::kSeat) {
-          out[at] = run * m;
-        } else {
-          const int64_t dst_row = (int64_t)run * m - 1;
-          if (run * m != 0 && dst_row >= 0 && dst_row < x.cell_num)
-            out[dst_row * x.path_num + col0 + c] = (int)(row + 1);
-        }
-      }
-    }
-    return;
-  }
-
-  if (bits_in != nullptr) {
-    for (int i = tid; i < x.rg * cols; i += kTileThreads) {
-      const int g = i / cols;
-      const int c = i - g * cols;
-      const int64_t group = x.tile * x.rg + g;
-      sm.bits[g * x.ec + c] =
-          group < num_groups ? static_cast<int>(bits_in[group * x.path_num + col0 + c]) : 0;
+  if (tid >= cols) return;
+  const int thr = MODE == Mode::kThrottle ? threshold[col0 + tid] : 0;
+  for (int r = 0; r < x.rg * kGroupRows; r++) {
+    const int64_t row = row0 + r;
+    if (row >= x.cell_num) break;
+    const int64_t at = row * x.path_num + col0 + tid;
+    const int m = mask[at];
+    run += m;
+    if constexpr (MODE == Mode::kThrottle) {
+      out[at] = (m == 1 && run <= thr) ? 1 : 0;
+    } else if constexpr (MODE == Mode::kSeat) {
+      out[at] = run * m;
+    } else {
+      const int64_t dst_row = (int64_t)run * m - 1;
+      if (run * m != 0 && dst_row >= 0 && dst_row < x.cell_num)
+        out[dst_row * x.path_num + col0 + tid] = (int)(row + 1);
     }
   }
-  if constexpr (MODE == Mode::kThrottle)
-    for (int c = tid; c < cols; c += kTileThreads) sm.thr[c] = threshold[col0 + c];
-  // cols <= 256 = kTileThreads: one path per thread; fetched before the barrier so that
-  // the global reads of the prologue overlap
-  const int my_prefix = tid < cols ? tile_prefix[x.tile * x.path_num + col0 + tid] : 0;
+}
+
+// 0/1 masks: write one tile from its bit words (sm.bits) and the per-path sums over all
+// earlier cells (`run` of thread c for path c, advanced by this tile on return).  Opens with
+// a CTA barrier, so sm.bits / sm.thr written just before the call are visible and sm.base
+// of an earlier tile is no longer read.
+template <Mode MODE>
+__device__ __forceinline__ void expand_binary(const TileCtx& x, const TileSmem& sm, int& run,
+                                              int* __restrict__ out) {
+  const int tid = threadIdx.x;
+  const int col0 = x.chunk * x.ec;
+  const int cols = (x.path_num - col0) < x.ec ? (x.path_num - col0) : x.ec;
+  const int64_t row0 = x.tile * x.rg * kGroupRows;
   __syncthreads();
-  if (tid < cols) {
-    int run = my_prefix;
+  if (tid < cols) {  // cols <= 256 = kTileThreads: one path per thread
     for (int g = 0; g < x.rg; g++) {
       sm.base[g * x.ec + tid] = run;
       run += __popc(static_cast<uint32_t>(sm.bits[g * x.ec + tid]));
@@ -848,6 +890,41 @@ __device__ __forceinline__ void expand_tile(const TileCtx& x, const TileSmem& sm
     q += step_q;
     if (q >= vec_per_row) { q -= vec_per_row; r += 1; }
   }
+}
+
+// Write the indices (or the throttled mask) of one tile from its bit words and the tile's
+// exclusive prefix in global memory.  `bits_in` != null: the words are first fetched from
+// global memory (separate-launch path); null: pack left them in shared memory.
+template <Mode MODE>
+__device__ __forceinline__ void expand_tile(const TileCtx& x, const TileSmem& sm,
+                                            const int* __restrict__ mask,
+                                            const uint32_t* __restrict__ bits_in,
+                                            const int* __restrict__ tile_prefix,
+                                            const int* __restrict__ flags,
+                                            int* __restrict__ out,
+                                            const int* __restrict__ threshold) {
+  const int tid = threadIdx.x;
+  const int col0 = x.chunk * x.ec;
+  const int cols = (x.path_num - col0) < x.ec ? (x.path_num - col0) : x.ec;
+  const int64_t num_groups = (x.cell_num + kGroupRows - 1) / kGroupRows;
+  // fetched before any barrier so that the global reads of the prologue overlap
+  int run = tid < cols ? tile_prefix[x.tile * x.path_num + col0 + tid] : 0;
+  if ((flags[0] & 1) != 0) {
+    expand_general<MODE>(x, mask, run, out, threshold);
+    return;
+  }
+  if (bits_in != nullptr) {
+    for (int i = tid; i < x.rg * cols; i += kTileThreads) {
+      const int g = i / cols;
+      const int c = i - g * cols;
+      const int64_t group = x.tile * x.rg + g;
+      sm.bits[g * x.ec + c] =
+          group < num_groups ? static_cast<int>(bits_in[group * x.path_num + col0 + c]) : 0;
+    }
+  }
+  if constexpr (MODE == Mode::kThrottle)
+    for (int c = tid; c < cols; c += kTileThreads) sm.thr[c] = threshold[col0 + c];
+  expand_binary<MODE>(x, sm, run, out);
 }
 
 struct TiledArgs {
@@ -905,29 +982,158 @@ __global__ void __launch_bounds__(kTileThreads) index_expand_tiled_kernel(const 
   expand_tile<MODE>(ctx_of(a), sm, a.mask, a.bits, a.tile_sums, a.flags, a.out, a.threshold);
 }
 
-// Small masks: the whole grid is resident at once, so pack, scan and expand run as one
-// cooperative launch with two grid-wide barriers; the bit words never leave shared memory
-// and two launch boundaries disappear.
+// ---------------------------------------------------------------------------- chained path
+// One launch, no grid-wide barrier.  A CTA takes a ticket; ticket k owns a run of
+// consecutive tiles of one path chunk.  It packs them all (the bit words stay in shared
+// memory), publishes the run's column sums, adds up the sums published by the tickets before
+// it and then writes its tiles.  A ticket only ever waits for SMALLER tickets, whose CTAs
+// have started by construction, so the kernel needs no co-residency guarantee.
+struct ChainArgs {
+  TiledArgs t;
+  unsigned long long* status;  // [ranges][path_num]: (1 << 32) | column sum once published
+  int* ticket;
+  int* error;  // set to 1 when a wait ran out
+  int tiles_per_cta;
+  int ranges;
+};
+
+constexpr int kChainFly = 16;            // status words a thread keeps in flight
+constexpr int kChainSpinLimit = 1 << 20;  // polls (each followed by a short sleep)
+
+__device__ __forceinline__ void status_publish(unsigned long long* p, int value) {
+  const unsigned long long w = (1ull << 32) | static_cast<unsigned>(value);
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ unsigned long long status_peek(const unsigned long long* p) {
+  unsigned long long w;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+  return w;
+}
+
 template <Mode MODE>
-__global__ void __launch_bounds__(kTileThreads, 3) index_fused_kernel(const TiledArgs a) {
+__global__ void __launch_bounds__(kTileThreads, 2) index_chain_kernel(const ChainArgs c) {
   extern __shared__ __align__(16) int s_dyn[];
-  __shared__ int s_warp[kTileWarps][4];
-  cooperative_groups::grid_group grid = cooperative_groups::this_grid();
-  const TileSmem sm = carve_tile_smem(s_dyn, a.ec, a.rg, a.pitch, true);
-  const TileCtx x = ctx_of(a);
-  pack_tile(x, sm, a.mask, nullptr, a.tile_sums, a.tile_flags);
-  grid.sync();
-  const int linear = blockIdx.y * gridDim.x + blockIdx.x;
-  const int scan_blocks = (a.path_num + 3) / 4;
-  const int total_blocks = gridDim.x * gridDim.y;
-  for (int cb = linear; cb < scan_blocks; cb += total_blocks) {
-    scan_tiles<MODE == Mode::kThrottle, kTileThreads>(
-        cb, a.tile_sums, a.num_tiles, a.path_num, a.tile_flags, a.num_tiles * a.chunks, a.flags,
-        a.loads, a.caps, a.ncap, a.capacity_padding, a.path_wise, a.prefix, a.threshold, s_warp);
-    __syncthreads();
+  __shared__ int s_ticket;
+  const TiledArgs& a = c.t;
+  const int tid = threadIdx.x;
+  if (tid == 0) s_ticket = atomicAdd(c.ticket, 1);
+  TileSmem sm = carve_tile_smem(s_dyn, a.ec, a.rg, a.pitch, true);
+  int* bits_all = s_dyn + tile_smem_ints(a.ec, a.rg, a.pitch, true);
+  for (int i = tid; i < 2 * a.ec + 1; i += kTileThreads) sm.sum[i] = 0;
+  __syncthreads();
+  const int ticket = s_ticket;
+  const int range = ticket / a.chunks;
+  TileCtx x;
+  x.cell_num = a.cell_num;
+  x.path_num = a.path_num;
+  x.ec = a.ec;
+  x.rg = a.rg;
+  x.pitch = a.pitch;
+  x.chunk = ticket - range * a.chunks;
+  x.chunks = a.chunks;
+  const int col0 = x.chunk * a.ec;
+  const int cols = (a.path_num - col0) < a.ec ? (a.path_num - col0) : a.ec;
+  const int64_t tile0 = (int64_t)range * c.tiles_per_cta;
+  const int64_t tile1 = (tile0 + c.tiles_per_cta) < a.num_tiles ? (tile0 + c.tiles_per_cta)
+                                                                 : a.num_tiles;
+  const int words_per_tile = a.rg * a.ec;
+
+  // read before this CTA publishes anything: the last ticket overwrites prefix[] only after
+  // it has seen every publication
+  int start = 0;
+  if (MODE == Mode::kThrottle && tid < cols) {
+    start = a.prefix[col0 + tid];
+    sm.thr[tid] = a.threshold[col0 + tid];
   }
-  grid.sync();
-  expand_tile<MODE>(x, sm, a.mask, nullptr, a.tile_sums, a.flags, a.out, a.threshold);
+
+  // two staging buffers: the copy of tile t + 1 is in flight while tile t is packed
+  int* const stage[2] = {sm.tile, bits_all + (size_t)c.tiles_per_cta * words_per_tile};
+  x.tile = tile0;
+  stage_tile_async(x, stage[0], bits_all, a.mask);
+  cp_async_commit();
+  for (int64_t t = tile0; t < tile1; t++) {
+    const int i = (int)(t - tile0);
+    if (t + 1 < tile1) {
+      x.tile = t + 1;
+      stage_tile_async(x, stage[(i + 1) & 1], bits_all + (size_t)(i + 1) * words_per_tile, a.mask);
+    }
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    x.tile = t;
+    TileSmem cur = sm;
+    cur.tile = stage[i & 1];
+    cur.bits = bits_all + (size_t)i * words_per_tile;
+    pack_staged(x, cur, nullptr);
+  }
+  const int own = tid < cols ? sm.sum[tid] + sm.extra[tid] : 0;
+  const bool general = *sm.flag != 0;
+  __threadfence();
+  if (tid < cols) status_publish(c.status + (int64_t)range * a.path_num + col0 + tid, own);
+
+  // sum of the tickets before this one: thread (part, path) takes every parts-th of them,
+  // kChainFly loads in flight at a time
+  int* s_before = sm.base;  // free until the first expand
+  for (int i = tid; i < a.ec; i += kTileThreads) s_before[i] = 0;
+  __syncthreads();
+  {
+    const int parts = kTileThreads / cols;
+    const int part = tid / cols;
+    const int path = tid - part * cols;
+    if (part < parts && range > 0) {
+      const unsigned long long* column = c.status + col0 + path;
+      int acc = 0;
+      for (int j0 = part; j0 < range; j0 += parts * kChainFly) {
+        unsigned long long w[kChainFly];
+        int spins = 0;
+        for (;;) {
+          bool ready = true;
+#pragma unroll
+          for (int u = 0; u < kChainFly; u++) {
+            const int j = j0 + u * parts;
+            w[u] = j < range ? status_peek(column + (int64_t)j * a.path_num) : (1ull << 32);
+          }
+#pragma unroll
+          for (int u = 0; u < kChainFly; u++) ready = ready && (w[u] >> 32) != 0;
+          if (ready) break;
+          if (++spins > kChainSpinLimit) {  // give up: flag it and carry on with what is there
+            *c.error = 1;
+            break;
+          }
+          __nanosleep(64);
+        }
+#pragma unroll
+        for (int u = 0; u < kChainFly; u++) acc += static_cast<int>(static_cast<unsigned>(w[u]));
+      }
+      if (acc != 0) atomicAdd(&s_before[path], acc);
+    }
+  }
+  __syncthreads();
+  int run = tid < cols ? s_before[tid] + start : 0;
+
+  if (range == c.ranges - 1 && tid < cols) {
+    const int total = run - start + own;
+    __threadfence();
+    if constexpr (MODE == Mode::kThrottle) {
+      const int thr = sm.thr[tid];
+      const int p = start + total;
+      a.prefix[col0 + tid] = p >= thr ? thr : p;
+    } else {
+      a.loads[col0 + tid] = map_load(total, col0 + tid, a.caps, a.ncap, a.capacity_padding != 0,
+                                     a.path_wise != 0);
+    }
+  }
+
+  for (int64_t t = tile0; t < tile1; t++) {
+    x.tile = t;
+    if (general) {
+      expand_general<MODE>(x, a.mask, run, a.out, a.threshold);
+    } else {
+      TileSmem cur = sm;
+      cur.bits = bits_all + (t - tile0) * words_per_tile;
+      expand_binary<MODE>(x, cur, run, a.out);
+    }
+  }
 }
 
 size_t tiled_scratch_bytes(int64_t cell_num, int path_num) {
@@ -937,38 +1143,67 @@ size_t tiled_scratch_bytes(int64_t cell_num, int path_num) {
   return 256 + round_up(groups * chunks * 4 + 4, 256) + 2 * round_up(groups * path_num * 4 + 4, 256);
 }
 
-// Resident-CTA capacity of the fused kernel per mode (cached per device and shared-memory
-// size by the caller's thread).
-template <Mode MODE>
-int fused_capacity(size_t smem) {
-  static thread_local std::map<std::pair<int, size_t>, int> cache;
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
-  const auto key = std::make_pair(dev, smem);
-  const auto hit = cache.find(key);
-  if (hit != cache.end()) return hit->second;
-  int per_sm = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, index_fused_kernel<MODE>,
-                                                    kTileThreads, smem) != cudaSuccess)
-    per_sm = 0;
-  const int capacity = per_sm * sm_count();
-  cache[key] = capacity;
-  return capacity;
-}
+constexpr int kChainCtasPerSm = 2;
+constexpr size_t kChainSmemLimit = 110 * 1024;
 
 template <Mode MODE>
-int launch_fused(const TiledArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
-  void* params[] = {const_cast<TiledArgs*>(&a)};
-  BRT_CUDA_TRY(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(index_fused_kernel<MODE>),
-                                           grid, dim3(kTileThreads), params, smem, stream));
+int launch_chain_mode(const ChainArgs& c, unsigned grid, size_t smem, cudaStream_t stream) {
+  static thread_local std::map<int, size_t> configured;  // device -> opted-in bytes
+  if (smem > 48 * 1024) {
+    int dev = 0;
+    BRT_CUDA_TRY(cudaGetDevice(&dev));
+    if (configured[dev] < smem) {
+      BRT_CUDA_TRY(cudaFuncSetAttribute(index_chain_kernel<MODE>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)kChainSmemLimit));
+      configured[dev] = kChainSmemLimit;
+    }
+  }
+  index_chain_kernel<MODE><<<grid, kTileThreads, smem, stream>>>(c), note_launch();
+  BRT_LAUNCH_CHECK("index_chain_kernel");
   return BRT_OK;
 }
 
-int fused_capacity_for(Mode mode, size_t smem) {
+int launch_chain(Mode mode, const TileGeom& g, int tiles_per_cta, int ranges, size_t smem,
+                 const int32_t* mask, int32_t* out, int32_t* loads, int64_t cell_num,
+                 int path_num, const int32_t* caps, int ncap, int capacity_padding,
+                 int path_wise, int32_t* prefix, const int32_t* threshold, void* scratch,
+                 cudaStream_t stream) {
+  ChainArgs c;
+  char* p = static_cast<char*>(scratch);
+  c.t.flags = reinterpret_cast<int*>(p);
+  c.error = c.t.flags + 1;
+  c.ticket = c.t.flags + 2;
+  c.status = reinterpret_cast<unsigned long long*>(p + 256);
+  c.tiles_per_cta = tiles_per_cta;
+  c.ranges = ranges;
+  c.t.tile_flags = nullptr;
+  c.t.tile_sums = nullptr;
+  c.t.bits = nullptr;
+  c.t.mask = mask;
+  c.t.out = out;
+  c.t.loads = loads;
+  c.t.caps = caps;
+  c.t.ncap = ncap;
+  c.t.capacity_padding = capacity_padding;
+  c.t.path_wise = path_wise;
+  c.t.prefix = prefix;
+  c.t.threshold = threshold;
+  c.t.cell_num = cell_num;
+  c.t.path_num = path_num;
+  c.t.ec = g.ec;
+  c.t.rg = g.rg;
+  c.t.pitch = g.pitch;
+  c.t.num_tiles = g.num_tiles;
+  c.t.chunks = g.col_chunks;
+  BRT_CUDA_TRY(cudaMemsetAsync(p, 0, 256 + (size_t)ranges * path_num * 8, stream));
+  if (mode == Mode::kTag)
+    BRT_CUDA_TRY(cudaMemsetAsync(out, 0, (size_t)cell_num * path_num * 4, stream));
+  const unsigned grid = (unsigned)ranges * (unsigned)g.col_chunks;
   switch (mode) {
-    case Mode::kSeat: return fused_capacity<Mode::kSeat>(smem);
-    case Mode::kTag: return fused_capacity<Mode::kTag>(smem);
-    default: return fused_capacity<Mode::kThrottle>(smem);
+    case Mode::kSeat: return launch_chain_mode<Mode::kSeat>(c, grid, smem, stream);
+    case Mode::kTag: return launch_chain_mode<Mode::kTag>(c, grid, smem, stream);
+    default: return launch_chain_mode<Mode::kThrottle>(c, grid, smem, stream);
   }
 }
 
@@ -980,23 +1215,23 @@ int launch_tiled(Mode mode, const int32_t* mask, int32_t* out, int32_t* loads, i
   BRT_REQUIRE(g.num_tiles <= 0x7fffffffLL && g.col_chunks <= 65535,
               "mask of %lld x %d cells is too large for one launch", (long long)cell_num,
               path_num);
-  // Fused single launch when some tile height lets the whole grid be resident at once:
-  // take the smallest such height (most CTAs).
-  bool fused = false;
-  {
-    const int rg_max = max_row_groups(g.ec);
-    const int64_t groups = g.num_groups * g.col_chunks;
-    if ((groups + rg_max - 1) / rg_max <= 4096) {  // cheap pre-filter
-      for (int rg = 1; rg <= rg_max; rg <<= 1) {
-        const TileGeom t = make_tile_geom(cell_num, path_num, rg);
-        const size_t smem = tile_smem_ints(t.ec, t.rg, t.pitch, true) * sizeof(int);
-        if (t.num_tiles * t.col_chunks <= fused_capacity_for(mode, smem)) {
-          g = t;
-          fused = true;
-          break;
-        }
-      }
-    }
+  // One chained launch when the bit words of a CTA's tiles fit in shared memory, else three
+  // launches (pack, scan, expand).  BRT_INDEX_PATH=split forces the latter (for tests).
+  const char* const forced = getenv("BRT_INDEX_PATH");
+  if (forced == nullptr || strcmp(forced, "split") != 0) {
+    int64_t target = (int64_t)sm_count() * kChainCtasPerSm / g.col_chunks;
+    if (target < 1) target = 1;
+    const int64_t ranges0 = g.num_tiles < target ? g.num_tiles : target;
+    const int64_t tiles_per_cta = (g.num_tiles + ranges0 - 1) / ranges0;
+    const int64_t ranges = (g.num_tiles + tiles_per_cta - 1) / tiles_per_cta;
+    const size_t smem = (tile_smem_ints(g.ec, g.rg, g.pitch, true) +
+                         (size_t)tiles_per_cta * g.rg * g.ec +
+                         (size_t)g.rg * kGroupRows * g.pitch) *
+                        sizeof(int);
+    if (smem <= kChainSmemLimit)
+      return launch_chain(mode, g, (int)tiles_per_cta, (int)ranges, smem, mask, out, loads,
+                          cell_num, path_num, caps, ncap, capacity_padding, path_wise, prefix,
+                          threshold, scratch, stream);
   }
   TiledArgs a;
   char* p = static_cast<char*>(scratch);
@@ -1029,31 +1264,24 @@ int launch_tiled(Mode mode, const int32_t* mask, int32_t* out, int32_t* loads, i
   const size_t smem_expand = tile_smem_ints(g.ec, g.rg, g.pitch, false) * sizeof(int);
   if (mode == Mode::kTag)
     BRT_CUDA_TRY(cudaMemsetAsync(out, 0, (size_t)cell_num * path_num * 4, stream));
-  if (fused) {
-    switch (mode) {
-      case Mode::kSeat: return launch_fused<Mode::kSeat>(a, grid, smem_full, stream);
-      case Mode::kTag: return launch_fused<Mode::kTag>(a, grid, smem_full, stream);
-      default: return launch_fused<Mode::kThrottle>(a, grid, smem_full, stream);
-    }
-  }
 
-  mask_pack_tiled_kernel<<<grid, kTileThreads, smem_full, stream>>>(a);
+  mask_pack_tiled_kernel<<<grid, kTileThreads, smem_full, stream>>>(a), note_launch();
   BRT_LAUNCH_CHECK("mask_pack_tiled_kernel");
   const unsigned scan_grid = (unsigned)((path_num + 3) / 4);
   if (mode == Mode::kThrottle)
-    tile_scan_wide_kernel<true><<<scan_grid, 1024, 0, stream>>>(a);
+    tile_scan_wide_kernel<true><<<scan_grid, 1024, 0, stream>>>(a), note_launch();
   else
-    tile_scan_wide_kernel<false><<<scan_grid, 1024, 0, stream>>>(a);
+    tile_scan_wide_kernel<false><<<scan_grid, 1024, 0, stream>>>(a), note_launch();
   BRT_LAUNCH_CHECK("tile_scan_wide_kernel");
   switch (mode) {
     case Mode::kSeat:
-      index_expand_tiled_kernel<Mode::kSeat><<<grid, kTileThreads, smem_expand, stream>>>(a);
+      index_expand_tiled_kernel<Mode::kSeat><<<grid, kTileThreads, smem_expand, stream>>>(a), note_launch();
       break;
     case Mode::kTag:
-      index_expand_tiled_kernel<Mode::kTag><<<grid, kTileThreads, smem_expand, stream>>>(a);
+      index_expand_tiled_kernel<Mode::kTag><<<grid, kTileThreads, smem_expand, stream>>>(a), note_launch();
       break;
     case Mode::kThrottle:
-      index_expand_tiled_kernel<Mode::kThrottle><<<grid, kTileThreads, smem_expand, stream>>>(a);
+      index_expand_tiled_kernel<Mode::kThrottle><<<grid, kTileThreads, smem_expand, stream>>>(a), note_launch();
       break;
   }
   BRT_LAUNCH_CHECK("index_expand_tiled_kernel");
@@ -1069,34 +1297,34 @@ int launch_scan(Mode mode, const Tiling& tl, const Scratch& sc, const int32_t* m
   BRT_CUDA_TRY(cudaMemsetAsync(sc.flags, 0, 256, stream));
   const dim3 grid((unsigned)tl.num_tiles, (unsigned)tl.col_chunks);
   mask_pack_kernel<V><<<grid, kThreads, 0, stream>>>(mask, sc.bits, sc.tile_sums, sc.flags,
-                                                     cell_num, path_num, tl.cgb, tl.slices);
+                                                     cell_num, path_num, tl.cgb, tl.slices), note_launch();
   BRT_LAUNCH_CHECK("mask_pack_kernel");
   const unsigned scan_grid = (unsigned)((path_num + 31) / 32);
   if (mode == Mode::kThrottle) {
     tile_scan_kernel<true><<<scan_grid, 1024, 0, stream>>>(
-        sc.tile_sums, tl.num_tiles, path_num, nullptr, nullptr, 0, 0, 0, prefix, threshold);
+        sc.tile_sums, tl.num_tiles, path_num, nullptr, nullptr, 0, 0, 0, prefix, threshold), note_launch();
   } else {
     tile_scan_kernel<false><<<scan_grid, 1024, 0, stream>>>(
         sc.tile_sums, tl.num_tiles, path_num, loads, caps, ncap, capacity_padding, path_wise,
-        nullptr, nullptr);
+        nullptr, nullptr), note_launch();
   }
   BRT_LAUNCH_CHECK("tile_scan_kernel");
   switch (mode) {
     case Mode::kSeat:
       index_expand_kernel<V, Mode::kSeat><<<grid, kThreads, 0, stream>>>(
           mask, sc.bits, sc.tile_sums, sc.flags, out, nullptr, cell_num, path_num, tl.cgb,
-          tl.slices);
+          tl.slices), note_launch();
       break;
     case Mode::kTag:
       BRT_CUDA_TRY(cudaMemsetAsync(out, 0, (size_t)cell_num * path_num * 4, stream));
       index_expand_kernel<V, Mode::kTag><<<grid, kThreads, 0, stream>>>(
           mask, sc.bits, sc.tile_sums, sc.flags, out, nullptr, cell_num, path_num, tl.cgb,
-          tl.slices);
+          tl.slices), note_launch();
       break;
     case Mode::kThrottle:
       index_expand_kernel<V, Mode::kThrottle><<<grid, kThreads, 0, stream>>>(
           mask, sc.bits, sc.tile_sums, sc.flags, out, threshold, cell_num, path_num, tl.cgb,
-          tl.slices);
+          tl.slices), note_launch();
       break;
   }
   BRT_LAUNCH_CHECK("index_expand_kernel");
@@ -1241,10 +1469,10 @@ BRT_API int brt_convert_index_format(const int32_t* origin_indices, int32_t* new
   if (tag_to_seat) {
     BRT_REQUIRE(loads != nullptr, "loads is null");
     tag_to_seat_kernel<<<(unsigned)blocks, kThreads, 0, st>>>(origin_indices, new_indices, loads,
-                                                              cell_num, path_num);
+                                                              cell_num, path_num), note_launch();
   } else {
     seat_to_tag_kernel<<<(unsigned)blocks, kThreads, 0, st>>>(origin_indices, new_indices,
-                                                              cell_num, path_num);
+                                                              cell_num, path_num), note_launch();
   }
   BRT_LAUNCH_CHECK("convert_index_format");
   return BRT_OK;

@@ -99,7 +99,7 @@ int launch_match(const int32_t* loads, int group_size, int world_size, int32_t* 
               "null pointer argument");
   BRT_REQUIRE(loads != reordered_loads, "reordered_loads must not alias loads");
   rank_match_kernel<<<1, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      loads, group_size, world_size, reorder_indices, reordered_loads);
+      loads, group_size, world_size, reorder_indices, reordered_loads), note_launch();
   BRT_LAUNCH_CHECK("rank_match_kernel");
   return BRT_OK;
 }

@@ -261,7 +261,8 @@ template <int IV, int GK, int DT, bool kStorePath>
 __device__ __forceinline__ int build_routes(const MoveArgs& a, int64_t cell,
                                             const int (&first_seat)[IV],
                                             const float (&first_gate)[IV], const int* s_loads,
-                                            const int* s_base, RouteSlot* slots, int lane) {
+                                            const int* s_base, RouteSlot* slots, int lane,
+                                            int max_slots = kMaxRoutes) {
   const int E = a.path_num;
   const int chunks = (E + 32 * IV - 1) / (32 * IV);
   int count = 0;
@@ -293,7 +294,7 @@ __device__ __forceinline__ int build_routes(const MoveArgs& a, int64_t cell,
           const int e = (c * 32 + l) * IV + j;
           const int seat_b = __shfl_sync(0xffffffffu, seat[j], l);
           const float g = __shfl_sync(0xffffffffu, gate[j], l);
-          if (count < kMaxRoutes && lane == 0) {
+          if (count < max_slots && lane == 0) {
             slots[count].row = s_base[e] + seat_b - 1;
             slots[count].gate = kStorePath ? __int_as_float(e) : g;
           }
@@ -417,7 +418,9 @@ __global__ void __launch_bounds__(kThreads, 4) dispatch_seat_kernel(const MoveAr
   }
 }
 
-// Writes zeros to every row (and tag) the move pass did not mark.
+// Writes zeros to every row (and tag) the move pass did not mark.  A warp owns the items
+// (row, 2 KB piece) warp, warp + warps, ...; its lanes fetch the marks of the next 32 of
+// them with one load, so a fully occupied output costs one mark latency per 32 items.
 template <int VB>
 __global__ void __launch_bounds__(kThreads) dispatch_zero_fill_kernel(const MoveArgs a) {
   using V = typename Chunk<VB>::type;
@@ -431,18 +434,28 @@ __global__ void __launch_bounds__(kThreads) dispatch_zero_fill_kernel(const Move
   const ItemStep step = step_of(warps, a.pieces_per_row);
   ItemCursor at = cursor_at(warp < items ? warp : 0, a.pieces_per_row);
   if (warp >= items) at.cell = a.total_rows;
-  for (; at.cell < a.total_rows; at = advance(at, step)) {
-    const int64_t row = at.cell;
-    const int piece = at.piece;
-    if (a.row_marks[row] != 0) continue;
-    V* dp = dst + row * a.row_vecs;
-    const int64_t v0 = (int64_t)piece * kPieceVecs + lane;
-#pragma unroll
-    for (int u = 0; u < kUnroll; u++) {
-      const int64_t v = v0 + u * 32;
-      if (v < a.row_vecs) store_stream(dp + v, zero);
+  for (int64_t first = warp; first < items; first += 32 * warps) {
+    // lane l looks at item first + l * warps
+    const int64_t mine = first + (int64_t)lane * warps;
+    const bool empty = mine < items && a.row_marks[mine / a.pieces_per_row] == 0;
+    const unsigned todo = __ballot_sync(0xffffffffu, empty);
+    if (todo == 0) {  // nothing to fill among these 32 items: skip them in one step
+      const int64_t next = first + 32 * warps;
+      if (next < items) at = cursor_at(next, a.pieces_per_row);
+      continue;
     }
-    if (piece == 0 && lane == 0 && a.new_tags != nullptr) a.new_tags[row] = 0;
+    for (int k = 0; k < 32 && at.cell < a.total_rows; k++, at = advance(at, step)) {
+      if (!((todo >> k) & 1u)) continue;
+      const int64_t row = at.cell;
+      V* dp = dst + row * a.row_vecs;
+      const int64_t v0 = (int64_t)at.piece * kPieceVecs + lane;
+#pragma unroll
+      for (int u = 0; u < kUnroll; u++) {
+        const int64_t v = v0 + u * 32;
+        if (v < a.row_vecs) store_stream(dp + v, zero);
+      }
+      if (at.piece == 0 && lane == 0 && a.new_tags != nullptr) a.new_tags[row] = 0;
+    }
   }
 }
 
@@ -519,18 +532,6 @@ __global__ void __launch_bounds__(kThreads) dispatch_tag_kernel(const MoveArgs a
 }
 
 // ---------------------------------------------------------------------------------- combine
-__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
-  const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem_src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() {
-  asm volatile("cp.async.commit_group;\n" ::: "memory");
-}
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
-}
-
 template <int VB, int DT, int GMODE>
 __device__ __forceinline__ void fold_chunk(float (&acc)[Lanes<VB, DT>::N],
                                            const typename Chunk<VB>::type& row, float g) {
@@ -684,6 +685,146 @@ __global__ void __launch_bounds__(kThreads, 3) combine_seat_async_kernel(const M
   cp_async_wait<0>();
 }
 
+// ---------------------------------------------------------------------------------- dispatch (async)
+constexpr int kCopyRoutes = 4;  // destinations per dispatch item kept in the route table
+
+// Per-warp staging area of the pipelined dispatch: one 2 KB source piece and its routes.
+struct alignas(16) CopyStage {
+  uint4 row[kPieceVecs];
+  RouteSlot route[kCopyRoutes];
+  int count;
+  int pad[3];
+};
+
+// 1-D seat-index dispatch of 16-byte rows.  Same ownership as dispatch_seat_kernel (a warp
+// owns a (cell, 2 KB piece)), but the piece travels through shared memory: the asynchronous
+// copy of the warp's NEXT item is in flight while the current one is stored to its routes,
+// and cells that no path kept are never read.
+template <int DT, bool WEIGHTED, int IV>
+__global__ void __launch_bounds__(kThreads, WEIGHTED ? 3 : 4) dispatch_seat_async_kernel(const MoveArgs a) {
+  constexpr int VB = 16;
+  constexpr int GK = WEIGHTED ? 2 : 0;
+  using V = uint4;
+  extern __shared__ __align__(16) unsigned char s_raw[];
+  CopyStage* s_stage = reinterpret_cast<CopyStage*>(s_raw);  // [kWarps][kStages]
+  int* s_loads = reinterpret_cast<int*>(s_raw + sizeof(CopyStage) * kWarps * kStages);
+  int* s_base = s_loads + a.path_num;
+  setup_paths(a.loads, a.path_num, a.max_path_load, s_loads, s_base);
+
+  const int lane = threadIdx.x & 31;
+  const int warp_in_cta = threadIdx.x >> 5;
+  const int64_t warp = (int64_t)blockIdx.x * kWarps + warp_in_cta;
+  const int64_t warps = (int64_t)gridDim.x * kWarps;
+  const int64_t items = a.cell_num * a.pieces_per_row;
+  const V* __restrict__ src = static_cast<const V*>(a.src);
+  V* __restrict__ dst = static_cast<V*>(a.dst);
+  const int E = a.path_num;
+  CopyStage* my = s_stage + warp_in_cta * kStages;
+
+  int seat[IV];
+  float gate[IV];
+  auto fetch = [&](const ItemCursor& c) {
+#pragma unroll
+    for (int j = 0; j < IV; j++) { seat[j] = 0; gate[j] = 1.f; }
+    if (c.cell < a.cell_num) {
+      load_index_chunk<IV>(a.indices, c.cell, E, 0, lane, seat);
+      load_gate_chunk<IV, GK, DT>(a.gates, c.cell, E, 0, lane, gate);
+    }
+  };
+  auto issue = [&](CopyStage& st, const ItemCursor& c) {
+    if (c.cell < a.cell_num) {
+      const int count = build_routes<IV, GK, DT, false>(a, c.cell, seat, gate, s_loads, s_base,
+                                                        st.route, lane, kCopyRoutes);
+      if (lane == 0) st.count = count;
+      if (count > 0) {
+        const int64_t first = (int64_t)c.piece * kPieceVecs;
+        const V* sp = src + c.cell * a.row_vecs + first;
+#pragma unroll
+        for (int u = 0; u < kCopyUnroll; u++) {
+          const int v = u * 32 + lane;
+          if (first + v < a.row_vecs) cp_async_16(&st.row[v], sp + v);
+        }
+      }
+    }
+    cp_async_commit();
+  };
+
+  const ItemStep step = step_of(warps, a.pieces_per_row);
+  ItemCursor at = cursor_at(warp < items ? warp : 0, a.pieces_per_row);
+  if (warp >= items) at.cell = a.cell_num;
+  ItemCursor ahead = advance(at, step);
+  ItemCursor ahead2 = advance(ahead, step);
+  int stage = 0;
+  fetch(at);
+  issue(my[0], at);
+  fetch(ahead);
+  while (at.cell < a.cell_num) {
+    issue(my[stage ^ 1], ahead);
+    fetch(ahead2);
+    cp_async_wait<1>();
+    __syncwarp();
+
+    const CopyStage& st = my[stage];
+    const int64_t cell = at.cell;
+    const int64_t first = (int64_t)at.piece * kPieceVecs;
+    const int count = st.count;
+    if (count > 0) {
+      const bool full = first + kPieceVecs <= a.row_vecs;
+      V regs[kCopyUnroll];
+#pragma unroll
+      for (int u = 0; u < kCopyUnroll; u++) regs[u] = st.row[u * 32 + lane];
+      const int staged = count < kCopyRoutes ? count : kCopyRoutes;
+      for (int r = 0; r < staged; r++) {
+        const RouteSlot slot = st.route[r];
+        V* dp = dst + (int64_t)slot.row * a.row_vecs + first + lane;
+#pragma unroll
+        for (int u = 0; u < kCopyUnroll; u++) {
+          if (!full && first + u * 32 + lane >= a.row_vecs) continue;
+          if constexpr (WEIGHTED)
+            store_stream(dp + u * 32, scale_chunk<VB, DT>(regs[u], slot.gate));
+          else
+            store_stream(dp + u * 32, regs[u]);
+        }
+        if (at.piece == 0 && lane == 0) {
+          a.row_marks[slot.row] = 1;
+          if (a.new_tags != nullptr) a.new_tags[slot.row] = a.old_tags[cell];
+        }
+      }
+      if (count > kCopyRoutes) {
+        // more routes than the table holds: walk the index row for the rest (warp-uniform)
+        int seen = 0;
+        for (int e = 0; e < E; e++) {
+          const int s = a.indices[cell * E + e];
+          if (s <= 0 || s > s_loads[e]) continue;
+          if (seen++ < kCopyRoutes) continue;
+          const int64_t row = (int64_t)s_base[e] + s - 1;
+          float g = 1.f;
+          if constexpr (WEIGHTED) g = gate_at<DT, 2>(a.gates, cell * E + e);
+          V* dp = dst + row * a.row_vecs + first + lane;
+#pragma unroll
+          for (int u = 0; u < kCopyUnroll; u++) {
+            if (!full && first + u * 32 + lane >= a.row_vecs) continue;
+            if constexpr (WEIGHTED)
+              store_stream(dp + u * 32, scale_chunk<VB, DT>(regs[u], g));
+            else
+              store_stream(dp + u * 32, regs[u]);
+          }
+          if (at.piece == 0 && lane == 0) {
+            a.row_marks[row] = 1;
+            if (a.new_tags != nullptr) a.new_tags[row] = a.old_tags[cell];
+          }
+        }
+      }
+    }
+    __syncwarp();
+    at = ahead;
+    ahead = ahead2;
+    ahead2 = advance(ahead2, step);
+    stage ^= 1;
+  }
+  cp_async_wait<0>();
+}
+
 // Register-only combine for rows that cannot be moved 16 bytes at a time.
 template <int VB, int DT, int GMODE>
 __global__ void __launch_bounds__(kThreads) combine_seat_kernel(const MoveArgs a) {
@@ -781,18 +922,43 @@ bool wide_rows(const int* indices, const void* gates, int gate_elem_bytes, int p
   return true;
 }
 
+// Opt a kernel into more than 48 KB of dynamic shared memory (once per kernel and device).
+template <void (*kKernel)(const MoveArgs)>
+void configure_smem(size_t stage_bytes) {
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || configured_device == dev) return;
+  cudaFuncSetAttribute(kKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                       (int)(stage_bytes + (size_t)kMaxPaths * 2 * sizeof(int)));
+  configured_device = dev;
+}
+
 template <int VB, int DT, bool WEIGHTED, bool IS_1D>
 void launch_dispatch(const MoveArgs& a, bool is_tag, cudaStream_t st) {
   const size_t smem = (size_t)a.path_num * 2 * sizeof(int);
   if (is_tag) {
     dispatch_tag_kernel<VB, DT, WEIGHTED, IS_1D>
-        <<<grid_for_items(a.total_rows * a.pieces_per_row), kThreads, smem, st>>>(a);
+        <<<grid_for_items(a.total_rows * a.pieces_per_row), kThreads, smem, st>>>(a), note_launch();
+  } else if (VB == 16 && IS_1D) {
+    if constexpr (VB == 16 && IS_1D) {
+      const size_t smem_async = sizeof(CopyStage) * kWarps * kStages + smem;
+      const unsigned grid = grid_for_resident(a.cell_num * a.pieces_per_row, WEIGHTED ? 3 : 4);
+      if (wide_rows(a.indices, a.gates, dtype_size(DT), a.path_num)) {
+        configure_smem<dispatch_seat_async_kernel<DT, WEIGHTED, 4>>(sizeof(CopyStage) * kWarps *
+                                                                    kStages);
+        dispatch_seat_async_kernel<DT, WEIGHTED, 4><<<grid, kThreads, smem_async, st>>>(a), note_launch();
+      } else {
+        configure_smem<dispatch_seat_async_kernel<DT, WEIGHTED, 1>>(sizeof(CopyStage) * kWarps *
+                                                                    kStages);
+        dispatch_seat_async_kernel<DT, WEIGHTED, 1><<<grid, kThreads, smem_async, st>>>(a), note_launch();
+      }
+    }
   } else if (wide_rows(a.indices, a.gates, dtype_size(DT), a.path_num)) {
     dispatch_seat_kernel<VB, DT, WEIGHTED, IS_1D, 4>
-        <<<grid_for_items(a.cell_num * a.pieces_per_row), kThreads, smem, st>>>(a);
+        <<<grid_for_items(a.cell_num * a.pieces_per_row), kThreads, smem, st>>>(a), note_launch();
   } else {
     dispatch_seat_kernel<VB, DT, WEIGHTED, IS_1D, 1>
-        <<<grid_for_items(a.cell_num * a.pieces_per_row), kThreads, smem, st>>>(a);
+        <<<grid_for_items(a.cell_num * a.pieces_per_row), kThreads, smem, st>>>(a), note_launch();
   }
 }
 
@@ -824,7 +990,7 @@ int dispatch_by_flags(const MoveArgs& a, int dtype, bool weighted, bool is_1d, b
 template <int VB>
 void launch_zero_fill(const MoveArgs& a, cudaStream_t st) {
   dispatch_zero_fill_kernel<VB>
-      <<<grid_for_items(a.total_rows * a.pieces_per_row), kThreads, 0, st>>>(a);
+      <<<grid_for_items(a.total_rows * a.pieces_per_row), kThreads, 0, st>>>(a), note_launch();
 }
 
 template <int DT, int GMODE, int IV>
@@ -841,7 +1007,7 @@ int launch_combine_async(const MoveArgs& a, cudaStream_t st) {
     configured_device = dev;
   }
   combine_seat_async_kernel<DT, GMODE, IV>
-      <<<grid_for_resident(a.cell_num * a.pieces_per_row, 3), kThreads, smem, st>>>(a);
+      <<<grid_for_resident(a.cell_num * a.pieces_per_row, 3), kThreads, smem, st>>>(a), note_launch();
   return BRT_OK;
 }
 
@@ -855,7 +1021,7 @@ int launch_combine(const MoveArgs& a, cudaStream_t st) {
   } else {
     const size_t smem = (size_t)a.path_num * 2 * sizeof(int);
     combine_seat_kernel<VB, DT, GMODE>
-        <<<grid_for_items(a.cell_num * a.pieces_per_row), kThreads, smem, st>>>(a);
+        <<<grid_for_items(a.cell_num * a.pieces_per_row), kThreads, smem, st>>>(a), note_launch();
     return BRT_OK;
   }
 }

@@ -1,6 +1,7 @@
 // Error reporting and device queries shared by every entry point of the C ABI.
 #include "common.cuh"
 
+#include <atomic>
 #include <cstring>
 
 namespace brt_b200 {
@@ -9,6 +10,12 @@ char* error_buffer() {
   static thread_local char buf[1024] = {0};
   return buf;
 }
+
+static std::atomic<uint64_t> g_launches{0};
+
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+uint64_t launch_count() { return g_launches.load(std::memory_order_relaxed); }
 
 void clear_error() { error_buffer()[0] = '\0'; }
 
@@ -42,5 +49,7 @@ extern "C" {
 BRT_API int brt_abi_version(void) { return 1; }
 
 BRT_API const char* brt_last_error(void) { return brt_b200::error_buffer(); }
+
+BRT_API uint64_t brt_kernel_launch_count(void) { return brt_b200::launch_count(); }
 
 }  // extern "C"

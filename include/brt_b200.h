@@ -52,6 +52,9 @@ typedef enum brt_dtype { BRT_F32 = 0, BRT_F16 = 1, BRT_BF16 = 2 } brt_dtype;
 BRT_API int brt_abi_version(void);
 /* Message of the last failing call made by this thread ("" if none). */
 BRT_API const char* brt_last_error(void);
+/* Kernels this library has launched in the process so far (all threads, all devices).
+ * Instrumentation for benchmarks; the reference has no counterpart. */
+BRT_API uint64_t brt_kernel_launch_count(void);
 
 /* ------------------------------------------------------------------ router: indices */
 

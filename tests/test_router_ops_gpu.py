@@ -40,17 +40,28 @@ def rand_mask(rng, T, E, k):
     return oracle.topk_hot_mask(rng.standard_normal((T, E)).astype(np.float32), k)
 
 
+@pytest.fixture(params=["auto", "split"])
+def index_path(request, monkeypatch):
+    """Runs a test once with the library's own choice of index kernels (one chained launch
+    whenever it fits) and once with the three-launch variant forced."""
+    if request.param == "split":
+        monkeypatch.setenv("BRT_INDEX_PATH", "split")
+    else:
+        monkeypatch.delenv("BRT_INDEX_PATH", raising=False)
+    return request.param
+
+
 INDEX_CASES = [
     # T, E, k
     (16, 4, 2), (1, 1, 1), (31, 2, 1), (33, 3, 2), (1037, 5, 2), (4096, 8, 1), (512, 16, 4),
     (4096, 16, 4), (777, 12, 3), (2048, 32, 2), (1500, 64, 2), (3000, 128, 1), (260, 260, 3),
-    (70, 1028, 5), (100000, 8, 1),
+    (70, 1028, 5), (100000, 8, 1), (300000, 128, 2), (150000, 32, 2), (9000, 512, 2),
 ]
 
 
 @pytest.mark.parametrize("T,E,k", INDEX_CASES)
 @pytest.mark.parametrize("tag", [False, True])
-def test_generate_indices(R, T, E, k, tag):
+def test_generate_indices(R, T, E, k, tag, index_path):
     rng = np.random.default_rng(T * 131 + E)
     mask = rand_mask(rng, T, E, k)
     exp_i, exp_l = oracle.generate_indices_and_loads(mask, is_tag_index=tag)
@@ -67,7 +78,7 @@ def test_generate_indices(R, T, E, k, tag):
     ([2, 4, 8, 16, 32, 64, 128, 256], True, True),
     ([2, 4, 8, 16, 32, 64, 128, 256], False, True),
 ])
-def test_generate_indices_capacities(R, caps, cpad, pwise):
+def test_generate_indices_capacities(R, caps, cpad, pwise, index_path):
     rng = np.random.default_rng(len(caps) * 7 + cpad)
     mask = rand_mask(rng, 600, 8, 3)
     mask[:, 5] = 0  # an empty path
@@ -103,7 +114,7 @@ def test_generate_indices_errors_and_empty(R):
                                      None, True)
 
 
-def test_generate_indices_general_integers(R):
+def test_generate_indices_general_integers(R, index_path):
     """Masks holding values other than 0/1 follow index = running sum * value
     (src/router/location.cu:176-178)."""
     rng = np.random.default_rng(5)
@@ -116,6 +127,14 @@ def test_generate_indices_general_integers(R):
     exp_i, exp_l = oracle.generate_indices_and_loads(mask)
     got_i, got_l = R.generate_indices_and_loads(dev(mask))
     assert np.array_equal(host(got_i), exp_i) and np.array_equal(host(got_l), exp_l)
+    # many tiles per CTA, a few non-binary values in only some of them
+    mask = rand_mask(rng, 60000, 16, 2)
+    mask[rng.integers(0, 60000, size=40), rng.integers(0, 16, size=40)] = 3
+    mask[41000, 3] = -2
+    exp_i, exp_l = oracle.generate_indices_and_loads(mask)
+    got_i, got_l = R.generate_indices_and_loads(dev(mask))
+    assert np.array_equal(host(got_l), exp_l)
+    assert np.array_equal(host(got_i), exp_i)
 
 
 def test_generate_indices_unaligned_view(R):
@@ -143,8 +162,8 @@ def test_throttle_golden(R, golden_dir):
 
 
 @pytest.mark.parametrize("T,E,k", [(16, 4, 2), (1037, 5, 2), (5000, 32, 2), (3000, 128, 1),
-                                   (40000, 8, 2)])
-def test_throttle(R, T, E, k):
+                                   (40000, 8, 2), (200000, 64, 2)])
+def test_throttle(R, T, E, k, index_path):
     rng = np.random.default_rng(T + E)
     mask = rand_mask(rng, T, E, k)
     prefix = rng.integers(0, 20, size=E).astype(np.int32)
