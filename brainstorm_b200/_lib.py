@@ -57,8 +57,12 @@ SIGNATURES = {
     "brt_p2p_free": (_int, [_vp]),
     "brt_p2p_push": (_int, [_vp, _int, _vp, _vp, _vp, _int, _int, ctypes.c_uint64, _vp, _vp,
                             _vp]),
+    "brt_p2p_push_buckets": (_int, [_vp, _vp, _int, _int, _int, _i64, _i64, _vp, _i64, _int, _int,
+                                    ctypes.c_uint64, _vp, _vp, _vp]),
     "brt_p2p_post": (_int, [_vp, _int, _int, _int, ctypes.c_uint64, _vp, _vp, _vp]),
-    "brt_p2p_wait": (_int, [_vp, _int, ctypes.c_uint64, _vp, _vp]),
+    "brt_p2p_exchange_sizes": (_int, [_vp, _int, _int, _int, ctypes.c_uint64, _vp, _vp, _vp, _vp,
+                                      _vp, _vp, _vp]),
+    "brt_p2p_wait": (_int, [_vp, _int, _int, ctypes.c_uint64, _vp, _vp]),
 }
 
 

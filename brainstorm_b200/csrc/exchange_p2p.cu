@@ -43,6 +43,7 @@ struct SignalList {
 };
 
 constexpr long long kChunkBytes = 32768;
+constexpr int kWays = 32;  // interleaved runs of the copy list (>= any world size)
 
 __device__ __forceinline__ void store_release_sys(unsigned long long* p, unsigned long long v) {
   asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
@@ -56,26 +57,34 @@ __device__ __forceinline__ unsigned long long load_acquire_sys(const unsigned lo
 __global__ void __launch_bounds__(kThreads)
 p2p_push_kernel(const char* __restrict__ src, const __grid_constant__ CopyList list,
                 const __grid_constant__ SignalList sig) {
+  // Chunks are visited in kWays interleaved runs of the list, so that at any moment the grid
+  // is writing to every destination of the list at once (all links and the local copy busy)
+  // rather than finishing one destination before it starts the next.
   const long long total_chunks = list.first_chunk[list.count];
-  for (long long chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
-    // which copy does this chunk belong to (count <= 96: linear scan from a hint is cheap)
-    int c = 0;
-    while (c + 1 < list.count && list.first_chunk[c + 1] <= chunk) c++;
+  const long long run = (total_chunks + kWays - 1) / kWays;
+  for (long long k = blockIdx.x; k < run * kWays; k += gridDim.x) {
+    const long long chunk = (k % kWays) * run + k / kWays;
+    if (chunk >= total_chunks) continue;
+    int lo = 0, hi = list.count - 1;  // last copy whose first chunk is <= chunk
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (list.first_chunk[mid] <= chunk) lo = mid; else hi = mid - 1;
+    }
+    const int c = lo;
     const long long at = (chunk - list.first_chunk[c]) * kChunkBytes;
     long long n = list.bytes[c] - at;
     if (n > kChunkBytes) n = kChunkBytes;
     const uint4* s = reinterpret_cast<const uint4*>(src + list.src_offset[c] + at);
     uint4* d = reinterpret_cast<uint4*>(list.dst[c] + at);
     const int vecs = (int)(n >> 4);
-    for (int v = threadIdx.x; v < vecs; v += kThreads * 4) {
-      uint4 r[4];
+    constexpr int kPer = (int)(kChunkBytes / 16 / kThreads);  // 8: the whole chunk in flight
+    uint4 r[kPer];
 #pragma unroll
-      for (int k = 0; k < 4; k++)
-        if (v + k * kThreads < vecs) r[k] = __ldcs(s + v + k * kThreads);
+    for (int i = 0; i < kPer; i++)
+      if (threadIdx.x + i * kThreads < vecs) r[i] = __ldcs(s + threadIdx.x + i * kThreads);
 #pragma unroll
-      for (int k = 0; k < 4; k++)
-        if (v + k * kThreads < vecs) d[v + k * kThreads] = r[k];
-    }
+    for (int i = 0; i < kPer; i++)
+      if (threadIdx.x + i * kThreads < vecs) d[threadIdx.x + i * kThreads] = r[i];
   }
   if (sig.world_size == 0) return;  // plain multi-range copy, nobody to tell
   // arrive: the last CTA to finish raises my flag at every rank
@@ -85,6 +94,119 @@ p2p_push_kernel(const char* __restrict__ src, const __grid_constant__ CopyList l
     const unsigned int prev = atomicAdd(sig.done_counter, 1u);
     if (prev == gridDim.x - 1) {
       *sig.done_counter = 0;  // ready for the next exchange (stream-ordered)
+      __threadfence_system();
+      for (int r = 0; r < sig.world_size; r++)
+        store_release_sys(sig.peer_flags[r] + sig.my_rank, sig.epoch);
+    }
+  }
+}
+
+// Device-planned push: the bucket sizes are still on the device (the host has not seen them
+// yet), so every CTA derives the copy list itself.  Bucket b = (destination rank i, local
+// expert j), b = i * group + j, holds sizes[b] rows of `grain` bytes.  The buckets bound for
+// rank i are packed back to back at plan.slot[i], the region of rank i's arena that belongs
+// to this rank, so no rank needs anybody else's sizes to place its data.  A destination whose
+// buckets would not fit its slot, or whose slot pointer is null (this rank itself), is left
+// out; the host takes the same decision from the gathered size matrix.
+constexpr int kMaxBuckets = 1024;
+
+struct BucketPlan {
+  int world_size;
+  int group_size;
+  long long grain;        // bytes per row, multiple of 16
+  long long stride_rows;  // source layout: 0 = packed, else bucket b starts at row b * stride
+  long long slot_bytes;
+  int expert_begin;  // only buckets whose local expert j is in [expert_begin, expert_end) move
+  int expert_end;
+  char* slot[kMaxRanks];
+};
+
+__global__ void __launch_bounds__(kThreads)
+p2p_push_buckets_kernel(const char* __restrict__ src, const int* __restrict__ sizes,
+                        const __grid_constant__ BucketPlan plan,
+                        const __grid_constant__ SignalList sig) {
+  __shared__ long long s_rows[kMaxBuckets + 1];   // exclusive prefix of the bucket rows
+  __shared__ long long s_first[kMaxBuckets + 1];  // exclusive prefix of the bucket chunks
+  __shared__ long long s_warp[kThreads / 32];
+  const int n = plan.world_size * plan.group_size;
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+
+  // two block-wide exclusive scans over strips of kThreads buckets
+  for (int pass = 0; pass < 2; pass++) {
+    long long carry = 0;
+    for (int b0 = 0; b0 < n; b0 += kThreads) {
+      const int b = b0 + threadIdx.x;
+      long long v = 0;
+      if (b < n) {
+        if (pass == 0) {
+          v = sizes[b] > 0 ? sizes[b] : 0;
+        } else {
+          const int i = b / plan.group_size;
+          const long long dest_rows = s_rows[(i + 1) * plan.group_size] - s_rows[i * plan.group_size];
+          const int j = b - i * plan.group_size;
+          const bool send = plan.slot[i] != nullptr && dest_rows * plan.grain <= plan.slot_bytes &&
+                            j >= plan.expert_begin && j < plan.expert_end;
+          const long long bytes = (s_rows[b + 1] - s_rows[b]) * plan.grain;
+          v = send ? (bytes + kChunkBytes - 1) / kChunkBytes : 0;
+        }
+      }
+      long long incl = v;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const long long up = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += up;
+      }
+      if (lane == 31) s_warp[warp] = incl;
+      __syncthreads();
+      long long before = carry;
+      for (int w = 0; w < warp; w++) before += s_warp[w];
+      long long strip = 0;
+      for (int w = 0; w < kThreads / 32; w++) strip += s_warp[w];
+      long long* out = pass == 0 ? s_rows : s_first;
+      if (b < n) out[b] = before + incl - v;
+      carry += strip;
+      __syncthreads();
+    }
+    if (threadIdx.x == 0) (pass == 0 ? s_rows : s_first)[n] = carry;
+    __syncthreads();
+  }
+
+  const long long total_chunks = s_first[n];
+  const long long run = (total_chunks + kWays - 1) / kWays;
+  for (long long k = blockIdx.x; k < run * kWays; k += gridDim.x) {
+    const long long chunk = (k % kWays) * run + k / kWays;
+    if (chunk >= total_chunks) continue;
+    int lo = 0, hi = n - 1;  // last bucket whose first chunk is <= chunk (empty ones skipped)
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (s_first[mid] <= chunk) lo = mid; else hi = mid - 1;
+    }
+    const int b = lo;
+    const int i = b / plan.group_size;
+    const long long at = (chunk - s_first[b]) * kChunkBytes;
+    long long bytes = (s_rows[b + 1] - s_rows[b]) * plan.grain - at;
+    if (bytes > kChunkBytes) bytes = kChunkBytes;
+    const long long src_row = plan.stride_rows ? (long long)b * plan.stride_rows : s_rows[b];
+    const long long dst_row = s_rows[b] - s_rows[i * plan.group_size];
+    const uint4* s = reinterpret_cast<const uint4*>(src + src_row * plan.grain + at);
+    uint4* d = reinterpret_cast<uint4*>(plan.slot[i] + dst_row * plan.grain + at);
+    const int vecs = (int)(bytes >> 4);
+    constexpr int kPer = (int)(kChunkBytes / 16 / kThreads);
+    uint4 r[kPer];
+#pragma unroll
+    for (int u = 0; u < kPer; u++)
+      if (threadIdx.x + u * kThreads < vecs) r[u] = __ldcs(s + threadIdx.x + u * kThreads);
+#pragma unroll
+    for (int u = 0; u < kPer; u++)
+      if (threadIdx.x + u * kThreads < vecs) d[threadIdx.x + u * kThreads] = r[u];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(sig.done_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *sig.done_counter = 0;
       __threadfence_system();
       for (int r = 0; r < sig.world_size; r++)
         store_release_sys(sig.peer_flags[r] + sig.my_rank, sig.epoch);
@@ -116,9 +238,10 @@ p2p_post_kernel(const int* __restrict__ values, const __grid_constant__ PostList
 }
 
 __global__ void p2p_wait_kernel(const unsigned long long* __restrict__ my_flags, int world_size,
-                                unsigned long long epoch, int* __restrict__ status) {
+                                int skip_rank, unsigned long long epoch,
+                                int* __restrict__ status) {
   const int r = threadIdx.x;
-  if (r >= world_size) return;
+  if (r >= world_size || r == skip_rank) return;
   unsigned long long start = 0;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
   unsigned int spins = 0;
@@ -227,6 +350,49 @@ BRT_API int brt_p2p_push(const void* src, int copy_count, const int64_t* src_off
   return BRT_OK;
 }
 
+BRT_API int brt_p2p_push_buckets(const void* src, const int32_t* sizes, int world_size,
+                                 int group_size, int my_rank, int64_t grain_bytes,
+                                 int64_t stride_rows, void* const* slot_ptrs, int64_t slot_bytes,
+                                 int expert_begin, int expert_end, uint64_t epoch,
+                                 void* const* peer_flag_arrays, void* my_done_counter,
+                                 void* stream) {
+  clear_error();
+  // src may be null for a rank that holds no rows (all its sizes are zero)
+  BRT_REQUIRE(sizes != nullptr && slot_ptrs != nullptr && peer_flag_arrays != nullptr &&
+                  my_done_counter != nullptr,
+              "null pointers");
+  BRT_REQUIRE(world_size >= 1 && world_size <= kMaxRanks && my_rank >= 0 && my_rank < world_size,
+              "bad rank %d of %d", my_rank, world_size);
+  BRT_REQUIRE(group_size >= 1 && (long long)world_size * group_size <= kMaxBuckets,
+              "at most %d buckets per device-planned push", kMaxBuckets);
+  BRT_REQUIRE(grain_bytes > 0 && grain_bytes % 16 == 0 && aligned_to(src, 16),
+              "rows must be 16-byte multiples and the source 16-byte aligned");
+  BRT_REQUIRE(stride_rows >= 0 && slot_bytes >= 0, "negative stride or slot size");
+  BucketPlan plan;
+  plan.world_size = world_size;
+  plan.group_size = group_size;
+  plan.grain = grain_bytes;
+  plan.stride_rows = stride_rows;
+  plan.slot_bytes = slot_bytes;
+  plan.expert_begin = expert_begin;
+  plan.expert_end = expert_end;
+  SignalList sig;
+  sig.world_size = world_size;
+  sig.my_rank = my_rank;
+  sig.epoch = epoch;
+  for (int r = 0; r < world_size; r++) {
+    BRT_REQUIRE(aligned_to(slot_ptrs[r], 16), "slot %d is not 16-byte aligned", r);
+    plan.slot[r] = static_cast<char*>(slot_ptrs[r]);
+    sig.peer_flags[r] = static_cast<unsigned long long*>(peer_flag_arrays[r]);
+  }
+  sig.done_counter = static_cast<unsigned int*>(my_done_counter);
+  p2p_push_buckets_kernel<<<(unsigned)(sm_count() * 4), kThreads, 0,
+                            static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const char*>(src), sizes, plan, sig), note_launch();
+  BRT_LAUNCH_CHECK("p2p_push_buckets_kernel");
+  return BRT_OK;
+}
+
 BRT_API int brt_p2p_post(const int32_t* values, int n, int world_size, int my_rank,
                          uint64_t epoch, void* const* peer_boards, void* const* peer_flag_arrays,
                          void* stream) {
@@ -249,13 +415,30 @@ BRT_API int brt_p2p_post(const int32_t* values, int n, int world_size, int my_ra
   return BRT_OK;
 }
 
-BRT_API int brt_p2p_wait(const void* my_flag_array, int world_size, uint64_t epoch,
-                         void* status_word, void* stream) {
+BRT_API int brt_p2p_exchange_sizes(const int32_t* values, int n, int world_size, int my_rank,
+                                   uint64_t epoch, void* const* peer_boards,
+                                   void* const* peer_flag_arrays, const void* my_flag_array,
+                                   const void* my_board, void* status_word, int32_t* host_out,
+                                   void* stream) {
+  if (int rc = brt_p2p_post(values, n, world_size, my_rank, epoch, peer_boards, peer_flag_arrays,
+                            stream))
+    return rc;
+  if (int rc = brt_p2p_wait(my_flag_array, world_size, -1, epoch, status_word, stream)) return rc;
+  BRT_REQUIRE(my_board != nullptr && host_out != nullptr, "null board or host buffer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BRT_CUDA_TRY(cudaMemcpyAsync(host_out, status_word, 4, cudaMemcpyDeviceToHost, st));
+  BRT_CUDA_TRY(cudaMemcpyAsync(host_out + 1, my_board, (size_t)world_size * n * 4,
+                               cudaMemcpyDeviceToHost, st));
+  return BRT_OK;
+}
+
+BRT_API int brt_p2p_wait(const void* my_flag_array, int world_size, int skip_rank,
+                         uint64_t epoch, void* status_word, void* stream) {
   clear_error();
   BRT_REQUIRE(my_flag_array != nullptr && status_word != nullptr, "null control pointers");
   BRT_REQUIRE(world_size >= 1 && world_size <= kMaxRanks, "bad world size %d", world_size);
   p2p_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const unsigned long long*>(my_flag_array), world_size, epoch,
+      static_cast<const unsigned long long*>(my_flag_array), world_size, skip_rank, epoch,
       static_cast<int*>(status_word)), note_launch();
   BRT_LAUNCH_CHECK("p2p_wait_kernel");
   return BRT_OK;

@@ -23,6 +23,10 @@ COUNTER_OFFSET = 512      # uint32
 STATUS_OFFSET = 1024      # int32, directly in front of the board so one copy reads both
 BOARD_OFFSET = 1028       # int32 [world][n]: bucket sizes posted by every rank
 BOARD_INTS = (CONTROL_BYTES - BOARD_OFFSET) // 4
+# The overlapped size exchange (sizes_begin / sizes_end) alternates between two boards, so a
+# rank that is already one exchange ahead cannot overwrite sizes that are still being read.
+BOARD2_OFFSET = 2048
+BOARD2_INTS = (CONTROL_BYTES - BOARD2_OFFSET) // 8
 
 
 class _DeviceBytes:
@@ -52,7 +56,8 @@ class PeerArena:
             p = ctypes.c_void_p()
             _lib.call("brt_p2p_open", buf, ctypes.byref(p))
             self.peer_base.append(p.value)
-        self.epoch = 0
+        self.epoch = 0        # value of the arrival flags: one per push
+        self.exchanges = 0    # exchanges begun: its parity selects the data half
         self.size_epoch = 0
         self._peer_base_np = np.array(self.peer_base, dtype=np.int64)
         self._size_flag_ptrs = (ctypes.c_void_p * world)(
@@ -61,13 +66,29 @@ class PeerArena:
         self._flag_ptrs = (ctypes.c_void_p * world)(*[b + FLAGS_OFFSET for b in self.peer_base])
         self._view = torch.as_tensor(_DeviceBytes(self.base, self.total), device="cuda")
         self.status = self._view[STATUS_OFFSET:STATUS_OFFSET + 4].view(torch.int32)
+        # overlapped size exchange: own stream, two boards, a pinned landing buffer
+        self.side = torch.cuda.Stream()
+        self._board2_ptrs = [
+            (ctypes.c_void_p * world)(*[b + BOARD2_OFFSET + 4 * k * BOARD2_INTS
+                                        for b in self.peer_base]) for k in range(2)]
+        self._pinned = torch.empty(1 + BOARD2_INTS, dtype=torch.int32).pin_memory()
+        self._pending = None
+        # per-source slots of the device-planned push: slot r of a half belongs to rank r
+        self.slot_bytes = (self.half_bytes // world) & ~255
+        self._slot_ptrs = [
+            (ctypes.c_void_p * world)(*[
+                None if r == rank else
+                self.peer_base[r] + self.half_offset(k) + rank * self.slot_bytes
+                for r in range(world)]) for k in range(2)]
 
-    def half_offset(self, epoch: int) -> int:
-        return CONTROL_BYTES + (epoch & 1) * self.half_bytes
+    def half_offset(self, exchange: int) -> int:
+        return CONTROL_BYTES + (exchange & 1) * self.half_bytes
 
-    def local_bytes(self, epoch: int, nbytes: int) -> torch.Tensor:
-        off = self.half_offset(epoch)
-        return self._view[off:off + nbytes]
+    def begin_exchange(self) -> int:
+        """Start a new exchange: all its pushes write the same data half.  Returns that
+        half's byte offset from the arena base."""
+        self.exchanges += 1
+        return self.half_offset(self.exchanges)
 
     def gather_sizes(self, sizes: torch.Tensor, stream: int) -> np.ndarray:
         """All ranks' int32 size vectors as a [world, n] host array (one device->host copy,
@@ -78,7 +99,7 @@ class PeerArena:
         self.size_epoch += 1
         _lib.call("brt_p2p_post", sizes.data_ptr(), n, self.world, self.rank, self.size_epoch,
                   self._board_ptrs, self._size_flag_ptrs, stream)
-        _lib.call("brt_p2p_wait", self.base + SIZE_FLAGS_OFFSET, self.world, self.size_epoch,
+        _lib.call("brt_p2p_wait", self.base + SIZE_FLAGS_OFFSET, self.world, -1, self.size_epoch,
                   self.base + STATUS_OFFSET, stream)
         words = self._view[STATUS_OFFSET:BOARD_OFFSET + 4 * self.world * n].view(torch.int32)
         host = words.cpu().numpy()
@@ -86,6 +107,56 @@ class PeerArena:
             raise RuntimeError("peer exchange timed out waiting for another rank "
                                "(brt_p2p_wait, 2 s limit)")
         return host[1:].reshape(self.world, n)
+
+    def fork_side(self) -> None:
+        """Order the side stream behind the work enqueued on the current stream so far."""
+        self.side.wait_stream(torch.cuda.current_stream())
+
+    def sizes_begin(self, sizes: torch.Tensor) -> None:
+        """Start the size exchange on the arena's side stream (call ``fork_side`` first, at
+        the point of the current stream the sizes depend on); work enqueued on the current
+        stream in the meantime overlaps it.  ``sizes_end`` returns the [world, n] host array."""
+        n = sizes.numel()
+        if self.world * n > BOARD2_INTS:
+            raise RuntimeError("size vector too long for the peer size board")
+        self.size_epoch += 1
+        k = self.size_epoch & 1
+        _lib.call("brt_p2p_exchange_sizes", sizes.data_ptr(), n, self.world, self.rank,
+                  self.size_epoch, self._board2_ptrs[k], self._size_flag_ptrs,
+                  self.base + SIZE_FLAGS_OFFSET, self.base + BOARD2_OFFSET + 4 * k * BOARD2_INTS,
+                  self.base + STATUS_OFFSET, self._pinned.data_ptr(), self.side.cuda_stream)
+        self._pending = (n, sizes)  # keeps the device vector alive until the copy is done
+
+    def sizes_end(self) -> np.ndarray:
+        n, _ = self._pending
+        self._pending = None
+        self.side.synchronize()
+        host = self._pinned[:1 + self.world * n].numpy().copy()
+        if host[0] != 0:
+            raise RuntimeError("peer exchange timed out waiting for another rank "
+                               "(brt_p2p_wait, 2 s limit)")
+        return host[1:].reshape(self.world, n)
+
+    def push_buckets(self, src: torch.Tensor, sizes: torch.Tensor, group_size: int,
+                     grain: int, stride_rows: int, expert_begin: int, expert_end: int,
+                     stream: int) -> int:
+        """Device-planned push (sizes stay on the device) of my remote buckets of the local
+        experts [expert_begin, expert_end) into my slot of every peer's current half; raises
+        my data flag everywhere.  Returns the flag epoch to wait for."""
+        self.epoch += 1
+        e = self.epoch
+        _lib.call("brt_p2p_push_buckets", src.data_ptr(), sizes.data_ptr(), self.world,
+                  group_size, self.rank, grain, stride_rows, self._slot_ptrs[self.exchanges & 1],
+                  self.slot_bytes, expert_begin, expert_end, e, self._flag_ptrs,
+                  self.base + COUNTER_OFFSET, stream)
+        return e
+
+    def wait_data(self, epoch: int, stream: int) -> None:
+        """Wait (bounded) on ``stream`` until every OTHER rank has raised data flag ``epoch``
+        in my arena.  My own pushes are ordered by the caller's stream dependencies, never by
+        a kernel that spins on a kernel of the same GPU."""
+        _lib.call("brt_p2p_wait", self.base + FLAGS_OFFSET, self.world, self.rank, epoch,
+                  self.base + STATUS_OFFSET, stream)
 
     @staticmethod
     def _i64(a) -> np.ndarray:
@@ -103,32 +174,32 @@ class PeerArena:
             _lib.call("brt_p2p_push", src_base, int(c.size), a.ctypes.data, b.ctypes.data,
                       c.ctypes.data, 0, 0, 0, None, None, stream)
 
-    def exchange(self, src: torch.Tensor, src_offsets, dst_ranks, dst_offsets, nbytes,
-                 stream: int, local_out: int = 0) -> int:
-        """Push byte ranges of ``src`` to ``dst_offsets`` inside the current half of the
-        destination ranks' arenas, signal, and wait for every rank's signal.  Ranges addressed
-        to this rank go straight to ``local_out + dst_offset`` when ``local_out`` is given.
-        Returns the epoch whose half now holds the data that peers sent to this rank."""
+    def push(self, src: torch.Tensor, src_offsets, dst_ptrs, nbytes, stream: int) -> int:
+        """Host-planned push of byte ranges of ``src`` to absolute addresses (see
+        ``peer_address``); raises my data flag everywhere.  Returns the flag epoch."""
         self.epoch += 1
         e = self.epoch
-        half = self.half_offset(e)
         nb = self._i64(nbytes)
-        ranks = self._i64(dst_ranks)
-        dp = self._peer_base_np[ranks] + half + self._i64(dst_offsets)
-        if local_out:
-            dp = np.where(ranks == self.rank, local_out + self._i64(dst_offsets), dp)
         keep = nb > 0
         so = np.ascontiguousarray(self._i64(src_offsets)[keep])
-        dp = np.ascontiguousarray(dp[keep])
+        dp = np.ascontiguousarray(self._i64(dst_ptrs)[keep])
         nb = np.ascontiguousarray(nb[keep])
         if nb.size > MAX_COPIES:
             raise RuntimeError("too many buckets for one peer push")
         _lib.call("brt_p2p_push", src.data_ptr(), int(nb.size), so.ctypes.data, dp.ctypes.data,
                   nb.ctypes.data, self.world, self.rank, e, self._flag_ptrs,
                   self.base + COUNTER_OFFSET, stream)
-        _lib.call("brt_p2p_wait", self.base + FLAGS_OFFSET, self.world, e,
-                  self.base + STATUS_OFFSET, stream)
         return e
+
+    def peer_address(self, ranks, offsets, local_out: int = 0) -> np.ndarray:
+        """Absolute addresses of ``offsets`` inside the current half of ``ranks``' arenas;
+        ranges addressed to this rank go to ``local_out + offset`` when that is given."""
+        ranks = self._i64(ranks)
+        offsets = self._i64(offsets)
+        dp = self._peer_base_np[ranks] + self.half_offset(self.exchanges) + offsets
+        if local_out:
+            dp = np.where(ranks == self.rank, local_out + offsets, dp)
+        return dp
 
 
 _arena: Optional[PeerArena] = None

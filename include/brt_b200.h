@@ -283,13 +283,33 @@ BRT_API int brt_group_sparse_all_to_all(const void* send_buffer, void* recv_buff
  *                 sized) and then stores `epoch` into slot `my_rank` of every rank's flag
  *                 array.  `my_done_counter` is a zero-initialised 4-byte word in local memory.
  *                 world_size == 0: no flag is raised (a plain multi-range copy).
+ * brt_p2p_push_buckets
+ *                 the same push planned on the device, for a sender whose bucket sizes are not
+ *                 on the host yet: `sizes` is the DEVICE vector of world_size * group_size
+ *                 row counts (bucket b = destination rank b / group_size), rows are
+ *                 `grain_bytes` long and bucket b starts at source row b * stride_rows
+ *                 (stride_rows == 0: buckets are packed).  The buckets of destination i are
+ *                 written back to back at slot_ptrs[i]; a destination whose slot pointer is
+ *                 null, or whose buckets exceed `slot_bytes`, is left out (the caller sees
+ *                 the same sizes later and moves that share another way).  Only buckets whose
+ *                 local expert index (b % group_size) lies in [expert_begin, expert_end) are
+ *                 moved, so that an exchange can be issued as a few pushes whose arrival is
+ *                 signalled one after the other; the packing inside a slot does not depend
+ *                 on that range.  At most 1024 buckets.  Raises the flags like brt_p2p_push.
  * brt_p2p_post    writes `n` int32 values (this rank's bucket sizes) into row `my_rank` of the
  *                 size board in every rank's arena and raises slot `my_rank` of the given flag
  *                 arrays; together with brt_p2p_wait this is the size exchange that precedes
  *                 a data exchange (the reference does it with an NCCL all-to-all,
  *                 src/backend/torch/distributed.cc:777-783).
- * brt_p2p_wait    enqueues a kernel that returns once every slot of `my_flag_array` holds a
- *                 value >= epoch.  The wait is bounded (2 s): on expiry it writes
+ * brt_p2p_exchange_sizes
+ *                 brt_p2p_post + brt_p2p_wait + an asynchronous copy of the status word
+ *                 (host_out[0]) and of this rank's board `my_board` (host_out[1 ..
+ *                 world_size * n]) into pinned host memory, all on `stream`: the whole size
+ *                 exchange in one call.  The caller synchronises the stream before reading.
+ * brt_p2p_wait    enqueues a kernel that returns once every slot of `my_flag_array` (except
+ *                 slot `skip_rank`, -1 for none) holds a value >= epoch.  A wait enqueued on
+ *                 another stream than this rank's own push passes its own rank as skip_rank,
+ *                 so that it only ever waits for kernels running on other GPUs.  The wait is bounded (2 s): on expiry it writes
  *                 BRT_ERR_TIMEOUT into `status_word` (a 4-byte device word the caller reads
  *                 back when convenient) and returns; it never blocks the GPU indefinitely.
  */
@@ -301,11 +321,22 @@ BRT_API int brt_p2p_push(const void* src, int copy_count, const int64_t* src_off
                          void* const* dst_ptrs, const int64_t* bytes, int world_size,
                          int my_rank, uint64_t epoch, void* const* peer_flag_arrays,
                          void* my_done_counter, void* stream);
+BRT_API int brt_p2p_push_buckets(const void* src, const int32_t* sizes, int world_size,
+                                 int group_size, int my_rank, int64_t grain_bytes,
+                                 int64_t stride_rows, void* const* slot_ptrs, int64_t slot_bytes,
+                                 int expert_begin, int expert_end, uint64_t epoch,
+                                 void* const* peer_flag_arrays, void* my_done_counter,
+                                 void* stream);
 BRT_API int brt_p2p_post(const int32_t* values, int n, int world_size, int my_rank,
                          uint64_t epoch, void* const* peer_boards, void* const* peer_flag_arrays,
                          void* stream);
-BRT_API int brt_p2p_wait(const void* my_flag_array, int world_size, uint64_t epoch,
-                         void* status_word, void* stream);
+BRT_API int brt_p2p_exchange_sizes(const int32_t* values, int n, int world_size, int my_rank,
+                                   uint64_t epoch, void* const* peer_boards,
+                                   void* const* peer_flag_arrays, const void* my_flag_array,
+                                   const void* my_board, void* status_word, int32_t* host_out,
+                                   void* stream);
+BRT_API int brt_p2p_wait(const void* my_flag_array, int world_size, int skip_rank,
+                         uint64_t epoch, void* status_word, void* stream);
 
 #ifdef __cplusplus
 }
