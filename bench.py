@@ -60,6 +60,15 @@ def capacity_of(w) -> int:
     return 0
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of each op's kernels, from the ncu
+# capture summarised in profiles/ncu_full_cfg2_routing_step_kernels.txt.  Dirty lines that
+# the 126 MB L2 still holds when a kernel ends are not in these counters, so the write-heavy
+# ops read below their algorithmic bytes.
+NCU_DRAM_TRAFFIC = {
+    "cfg2": {"throttle": 4.24e6, "indices": 4.24e6, "dispatch": 86.1e6, "combine": 110.3e6},
+}
+
+
 def make_workload(name: str, rank: int = 0, local_bias: float = 0.0, world: int = 1):
     """Host (CPU) tensors of one workload: activations, fp32 logits, softmax scores, top-k hot
     mask, combine gates.  Generated on CPU in fp32 so that the CPU checker and the GPU see the
@@ -349,7 +358,10 @@ def run_gpu(args):
         "dispatch_combine_only": {"tokens_per_s": world * T / (dc_ms * 1e-3), "ms": dc_ms},
         "roofline": {"bound": "hbm", "kernel": dominant,
                      "achieved": kernels[dominant]["achieved_gbs"], "peak": peak, "unit": "GB/s",
-                     "frac": kernels[dominant]["frac"], "traffic": None,
+                     "frac": kernels[dominant]["frac"],
+                     "traffic": NCU_DRAM_TRAFFIC.get(args.workload, {}).get(dominant),
+                     "traffic_note": "ncu DRAM counters of one launch; writes still held in "
+                                     "L2 at kernel end are not counted",
                      "peak_kind": f"{peak_kind} copy bandwidth",
                      "nominal_frac_of_8000": round(kernels[dominant]["achieved_gbs"] / 8000, 4)},
         "kernels": kernels,

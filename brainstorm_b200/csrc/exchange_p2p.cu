@@ -16,6 +16,8 @@
 // what makes a single arrive/wait per exchange sufficient: a peer can only start writing a
 // half again after I have signalled the exchange in between, and that signal is enqueued on
 // my stream behind my copy out of that half.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace brt_b200 {
@@ -263,6 +265,17 @@ __global__ void p2p_wait_kernel(const unsigned long long* __restrict__ my_flags,
 
 using namespace brt_b200;
 
+namespace {
+// CTAs per SM of the push kernels.  One per SM already saturates an NVLink direction (about
+// 655 GB/s measured at 1, 2, 4 and 8); two leave room for the copy-out kernels that run beside
+// a push on the side stream.  BRT_P2P_CTAS_PER_SM overrides it.
+int push_ctas_per_sm() {
+  const char* v = getenv("BRT_P2P_CTAS_PER_SM");
+  const int n = v != nullptr ? atoi(v) : 0;
+  return n >= 1 && n <= 8 ? n : 2;
+}
+}  // namespace
+
 extern "C" {
 
 BRT_API int brt_p2p_alloc(size_t bytes, void** dev_ptr, void* ipc_handle_out) {
@@ -341,7 +354,8 @@ BRT_API int brt_p2p_push(const void* src, int copy_count, const int64_t* src_off
     sig.peer_flags[r] = static_cast<unsigned long long*>(peer_flag_arrays[r]);
   sig.done_counter = static_cast<unsigned int*>(my_done_counter);
   long long grid = chunks;
-  const long long cap = (long long)sm_count() * 4;
+  // a flag-less call is a local copy, bound by HBM rather than by a link: fill the SMs
+  const long long cap = (long long)sm_count() * (world_size == 0 ? 8 : push_ctas_per_sm());
   if (grid > cap) grid = cap;
   if (grid < 1) grid = 1;
   p2p_push_kernel<<<(unsigned)grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
@@ -386,7 +400,7 @@ BRT_API int brt_p2p_push_buckets(const void* src, const int32_t* sizes, int worl
     sig.peer_flags[r] = static_cast<unsigned long long*>(peer_flag_arrays[r]);
   }
   sig.done_counter = static_cast<unsigned int*>(my_done_counter);
-  p2p_push_buckets_kernel<<<(unsigned)(sm_count() * 4), kThreads, 0,
+  p2p_push_buckets_kernel<<<(unsigned)(sm_count() * push_ctas_per_sm()), kThreads, 0,
                             static_cast<cudaStream_t>(stream)>>>(
       static_cast<const char*>(src), sizes, plan, sig), note_launch();
   BRT_LAUNCH_CHECK("p2p_push_buckets_kernel");
