@@ -60,12 +60,14 @@ def capacity_of(w) -> int:
     return 0
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of each op's kernels, from the ncu
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of each timed kernel, from the ncu
 # capture summarised in profiles/ncu_full_cfg2_routing_step_kernels.txt.  Dirty lines that
 # the 126 MB L2 still holds when a kernel ends are not in these counters, so the write-heavy
 # ops read below their algorithmic bytes.
-NCU_DRAM_TRAFFIC = {
-    "cfg2": {"throttle": 4.24e6, "indices": 4.24e6, "dispatch": 86.1e6, "combine": 110.3e6},
+NCU_DRAM_KERNEL_TRAFFIC = {
+    "cfg2": {"throttle_chain_kernel": 4.24e6, "index_chain_kernel": 4.24e6,
+             "dispatch_move_kernel": 84.5e6, "dispatch_zero_fill_kernel": 1.6e6,
+             "combine_kernel": 110.3e6},
 }
 
 
@@ -113,6 +115,9 @@ def algorithmic_bytes(w, idx: np.ndarray, loads: np.ndarray, total_rows: int):
         "indices": 8 * T * E + 4 * E,
         "dispatch": Tr * d * s + total_rows * d * s + 4 * T * E,
         "combine": R * d * s + T * d * s + 8 * T * E,
+        # the two kernels of a dispatch: rows moved to their routes, rows nobody landed on
+        "dispatch_move": Tr * d * s + R * d * s + 4 * T * E,
+        "dispatch_zero_fill": (total_rows - R) * d * s + total_rows,
         "R": R, "T_r": Tr, "L": total_rows,
     }
 
@@ -319,6 +324,24 @@ def run_gpu(args):
     clocks = sampler.stop() if rank == 0 else None
     eager_ms = e_start.elapsed_time(e_end) / args.steps
 
+    # Per-kernel device times: the library brackets each of its hot kernels with CUDA events
+    # on the launching stream while profiling is on (one more eager pass, same spin trick).
+    from brainstorm_b200 import _lib as brt_lib
+    import ctypes
+    brt_lib.query("brt_profile_enable", 1)
+    if not distributed:
+        try:
+            torch.cuda._sleep(int(60e6))
+        except Exception:
+            pass
+    for i in range(args.steps):
+        step()
+    barrier()
+    brt_lib.query("brt_profile_enable", 0)
+    report = ctypes.create_string_buffer(8192)
+    brt_lib.call("brt_profile_report", report, len(report))
+    timed = json.loads(report.value.decode())
+
     names = ["throttle", "indices", "dispatch", "a2a_forward", "a2a_backward", "combine"]
     op_ms = {n: statistics.mean(ev[i][j].elapsed_time(ev[i][j + 1]) for i in range(args.steps))
              for j, n in enumerate(names)}
@@ -336,8 +359,25 @@ def run_gpu(args):
             gbs = ab[n] / (op_ms[n] * 1e-3) / 1e9
             kernels[n] = {"ms": round(op_ms[n], 5), "algorithmic_bytes": ab[n],
                           "achieved_gbs": round(gbs, 1), "frac": round(gbs / peak, 4)}
-    dominant = max(kernels, key=lambda n: kernels[n]["ms"])
     dc_ms = op_ms["dispatch"] + op_ms["combine"]
+    # which algorithmic byte count belongs to which timed kernel
+    kernel_bytes = {"throttle_chain_kernel": ab["throttle"], "throttle_split_kernels": ab["throttle"],
+                    "index_chain_kernel": ab["indices"], "index_split_kernels": ab["indices"],
+                    "dispatch_move_kernel": ab["dispatch_move"],
+                    "dispatch_zero_fill_kernel": ab["dispatch_zero_fill"],
+                    "combine_kernel": ab["combine"]}
+    device_kernels = {}
+    for name, t in timed.items():
+        if name not in kernel_bytes or t["launches"] == 0:
+            continue
+        ms = t["total_ms"] / t["launches"]
+        gbs = kernel_bytes[name] / (ms * 1e-3) / 1e9 if ms > 0 else 0.0
+        device_kernels[name] = {"launches": t["launches"], "ms": round(ms, 5),
+                                "algorithmic_bytes": kernel_bytes[name],
+                                "achieved_gbs": round(gbs, 1), "frac": round(gbs / peak, 4)}
+    dominant = max(device_kernels, key=lambda n: device_kernels[n]["ms"])
+    dominant_op = {"dispatch_move_kernel": "dispatch", "dispatch_zero_fill_kernel": "dispatch",
+                   "combine_kernel": "combine"}.get(dominant, "indices")
 
     # ---- end to end through the router API with host buffers
     e2e = measure_e2e(wl, dev, args, ScatterRouter, GatherRouter, distributed, world)
@@ -357,13 +397,17 @@ def run_gpu(args):
                    "parallelism": f"ep{world}" if distributed else "single"},
         "dispatch_combine_only": {"tokens_per_s": world * T / (dc_ms * 1e-3), "ms": dc_ms},
         "roofline": {"bound": "hbm", "kernel": dominant,
-                     "achieved": kernels[dominant]["achieved_gbs"], "peak": peak, "unit": "GB/s",
-                     "frac": kernels[dominant]["frac"],
-                     "traffic": NCU_DRAM_TRAFFIC.get(args.workload, {}).get(dominant),
+                     "achieved": device_kernels[dominant]["achieved_gbs"], "peak": peak,
+                     "unit": "GB/s", "frac": device_kernels[dominant]["frac"],
+                     "traffic": NCU_DRAM_KERNEL_TRAFFIC.get(args.workload, {}).get(dominant),
                      "traffic_note": "ncu DRAM counters of one launch; writes still held in "
                                      "L2 at kernel end are not counted",
                      "peak_kind": f"{peak_kind} copy bandwidth",
-                     "nominal_frac_of_8000": round(kernels[dominant]["achieved_gbs"] / 8000, 4)},
+                     "timing": "CUDA events around each launch of the kernel, on its stream",
+                     "nominal_frac_of_8000":
+                         round(device_kernels[dominant]["achieved_gbs"] / 8000, 4),
+                     "whole_op": {"op": dominant_op, **kernels[dominant_op]}},
+        "device_kernels": device_kernels,
         "kernels": kernels,
         "routing": {"kept_routes": ab["R"], "cells_routed": ab["T_r"], "output_rows": ab["L"]},
         "gpu_launches": int(round(args.steps * launches_per_step)),

@@ -23,6 +23,8 @@ SIGNATURES = {
     "brt_abi_version": (_int, []),
     "brt_last_error": (ctypes.c_char_p, []),
     "brt_kernel_launch_count": (ctypes.c_uint64, []),
+    "brt_profile_enable": (None, [_int]),
+    "brt_profile_report": (_int, [_vp, _sz]),
     "brt_index_scratch_bytes": (_sz, [_i64, _int]),
     "brt_generate_indices_and_loads": (
         _int, [_vp, _vp, _vp, _i64, _int, _vp, _int, _int, _int, _int, _vp, _sz, _vp]),

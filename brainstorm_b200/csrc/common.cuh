@@ -23,6 +23,17 @@ void clear_error();
 // brt_kernel_launch_count()).
 void note_launch();
 
+// Optional per-kernel timing (off by default; brt_profile_enable).  While it is on, a
+// KernelTimer records a CUDA event on the launching stream before and after the launches it
+// brackets; brt_profile_report sums the elapsed times per name.  Never enable it while a
+// stream is being captured into a graph.
+struct KernelTimer {
+  KernelTimer(const char* name, cudaStream_t stream);
+  ~KernelTimer();
+  cudaStream_t stream_;
+  void* slot_;
+};
+
 // Number of SMs of the current device (cached per device).
 int sm_count();
 

@@ -1159,6 +1159,8 @@ int launch_chain_mode(const ChainArgs& c, unsigned grid, size_t smem, cudaStream
       configured[dev] = kChainSmemLimit;
     }
   }
+  const KernelTimer timer(MODE == Mode::kThrottle ? "throttle_chain_kernel" : "index_chain_kernel",
+                          stream);
   index_chain_kernel<MODE><<<grid, kTileThreads, smem, stream>>>(c), note_launch();
   BRT_LAUNCH_CHECK("index_chain_kernel");
   return BRT_OK;
@@ -1265,6 +1267,8 @@ int launch_tiled(Mode mode, const int32_t* mask, int32_t* out, int32_t* loads, i
   if (mode == Mode::kTag)
     BRT_CUDA_TRY(cudaMemsetAsync(out, 0, (size_t)cell_num * path_num * 4, stream));
 
+  const KernelTimer timer(mode == Mode::kThrottle ? "throttle_split_kernels" : "index_split_kernels",
+                          stream);
   mask_pack_tiled_kernel<<<grid, kTileThreads, smem_full, stream>>>(a), note_launch();
   BRT_LAUNCH_CHECK("mask_pack_tiled_kernel");
   const unsigned scan_grid = (unsigned)((path_num + 3) / 4);

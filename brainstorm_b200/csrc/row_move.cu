@@ -935,6 +935,7 @@ void configure_smem(size_t stage_bytes) {
 
 template <int VB, int DT, bool WEIGHTED, bool IS_1D>
 void launch_dispatch(const MoveArgs& a, bool is_tag, cudaStream_t st) {
+  const KernelTimer timer(is_tag ? "dispatch_tag_kernel" : "dispatch_move_kernel", st);
   const size_t smem = (size_t)a.path_num * 2 * sizeof(int);
   if (is_tag) {
     dispatch_tag_kernel<VB, DT, WEIGHTED, IS_1D>
@@ -989,6 +990,7 @@ int dispatch_by_flags(const MoveArgs& a, int dtype, bool weighted, bool is_1d, b
 
 template <int VB>
 void launch_zero_fill(const MoveArgs& a, cudaStream_t st) {
+  const KernelTimer timer("dispatch_zero_fill_kernel", st);
   dispatch_zero_fill_kernel<VB>
       <<<grid_for_items(a.total_rows * a.pieces_per_row), kThreads, 0, st>>>(a), note_launch();
 }
@@ -1006,6 +1008,7 @@ int launch_combine_async(const MoveArgs& a, cudaStream_t st) {
                                             (size_t)kMaxPaths * 2 * sizeof(int))));
     configured_device = dev;
   }
+  const KernelTimer timer("combine_kernel", st);
   combine_seat_async_kernel<DT, GMODE, IV>
       <<<grid_for_resident(a.cell_num * a.pieces_per_row, 3), kThreads, smem, st>>>(a), note_launch();
   return BRT_OK;
@@ -1020,6 +1023,7 @@ int launch_combine(const MoveArgs& a, cudaStream_t st) {
     return launch_combine_async<DT, GMODE, 1>(a, st);
   } else {
     const size_t smem = (size_t)a.path_num * 2 * sizeof(int);
+    const KernelTimer timer("combine_kernel", st);
     combine_seat_kernel<VB, DT, GMODE>
         <<<grid_for_items(a.cell_num * a.pieces_per_row), kThreads, smem, st>>>(a), note_launch();
     return BRT_OK;

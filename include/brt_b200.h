@@ -55,6 +55,13 @@ BRT_API const char* brt_last_error(void);
 /* Kernels this library has launched in the process so far (all threads, all devices).
  * Instrumentation for benchmarks; the reference has no counterpart. */
 BRT_API uint64_t brt_kernel_launch_count(void);
+/* Per-kernel device times for benchmarks (no counterpart in the reference).  While enabled,
+ * the library records a CUDA event on the launching stream before and after each of its hot
+ * kernels; brt_profile_report waits for the recorded launches, writes
+ * {"kernel": {"launches": n, "total_ms": t}, ...} as JSON text into `out` and forgets them.
+ * Leave it off (the default) while a stream is being captured into a CUDA graph. */
+BRT_API void brt_profile_enable(int on);
+BRT_API int brt_profile_report(char* out, size_t out_bytes);
 
 /* ------------------------------------------------------------------ router: indices */
 
