@@ -113,6 +113,87 @@ def generate_indices_and_loads(
     return indices, loads
 
 
+_GATE = {"topk": 0, "threshold": 1}
+_ROUTE_OUT = {"mask": 0, "throttled_mask": 1, "seat_indices": 2}
+
+
+def route_scores_supported(score: torch.Tensor) -> bool:
+    """Whether ``route_scores`` can take ``score`` (the single-launch gate wants contiguous
+    fp32 CUDA scores over a multiple of 4 and at most 256 paths)."""
+    return (score.is_cuda and score.dtype == torch.float32 and score.dim() == 2
+            and score.is_contiguous() and score.size(1) % 4 == 0 and 0 < score.size(1) <= 256
+            and score.data_ptr() % 16 == 0)
+
+
+def route_scores(
+    score: torch.Tensor,
+    decision: str = "topk",
+    top_k: int = 1,
+    threshold: float = 0.0,
+    residual_path: int = -1,
+    output: str = "mask",
+    supported_capacities: Optional[torch.Tensor] = None,
+    capacity_padding: bool = False,
+    path_wise_padding: bool = False,
+    prefix: Optional[torch.Tensor] = None,
+    throttle_capacity: Optional[torch.Tensor] = None,
+    with_gates: bool = False,
+):
+    """Route decision and index scan in one launch, straight from the gate's scores (no
+    counterpart in the reference's extension: it fuses a protocol of
+    python/brt/router/protocol/ with ``throttle_hotmask`` / ``generate_indices_and_loads``).
+
+    ``output`` = "mask": (hot_mask, cells per path); "throttled_mask": (hot_mask cut at
+    ``throttle_capacity`` on top of ``prefix``, prefix) with ``prefix`` updated in place;
+    "seat_indices": (indices, loads) as ``generate_indices_and_loads`` of the hot mask.
+    ``with_gates`` appends the picked scores renormalised to sum 1 per cell.  Raises
+    ``NotImplementedError`` when the scores do not fit the single-launch kernel; callers then
+    route in two steps."""
+    _check_cuda(score, "score")
+    if decision not in _GATE or output not in _ROUTE_OUT:
+        raise RuntimeError(f"unknown decision {decision!r} or output {output!r}")
+    if not route_scores_supported(score):
+        raise NotImplementedError("route_scores needs contiguous fp32 scores over a multiple "
+                                  "of 4 and at most 256 paths")
+    T, E = score.shape
+    dev = score.device
+    with torch.cuda.device(dev):
+        out = torch.empty((T, E), dtype=torch.int32, device=dev)
+        loads = torch.empty((E,), dtype=torch.int32, device=dev)
+        gates = torch.empty((T, E), dtype=torch.float32, device=dev) if with_gates else None
+        caps, ncap = None, 0
+        if supported_capacities is not None:
+            _check_cuda(supported_capacities, "supported_capacities")
+            caps = _int32c(supported_capacities, "supported_capacities")
+            ncap = caps.size(0)
+        thr = None
+        if output == "throttled_mask":
+            if prefix is None or throttle_capacity is None:
+                raise RuntimeError("a throttled mask needs prefix and throttle_capacity")
+            _check_cuda(prefix, "prefix")
+            _check_cuda(throttle_capacity, "throttle_capacity")
+            if prefix.dtype != torch.int32 or not prefix.is_contiguous() or prefix.numel() != E:
+                raise RuntimeError("prefix must be a contiguous int32 tensor of one entry per "
+                                   "path (it is updated in place)")
+            thr = _int32c(throttle_capacity, "throttle_capacity")
+            if thr.numel() != E:
+                raise RuntimeError("CHECK_EQ fails.")
+        nbytes = _lib.query("brt_index_scratch_bytes", T, E)
+        scratch = _scratch.get("index", dev, nbytes)
+        try:
+            _lib.call("brt_route_scores", _ptr(score), T, E, _GATE[decision], int(top_k),
+                      float(threshold), int(residual_path), _ROUTE_OUT[output], _ptr(out),
+                      _ptr(loads), _ptr(caps), ncap, int(bool(capacity_padding)),
+                      int(bool(path_wise_padding)), _ptr(prefix), _ptr(thr), _ptr(gates),
+                      _ptr(scratch), scratch.numel(), _stream(dev))
+        except _lib.BrtError as exc:
+            if exc.status == 4:  # BRT_ERR_UNSUPPORTED: too many scores for one launch
+                raise NotImplementedError(str(exc)) from None
+            raise
+    second = prefix if output == "throttled_mask" else loads
+    return (out, second, gates) if with_gates else (out, second)
+
+
 def convert_index_format(origin_indices: torch.Tensor, loads: torch.Tensor, is_to_tag: bool):
     """src/backend/torch/router.cc:90-110.  As in the reference, ``is_to_tag`` travels into
     the launcher's ``tag_to_seat`` argument, so ``True`` converts tag indices to seat

@@ -31,6 +31,9 @@ SIGNATURES = {
     "brt_static_index_scratch_bytes": (_sz, []),
     "brt_generate_indices_and_loads_static": (
         _int, [_vp, _vp, _vp, _i64, _int, _vp, _int, _int, _int, _int, _vp]),
+    "brt_route_scores": (
+        _int, [_vp, _i64, _int, _int, _int, ctypes.c_float, _int, _int, _vp, _vp, _vp, _int, _int,
+               _int, _vp, _vp, _vp, _vp, _sz, _vp]),
     "brt_throttle_hotmask": (_int, [_vp, _vp, _vp, _vp, _i64, _int, _vp, _sz, _vp]),
     "brt_convert_index_format": (_int, [_vp, _vp, _vp, _i64, _int, _int, _vp]),
     "brt_dispatch_scratch_bytes": (_sz, [_i64, _int]),
@@ -69,7 +72,11 @@ SIGNATURES = {
 
 
 class BrtError(RuntimeError):
-    pass
+    """A failed library call; ``status`` is the brt_status code (0 when not from the library)."""
+
+    def __init__(self, message: str, status: int = 0):
+        super().__init__(message)
+        self.status = status
 
 
 def load():
@@ -106,7 +113,7 @@ def call(name: str, *args):
     rc = fn(*args)
     if rc != 0:
         msg = lib.brt_last_error().decode("utf-8", "replace")
-        raise BrtError(f"{name} failed (status {rc}): {msg}")
+        raise BrtError(f"{name} failed (status {rc}): {msg}", rc)
 
 
 def query(name: str, *args):

@@ -46,7 +46,7 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kGroupRows = 32;  // cells per bit word
 
-enum class Mode { kSeat, kTag, kThrottle };
+enum class Mode { kSeat, kTag, kThrottle, kMask };  // kMask: write the 0/1 mask itself
 
 // How a [cell, path] int32 matrix is cut into CTA tiles.
 struct Tiling {
@@ -821,6 +821,8 @@ __device__ __forceinline__ void expand_general(const TileCtx& x, const int* __re
       out[at] = (m == 1 && run <= thr) ? 1 : 0;
     } else if constexpr (MODE == Mode::kSeat) {
       out[at] = run * m;
+    } else if constexpr (MODE == Mode::kMask) {
+      out[at] = m != 0 ? 1 : 0;
     } else {
       const int64_t dst_row = (int64_t)run * m - 1;
       if (run * m != 0 && dst_row >= 0 && dst_row < x.cell_num)
@@ -872,6 +874,8 @@ __device__ __forceinline__ void expand_binary(const TileCtx& x, const TileSmem& 
       const int seat = b[j] + __popc(w[j] & low);
       if constexpr (MODE == Mode::kThrottle)
         v[j] = (bit && seat <= sm.thr[4 * q + j]) ? 1 : 0;
+      else if constexpr (MODE == Mode::kMask)
+        v[j] = bit;
       else
         v[j] = bit ? seat : 0;
     }
@@ -982,6 +986,89 @@ __global__ void __launch_bounds__(kTileThreads) index_expand_tiled_kernel(const 
   expand_tile<MODE>(ctx_of(a), sm, a.mask, a.bits, a.tile_sums, a.flags, a.out, a.threshold);
 }
 
+// ------------------------------------------------------------------------------- gate rows
+// Route decision of a staged tile of fp32 scores, in place: every row of the tile is replaced
+// by its 0/1 hot mask (as int32), so that pack_staged can go on as if a mask had been staged.
+//   kind 1: ones at the top_k largest scores of the row (python/brt/router/protocol/topk.py:
+//           26-31); equal scores go to the lower path index;
+//   kind 2: ones where score > threshold; a row without any goes to residual_path when that
+//           is >= 0 (python/brt/router/protocol/threshold.py:23-39).
+// gates_out (optional, [cell, path] fp32): the picked scores divided by their sum clamped at
+// FLT_EPSILON, zero elsewhere (python/brt/router/protocol/swin_moe.py:193-204).
+struct GateArgs {
+  int kind;  // 0: the input is a mask already
+  int top_k;
+  float threshold;
+  int residual_path;
+  float* gates_out;
+};
+
+__device__ __forceinline__ void gate_rows(const TileCtx& x, int* stage, const GateArgs& g) {
+  constexpr int kPerLane = 8;  // path_num <= 256
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int cols = x.path_num;  // a gated tile spans every path
+  const int64_t row0 = x.tile * x.rg * kGroupRows;
+  const int tile_rows = x.rg * kGroupRows;
+  for (int r = warp; r < tile_rows; r += kTileWarps) {
+    const int64_t row = row0 + r;
+    if (row >= x.cell_num) break;  // warp-uniform; rows beyond the mask were staged as zeros
+    int* p = stage + r * x.pitch;
+    float v[kPerLane];
+#pragma unroll
+    for (int i = 0; i < kPerLane; i++) {
+      const int c = lane + 32 * i;
+      v[i] = c < cols ? __int_as_float(p[c]) : -INFINITY;
+    }
+    unsigned picked = 0;
+    float denom = 0.f;
+    if (g.kind == 1) {
+      for (int t = 0; t < g.top_k; t++) {
+        float best = -INFINITY;
+        int col = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < kPerLane; i++) {
+          const int c = lane + 32 * i;
+          if (c < cols && !((picked >> i) & 1u) && (col == 0x7fffffff || v[i] > best)) {
+            best = v[i];
+            col = c;
+          }
+        }
+#pragma unroll
+        for (int off = 16; off != 0; off >>= 1) {
+          const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+          const int oc = __shfl_xor_sync(0xffffffffu, col, off);
+          if (oc != 0x7fffffff && (col == 0x7fffffff || ob > best || (ob == best && oc < col))) {
+            best = ob;
+            col = oc;
+          }
+        }
+        if (col == 0x7fffffff) break;  // fewer paths than top_k
+        if ((col & 31) == lane) picked |= 1u << (col >> 5);
+        denom = __fadd_rn(denom, best);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < kPerLane; i++)
+        if (lane + 32 * i < cols && v[i] > g.threshold) picked |= 1u << i;
+      if (g.residual_path >= 0 && __ballot_sync(0xffffffffu, picked != 0) == 0 &&
+          (g.residual_path & 31) == lane)
+        picked |= 1u << (g.residual_path >> 5);
+    }
+    denom = fmaxf(denom, 1.1920928955078125e-07f);
+#pragma unroll
+    for (int i = 0; i < kPerLane; i++) {
+      const int c = lane + 32 * i;
+      if (c < cols) {
+        const bool hot = (picked >> i) & 1u;
+        p[c] = hot ? 1 : 0;
+        if (g.gates_out != nullptr)
+          __stcs(g.gates_out + row * x.path_num + c, hot ? __fdiv_rn(v[i], denom) : 0.f);
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------- chained path
 // One launch, no grid-wide barrier.  A CTA takes a ticket; ticket k owns a run of
 // consecutive tiles of one path chunk.  It packs them all (the bit words stay in shared
@@ -990,6 +1077,7 @@ __global__ void __launch_bounds__(kTileThreads) index_expand_tiled_kernel(const 
 // have started by construction, so the kernel needs no co-residency guarantee.
 struct ChainArgs {
   TiledArgs t;
+  GateArgs gate;
   unsigned long long* status;  // [ranges][path_num]: (1 << 32) | column sum once published
   int* ticket;
   int* error;  // set to 1 when a wait ran out
@@ -1010,7 +1098,7 @@ __device__ __forceinline__ unsigned long long status_peek(const unsigned long lo
   return w;
 }
 
-template <Mode MODE>
+template <Mode MODE, bool GATED>
 __global__ void __launch_bounds__(kTileThreads, 2) index_chain_kernel(const ChainArgs c) {
   extern __shared__ __align__(16) int s_dyn[];
   __shared__ int s_ticket;
@@ -1061,6 +1149,10 @@ __global__ void __launch_bounds__(kTileThreads, 2) index_chain_kernel(const Chai
     cp_async_wait<1>();
     __syncthreads();
     x.tile = t;
+    if constexpr (GATED) {  // the staged tile holds scores: decide the routes in place
+      gate_rows(x, stage[i & 1], c.gate);
+      __syncthreads();
+    }
     TileSmem cur = sm;
     cur.tile = stage[i & 1];
     cur.bits = bits_all + (size_t)i * words_per_tile;
@@ -1146,22 +1238,24 @@ size_t tiled_scratch_bytes(int64_t cell_num, int path_num) {
 constexpr int kChainCtasPerSm = 2;
 constexpr size_t kChainSmemLimit = 110 * 1024;
 
-template <Mode MODE>
+template <Mode MODE, bool GATED>
 int launch_chain_mode(const ChainArgs& c, unsigned grid, size_t smem, cudaStream_t stream) {
   static thread_local std::map<int, size_t> configured;  // device -> opted-in bytes
   if (smem > 48 * 1024) {
     int dev = 0;
     BRT_CUDA_TRY(cudaGetDevice(&dev));
     if (configured[dev] < smem) {
-      BRT_CUDA_TRY(cudaFuncSetAttribute(index_chain_kernel<MODE>,
+      BRT_CUDA_TRY(cudaFuncSetAttribute(index_chain_kernel<MODE, GATED>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         (int)kChainSmemLimit));
       configured[dev] = kChainSmemLimit;
     }
   }
-  const KernelTimer timer(MODE == Mode::kThrottle ? "throttle_chain_kernel" : "index_chain_kernel",
+  const KernelTimer timer(GATED ? "route_scores_kernel"
+                                : MODE == Mode::kThrottle ? "throttle_chain_kernel"
+                                                          : "index_chain_kernel",
                           stream);
-  index_chain_kernel<MODE><<<grid, kTileThreads, smem, stream>>>(c), note_launch();
+  index_chain_kernel<MODE, GATED><<<grid, kTileThreads, smem, stream>>>(c), note_launch();
   BRT_LAUNCH_CHECK("index_chain_kernel");
   return BRT_OK;
 }
@@ -1170,8 +1264,9 @@ int launch_chain(Mode mode, const TileGeom& g, int tiles_per_cta, int ranges, si
                  const int32_t* mask, int32_t* out, int32_t* loads, int64_t cell_num,
                  int path_num, const int32_t* caps, int ncap, int capacity_padding,
                  int path_wise, int32_t* prefix, const int32_t* threshold, void* scratch,
-                 cudaStream_t stream) {
+                 cudaStream_t stream, const GateArgs* gate = nullptr) {
   ChainArgs c;
+  c.gate = gate != nullptr ? *gate : GateArgs{0, 0, 0.f, -1, nullptr};
   char* p = static_cast<char*>(scratch);
   c.t.flags = reinterpret_cast<int*>(p);
   c.error = c.t.flags + 1;
@@ -1202,17 +1297,24 @@ int launch_chain(Mode mode, const TileGeom& g, int tiles_per_cta, int ranges, si
   if (mode == Mode::kTag)
     BRT_CUDA_TRY(cudaMemsetAsync(out, 0, (size_t)cell_num * path_num * 4, stream));
   const unsigned grid = (unsigned)ranges * (unsigned)g.col_chunks;
+  if (gate != nullptr) {
+    switch (mode) {
+      case Mode::kSeat: return launch_chain_mode<Mode::kSeat, true>(c, grid, smem, stream);
+      case Mode::kMask: return launch_chain_mode<Mode::kMask, true>(c, grid, smem, stream);
+      default: return launch_chain_mode<Mode::kThrottle, true>(c, grid, smem, stream);
+    }
+  }
   switch (mode) {
-    case Mode::kSeat: return launch_chain_mode<Mode::kSeat>(c, grid, smem, stream);
-    case Mode::kTag: return launch_chain_mode<Mode::kTag>(c, grid, smem, stream);
-    default: return launch_chain_mode<Mode::kThrottle>(c, grid, smem, stream);
+    case Mode::kSeat: return launch_chain_mode<Mode::kSeat, false>(c, grid, smem, stream);
+    case Mode::kTag: return launch_chain_mode<Mode::kTag, false>(c, grid, smem, stream);
+    default: return launch_chain_mode<Mode::kThrottle, false>(c, grid, smem, stream);
   }
 }
 
 int launch_tiled(Mode mode, const int32_t* mask, int32_t* out, int32_t* loads, int64_t cell_num,
                  int path_num, const int32_t* caps, int ncap, int capacity_padding,
                  int path_wise, int32_t* prefix, const int32_t* threshold, void* scratch,
-                 cudaStream_t stream) {
+                 cudaStream_t stream, const GateArgs* gate = nullptr) {
   TileGeom g = make_tile_geom(cell_num, path_num);
   BRT_REQUIRE(g.num_tiles <= 0x7fffffffLL && g.col_chunks <= 65535,
               "mask of %lld x %d cells is too large for one launch", (long long)cell_num,
@@ -1220,7 +1322,7 @@ int launch_tiled(Mode mode, const int32_t* mask, int32_t* out, int32_t* loads, i
   // One chained launch when the bit words of a CTA's tiles fit in shared memory, else three
   // launches (pack, scan, expand).  BRT_INDEX_PATH=split forces the latter (for tests).
   const char* const forced = getenv("BRT_INDEX_PATH");
-  if (forced == nullptr || strcmp(forced, "split") != 0) {
+  if (gate != nullptr || forced == nullptr || strcmp(forced, "split") != 0) {
     int64_t target = (int64_t)sm_count() * kChainCtasPerSm / g.col_chunks;
     if (target < 1) target = 1;
     const int64_t ranges0 = g.num_tiles < target ? g.num_tiles : target;
@@ -1233,8 +1335,12 @@ int launch_tiled(Mode mode, const int32_t* mask, int32_t* out, int32_t* loads, i
     if (smem <= kChainSmemLimit)
       return launch_chain(mode, g, (int)tiles_per_cta, (int)ranges, smem, mask, out, loads,
                           cell_num, path_num, caps, ncap, capacity_padding, path_wise, prefix,
-                          threshold, scratch, stream);
+                          threshold, scratch, stream, gate);
   }
+  if (gate != nullptr)
+    return set_error(BRT_ERR_UNSUPPORTED,
+                     "%lld x %d scores do not fit the single-launch gate; route in two steps",
+                     (long long)cell_num, path_num);
   TiledArgs a;
   char* p = static_cast<char*>(scratch);
   a.flags = reinterpret_cast<int*>(p);
@@ -1454,6 +1560,57 @@ BRT_API int brt_throttle_hotmask(const int32_t* hotmask, int32_t* throttled, int
   return run_scan(Mode::kThrottle, hotmask, throttled, nullptr, cell_num, path_num, nullptr, 0,
                   0, 0, prefix, threshold, scratch, scratch_bytes,
                   static_cast<cudaStream_t>(stream));
+}
+
+BRT_API int brt_route_scores(const float* scores, int64_t cell_num, int path_num, int decision,
+                             int top_k, float threshold, int residual_path, int output,
+                             int32_t* out, int32_t* loads, const int32_t* capacities,
+                             int capacity_num, int capacity_padding, int path_wise_padding,
+                             int32_t* prefix, const int32_t* throttle_capacity, float* gates_out,
+                             void* scratch, size_t scratch_bytes, void* stream) {
+  clear_error();
+  BRT_REQUIRE(cell_num >= 0 && path_num > 0, "bad shape: cell_num=%lld path_num=%d",
+              (long long)cell_num, path_num);
+  BRT_REQUIRE(decision == BRT_GATE_TOPK || decision == BRT_GATE_THRESHOLD, "unknown decision %d",
+              decision);
+  BRT_REQUIRE(decision != BRT_GATE_TOPK || (top_k >= 1 && top_k <= path_num),
+              "top_k=%d outside [1, %d]", top_k, path_num);
+  BRT_REQUIRE(residual_path < path_num, "residual_path=%d outside the %d paths", residual_path,
+              path_num);
+  BRT_REQUIRE(output == BRT_ROUTE_MASK || output == BRT_ROUTE_THROTTLED_MASK ||
+                  output == BRT_ROUTE_SEAT_INDICES,
+              "unknown output %d", output);
+  BRT_REQUIRE(output != BRT_ROUTE_THROTTLED_MASK || (prefix != nullptr && throttle_capacity != nullptr),
+              "a throttled mask needs prefix and throttle_capacity");
+  BRT_REQUIRE(output == BRT_ROUTE_THROTTLED_MASK || loads != nullptr, "loads is null");
+  BRT_REQUIRE(capacity_num >= 0 && (capacity_num == 0 || capacities != nullptr),
+              "capacities missing");
+  BRT_REQUIRE(!path_wise_padding || capacity_num == path_num,
+              "path-wise padding needs one capacity per path");
+  if (cell_num == 0) {
+    if (output != BRT_ROUTE_THROTTLED_MASK)
+      BRT_CUDA_TRY(cudaMemsetAsync(loads, 0, (size_t)path_num * 4, static_cast<cudaStream_t>(stream)));
+    return BRT_OK;
+  }
+  BRT_REQUIRE(scores != nullptr && out != nullptr, "scores or out is null");
+  if (path_num % 4 != 0 || path_num > 256 || !aligned_to(scores, 16) || !aligned_to(out, 16) ||
+      (gates_out != nullptr && !aligned_to(gates_out, 4)))
+    return set_error(BRT_ERR_UNSUPPORTED,
+                     "the single-launch gate needs path_num %% 4 == 0, path_num <= 256 and "
+                     "16-byte aligned arrays; route in two steps");
+  BRT_REQUIRE(scratch != nullptr && aligned_to(scratch, 256),
+              "scratch must be a 256-byte aligned device buffer");
+  const size_t need = scratch_bytes_for(cell_num, path_num);
+  if (scratch_bytes < need)
+    return set_error(BRT_ERR_SCRATCH_TOO_SMALL, "scratch holds %zu bytes, %zu needed",
+                     scratch_bytes, need);
+  const GateArgs gate{decision == BRT_GATE_TOPK ? 1 : 2, top_k, threshold, residual_path, gates_out};
+  const Mode mode = output == BRT_ROUTE_MASK ? Mode::kMask
+                    : output == BRT_ROUTE_THROTTLED_MASK ? Mode::kThrottle
+                                                         : Mode::kSeat;
+  return launch_tiled(mode, reinterpret_cast<const int32_t*>(scores), out, loads, cell_num,
+                      path_num, capacities, capacity_num, capacity_padding, path_wise_padding,
+                      prefix, throttle_capacity, scratch, static_cast<cudaStream_t>(stream), &gate);
 }
 
 BRT_API int brt_convert_index_format(const int32_t* origin_indices, int32_t* new_indices,

@@ -139,6 +139,47 @@ BRT_API int brt_convert_index_format(const int32_t* origin_indices, int32_t* new
                                      const int32_t* loads, int64_t cell_num, int path_num,
                                      int tag_to_seat, void* stream);
 
+/* ------------------------------------------------------------------ router: fused gate */
+
+typedef enum brt_gate_decision { BRT_GATE_TOPK = 0, BRT_GATE_THRESHOLD = 1 } brt_gate_decision;
+typedef enum brt_route_output {
+  BRT_ROUTE_MASK = 0,           /* out = hot mask, loads = cells routed to every path */
+  BRT_ROUTE_THROTTLED_MASK = 1, /* out = hot mask cut at throttle_capacity, prefix updated */
+  BRT_ROUTE_SEAT_INDICES = 2    /* out = seat indices, loads as brt_generate_indices_and_loads */
+} brt_route_output;
+
+/*
+ * Route decision and index scan in one launch, straight from the gate's scores: what the
+ * reference does with a protocol (torch.topk + scatter_, python/brt/router/protocol/topk.py:
+ * 26-31; score > threshold with a residual path, protocol/threshold.py:23-39; the first pick
+ * cut at the runtime capacity, protocol/swin_moe.py:69-80 with ThrottleHotmask,
+ * src/router/location.cu:304-315) followed by GenerateIndicesAndLoads
+ * (include/brt/router/location.h:29-39), without the hot mask ever reaching memory unless it
+ * is the requested output.
+ *
+ *   scores   fp32 [cell_num, path_num], row-major
+ *   decision BRT_GATE_TOPK: ones at the top_k largest scores of a cell (equal scores: the
+ *            lower path wins; the reference leaves ties to torch.topk);
+ *            BRT_GATE_THRESHOLD: ones where score > threshold, and residual_path (>= 0) for
+ *            a cell that would otherwise go nowhere
+ *   output   see brt_route_output; capacities / capacity_padding / path_wise_padding as in
+ *            brt_generate_indices_and_loads (BRT_ROUTE_SEAT_INDICES only); prefix and
+ *            throttle_capacity as in brt_throttle_hotmask (BRT_ROUTE_THROTTLED_MASK only)
+ *   gates_out optional fp32 [cell_num, path_num]: picked scores divided by their sum
+ *            (clamped at FLT_EPSILON), zero elsewhere (protocol/swin_moe.py:193-204)
+ *   scratch  brt_index_scratch_bytes(cell_num, path_num) bytes
+ *
+ * Returns BRT_ERR_UNSUPPORTED (nothing launched) when path_num is not a multiple of 4 or
+ * exceeds 256, an array is not 16-byte aligned, or the scores are too many for the
+ * single-launch kernel; the caller then routes in two steps.
+ */
+BRT_API int brt_route_scores(const float* scores, int64_t cell_num, int path_num, int decision,
+                             int top_k, float threshold, int residual_path, int output,
+                             int32_t* out, int32_t* loads, const int32_t* capacities,
+                             int capacity_num, int capacity_padding, int path_wise_padding,
+                             int32_t* prefix, const int32_t* throttle_capacity, float* gates_out,
+                             void* scratch, size_t scratch_bytes, void* stream);
+
 /* ------------------------------------------------------------------ router: data movement */
 
 /* Scratch needed by brt_dispatch_with_indices_and_loads for `total_rows` output rows. */

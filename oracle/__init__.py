@@ -117,6 +117,40 @@ def softmax(logits: np.ndarray) -> np.ndarray:
     return (e / e.sum(axis=1, keepdims=True)).astype(np.float32)
 
 
+def renormalised_topk_score(score: np.ndarray, top_k: int) -> np.ndarray:
+    """python/brt/router/protocol/swin_moe.py:193-204 — the top-k scores of each row divided
+    by their sum (clamped at float32 eps, summed in pick order), zeros elsewhere."""
+    T, E = score.shape
+    order = np.argsort(-score, axis=1, kind="stable")[:, :top_k]
+    vals = np.take_along_axis(score, order, axis=1).astype(np.float32)
+    denom = np.zeros((T,), dtype=np.float32)
+    for j in range(vals.shape[1]):
+        denom = (denom + vals[:, j]).astype(np.float32)
+    denom = np.maximum(denom, np.finfo(np.float32).eps)
+    out = np.zeros((T, E), dtype=np.float32)
+    np.put_along_axis(out, order, (vals / denom[:, None]).astype(np.float32), axis=1)
+    return out
+
+
+def route_scores(score: np.ndarray, decision: str = "topk", top_k: int = 1,
+                 threshold: float = 0.0, residual_path: int = -1, output: str = "mask",
+                 supported_capacities=None, capacity_padding: bool = False,
+                 path_wise_padding: bool = False, prefix=None, throttle_capacity=None):
+    """A protocol of python/brt/router/protocol/ (topk.py:26-31, threshold.py:23-39) followed
+    by nothing ("mask": mask and cells per path), by throttle_hotmask ("throttled_mask") or
+    by generate_indices_and_loads ("seat_indices"), composed from the functions of this file."""
+    if decision == "topk":
+        mask = topk_hot_mask(score, top_k)
+    else:
+        mask = threshold_hot_mask(score, threshold, residual_path)
+    if output == "mask":
+        return mask, mask.sum(axis=0).astype(np.int32)
+    if output == "throttled_mask":
+        return throttle_hotmask(mask, prefix, throttle_capacity)
+    return generate_indices_and_loads(mask, supported_capacities, capacity_padding,
+                                      path_wise_padding, False)
+
+
 # --------------------------------------------------------------------------- index generation
 
 

@@ -263,3 +263,26 @@ def test_sparse_a2a_sample_round_trip():
             [f[0] for f in fwd], [f[1] for f in fwd], [f[2] for f in fwd], True)
         for me in range(W):
             assert np.array_equal(back[me], xs_p[me])
+
+
+def test_route_scores_checker_matches_reference_protocols(golden_dir):
+    """oracle.route_scores composes a protocol with the index functions; its masks must be the
+    ones the reference's protocol classes produced (tests/golden/make_golden.py)."""
+    z = np.load(golden_dir / "ref_python_vectors.npz")
+    score, sig = z["proto/score"], z["proto/sigmoid"]
+    for k in (1, 2, 3):
+        mask, counts = oracle.route_scores(score, "topk", k, output="mask")
+        assert np.array_equal(mask, z[f"proto/topk{k}"])
+        assert np.array_equal(counts, z[f"proto/topk{k}"].sum(axis=0))
+        idx, loads = oracle.route_scores(score, "topk", k, output="seat_indices")
+        exp_i, exp_l = oracle.generate_indices_and_loads(z[f"proto/topk{k}"])
+        assert np.array_equal(idx, exp_i) and np.array_equal(loads, exp_l)
+    mask, _ = oracle.route_scores(sig, "threshold", threshold=0.5, output="mask")
+    assert np.array_equal(mask, z["proto/threshold_0.5"])
+    mask, _ = oracle.route_scores(sig, "threshold", threshold=0.8, residual_path=3, output="mask")
+    assert np.array_equal(mask, z["proto/threshold_0.8_residual3"])
+    gates = oracle.renormalised_topk_score(score, 2)
+    assert np.array_equal(gates != 0, z["proto/topk2"] != 0)
+    picked = np.sort(score, axis=1)[:, -2:]
+    np.testing.assert_allclose(gates.sum(axis=1), picked.sum(1) / np.maximum(
+        picked.sum(1), np.finfo(np.float32).eps), rtol=1e-6)
