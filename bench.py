@@ -379,6 +379,10 @@ def run_gpu(args):
     dominant_op = {"dispatch_move_kernel": "dispatch", "dispatch_zero_fill_kernel": "dispatch",
                    "combine_kernel": "combine"}.get(dominant, "indices")
 
+    # ---- the gate in front of the path: scores -> mask (-> indices), torch ops of the
+    # reference's protocol beside the library's single-launch gate
+    gate = measure_gate(wl, dev, w, R, padded, caps)
+
     # ---- end to end through the router API with host buffers
     e2e = measure_e2e(wl, dev, args, ScatterRouter, GatherRouter, distributed, world)
 
@@ -408,6 +412,7 @@ def run_gpu(args):
                          round(device_kernels[dominant]["achieved_gbs"] / 8000, 4),
                      "whole_op": {"op": dominant_op, **kernels[dominant_op]}},
         "device_kernels": device_kernels,
+        "gate": gate,
         "kernels": kernels,
         "routing": {"kept_routes": ab["R"], "cells_routed": ab["T_r"], "output_rows": ab["L"]},
         "gpu_launches": int(round(args.steps * launches_per_step)),
@@ -436,6 +441,62 @@ def run_gpu(args):
     if distributed:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def measure_gate(wl, dev, w, R, padded, caps):
+    """Device time (CUDA events, median of 11, L2 flushed in between) of turning the fp32
+    score matrix into seat indices: the reference's protocol as torch ops (topk, zeros,
+    scatter_) followed by this library's throttle and index ops, beside the library's gate
+    kernel, which takes the scores straight to the (throttled) mask or to the indices."""
+    score = wl["score"].to(dev)
+    if not R.route_scores_supported(score):
+        return None
+    T, E, k = w["T"], w["E"], w["k"]
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev)
+
+    def torch_protocol():
+        picks = torch.topk(score, k, dim=1).indices
+        mask = torch.zeros((T, E), dtype=torch.int32, device=dev).scatter_(1, picks, 1)
+        if padded:
+            mask, _ = R.throttle_hotmask(mask, torch.zeros(E, dtype=torch.int32, device=dev), caps)
+        return R.generate_indices_and_loads(mask, caps)
+
+    def gate_kernel():
+        if padded:  # decision + throttle in one launch, then the index scan
+            mask, _ = R.route_scores(score, "topk", k, output="throttled_mask",
+                                     prefix=torch.zeros(E, dtype=torch.int32, device=dev),
+                                     throttle_capacity=caps)
+            return R.generate_indices_and_loads(mask, caps)
+        return R.route_scores(score, "topk", k, output="seat_indices")
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(11):
+            flush.zero_()
+            try:
+                torch.cuda._sleep(400000)  # lets the host enqueue the whole chain first
+            except Exception:
+                pass
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            out = fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return sorted(ts)[len(ts) // 2], out
+
+    t_torch, (i0, l0) = timed(torch_protocol)
+    t_gate, (i1, l1) = timed(gate_kernel)
+    return {"scores_to_indices_ms": {"torch_protocol_then_index_ops": round(t_torch, 5),
+                                     "gate_kernel": round(t_gate, 5)},
+            "same_result": bool(torch.equal(i0, i1) and torch.equal(l0, l1)),
+            "launches": {"torch_protocol_then_index_ops": "topk, zeros, scatter_"
+                         + (", throttle, indices" if padded else ", indices"),
+                         "gate_kernel": "route_scores(throttled mask), indices" if padded
+                         else "route_scores(seat indices)"}}
 
 
 def measure_e2e(wl, dev, args, ScatterRouter, GatherRouter, distributed, world):

@@ -1003,70 +1003,89 @@ struct GateArgs {
   float* gates_out;
 };
 
-__device__ __forceinline__ void gate_rows(const TileCtx& x, int* stage, const GateArgs& g) {
-  constexpr int kPerLane = 8;  // path_num <= 256
+// fp32 bits -> unsigned key with the same order (and back); key 0 is below every score
+__device__ __forceinline__ unsigned score_key(int bits) {
+  const unsigned u = static_cast<unsigned>(bits);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_score(unsigned key) {
+  const unsigned u = (key & 0x80000000u) ? (key & 0x7fffffffu) : ~key;
+  return __uint_as_float(u);
+}
+
+// PER scores per lane, L lanes per row (L < 32 only with PER == 1: 32 / L rows per warp).
+// A pick costs two warp reductions: the largest key among the row's unpicked scores, then
+// the lowest path that holds it.
+template <int PER, int L>
+__device__ __forceinline__ void gate_rows_as(const TileCtx& x, int* stage, const GateArgs& g) {
+  constexpr int kRowsPerWarp = 32 / L;
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
+  const int sub = lane / L;
+  const int l = lane - sub * L;
+  const unsigned members = L == 32 ? 0xffffffffu : (((1u << L) - 1u) << (sub * L));
   const int cols = x.path_num;  // a gated tile spans every path
   const int64_t row0 = x.tile * x.rg * kGroupRows;
   const int tile_rows = x.rg * kGroupRows;
-  for (int r = warp; r < tile_rows; r += kTileWarps) {
+  for (int r = warp * kRowsPerWarp + sub; r < tile_rows; r += kTileWarps * kRowsPerWarp) {
     const int64_t row = row0 + r;
-    if (row >= x.cell_num) break;  // warp-uniform; rows beyond the mask were staged as zeros
+    if (row >= x.cell_num) break;  // uniform per row group; later rows were staged as zeros
     int* p = stage + r * x.pitch;
-    float v[kPerLane];
+    unsigned key[PER];
 #pragma unroll
-    for (int i = 0; i < kPerLane; i++) {
-      const int c = lane + 32 * i;
-      v[i] = c < cols ? __int_as_float(p[c]) : -INFINITY;
+    for (int i = 0; i < PER; i++) {
+      const int c = l + L * i;
+      key[i] = c < cols ? score_key(p[c]) : 0u;
     }
     unsigned picked = 0;
     float denom = 0.f;
     if (g.kind == 1) {
       for (int t = 0; t < g.top_k; t++) {
-        float best = -INFINITY;
-        int col = 0x7fffffff;
+        unsigned mine = 0;
 #pragma unroll
-        for (int i = 0; i < kPerLane; i++) {
-          const int c = lane + 32 * i;
-          if (c < cols && !((picked >> i) & 1u) && (col == 0x7fffffff || v[i] > best)) {
-            best = v[i];
-            col = c;
-          }
-        }
+        for (int i = 0; i < PER; i++)
+          if (!((picked >> i) & 1u) && key[i] > mine) mine = key[i];
+        const unsigned best = __reduce_max_sync(members, mine);
+        if (best == 0u) break;  // fewer paths than top_k
+        unsigned my_col = 0xffffffffu;
 #pragma unroll
-        for (int off = 16; off != 0; off >>= 1) {
-          const float ob = __shfl_xor_sync(0xffffffffu, best, off);
-          const int oc = __shfl_xor_sync(0xffffffffu, col, off);
-          if (oc != 0x7fffffff && (col == 0x7fffffff || ob > best || (ob == best && oc < col))) {
-            best = ob;
-            col = oc;
-          }
-        }
-        if (col == 0x7fffffff) break;  // fewer paths than top_k
-        if ((col & 31) == lane) picked |= 1u << (col >> 5);
-        denom = __fadd_rn(denom, best);
+        for (int i = PER - 1; i >= 0; i--)
+          if (!((picked >> i) & 1u) && key[i] == best) my_col = l + L * i;
+        const unsigned col = __reduce_min_sync(members, my_col);
+        if (col == my_col) picked |= 1u << (col / L);
+        denom = __fadd_rn(denom, key_score(best));
       }
     } else {
 #pragma unroll
-      for (int i = 0; i < kPerLane; i++)
-        if (lane + 32 * i < cols && v[i] > g.threshold) picked |= 1u << i;
-      if (g.residual_path >= 0 && __ballot_sync(0xffffffffu, picked != 0) == 0 &&
-          (g.residual_path & 31) == lane)
-        picked |= 1u << (g.residual_path >> 5);
+      for (int i = 0; i < PER; i++)
+        if (l + L * i < cols && key_score(key[i]) > g.threshold) picked |= 1u << i;
+      if (g.residual_path >= 0 && __ballot_sync(members, picked != 0) == 0 &&
+          (g.residual_path % L) == l)
+        picked |= 1u << (g.residual_path / L);
     }
     denom = fmaxf(denom, 1.1920928955078125e-07f);
 #pragma unroll
-    for (int i = 0; i < kPerLane; i++) {
-      const int c = lane + 32 * i;
+    for (int i = 0; i < PER; i++) {
+      const int c = l + L * i;
       if (c < cols) {
         const bool hot = (picked >> i) & 1u;
-        p[c] = hot ? 1 : 0;
         if (g.gates_out != nullptr)
-          __stcs(g.gates_out + row * x.path_num + c, hot ? __fdiv_rn(v[i], denom) : 0.f);
+          __stcs(g.gates_out + row * x.path_num + c,
+                 hot ? __fdiv_rn(key_score(key[i]), denom) : 0.f);
+        p[c] = hot ? 1 : 0;
       }
     }
   }
+}
+
+__device__ __forceinline__ void gate_rows(const TileCtx& x, int* stage, const GateArgs& g) {
+  const int cols = x.path_num;  // <= 256, warp-uniform
+  if (cols <= 8) gate_rows_as<1, 8>(x, stage, g);
+  else if (cols <= 16) gate_rows_as<1, 16>(x, stage, g);
+  else if (cols <= 32) gate_rows_as<1, 32>(x, stage, g);
+  else if (cols <= 64) gate_rows_as<2, 32>(x, stage, g);
+  else if (cols <= 128) gate_rows_as<4, 32>(x, stage, g);
+  else gate_rows_as<8, 32>(x, stage, g);
 }
 
 // ---------------------------------------------------------------------------- chained path

@@ -26,12 +26,22 @@ def process_mask(hot_mask, prefix_base, capacity, score_sorted=False, score=None
 
 
 def topk_hot_mask(score: torch.Tensor, top_k: int) -> torch.Tensor:
+    if c_router.route_scores_supported(score) and 1 <= top_k <= score.size(1):
+        try:
+            return c_router.route_scores(score, "topk", top_k, output="mask")[0]
+        except NotImplementedError:
+            pass
     picks = torch.topk(score, top_k, dim=1).indices
     return torch.zeros(score.shape, dtype=torch.int32, device=score.device).scatter_(1, picks, 1)
 
 
 def renormalised_topk_score(score: torch.Tensor, top_k: int) -> torch.Tensor:
     """Scores of the top-k paths divided by their sum (clamped at eps), zero elsewhere."""
+    if c_router.route_scores_supported(score) and 1 <= top_k <= score.size(1):
+        try:
+            return c_router.route_scores(score, "topk", top_k, output="mask", with_gates=True)[2]
+        except NotImplementedError:
+            pass
     vals, picks = torch.topk(score, top_k, dim=1)
     denom = torch.clamp(vals.sum(dim=1, keepdim=True), min=torch.finfo(score.dtype).eps)
     return torch.zeros_like(score).scatter_(1, picks, vals / denom)
@@ -61,6 +71,19 @@ class SwinMoEProtocol(ProtocolBase):
 
     def make_route_decision(self, score, logits_wo_noise=None, logits=None):
         T, E = score.shape
+        if not self.batch_prioritized_routing and c_router.route_scores_supported(score):
+            # first pick and throttle in one launch of the library's gate kernel
+            cap = self.runtime_capacity(T, E)
+            runtime_capacities = torch.full((E,), cap, dtype=torch.int32, device=score.device)
+            prefix = torch.zeros((E,), dtype=torch.int32, device=score.device)
+            try:
+                hot_mask, _ = c_router.route_scores(score, "topk", 1, output="throttled_mask",
+                                                    prefix=prefix,
+                                                    throttle_capacity=runtime_capacities)
+                loss = self.generate_auxiliary(score, logits_wo_noise, logits, None)
+                return hot_mask, runtime_capacities, score, loss
+            except NotImplementedError:
+                pass
         first_pick = torch.topk(score, self.top_k, dim=1).indices[:, :1]
         hot_mask = torch.zeros((T, E), dtype=torch.int32, device=score.device)
         hot_mask.scatter_(1, first_pick, 1)

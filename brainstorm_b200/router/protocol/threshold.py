@@ -1,6 +1,7 @@
 """Threshold protocols (python/brt/router/protocol/threshold.py:14-94)."""
 import torch
 
+from ..._C import router as c_router
 from .base import ProtocolBase, register_protocol
 
 __all__ = ["ThresholdProtocol", "ResidualThresholdProtocol", "BinaryThresholdProtocol"]
@@ -17,6 +18,12 @@ class ThresholdProtocol(ProtocolBase):
         self.residual_path = residual_path
 
     def make_route_decision(self, score: torch.Tensor) -> torch.Tensor:
+        if c_router.route_scores_supported(score) and self.residual_path < score.size(1):
+            try:  # the library's single-launch gate
+                return c_router.route_scores(score, "threshold", threshold=self.threshold,
+                                             residual_path=self.residual_path, output="mask")[0]
+            except NotImplementedError:
+                pass
         mask = (score > self.threshold).to(torch.int32)
         if self.residual_path >= 0:
             nowhere = (mask.sum(dim=1) == 0).to(torch.int32)
