@@ -987,8 +987,9 @@ __global__ void __launch_bounds__(kTileThreads) index_expand_tiled_kernel(const 
 }
 
 // ------------------------------------------------------------------------------- gate rows
-// Route decision of a staged tile of fp32 scores, in place: every row of the tile is replaced
-// by its 0/1 hot mask (as int32), so that pack_staged can go on as if a mask had been staged.
+// Route decision of a staged tile of fp32 scores.  A warp (or a part of it, for narrow rows)
+// decides one row at a time and keeps the outcome as bits of the column words of the row's
+// 32-cell group; the words of all warps meet in shared memory, so no mask is ever written.
 //   kind 1: ones at the top_k largest scores of the row (python/brt/router/protocol/topk.py:
 //           26-31); equal scores go to the lower path index;
 //   kind 2: ones where score > threshold; a row without any goes to residual_path when that
@@ -1017,7 +1018,8 @@ __device__ __forceinline__ float key_score(unsigned key) {
 // A pick costs two warp reductions: the largest key among the row's unpicked scores, then
 // the lowest path that holds it.
 template <int PER, int L>
-__device__ __forceinline__ void gate_rows_as(const TileCtx& x, int* stage, const GateArgs& g) {
+__device__ __forceinline__ void gate_rows_as(const TileCtx& x, const int* stage, int* bits,
+                                             int* sums, const GateArgs& g) {
   constexpr int kRowsPerWarp = 32 / L;
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -1027,10 +1029,32 @@ __device__ __forceinline__ void gate_rows_as(const TileCtx& x, int* stage, const
   const int cols = x.path_num;  // a gated tile spans every path
   const int64_t row0 = x.tile * x.rg * kGroupRows;
   const int tile_rows = x.rg * kGroupRows;
+  // column bit words of the 32-cell group this lane is in, for the rows it has seen so far;
+  // handed to shared memory (where the other warps' rows of the group meet) when the group
+  // changes
+  unsigned word[PER];
+#pragma unroll
+  for (int i = 0; i < PER; i++) word[i] = 0;
+  int group = 0;
+  auto flush = [&]() {
+#pragma unroll
+    for (int i = 0; i < PER; i++) {
+      if (word[i] != 0) {
+        const int c = l + L * i;
+        atomicOr(reinterpret_cast<unsigned*>(bits) + group * x.ec + c, word[i]);
+        atomicAdd(sums + c, __popc(word[i]));
+        word[i] = 0;
+      }
+    }
+  };
   for (int r = warp * kRowsPerWarp + sub; r < tile_rows; r += kTileWarps * kRowsPerWarp) {
     const int64_t row = row0 + r;
     if (row >= x.cell_num) break;  // uniform per row group; later rows were staged as zeros
-    int* p = stage + r * x.pitch;
+    if ((r >> 5) != group) {
+      flush();
+      group = r >> 5;
+    }
+    const int* p = stage + r * x.pitch;
     unsigned key[PER];
 #pragma unroll
     for (int i = 0; i < PER; i++) {
@@ -1063,29 +1087,35 @@ __device__ __forceinline__ void gate_rows_as(const TileCtx& x, int* stage, const
           (g.residual_path % L) == l)
         picked |= 1u << (g.residual_path / L);
     }
-    denom = fmaxf(denom, 1.1920928955078125e-07f);
+    const int rr = r & 31;
 #pragma unroll
-    for (int i = 0; i < PER; i++) {
-      const int c = l + L * i;
-      if (c < cols) {
-        const bool hot = (picked >> i) & 1u;
-        if (g.gates_out != nullptr)
+    for (int i = 0; i < PER; i++) word[i] |= ((picked >> i) & 1u) << rr;
+    if (g.gates_out != nullptr) {
+      denom = fmaxf(denom, 1.1920928955078125e-07f);
+#pragma unroll
+      for (int i = 0; i < PER; i++) {
+        const int c = l + L * i;
+        if (c < cols)
           __stcs(g.gates_out + row * x.path_num + c,
-                 hot ? __fdiv_rn(key_score(key[i]), denom) : 0.f);
-        p[c] = hot ? 1 : 0;
+                 ((picked >> i) & 1u) ? __fdiv_rn(key_score(key[i]), denom) : 0.f);
       }
     }
   }
+  flush();
 }
 
-__device__ __forceinline__ void gate_rows(const TileCtx& x, int* stage, const GateArgs& g) {
+// Decide the routes of a staged tile of scores and leave the result as column bit words in
+// `bits` (zeroed beforehand) and per-path counts added to `sums`: what pack_staged produces
+// from a staged mask, without a mask in between.  The caller passes a CTA barrier next.
+__device__ __forceinline__ void gate_rows(const TileCtx& x, const int* stage, int* bits,
+                                          int* sums, const GateArgs& g) {
   const int cols = x.path_num;  // <= 256, warp-uniform
-  if (cols <= 8) gate_rows_as<1, 8>(x, stage, g);
-  else if (cols <= 16) gate_rows_as<1, 16>(x, stage, g);
-  else if (cols <= 32) gate_rows_as<1, 32>(x, stage, g);
-  else if (cols <= 64) gate_rows_as<2, 32>(x, stage, g);
-  else if (cols <= 128) gate_rows_as<4, 32>(x, stage, g);
-  else gate_rows_as<8, 32>(x, stage, g);
+  if (cols <= 8) gate_rows_as<1, 8>(x, stage, bits, sums, g);
+  else if (cols <= 16) gate_rows_as<1, 16>(x, stage, bits, sums, g);
+  else if (cols <= 32) gate_rows_as<1, 32>(x, stage, bits, sums, g);
+  else if (cols <= 64) gate_rows_as<2, 32>(x, stage, bits, sums, g);
+  else if (cols <= 128) gate_rows_as<4, 32>(x, stage, bits, sums, g);
+  else gate_rows_as<8, 32>(x, stage, bits, sums, g);
 }
 
 // ---------------------------------------------------------------------------- chained path
@@ -1168,14 +1198,15 @@ __global__ void __launch_bounds__(kTileThreads, 2) index_chain_kernel(const Chai
     cp_async_wait<1>();
     __syncthreads();
     x.tile = t;
-    if constexpr (GATED) {  // the staged tile holds scores: decide the routes in place
-      gate_rows(x, stage[i & 1], c.gate);
-      __syncthreads();
-    }
     TileSmem cur = sm;
     cur.tile = stage[i & 1];
     cur.bits = bits_all + (size_t)i * words_per_tile;
-    pack_staged(x, cur, nullptr);
+    if constexpr (GATED) {  // the staged tile holds scores: straight to bit words and counts
+      gate_rows(x, cur.tile, cur.bits, sm.sum, c.gate);
+      __syncthreads();
+    } else {
+      pack_staged(x, cur, nullptr);
+    }
   }
   const int own = tid < cols ? sm.sum[tid] + sm.extra[tid] : 0;
   const bool general = *sm.flag != 0;
