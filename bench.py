@@ -103,7 +103,7 @@ def make_workload(name: str, rank: int = 0, local_bias: float = 0.0, world: int 
 
 
 def algorithmic_bytes(w, idx: np.ndarray, loads: np.ndarray, total_rows: int):
-    """Minimum HBM bytes of each op for this routing (see DESIGN.md): R kept routes, T_r cells
+    """Minimum HBM bytes of each op for this routing: R kept routes, T_r cells
     with at least one kept route, L output rows."""
     T, d, E = w["T"], w["d"], w["E"]
     s = 4 if w["dtype"] == "f32" else 2

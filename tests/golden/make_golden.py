@@ -1,8 +1,8 @@
 """Regenerates the fixtures in this directory from the reference tree.
 
-Run in a container that has the reference project checked out (default
-/root/reference, override with BRT_REFERENCE_ROOT) and the reference extensions built
-by ``python oracle/build.py --ref``:
+Run where the reference project is checked out (its location comes from
+BRT_REFERENCE_ROOT) and the reference extensions have been built by
+``python oracle/build.py --ref``:
 
     python tests/golden/make_golden.py
 

@@ -213,8 +213,8 @@ def test_locality_reorder_rules():
     output column c = input column reorder[c]."""
     m = np.array([[5, 1, 9], [9, 2, 3], [4, 8, 9]], dtype=np.int32)
     out, idx = oracle.locality_reorder(m, 3)
-    # round 1: max 9 first at (0,2) -> reorder[0]=2; round 2: remaining rows 1,2 x cols 0,1:
-    # max 9 at (1,0) -> reorder[1]=0; round 3: (2,1) -> reorder[2]=1
+    # pick 1: max 9 first at (0,2) -> reorder[0]=2; pick 2: remaining rows 1,2 x cols 0,1:
+    # max 9 at (1,0) -> reorder[1]=0; pick 3: (2,1) -> reorder[2]=1
     assert idx.tolist() == [2, 0, 1]
     assert np.array_equal(out, m[:, [2, 0, 1]])
     eye = np.eye(4, dtype=np.int32) * 7
