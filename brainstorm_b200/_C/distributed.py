@@ -297,101 +297,32 @@ def _remember(key: bytes, value) -> None:
         _matrix_cache.pop(next(iter(_matrix_cache)))
 
 
-PHASES = 4  # pushes per exchange; the copy-out of one overlaps the transfer of the next
-
-
-def _phase_ranges(G: int):
-    """Split the local experts [0, G) into at most PHASES contiguous ranges."""
-    k = max(1, min(PHASES, G))
-    cuts = [(G * p) // k for p in range(k + 1)]
-    return [(cuts[p], cuts[p + 1]) for p in range(k) if cuts[p + 1] > cuts[p]]
-
-
 def _sparse_forward_p2p(x, send_sizes, stride, group_size):
-    """Forward packed exchange over peer memory.  The data leaves before the host knows any
-    size: device-planned pushes (one per range of local experts) pack my buckets for rank i
-    into my slot of rank i's arena while the size matrix travels on a side stream.  Once the
-    sizes are on the host (every rank sees the whole matrix, so every rank takes the same
-    decisions) the output is allocated and, range by range as the data arrives, the received
-    buckets are laid out expert-major on the side stream."""
+    """Forward packed exchange over peer memory (planned by the library's exchange context).
+    The data leaves before the host knows any size: device-planned pushes, one per range of
+    local experts, pack my buckets for rank i into my slot of rank i's arena while the size
+    matrix travels on a side stream.  Once the sizes are on the host (every rank sees the
+    whole matrix, so every rank takes the same decisions) the output is allocated and, range
+    by range as the data arrives, the received buckets are laid out expert-major on the side
+    stream."""
     rank, W = _world()
     G = group_size
-    dev = x.device
     arena = p2p.arena()
-    main = torch.cuda.current_stream(dev)
-    stream = main.cuda_stream
-    side = arena.side.cuda_stream
     sizes32 = send_sizes.to(torch.int32).contiguous()
     grain = _row_bytes(x)
-    early = grain > 0 and W * G <= 1024
-    phases = _phase_ranges(G)
-    arena.fork_side()
-    half = arena.begin_exchange()
-    epochs = [arena.push_buckets(x, sizes32, G, grain, stride, lo, hi, stream)
-              for lo, hi in phases] if early else []
-    arena.sizes_begin(sizes32)
-    S = arena.sizes_end().reshape(W, W, G).astype(np.int64)
-    send_np = np.ascontiguousarray(S[rank].reshape(-1).astype(np.int32))
-    recv_np = np.ascontiguousarray(S[:, rank, :].T.reshape(-1).astype(np.int32))  # [G, W]
-    pair_rows = S.sum(axis=2)                                   # [src, dst]
-    np.fill_diagonal(pair_rows, 0)
-    if not early or int(pair_rows.max()) * grain > arena.slot_bytes:
+    arena.forward_begin(x, sizes32, G, grain, stride)
+    S, out_rows, fits = arena.forward_sizes()
+    S3 = S.reshape(W, W, G)
+    send_np = np.ascontiguousarray(S3[rank].reshape(-1))
+    recv_np = np.ascontiguousarray(S3[:, rank, :].T.reshape(-1))            # [G, W]
+    if not fits:
         return None, send_np, recv_np                          # same answer on every rank
-    mine_from = S[:, rank, :]                                   # [src, j] rows bound for me
-    rows = mine_from.T.reshape(-1)                              # expert-major [(j, src)]
-    starts = (np.arange(G * W, dtype=np.int64) * stride) if stride else np.cumsum(rows) - rows
-    out_rows = stride * W * G if stride else int(rows.sum())
     shape = list(x.shape)
     shape[0] = out_rows
-    out = torch.empty(shape, dtype=x.dtype, device=dev)
-    # my own buckets go from x to their place while the pushes are still running
-    own = S[rank].reshape(-1)
-    own_rows = (np.arange(W * G, dtype=np.int64) * stride) if stride else np.cumsum(own) - own
-    local = slice(rank * G, (rank + 1) * G)
-    at_me = starts.reshape(G, W)[:, rank]
-    arena.copy_ranges(x.data_ptr(), own_rows[local] * grain, out.data_ptr() + at_me * grain,
-                      own[local] * grain, side)
-    # the other buckets sit packed per source in that source's slot of my arena half
-    in_slot = (np.cumsum(mine_from, axis=1) - mine_from) * grain            # [src, j]
-    slot_at = half + np.arange(W, dtype=np.int64)[:, None] * arena.slot_bytes
-    src_off = (in_slot + slot_at).T.reshape(-1)                              # [(j, src)]
-    remote = np.tile(np.arange(W), G) != rank
-    nbytes = np.where(remote, rows, 0) * grain
-    dst = out.data_ptr() + starts * grain
-    for (lo, hi), e in zip(phases, epochs):
-        part = slice(lo * W, hi * W)
-        arena.wait_data(e, side)
-        arena.copy_ranges(arena.base, src_off[part], dst[part], nbytes[part], side)
-    main.wait_stream(arena.side)
-    # the inverse exchange is planned now, while this one is still moving data
-    _remember(send_np.tobytes(), (S, _backward_plan(S, rank, W, G, stride)))
+    out = torch.empty(shape, dtype=x.dtype, device=x.device)
+    arena.forward_finish(x, out)
+    _remember(send_np.tobytes(), (S, recv_np))
     return out, send_np, recv_np
-
-
-def _backward_plan(S, rank, W, G, stride):
-    """Row-level placement of the inverse exchange for size matrix ``S`` (no pointers in it,
-    so the forward call can prepare it while its own data is still moving)."""
-    held = S[:, rank, :].T.reshape(-1)                          # expert-major [j*W + i]
-    src_rows = (np.arange(G * W, dtype=np.int64) * stride) if stride else \
-        (np.cumsum(held) - held)
-    flat = S.reshape(W, W * G)                                  # every rank's rank-major sizes
-    rank_major_starts = (np.broadcast_to(np.arange(W * G, dtype=np.int64) * stride, (W, W * G))
-                         if stride else np.cumsum(flat, axis=1) - flat)
-    rows_out = np.full(W, stride * W * G, dtype=np.int64) if stride else S.sum(axis=(1, 2))
-    # what comes back to me, by the expert range it was sent in: bucket (i, j) of my
-    # rank-major layout returns from rank i in the push that covers expert j
-    experts = np.tile(np.arange(G), W)
-    sources = np.repeat(np.arange(W), G)
-    return {
-        "held": held, "src_rows": src_rows, "dst_rank": np.tile(np.arange(W), G),
-        # bucket (j, i) returns to rank i at the start of its bucket (me, j)
-        "dst_rows": np.ascontiguousarray(rank_major_starts[:, rank * G:(rank + 1) * G].T.reshape(-1)),
-        "out_rows": int(rows_out[rank]), "max_rows": int(rows_out.max()),
-        "my_starts": np.ascontiguousarray(rank_major_starts[rank]),
-        "my_rows": np.where(sources != rank, flat[rank], 0),
-        "back_in": [np.flatnonzero((experts >= lo) & (experts < hi)) for lo, hi in _phase_ranges(G)],
-        "expect_send": np.ascontiguousarray(held.astype(np.int32)), "stride": stride,
-    }
 
 
 def _sparse_backward_p2p(x, send_np, recv_np, stride, group_size):
@@ -402,39 +333,20 @@ def _sparse_backward_p2p(x, send_np, recv_np, stride, group_size):
     rank, W = _world()
     G = group_size
     hit = _matrix_cache.get(recv_np.tobytes())
-    if hit is None:
+    if hit is None or not np.array_equal(hit[1], send_np):
         return None
-    S, plan = hit
-    if plan is None or plan["stride"] != stride:
-        plan = _backward_plan(S, rank, W, G, stride)
-        _remember(recv_np.tobytes(), (S, plan))
-    if not np.array_equal(plan["expect_send"], send_np):
-        return None
+    S = hit[0]
     arena = p2p.arena()
     grain = _row_bytes(x)
-    if grain == 0 or plan["max_rows"] * grain > arena.half_bytes:
+    n = W * G
+    out_rows = stride * n if stride else int(np.maximum(S[rank], 0).sum())
+    max_rows = stride * n if stride else int(np.maximum(S, 0).sum(axis=1).max())
+    if grain == 0 or max_rows * grain > arena.half_bytes:
         return None
     shape = list(x.shape)
-    shape[0] = plan["out_rows"]
+    shape[0] = out_rows
     out = torch.empty(shape, dtype=x.dtype, device=x.device)
-    main = torch.cuda.current_stream(x.device)
-    stream = main.cuda_stream
-    side = arena.side.cuda_stream
-    arena.fork_side()
-    half = arena.begin_exchange()
-    src_off = plan["src_rows"] * grain
-    dst = arena.peer_address(plan["dst_rank"], plan["dst_rows"] * grain, local_out=out.data_ptr())
-    nbytes = plan["held"] * grain
-    epochs = []
-    for lo, hi in _phase_ranges(G):
-        part = slice(lo * W, hi * W)
-        epochs.append(arena.push(x, src_off[part], dst[part], nbytes[part], stream))
-    at = plan["my_starts"] * grain
-    back = plan["my_rows"] * grain
-    for e, idx in zip(epochs, plan["back_in"]):
-        arena.wait_data(e, side)
-        arena.copy_ranges(arena.base, half + at[idx], out.data_ptr() + at[idx], back[idx], side)
-    main.wait_stream(arena.side)
+    arena.backward(S, G, grain, stride, x, out)
     return out
 
 

@@ -67,6 +67,13 @@ SIGNATURES = {
     "brt_p2p_post": (_int, [_vp, _int, _int, _int, ctypes.c_uint64, _vp, _vp, _vp]),
     "brt_p2p_exchange_sizes": (_int, [_vp, _int, _int, _int, ctypes.c_uint64, _vp, _vp, _vp, _vp,
                                       _vp, _vp, _vp]),
+    "brt_p2p_ctx_create": (_int, [_int, _int, _vp, _vp, _sz, _vp]),
+    "brt_p2p_ctx_destroy": (None, [_vp]),
+    "brt_p2p_ctx_slot_bytes": (_sz, [_vp]),
+    "brt_p2p_forward_begin": (_int, [_vp, _vp, _vp, _int, _i64, _i64, _vp, _vp]),
+    "brt_p2p_forward_sizes": (_int, [_vp, _vp, _vp, _vp, _vp]),
+    "brt_p2p_forward_finish": (_int, [_vp, _vp, _vp, _vp, _vp]),
+    "brt_p2p_backward": (_int, [_vp, _vp, _int, _i64, _i64, _vp, _vp, _vp, _vp]),
     "brt_p2p_wait": (_int, [_vp, _int, _int, ctypes.c_uint64, _vp, _vp]),
 }
 

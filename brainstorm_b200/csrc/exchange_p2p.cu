@@ -354,10 +354,13 @@ BRT_API int brt_p2p_push(const void* src, int copy_count, const int64_t* src_off
     sig.peer_flags[r] = static_cast<unsigned long long*>(peer_flag_arrays[r]);
   sig.done_counter = static_cast<unsigned int*>(my_done_counter);
   long long grid = chunks;
-  // a flag-less call is a local copy, bound by HBM rather than by a link: fill the SMs
-  const long long cap = (long long)sm_count() * (world_size == 0 ? 8 : push_ctas_per_sm());
+  // a flag-less call is a local copy, bound by HBM rather than by a link; it gets more CTAs
+  // than a push, but not the whole SM: the next push has to find room beside it
+  const long long cap = (long long)sm_count() * (world_size == 0 ? 4 : push_ctas_per_sm());
   if (grid > cap) grid = cap;
   if (grid < 1) grid = 1;
+  const KernelTimer timer(world_size == 0 ? "p2p_copy_kernel" : "p2p_push_kernel",
+                          static_cast<cudaStream_t>(stream));
   p2p_push_kernel<<<(unsigned)grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const char*>(src), list, sig), note_launch();
   BRT_LAUNCH_CHECK("p2p_push_kernel");
@@ -400,6 +403,7 @@ BRT_API int brt_p2p_push_buckets(const void* src, const int32_t* sizes, int worl
     sig.peer_flags[r] = static_cast<unsigned long long*>(peer_flag_arrays[r]);
   }
   sig.done_counter = static_cast<unsigned int*>(my_done_counter);
+  const KernelTimer timer("p2p_push_buckets_kernel", static_cast<cudaStream_t>(stream));
   p2p_push_buckets_kernel<<<(unsigned)(sm_count() * push_ctas_per_sm()), kThreads, 0,
                             static_cast<cudaStream_t>(stream)>>>(
       static_cast<const char*>(src), sizes, plan, sig), note_launch();
@@ -451,6 +455,7 @@ BRT_API int brt_p2p_wait(const void* my_flag_array, int world_size, int skip_ran
   clear_error();
   BRT_REQUIRE(my_flag_array != nullptr && status_word != nullptr, "null control pointers");
   BRT_REQUIRE(world_size >= 1 && world_size <= kMaxRanks, "bad world size %d", world_size);
+  const KernelTimer timer("p2p_wait_kernel", static_cast<cudaStream_t>(stream));
   p2p_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const unsigned long long*>(my_flag_array), world_size, skip_rank, epoch,
       static_cast<int*>(status_word)), note_launch();

@@ -386,6 +386,49 @@ BRT_API int brt_p2p_exchange_sizes(const int32_t* values, int n, int world_size,
 BRT_API int brt_p2p_wait(const void* my_flag_array, int world_size, int skip_rank,
                          uint64_t epoch, void* status_word, void* stream);
 
+/*
+ * Exchange context: the host-side planning of the two sparse exchanges on top of the calls
+ * above, so that a forward or an inverse exchange costs the host a few calls.  It owns the
+ * arena bookkeeping (flag epochs, which half is current, the per-source slots of a half, a
+ * pinned buffer for the size matrix) for an arena whose control block it lays out itself
+ * (flags at 0 and 256, completion counter at 512, status word at 1024, two size boards from
+ * 2048, data halves from 65536).  `arenas[r]` is rank r's arena as mapped in this process
+ * (`my_arena` for r == my_rank).
+ *
+ * brt_p2p_forward_begin   group_sparse_all_to_all, part 1 (src/distributed/collective.cc:
+ *                 142-185 in the reference): enqueues the device-planned pushes of this
+ *                 rank's buckets on `main_stream` and the size exchange on `side_stream`
+ *                 (ordered behind what `main_stream` holds so far).  BRT_ERR_UNSUPPORTED: too
+ *                 many buckets, nothing enqueued.
+ * brt_p2p_forward_sizes   waits for the size exchange; returns the gathered matrix
+ *                 ([sender][destination * group_size + expert] int32, valid until the next
+ *                 begin), this rank's output row count and whether every rank-to-rank share
+ *                 fits its slot (if not, every rank sees the same and the caller moves the
+ *                 rows another way).
+ * brt_p2p_forward_finish  enqueues on `side_stream` the copy of this rank's own buckets and,
+ *                 push by push behind a bounded wait, the expert-major copy-out of what the
+ *                 peers sent into `out`; `main_stream` then waits for `side_stream`.
+ * brt_p2p_backward        size_known_group_sparse_all_to_all (collective.cc:187-224): given
+ *                 the size matrix of the matching forward exchange, pushes every bucket back
+ *                 to its final offset at its owner (own buckets straight into `out`) and
+ *                 copies out what comes back, with the same stream discipline.
+ */
+typedef struct brt_p2p_ctx brt_p2p_ctx;
+BRT_API int brt_p2p_ctx_create(int world_size, int my_rank, void* my_arena,
+                               void* const* arenas, size_t half_bytes, brt_p2p_ctx** out);
+BRT_API void brt_p2p_ctx_destroy(brt_p2p_ctx* ctx);
+BRT_API size_t brt_p2p_ctx_slot_bytes(const brt_p2p_ctx* ctx);
+BRT_API int brt_p2p_forward_begin(brt_p2p_ctx* ctx, const void* rows, const int32_t* sizes,
+                                  int group_size, int64_t grain_bytes, int64_t stride_rows,
+                                  void* main_stream, void* side_stream);
+BRT_API int brt_p2p_forward_sizes(brt_p2p_ctx* ctx, void* side_stream,
+                                  const int32_t** size_matrix, int64_t* out_rows, int* fits);
+BRT_API int brt_p2p_forward_finish(brt_p2p_ctx* ctx, const void* rows, void* out,
+                                   void* main_stream, void* side_stream);
+BRT_API int brt_p2p_backward(brt_p2p_ctx* ctx, const int32_t* size_matrix, int group_size,
+                             int64_t grain_bytes, int64_t stride_rows, const void* rows,
+                             void* out, void* main_stream, void* side_stream);
+
 #ifdef __cplusplus
 }
 #endif
