@@ -40,6 +40,9 @@ WORKLOADS = {
     "cfg3": dict(T=262144, d=768, E=128, k=1, dtype="bf16", seed=3, bias="zipf", cap="ceil2.0",
                  desc="Switch-Base-128-like top-1 bf16, T=262144 d=768 E=128, Zipf-biased "
                       "logits, capacity factor 2.0 with drop"),
+    "cfg3nd": dict(T=262144, d=768, E=128, k=1, dtype="bf16", seed=3, bias="zipf", cap="none",
+                   desc="Switch-Base-128-like top-1 bf16, T=262144 d=768 E=128, Zipf-biased "
+                        "logits, no-drop variant (packed output sized by the generated loads)"),
     "cfg4": dict(T=65536, d=2048, E=64, k=2, dtype="bf16", seed=4, bias="normal1.0", cap="none",
                  desc="expert-parallel top-2 bf16 per GPU T=65536 d=2048 E=64, no capacity"),
 }
@@ -197,7 +200,7 @@ def run_gpu(args):
     from brainstorm_b200.router import GatherRouter, ScatterRouter
     from brainstorm_b200.runtime import distributed as brt_dist
 
-    wl = make_workload(args.workload, rank=rank, world=world)
+    wl = make_workload(args.workload, rank=rank, local_bias=args.local_bias, world=world)
     w = wl["spec"]
     T, d, E = w["T"], w["d"], w["E"]
     cap = wl["cap"]
@@ -423,6 +426,7 @@ def run_gpu(args):
         "eager_ms_per_step": eager_host_ms, "eager_device_ms_per_step": eager_ms,
     }
     if distributed:
+        result["locality"] = measure_locality(loads, world, dev, brt_dist)
         fwd = a2a_bytes[0] * (world - 1) / world
         result["a2a"] = {
             "forward_ms": op_ms["a2a_forward"], "backward_ms": op_ms["a2a_backward"],
@@ -441,6 +445,33 @@ def run_gpu(args):
     if distributed:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def measure_locality(loads, world, dev, brt_dist):
+    """The greedy rank matching on the gathered [W, W, G] load matrix: kernel time (CUDA
+    events, median of 11) and the rows that stay on their own rank before and after it."""
+    import torch.distributed as dist
+    from brainstorm_b200._C import distributed as D
+
+    G = loads.numel() // world
+    mine = loads.to(torch.int32).contiguous()
+    rows = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(rows, mine)
+    matrix = torch.stack(rows).reshape(world, world, G).contiguous()
+    ts = []
+    for _ in range(14):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        reordered, order = D.group_locality_reorder(matrix, world, G)
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b) * 1e3)
+    total = int(matrix.sum())
+    diag = lambda m: int(sum(int(m[i, i].sum()) for i in range(world)))
+    return {"reorder_kernel_us": round(sorted(ts[3:])[5], 2),
+            "local_rows_fraction": round(diag(matrix) / max(total, 1), 4),
+            "local_rows_fraction_after_reorder": round(diag(reordered) / max(total, 1), 4),
+            "reorder_indices": order.tolist()}
 
 
 def measure_gate(wl, dev, w, R, padded, caps):
@@ -702,6 +733,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--local-bias", type=float, default=0.0,
+                    help="added to the logits of a rank's own experts (N>1): 2.0 sends about "
+                         "60%% of the top-2 picks of cfg4 to local experts")
     ap.add_argument("--no-graph", action="store_true",
                     help="time eager launches instead of a CUDA graph replay")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)

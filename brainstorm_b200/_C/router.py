@@ -40,6 +40,11 @@ def _int32c(t: torch.Tensor, name: str) -> torch.Tensor:
     return t if t.is_contiguous() else t.contiguous()
 
 
+def _contig_rows(t: torch.Tensor, cell_size: int) -> torch.Tensor:
+    flat = t.reshape(t.size(0), cell_size)
+    return flat if flat.is_contiguous() else flat.contiguous()
+
+
 class _ScratchPool:
     """One reusable scratch buffer per (device, purpose).  Reuse is safe for calls enqueued
     on the same stream; a different stream gets its own buffer."""
@@ -446,9 +451,18 @@ def combine_with_indices_and_loads(
             # caller's tensor comes back unchanged
             out = out_data
         else:
-            flat = in_data.reshape(in_data.size(0), cell_size)
-            out = torch.zeros((n, cell_size), dtype=in_data.dtype, device=dev)
-            out.index_add_(0, route_indices.reshape(-1).to(torch.int64), flat)
+            flat = _contig_rows(in_data, cell_size)
+            index = route_indices.reshape(-1).to(torch.int32)
+            if index.numel() != flat.size(0):
+                raise RuntimeError("CHECK_EQ fails.")
+            out = torch.empty((n, cell_size), dtype=in_data.dtype, device=dev)
+            if in_data.dtype not in _DT:
+                raise RuntimeError(f"unsupported data type {in_data.dtype}")
+            nbytes = _lib.query("brt_sum_rows_scratch_bytes", flat.size(0), n)
+            scratch = _scratch.get("row_sum", dev, nbytes)
+            _lib.call("brt_sum_rows_by_index", _ptr(flat), _ptr(index), _ptr(out), flat.size(0),
+                      n, cell_size, _DT[in_data.dtype], _ptr(scratch), scratch.numel(),
+                      _stream(dev))
             out = out.reshape((n,) + tuple(in_data.shape[1:]))
             if ever_padded and int(tags_value[0].item()) == 0:
                 out = out.narrow(0, 1, n - 1)

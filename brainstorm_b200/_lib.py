@@ -42,6 +42,8 @@ SIGNATURES = {
                _int, _vp, _sz, _vp]),
     "brt_combine_with_indices_and_loads": (
         _int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _i32, _int, _int, _int, _vp]),
+    "brt_sum_rows_scratch_bytes": (_sz, [_i64, _i64]),
+    "brt_sum_rows_by_index": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
     "brt_locality_reorder": (_int, [_vp, _int, _vp, _vp, _vp]),
     "brt_group_locality_reorder": (_int, [_vp, _int, _int, _vp, _vp, _vp]),
     "brt_nccl_get_unique_id": (_int, [_vp]),

@@ -223,6 +223,21 @@ BRT_API int brt_combine_with_indices_and_loads(
     const int32_t* loads, int64_t cell_num, int64_t cell_size, int path_num,
     int32_t max_path_load, int is_residual, int dtype, int gates_dtype, void* stream);
 
+/*
+ * Sum of rows by destination index: out_rows[o] = sum of in_rows[r] over the rows r with
+ * row_index[r] == o, added in ascending r in fp32 (16-bit types are rounded once); rows of
+ * `out_rows` that nobody points at come back as zeros.  This is the tag-index branch of
+ * combine_with_indices_and_loads, which the reference's binding computes with torch
+ * (scatter_reduce("sum") over the inverse indices of unique(tags),
+ * src/backend/torch/router.cc:449-459) because its launcher has no tag-index combine
+ * (src/router/route.cu:519-521).  Entries of row_index outside [0, rows_out) are ignored.
+ * scratch: brt_sum_rows_scratch_bytes(rows_in, rows_out) bytes, 256-byte aligned.
+ */
+BRT_API size_t brt_sum_rows_scratch_bytes(int64_t rows_in, int64_t rows_out);
+BRT_API int brt_sum_rows_by_index(const void* in_rows, const int32_t* row_index, void* out_rows,
+                                  int64_t rows_in, int64_t rows_out, int64_t cell_size,
+                                  int dtype, void* scratch, size_t scratch_bytes, void* stream);
+
 /* ------------------------------------------------------------------ distributed: rank reorder */
 
 /*

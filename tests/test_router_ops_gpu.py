@@ -345,3 +345,32 @@ def test_notebook_round_trip(R):
     fused2, floads = R.fuse_split_cells_from_paths(datas, is_load_fuse=True, loads=sloads)
     (final2,) = R.combine_with_indices_and_loads(fused2, idx, floads)
     assert torch.equal(final2, 2 * x)
+
+
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("rows_in,rows_out,cell", [(1, 1, 8), (37, 9, 3), (300, 40, 24),
+                                                   (5000, 1200, 64), (256, 64, 4100),
+                                                   (20000, 20000, 16)])
+def test_tag_combine_sums_rows_in_source_order(R, dtype, rows_in, rows_out, cell):
+    """Tag-index combine (src/backend/torch/router.cc:449-459): rows that share an inverse
+    index are added up; this library adds them in ascending source order, in fp32, which the
+    plain loop below restates."""
+    rng = np.random.default_rng(rows_in + rows_out + cell)
+    x32 = rng.standard_normal((rows_in, cell)).astype(np.float32)
+    index = rng.integers(0, rows_out, size=rows_in).astype(np.int64)
+    if rows_out > 2:
+        index[index == 1] = 0                      # destination 1 gets nothing
+    tags = np.arange(1, rows_out + 1, dtype=np.int32)
+    x = torch.from_numpy(x32).to(DTYPES[dtype]).cuda()
+    exp = np.zeros((rows_out, cell), dtype=np.float32)
+    xs = x.float().cpu().numpy()
+    for r in range(rows_in):
+        exp[index[r]] = exp[index[r]] + xs[r]
+    exp_t = torch.from_numpy(exp).to(DTYPES[dtype])
+    out, otags, n = R.combine_with_indices_and_loads(
+        x, torch.from_numpy(index).cuda(), None, tags=torch.from_numpy(tags).cuda(),
+        is_tag_index=True, ever_padded=False)
+    assert n.item() == rows_out and torch.equal(otags.cpu(), torch.from_numpy(tags))
+    assert out.shape == (rows_out, cell)
+    assert torch.equal(out.cpu().view(torch.int16 if dtype != "f32" else torch.int32),
+                       exp_t.view(torch.int16 if dtype != "f32" else torch.int32))
