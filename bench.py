@@ -43,6 +43,11 @@ WORKLOADS = {
     "cfg3nd": dict(T=262144, d=768, E=128, k=1, dtype="bf16", seed=3, bias="zipf", cap="none",
                    desc="Switch-Base-128-like top-1 bf16, T=262144 d=768 E=128, Zipf-biased "
                         "logits, no-drop variant (packed output sized by the generated loads)"),
+    "cfg5": dict(T=64, d=256 * 56 * 56, E=8, k=0, dtype="f32", seed=5, bias="none", cap="none",
+                 protocol="threshold", threshold=0.5,
+                 desc="dynamic-routing threshold router fp32: 64 samples of [256,56,56], 8 "
+                      "branches, sigmoid gates, threshold 0.5, empty routes allowed, samples "
+                      "gathered back by sum (seat-index kernels)"),
     "cfg4": dict(T=65536, d=2048, E=64, k=2, dtype="bf16", seed=4, bias="normal1.0", cap="none",
                  desc="expert-parallel top-2 bf16 per GPU T=65536 d=2048 E=64, no capacity"),
 }
@@ -93,6 +98,12 @@ def make_workload(name: str, rank: int = 0, local_bias: float = 0.0, world: int 
     if local_bias and world > 1:
         G = E // world
         logits[:, rank * G:(rank + 1) * G] += local_bias
+    if w.get("protocol") == "threshold":
+        # python/brt/router/protocol/threshold.py:23-39; every kept route weighs 1
+        score = torch.sigmoid(logits)
+        mask = (score > w["threshold"]).to(torch.int32)
+        return dict(name=name, spec=w, x=x, logits=logits, score=score, mask=mask,
+                    gates=mask.to(torch.float32), cap=capacity_of(w))
     score = torch.softmax(logits, dim=1)
     vals, picks = torch.topk(score, k, dim=1)
     mask = torch.zeros((T, E), dtype=torch.int32).scatter_(1, picks, 1)
@@ -485,20 +496,27 @@ def measure_gate(wl, dev, w, R, padded, caps):
     T, E, k = w["T"], w["E"], w["k"]
     flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev)
 
+    threshold = w.get("threshold") if w.get("protocol") == "threshold" else None
+    decide = dict(decision="threshold", threshold=threshold) if threshold is not None else \
+        dict(decision="topk", top_k=k)
+
     def torch_protocol():
-        picks = torch.topk(score, k, dim=1).indices
-        mask = torch.zeros((T, E), dtype=torch.int32, device=dev).scatter_(1, picks, 1)
+        if threshold is not None:
+            mask = (score > threshold).to(torch.int32)
+        else:
+            picks = torch.topk(score, k, dim=1).indices
+            mask = torch.zeros((T, E), dtype=torch.int32, device=dev).scatter_(1, picks, 1)
         if padded:
             mask, _ = R.throttle_hotmask(mask, torch.zeros(E, dtype=torch.int32, device=dev), caps)
         return R.generate_indices_and_loads(mask, caps)
 
     def gate_kernel():
         if padded:  # decision + throttle in one launch, then the index scan
-            mask, _ = R.route_scores(score, "topk", k, output="throttled_mask",
+            mask, _ = R.route_scores(score, output="throttled_mask",
                                      prefix=torch.zeros(E, dtype=torch.int32, device=dev),
-                                     throttle_capacity=caps)
+                                     throttle_capacity=caps, **decide)
             return R.generate_indices_and_loads(mask, caps)
-        return R.route_scores(score, "topk", k, output="seat_indices")
+        return R.route_scores(score, output="seat_indices", **decide)
 
     def timed(fn):
         for _ in range(3):
@@ -524,7 +542,8 @@ def measure_gate(wl, dev, w, R, padded, caps):
     return {"scores_to_indices_ms": {"torch_protocol_then_index_ops": round(t_torch, 5),
                                      "gate_kernel": round(t_gate, 5)},
             "same_result": bool(torch.equal(i0, i1) and torch.equal(l0, l1)),
-            "launches": {"torch_protocol_then_index_ops": "topk, zeros, scatter_"
+            "launches": {"torch_protocol_then_index_ops":
+                         ("compare, cast" if threshold is not None else "topk, zeros, scatter_")
                          + (", throttle, indices" if padded else ", indices"),
                          "gate_kernel": "route_scores(throttled mask), indices" if padded
                          else "route_scores(seat indices)"}}
@@ -543,8 +562,12 @@ def measure_e2e(wl, dev, args, ScatterRouter, GatherRouter, distributed, world):
     fkw = {"max_path_padding": padded, "max_path_load": cap}
     if padded:
         fkw["supported_capacities"] = [cap]
-    scatter = ScatterRouter(protocol_type="topk", fabric_type=f"{kind}_dispatch",
-                            protocol_kwargs={"top_k": w["k"]}, fabric_kwargs=fkw).to(dev)
+    if w.get("protocol") == "threshold":
+        proto, pkw = "threshold", {"threshold": w["threshold"]}
+    else:
+        proto, pkw = "topk", {"top_k": w["k"]}
+    scatter = ScatterRouter(protocol_type=proto, fabric_type=f"{kind}_dispatch",
+                            protocol_kwargs=pkw, fabric_kwargs=fkw).to(dev)
     gather = GatherRouter(fabric_type=f"{kind}_combine",
                           fabric_kwargs={"transform": True, "max_path_padding": padded}).to(dev)
     x_h = wl["x"].pin_memory()
@@ -626,7 +649,7 @@ def measure_e2e(wl, dev, args, ScatterRouter, GatherRouter, distributed, world):
     d2h = out_h.numel() * out_h.element_size()
     return {"value": world * T / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms,
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-            "api": "ScatterRouter(topk, fused_dispatch) -> GatherRouter(fused_combine)",
+            "api": f"ScatterRouter({proto}, fused_dispatch) -> GatherRouter(fused_combine)",
             "schedule": "copy-in, route and copy-out of consecutive steps overlap (2 slots)",
             "serial_ms_per_step": serial_ms,
             "serial_value": world * T / (serial_ms * 1e-3)}

@@ -654,26 +654,48 @@ __global__ void __launch_bounds__(kThreads, 3) combine_seat_async_kernel(const M
         store_stream(dp + u * 32, pack_chunk<VB, DT>(acc));
       }
     } else if (count > kMaxRoutes) {
-      // more routes than the staging area holds: walk the index row for the rest
+      // More routes than the staging area holds: the rest is fetched straight from global
+      // memory, two 512-byte chunks of the piece at a time; the loads of a route are issued
+      // before the previous route is folded, so one route's latency hides behind the other's
+      // arithmetic.  The order stays ascending in the path index.
 #pragma unroll 1
-      for (int u = 0; u < kFoldUnroll; u++) {
-        const int v = u * 32 + lane;
-        if (first + v >= a.row_vecs) continue;
-        float acc[L::N];
+      for (int h = 0; h < kFoldUnroll; h += 2) {
+        const int v0 = h * 32 + lane, v1 = v0 + 32;
+        const bool in0 = first + v0 < a.row_vecs, in1 = first + v1 < a.row_vecs;
+        float acc0[L::N], acc1[L::N];
 #pragma unroll
-        for (int n = 0; n < L::N; n++) acc[n] = 0.f;
-        fold_chunk<VB, DT, GMODE>(acc, r0[u * 32], g0);
-        fold_chunk<VB, DT, GMODE>(acc, r1[u * 32], g1);
+        for (int n = 0; n < L::N; n++) acc0[n] = acc1[n] = 0.f;
+        fold_chunk<VB, DT, GMODE>(acc0, r0[h * 32], g0);
+        fold_chunk<VB, DT, GMODE>(acc1, r0[h * 32 + 32], g0);
+        fold_chunk<VB, DT, GMODE>(acc0, r1[h * 32], g1);
+        fold_chunk<VB, DT, GMODE>(acc1, r1[h * 32 + 32], g1);
+        V held0 = zero_chunk<V>(), held1 = zero_chunk<V>();
+        float held_gate = 0.f;
+        bool pending = false;
         int seen = 0;
         for (int e = 0; e < E; e++) {
           const int s = a.indices[cell * E + e];
           if (s <= 0 || s > s_loads[e]) continue;
           if (seen++ < kMaxRoutes) continue;
-          const V row =
-              load_stream(src + ((int64_t)s_base[e] + s - 1) * a.row_vecs + first + v);
-          fold_chunk<VB, DT, GMODE>(acc, row, gate_at<DT, GMODE>(a.gates, cell * E + e));
+          const V* rp = src + ((int64_t)s_base[e] + s - 1) * a.row_vecs + first;
+          const V next0 = in0 ? load_stream(rp + v0) : zero_chunk<V>();
+          const V next1 = in1 ? load_stream(rp + v1) : zero_chunk<V>();
+          const float next_gate = gate_at<DT, GMODE>(a.gates, cell * E + e);
+          if (pending) {
+            fold_chunk<VB, DT, GMODE>(acc0, held0, held_gate);
+            fold_chunk<VB, DT, GMODE>(acc1, held1, held_gate);
+          }
+          held0 = next0;
+          held1 = next1;
+          held_gate = next_gate;
+          pending = true;
         }
-        store_stream(dp + u * 32, pack_chunk<VB, DT>(acc));
+        if (pending) {
+          fold_chunk<VB, DT, GMODE>(acc0, held0, held_gate);
+          fold_chunk<VB, DT, GMODE>(acc1, held1, held_gate);
+        }
+        if (in0) store_stream(dp + h * 32, pack_chunk<VB, DT>(acc0));
+        if (in1) store_stream(dp + h * 32 + 32, pack_chunk<VB, DT>(acc1));
       }
     }
     __syncwarp();
