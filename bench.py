@@ -247,8 +247,9 @@ def run_gpu(args):
             rec(4)
             routed = brt_dist.size_known_group_sparse_a2a(recv, out_loads, in_loads, padded)
             rec(5)
-            a2a_bytes[0] = int(in_loads.sum()) * d * x.element_size() if not padded else \
-                int(routed.numel() * x.element_size())
+            # rows this rank really sends to OTHER ranks (in_loads: my send sizes, [W, G])
+            sent = in_loads.reshape(world, -1)
+            a2a_bytes[0] = int(sent.sum() - sent[rank].sum()) * d * x.element_size()
         else:
             rec(4)
             rec(5)
@@ -438,10 +439,10 @@ def run_gpu(args):
     }
     if distributed:
         result["locality"] = measure_locality(loads, world, dev, brt_dist)
-        fwd = a2a_bytes[0] * (world - 1) / world
+        fwd = a2a_bytes[0]
         result["a2a"] = {
             "forward_ms": op_ms["a2a_forward"], "backward_ms": op_ms["a2a_backward"],
-            "bytes_per_rank_per_direction": a2a_bytes[0],
+            "remote_bytes_per_rank_per_direction": a2a_bytes[0],
             "bus_gbs_forward": fwd / (op_ms["a2a_forward"] * 1e-3) / 1e9,
             "bus_gbs_backward": fwd / (op_ms["a2a_backward"] * 1e-3) / 1e9,
             "nvlink_peak_gbs_per_direction": 900.0,
