@@ -46,7 +46,8 @@ def main():
         pass
 
     # ---- packed (sparse) exchange, forward and back, for G local experts
-    for G, d, hi in ((1, 8, 40), (2, 16, 30), (4, 5, 12)):
+    # (d = 5 floats is not a 16-byte multiple: that case takes the NCCL transport either way)
+    for G, d, hi in ((1, 8, 40), (2, 16, 30), (4, 5, 12), (4, 8, 12), (3, 4, 20), (5, 12, 7)):
         all_in = [rank_inputs(r, W, G, d, hi) for r in range(W)]
         fwd = oracle.sim_group_sparse_all_to_all([a[0] for a in all_in], [a[1] for a in all_in])
         x, sizes = all_in[rank]
@@ -59,19 +60,22 @@ def main():
         back = brt_dist.size_known_group_sparse_a2a(out, out_loads, in_loads)
         assert np.array_equal(back.cpu().numpy(), x), f"rank {rank} round trip G={G}"
     # padded buckets
-    G, d, stride = 2, 4, 16
-    all_in = [rank_inputs(r, W, G, d, stride + 1, stride) for r in range(W)]
-    x, sizes = all_in[rank]
-    out, out_loads, in_loads = brt_dist.group_sparse_a2a(
-        torch.from_numpy(x).to(dev), torch.from_numpy(sizes).to(dev), True, stride)
-    fwd = oracle.sim_group_sparse_all_to_all([a[0] for a in all_in], [a[1] for a in all_in],
-                                             True, stride)
-    o = out.cpu().numpy()
-    for b, n in enumerate(out_loads.numpy()):
-        assert np.array_equal(o[b * stride:b * stride + n], fwd[rank][0][b * stride:b * stride + n])
-    back = brt_dist.size_known_group_sparse_a2a(out, out_loads, in_loads, True).cpu().numpy()
-    for b, n in enumerate(sizes):
-        assert np.array_equal(back[b * stride:b * stride + n], x[b * stride:b * stride + n])
+    for G, d, stride in ((2, 4, 16), (3, 8, 10), (1, 4, 7)):
+        all_in = [rank_inputs(r, W, G, d, stride + 1, stride) for r in range(W)]
+        x, sizes = all_in[rank]
+        out, out_loads, in_loads = brt_dist.group_sparse_a2a(
+            torch.from_numpy(x).to(dev), torch.from_numpy(sizes).to(dev), True, stride)
+        fwd = oracle.sim_group_sparse_all_to_all([a[0] for a in all_in],
+                                                 [a[1] for a in all_in], True, stride)
+        o = out.cpu().numpy()
+        for b, n in enumerate(out_loads.numpy().reshape(-1)):
+            assert np.array_equal(o[b * stride:b * stride + n],
+                                  fwd[rank][0][b * stride:b * stride + n]), (G, b)
+        back = brt_dist.size_known_group_sparse_a2a(out, out_loads, in_loads,
+                                                    True).cpu().numpy()
+        for b, n in enumerate(sizes):
+            assert np.array_equal(back[b * stride:b * stride + n],
+                                  x[b * stride:b * stride + n]), (G, b)
 
     # ---- padded-slot exchange with the locality tail
     for G in (1, 2):
