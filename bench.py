@@ -136,6 +136,21 @@ def algorithmic_bytes(w, idx: np.ndarray, loads: np.ndarray, total_rows: int):
     }
 
 
+def config_of(name: str, world: int) -> dict:
+    """The `config` object of the JSON line; both arms print the same one."""
+    w = WORKLOADS[name]
+    s = 4 if w["dtype"] == "f32" else 2
+    distributed = world > 1
+    return {"workload": f"{name}: {w['desc']}",
+            "step": "throttle + seat indices/loads + dispatch + "
+                    + ("sparse all-to-all forward and back + " if distributed else "")
+                    + "weighted combine",
+            "l2": "inputs and outputs of a step exceed the 126 MB L2"
+                  if (w["T"] * w["d"] * s * 3) > 126e6 else
+                  "working set fits in L2; numbers are L2-assisted",
+            "parallelism": f"ep{world}" if distributed else "single"}
+
+
 # --------------------------------------------------------------------------------- clocks
 class ClockSampler:
     """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
@@ -383,14 +398,21 @@ def run_gpu(args):
                     "combine_kernel": ab["combine"]}
     device_kernels = {}
     for name, t in timed.items():
-        if name not in kernel_bytes or t["launches"] == 0:
+        if t["launches"] == 0:
+            continue
+        if name.startswith("p2p_"):  # exchange kernels: bound by NVLink, not by HBM
+            device_kernels[name] = {"launches": t["launches"],
+                                    "ms": round(t["total_ms"] / t["launches"], 5)}
+            continue
+        if name not in kernel_bytes:
             continue
         ms = t["total_ms"] / t["launches"]
         gbs = kernel_bytes[name] / (ms * 1e-3) / 1e9 if ms > 0 else 0.0
         device_kernels[name] = {"launches": t["launches"], "ms": round(ms, 5),
                                 "algorithmic_bytes": kernel_bytes[name],
                                 "achieved_gbs": round(gbs, 1), "frac": round(gbs / peak, 4)}
-    dominant = max(device_kernels, key=lambda n: device_kernels[n]["ms"])
+    dominant = max((n for n in device_kernels if not n.startswith("p2p_")),
+                   key=lambda n: device_kernels[n]["ms"])
     dominant_op = {"dispatch_move_kernel": "dispatch", "dispatch_zero_fill_kernel": "dispatch",
                    "combine_kernel": "combine"}.get(dominant, "indices")
 
@@ -406,14 +428,7 @@ def run_gpu(args):
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
-        "config": {"workload": f"{args.workload}: {w['desc']}",
-                   "step": "throttle + seat indices/loads + dispatch + "
-                           + ("sparse all-to-all forward and back + " if distributed else "")
-                           + "weighted combine",
-                   "l2": "inputs and outputs of a step exceed the 126 MB L2"
-                         if (T * d * x.element_size() * 3) > 126e6 else
-                         "working set fits in L2; numbers are L2-assisted",
-                   "parallelism": f"ep{world}" if distributed else "single"},
+        "config": config_of(args.workload, world),
         "dispatch_combine_only": {"tokens_per_s": world * T / (dc_ms * 1e-3), "ms": dc_ms},
         "roofline": {"bound": "hbm", "kernel": dominant,
                      "achieved": device_kernels[dominant]["achieved_gbs"], "peak": peak,
@@ -438,15 +453,39 @@ def run_gpu(args):
         "eager_ms_per_step": eager_host_ms, "eager_device_ms_per_step": eager_ms,
     }
     if distributed:
+        result["checks"] = exchange_checks(dev, rank, world, x, mask, gates, caps, cap, padded,
+                                           R, brt_dist)
+        plain = measure_a2a_cfg4(dev, rank, world, R, brt_dist, 0.0)
+        plain.pop("loads_rank")
+        result["a2a_cfg4"] = plain
+        skewed = measure_a2a_cfg4(dev, rank, world, R, brt_dist, 2.0)
+        skew_loads = skewed.pop("loads_rank")
+        skewed["locality"] = measure_locality(skew_loads, world, dev, brt_dist)
+        result["locality_cfg4"] = skewed
+        result["checks"]["a2a_cfg4_round_trip_bit_exact"] = bool(
+            plain["round_trip_bit_exact"] and skewed["round_trip_bit_exact"])
         result["locality"] = measure_locality(loads, world, dev, brt_dist)
         fwd = a2a_bytes[0]
+        land = device_kernels.get("p2p_land_forward_kernel")
+        if land is not None and land["ms"] > 0:
+            # at N > 1 the step is bound by the exchange: its landing kernel against NVLink
+            gbs = fwd / (land["ms"] * 1e-3) / 1e9
+            result["roofline_hbm_kernel"] = result["roofline"]
+            result["roofline"] = {
+                "bound": "nvlink", "kernel": "p2p_land_forward_kernel", "achieved": round(gbs, 1),
+                "peak": 900.0, "unit": "GB/s", "frac": round(gbs / 900.0, 4), "traffic": None,
+                "peak_kind": "nominal NVLink 5 bandwidth per direction per GPU; a peer copy "
+                             "on this pool measures 770 GB/s",
+                "frac_of_measured_peer_copy": round(gbs / 770.0, 4),
+                "timing": "CUDA events around each launch of the kernel, on its stream; "
+                          "bytes = what this rank sends to other ranks in one exchange"}
         result["a2a"] = {
             "forward_ms": op_ms["a2a_forward"], "backward_ms": op_ms["a2a_backward"],
             "remote_bytes_per_rank_per_direction": a2a_bytes[0],
             "bus_gbs_forward": fwd / (op_ms["a2a_forward"] * 1e-3) / 1e9,
             "bus_gbs_backward": fwd / (op_ms["a2a_backward"] * 1e-3) / 1e9,
             "nvlink_peak_gbs_per_direction": 900.0,
-            "transport": "peer-memory push kernels over NVLink"
+            "transport": "peer-memory landing kernels over NVLink"
                          if __import__("brainstorm_b200.runtime.p2p", fromlist=["arena"]).arena()
                          is not None else "nccl send/recv",
         }
@@ -454,9 +493,158 @@ def run_gpu(args):
         result["cpu_baseline"] = cpu_baseline(wl, budget_s=args.cpu_seconds)
     if rank == 0:
         print(json.dumps(result))
+    failed = distributed and not all(v for v in result["checks"].values() if isinstance(v, bool))
     if distributed:
         dist.barrier()
         dist.destroy_process_group()
+    if failed:
+        raise SystemExit("bench.py: an exchange check failed (see \"checks\" in the line above)")
+
+
+def exchange_checks(dev, rank, world, x, mask, gates, caps, cap, padded, R, brt_dist):
+    """Correctness of the expert-parallel step on THIS run's ranks, outside any timed region:
+    (1) the round trip forward -> inverse returns the dispatched rows bit for bit;
+    (2) every row lands where the reference's walk puts it (src/distributed/collective.cc:
+        142-182): rows that carry (source rank, source row) are exchanged and the receiver
+        checks each [local expert][source] segment against the size matrix of all ranks;
+    (3) the step's output equals the same step without any exchange (identity expert).
+    Every verdict is the AND over all ranks."""
+    import torch.distributed as dist
+
+    m = mask
+    if padded:
+        m, _ = R.throttle_hotmask(mask, torch.zeros_like(caps), caps)
+    idx, loads = R.generate_indices_and_loads(m, caps)
+    (routed,) = R.dispatch_with_indices_and_loads(x, idx, loads, None, False, None, padded, cap)
+    (local_out,) = R.combine_with_indices_and_loads(routed, idx, loads, gates, None, padded)
+    recv, out_loads, in_loads = brt_dist.group_sparse_a2a(routed, loads, padded, cap)
+    back = brt_dist.size_known_group_sparse_a2a(recv, out_loads, in_loads, padded)
+    round_trip = bool(torch.equal(back, routed))
+    (ep_out,) = R.combine_with_indices_and_loads(back, idx, loads, gates, None, padded)
+    same_as_local = bool(torch.equal(ep_out, local_out))
+
+    # (2) landing layout, with 16-byte rows that name their origin
+    E = loads.numel()
+    G = E // world
+    n_rows = routed.size(0)
+    ident = torch.empty((n_rows, 4), dtype=torch.int32, device=dev)
+    ident[:, 0] = rank
+    ident[:, 1] = torch.arange(n_rows, dtype=torch.int32, device=dev)
+    ident[:, 2:] = 0
+    got, _, _ = brt_dist.group_sparse_a2a(ident, loads, padded, cap)
+    all_loads = [torch.empty_like(loads) for _ in range(world)]
+    dist.all_gather(all_loads, loads.contiguous())
+    S = torch.stack(all_loads).cpu().numpy().astype(np.int64)       # [source][global expert]
+    starts = np.zeros_like(S)
+    if padded:
+        starts[:] = np.arange(E)[None, :] * cap
+    else:
+        starts[:, 1:] = np.cumsum(S, axis=1)[:, :-1]
+    want_rank, want_row, at = [], [], []
+    cursor = 0
+    for j in range(G):
+        for src in range(world):
+            e = rank * G + j
+            cnt = int(min(S[src, e], cap) if padded else S[src, e])
+            want_rank.append(np.full(cnt, src, dtype=np.int32))
+            want_row.append(starts[src, e] + np.arange(cnt))
+            at.append((cursor if not padded else (j * world + src) * cap) + np.arange(cnt))
+            cursor += cnt
+    at = torch.from_numpy(np.concatenate(at)).to(dev)
+    want_rank = torch.from_numpy(np.concatenate(want_rank)).to(dev)
+    want_row = torch.from_numpy(np.concatenate(want_row).astype(np.int32)).to(dev)
+    rows_ok = got.size(0) == (E * cap if padded else cursor)
+    layout = bool(rows_ok and torch.equal(got[at, 0], want_rank)
+                  and torch.equal(got[at, 1], want_row))
+    verdict = torch.tensor([int(round_trip), int(layout), int(same_as_local)], device=dev)
+    dist.all_reduce(verdict, op=dist.ReduceOp.MIN)
+    v = verdict.tolist()
+    return {"round_trip_bit_exact": bool(v[0]), "forward_layout_matches_reference_walk": bool(v[1]),
+            "step_equals_single_rank_step": bool(v[2]), "ranks": world,
+            "rows_exchanged_per_rank": int(n_rows)}
+
+
+def measure_a2a_cfg4(dev, rank, world, R, brt_dist, local_bias: float, iters: int = 10):
+    """The exchange the metric's all-to-all figure is quoted on (cfg4: T = 65536 tokens per
+    rank, d = 2048 bf16, 64 experts, top-2, packed buckets), forward and back, with the timing
+    protocol of benchmark/micro/distributed/sparse_a2a.py:53-100: CUDA events around
+    group_sparse_a2a and size_known_group_sparse_a2a, host work of the calls included.
+    Bus GB/s = bytes this rank sends to OTHER ranks / time; the slowest rank counts.
+    ``local_bias`` > 0 skews each rank's picks towards its own experts
+    (benchmark/micro/distributed/placement_a2a.py:54-80 measures that case)."""
+    import torch.distributed as dist
+    from brainstorm_b200 import _lib as brt_lib
+
+    w = WORKLOADS["cfg4"]
+    T, d, E, k = w["T"], w["d"], w["E"], w["k"]
+    G = E // world
+    g = torch.Generator(device="cpu").manual_seed(4000 + rank)
+    gb = torch.Generator(device="cpu").manual_seed(4999)
+    logits = torch.randn((T, E), generator=g) + torch.randn((E,), generator=gb)
+    if local_bias:
+        logits[:, rank * G:(rank + 1) * G] += local_bias
+    picks = torch.topk(logits, k, dim=1).indices
+    mask = torch.zeros((T, E), dtype=torch.int32).scatter_(1, picks, 1).to(dev)
+    _, loads = R.generate_indices_and_loads(mask)
+    rows = int(loads.sum().item())
+    x = torch.empty((rows, d), dtype=torch.bfloat16, device=dev).normal_()
+    sent = loads.reshape(world, G).sum(dim=1)
+    remote = int((sent.sum() - sent[rank]).item()) * d * 2
+
+    def once(record=None):
+        if record:
+            record[0].record()
+        recv, out_loads, in_loads = brt_dist.group_sparse_a2a(x, loads)
+        if record:
+            record[1].record()
+        back = brt_dist.size_known_group_sparse_a2a(recv, out_loads, in_loads)
+        if record:
+            record[2].record()
+        return back
+
+    for _ in range(3):
+        back = once()
+    ok = bool(torch.equal(back, x))
+    dist.barrier()
+    torch.cuda.synchronize()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(iters)]
+    brt_lib.query("brt_profile_enable", 1)
+    for i in range(iters):
+        once(evs[i])
+    torch.cuda.synchronize()
+    brt_lib.query("brt_profile_enable", 0)
+    import ctypes
+    report = ctypes.create_string_buffer(8192)
+    brt_lib.call("brt_profile_report", report, len(report))
+    timed = json.loads(report.value.decode())
+    fwd = statistics.mean(e[0].elapsed_time(e[1]) for e in evs)
+    bwd = statistics.mean(e[1].elapsed_time(e[2]) for e in evs)
+    stats = torch.tensor([fwd, bwd, -float(remote), float(ok)], device=dev, dtype=torch.float64)
+    dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    fwd, bwd, min_remote, _ = stats.tolist()
+    all_ok = torch.tensor([int(ok)], device=dev)
+    dist.all_reduce(all_ok, op=dist.ReduceOp.MIN)
+    min_remote = -min_remote
+    kernels = {name: round(t["total_ms"] / max(t["launches"], 1), 5)
+               for name, t in timed.items() if name.startswith("p2p_")}
+    from brainstorm_b200.runtime import p2p
+    return {
+        "workload": "cfg4 exchange: T=65536 per rank, d=2048 bf16, E=64, top-2, packed buckets"
+                    + (f", logits of a rank's own experts +{local_bias}" if local_bias else ""),
+        "forward_ms": fwd, "backward_ms": bwd, "iterations": iters,
+        "remote_bytes_per_rank_per_direction": remote,
+        "bus_gbs_forward": min_remote / (fwd * 1e-3) / 1e9,
+        "bus_gbs_backward": min_remote / (bwd * 1e-3) / 1e9,
+        "frac_of_900_forward": min_remote / (fwd * 1e-3) / 1e9 / 900.0,
+        "frac_of_900_backward": min_remote / (bwd * 1e-3) / 1e9 / 900.0,
+        "bytes_note": "bus figures use the rank that sends the FEWEST remote bytes and the "
+                      "slowest rank's time",
+        "kernel_ms_rank0": kernels,
+        "round_trip_bit_exact": bool(all_ok.item()),
+        "transport": "peer-memory landing kernels over NVLink" if p2p.arena() is not None
+                     else "nccl send/recv",
+        "loads_rank": loads,
+    }
 
 
 def measure_locality(loads, world, dev, brt_dist):
@@ -722,10 +910,10 @@ def run_reference(args):
         xt.view(torch.int16).numpy().view(np.uint16)
     wl["mask_np"] = wl["mask"].numpy()
     wl["gates_np"] = wl["gates"].numpy()
-    warm = max(1, min(args.warmup, 3))
+    warm = max(args.warmup, 3)  # the same rule as the GPU arm
     for _ in range(warm):
         cpu_pass(wl, oracle)
-    steps = max(1, min(args.steps, 20))
+    steps = max(1, args.steps)
     t0 = time.perf_counter()
     for _ in range(steps):
         cpu_pass(wl, oracle)
@@ -736,14 +924,14 @@ def run_reference(args):
         "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"],
         "data": "synthetic",
-        "config": {"workload": f"{args.workload}: {w['desc']}",
-                   "step": "throttle + seat indices/loads + dispatch + weighted combine",
-                   "note": "the reference has no CPU implementation of its fused router ops "
-                           "(every op asserts CUDA tensors); this is its algorithm restated in "
-                           "C + OpenMP (oracle/), on all host cores"},
+        "config": config_of(args.workload, max(1, args.gpus)),
         "cpu_baseline": {"value": value, "unit": UNIT,
                          "cores": min(cores, oracle.max_threads()), "kind": "port",
-                         "sample": f"whole batch of {w['T']} tokens per step, {steps} steps"},
+                         "sample": f"whole batch of {w['T']} tokens per step, {steps} steps",
+                         "note": "the reference has no CPU implementation of its fused router "
+                                 "ops (every op asserts CUDA tensors); this is its algorithm "
+                                 "restated in C + OpenMP (oracle/), on all host cores, one "
+                                 "rank's batch"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))

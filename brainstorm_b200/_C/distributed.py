@@ -270,9 +270,6 @@ def _sparse_a2a(x, send_np, recv_np, stride_rows, out_rows, group_size, forward)
     return out
 
 
-_matrix_cache = {}
-
-
 def _row_bytes(x: torch.Tensor) -> int:
     """Bytes of one row (the same on every rank, even on one that holds no rows)."""
     n = x.element_size()
@@ -282,90 +279,63 @@ def _row_bytes(x: torch.Tensor) -> int:
 
 
 def _p2p_usable(x: torch.Tensor, world: int, group_size: int) -> bool:
+    """Whether the peer-memory exchange can move ``x``.  Only facts that are the same on every
+    rank decide (arena present, bucket count, row size), so all ranks take the same path."""
     a = p2p.arena()
-    if a is None or world * group_size > p2p.MAX_COPIES or x.dim() < 1:
+    if a is None or not p2p.buckets_supported(world, group_size) or x.dim() < 1:
         return False
     row_bytes = _row_bytes(x)
-    return row_bytes > 0 and row_bytes % 16 == 0 and x.data_ptr() % 16 == 0
+    if row_bytes <= 0 or row_bytes % 16 != 0:
+        return False
+    if x.data_ptr() % 16 != 0:
+        raise RuntimeError("rows of the peer exchange must start on a 16-byte boundary")
+    return True
 
 
-def _remember(key: bytes, value) -> None:
-    """Keep the size matrices of the most recent forward exchanges (for their inverses)."""
-    _matrix_cache.pop(key, None)
-    _matrix_cache[key] = value
-    while len(_matrix_cache) > 16:
-        _matrix_cache.pop(next(iter(_matrix_cache)))
+_TAG = "_brt_exchange"
 
 
-def _sparse_forward_p2p(x, send_sizes, stride, group_size):
-    """Forward packed exchange over peer memory (planned by the library's exchange context).
-    The data leaves before the host knows any size: device-planned pushes, one per range of
-    local experts, pack my buckets for rank i into my slot of rank i's arena while the size
-    matrix travels on a side stream.  Once the sizes are on the host (every rank sees the
-    whole matrix, so every rank takes the same decisions) the output is allocated and, range
-    by range as the data arrives, the received buckets are laid out expert-major on the side
-    stream."""
-    rank, W = _world()
-    G = group_size
-    arena = p2p.arena()
-    sizes32 = send_sizes.to(torch.int32).contiguous()
-    grain = _row_bytes(x)
-    arena.forward_begin(x, sizes32, G, grain, stride)
-    S, out_rows, fits = arena.forward_sizes()
-    S3 = S.reshape(W, W, G)
-    send_np = np.ascontiguousarray(S3[rank].reshape(-1))
-    recv_np = np.ascontiguousarray(S3[:, rank, :].T.reshape(-1))            # [G, W]
-    if not fits:
-        return None, send_np, recv_np                          # same answer on every rank
-    shape = list(x.shape)
-    shape[0] = out_rows
-    out = torch.empty(shape, dtype=x.dtype, device=x.device)
-    arena.forward_finish(x, out)
-    _remember(send_np.tobytes(), (S, recv_np))
-    return out, send_np, recv_np
-
-
-def _sparse_backward_p2p(x, send_np, recv_np, stride, group_size):
-    """Inverse exchange; the size matrix of the matching forward call is reused, so nothing
-    is exchanged or synchronised before the data moves.  Host-planned pushes (one per range
-    of local experts) write every bucket at its final offset inside the owner's arena half;
-    the owner copies each range out on a side stream while the next one is still moving."""
-    rank, W = _world()
-    G = group_size
-    hit = _matrix_cache.get(recv_np.tobytes())
-    if hit is None or not np.array_equal(hit[1], send_np):
-        return None
-    S = hit[0]
-    arena = p2p.arena()
-    grain = _row_bytes(x)
-    n = W * G
-    out_rows = stride * n if stride else int(np.maximum(S[rank], 0).sum())
-    max_rows = stride * n if stride else int(np.maximum(S, 0).sum(axis=1).max())
-    if grain == 0 or max_rows * grain > arena.half_bytes:
-        return None
-    shape = list(x.shape)
-    shape[0] = out_rows
-    out = torch.empty(shape, dtype=x.dtype, device=x.device)
-    arena.backward(S, G, grain, stride, x, out)
-    return out
+def _landed(arena, ptr: int, rows: int, like: torch.Tensor) -> torch.Tensor:
+    out = arena.view(ptr, rows, like)
+    return out if p2p.ZERO_COPY else out.clone()
 
 
 def group_sparse_all_to_all(in_data: torch.Tensor, send_sizes: torch.Tensor,
                             max_path_padding: bool = False, max_path_load: int = 0):
-    """(out_data, recv_sizes [G, W] on CPU, send_sizes [W, G] on CPU)."""
+    """(out_data, recv_sizes [G, W] on CPU, send_sizes [W, G] on CPU).
+
+    Over the peer-memory transport ``out_data`` is a view of this rank's landing half (see
+    ``brainstorm_b200.runtime.p2p``), and both size tensors carry the identifier of the
+    exchange, which is how ``size_known_group_sparse_all_to_all`` finds the size matrix that
+    every rank kept for the way back."""
     _check_cuda(in_data, "in_data")
     _check_cuda(send_sizes, "send_sizes")
-    _, W = _world()
+    rank, W = _world()
     group_size = send_sizes.numel() // W
     with torch.cuda.device(in_data.device):
         x = _contig(in_data)
         if _p2p_usable(x, W, group_size) and not (max_path_padding and not max_path_load):
+            # The rows leave before the host knows any size: the landing kernel reads the size
+            # matrix from the boards on the device.  The host only waits for the matrix (to
+            # shape the output and to return the CPU size tensors of the reference's API).
+            arena = p2p.arena()
             stride = int(max_path_load) if max_path_padding else 0
-            out, send_np, recv_np = _sparse_forward_p2p(x, send_sizes, stride, group_size)
-            if out is None:  # does not fit the arena: NCCL, sizes already known
+            x = arena.safe_source(x)
+            sizes32 = send_sizes.to(torch.int32).contiguous()
+            S, out_rows, fits, ptr, xid = arena.sparse_forward(x, sizes32, group_size,
+                                                               _row_bytes(x), stride)
+            S3 = S.reshape(W, W, group_size)
+            send_np = np.ascontiguousarray(S3[rank].reshape(-1))
+            recv_np = np.ascontiguousarray(S3[:, rank, :].T.reshape(-1))      # [G, W]
+            if fits:
+                out = _landed(arena, ptr, out_rows, x)
+            else:  # some rank's rows exceed its landing half: NCCL on every rank, sizes known
                 rows = a2a_plan.total_rows(recv_np, stride)
                 out = _sparse_a2a(x, send_np, recv_np, stride, rows, group_size, True)
-            return [out, torch.from_numpy(recv_np.copy()), torch.from_numpy(send_np.copy())]
+            recv_t, send_t = torch.from_numpy(recv_np), torch.from_numpy(send_np)
+            setattr(recv_t, _TAG, (xid, group_size))
+            setattr(send_t, _TAG, (xid, group_size))
+            return [out, recv_t, send_t]
         recv_dev = _exchange_sizes(send_sizes.to(torch.int32))
         send_np, recv_np = _host_sizes(send_sizes, recv_dev)
         recv_np = a2a_plan.to_expert_major(recv_np, W)
@@ -382,21 +352,30 @@ def size_known_group_sparse_all_to_all(in_data: torch.Tensor, send_sizes: torch.
                                        recv_sizes: torch.Tensor,
                                        max_path_padding: bool = False) -> torch.Tensor:
     """Inverse of ``group_sparse_all_to_all``: ``send_sizes`` is that call's second output
-    ([G, W]), ``recv_sizes`` its third ([W, G])."""
+    ([G, W]), ``recv_sizes`` its third ([W, G]).
+
+    The peer-memory transport is taken when both tensors are the very objects the forward call
+    returned (they name the exchange whose size matrix every rank kept); tensors built by the
+    caller go over NCCL.  Which of the two happens depends on the program only, never on the
+    data, so the ranks cannot disagree."""
     _check_cuda(in_data, "in_data")
     _, W = _world()
     group_size = send_sizes.numel() // W
-    send_np, recv_np = _host_sizes(send_sizes, recv_sizes)
-    if max_path_padding:
-        rows = in_data.size(0)
-        stride = rows // send_np.size
-    else:
-        stride = 0
-        rows = a2a_plan.total_rows(recv_np)
     with torch.cuda.device(in_data.device):
         x = _contig(in_data)
-        if _p2p_usable(x, W, group_size):
-            out = _sparse_backward_p2p(x, send_np, recv_np, stride, group_size)
-            if out is not None:
-                return out
+        n = W * group_size
+        stride = x.size(0) // n if max_path_padding else 0
+        tag = getattr(send_sizes, _TAG, None)
+        if tag is not None and tag == getattr(recv_sizes, _TAG, None) and \
+                tag[1] == group_size and _p2p_usable(x, W, group_size):
+            arena = p2p.arena()
+            x = arena.safe_source(x)
+            try:
+                ptr, rows = arena.sparse_backward(tag[0], group_size, _row_bytes(x), stride, x)
+                return _landed(arena, ptr, rows, x)
+            except _lib.BrtError as exc:
+                if exc.status != 4:  # BRT_ERR_UNSUPPORTED is the same verdict on every rank
+                    raise
+        send_np, recv_np = _host_sizes(send_sizes, recv_sizes)
+        rows = x.size(0) if max_path_padding else a2a_plan.total_rows(recv_np)
         return _sparse_a2a(x, send_np, recv_np, stride, rows, group_size, False)

@@ -64,11 +64,24 @@ class _ScratchPool:
 _scratch = _ScratchPool()
 
 
+def check_index_status() -> None:
+    """Raise (once) if an index scan enqueued earlier gave up a bounded wait: its indices and
+    loads are wrong.  Reads a word of host memory that the kernels write, no device
+    synchronisation; every index op calls it on entry, so the error surfaces at the next
+    index op at the latest."""
+    if _lib.query("brt_index_status") != 0:
+        _lib.query("brt_index_status_reset")
+        raise _lib.BrtError("an index scan gave up waiting for the column sums of an earlier "
+                            "CTA (BRT_ERR_TIMEOUT); the indices and loads it returned are "
+                            "not valid", 7)
+
+
 def throttle_hotmask(hotmask: torch.Tensor, prefix: torch.Tensor, threshold: torch.Tensor):
     """src/backend/torch/router.cc:15-31.  ``prefix`` is updated in place and returned."""
     _check_cuda(hotmask, "hotmask")
     _check_cuda(prefix, "prefix")
     _check_cuda(threshold, "threshold")
+    check_index_status()
     if hotmask.size(1) != prefix.size(0) or hotmask.size(1) != threshold.size(0):
         raise RuntimeError("CHECK_EQ fails.")
     hotmask = _int32c(hotmask, "hotmask")
@@ -95,6 +108,7 @@ def generate_indices_and_loads(
 ):
     """src/backend/torch/router.cc:48-80."""
     _check_cuda(hot_mask, "hot_mask")
+    check_index_status()
     hot_mask = _int32c(hot_mask, "hot_mask")
     T, E = hot_mask.shape
     with torch.cuda.device(hot_mask.device):
@@ -155,6 +169,7 @@ def route_scores(
     ``NotImplementedError`` when the scores do not fit the single-launch kernel; callers then
     route in two steps."""
     _check_cuda(score, "score")
+    check_index_status()
     if decision not in _GATE or output not in _ROUTE_OUT:
         raise RuntimeError(f"unknown decision {decision!r} or output {output!r}")
     if not route_scores_supported(score):
@@ -171,6 +186,8 @@ def route_scores(
             _check_cuda(supported_capacities, "supported_capacities")
             caps = _int32c(supported_capacities, "supported_capacities")
             ncap = caps.size(0)
+        if capacity_padding and ncap < 1:
+            raise RuntimeError("capacity_padding needs at least one supported capacity")
         thr = None
         if output == "throttled_mask":
             if prefix is None or throttle_capacity is None:

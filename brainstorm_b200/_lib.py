@@ -17,6 +17,7 @@ _i64 = ctypes.c_int64
 _i32 = ctypes.c_int32
 _int = ctypes.c_int
 _sz = ctypes.c_size_t
+_u64 = ctypes.c_uint64
 
 # name -> (restype, argtypes); kept in step with include/brt_b200.h
 SIGNATURES = {
@@ -31,6 +32,9 @@ SIGNATURES = {
     "brt_static_index_scratch_bytes": (_sz, []),
     "brt_generate_indices_and_loads_static": (
         _int, [_vp, _vp, _vp, _i64, _int, _vp, _int, _int, _int, _int, _vp]),
+    "brt_index_status": (_int, []),
+    "brt_index_status_reset": (None, []),
+    "brt_index_set_test_hooks": (None, [_int, _int]),
     "brt_route_scores": (
         _int, [_vp, _i64, _int, _int, _int, ctypes.c_float, _int, _int, _vp, _vp, _vp, _int, _int,
                _int, _vp, _vp, _vp, _vp, _sz, _vp]),
@@ -62,21 +66,21 @@ SIGNATURES = {
     "brt_p2p_open": (_int, [_vp, ctypes.POINTER(_vp)]),
     "brt_p2p_close": (_int, [_vp]),
     "brt_p2p_free": (_int, [_vp]),
-    "brt_p2p_push": (_int, [_vp, _int, _vp, _vp, _vp, _int, _int, ctypes.c_uint64, _vp, _vp,
-                            _vp]),
-    "brt_p2p_push_buckets": (_int, [_vp, _vp, _int, _int, _int, _i64, _i64, _vp, _i64, _int, _int,
-                                    ctypes.c_uint64, _vp, _vp, _vp]),
-    "brt_p2p_post": (_int, [_vp, _int, _int, _int, ctypes.c_uint64, _vp, _vp, _vp]),
-    "brt_p2p_exchange_sizes": (_int, [_vp, _int, _int, _int, ctypes.c_uint64, _vp, _vp, _vp, _vp,
-                                      _vp, _vp, _vp]),
+    "brt_p2p_push": (_int, [_vp, _int, _vp, _vp, _vp, _int, _int, _u64, _vp, _vp, _vp]),
+    "brt_p2p_post": (_int, [_vp, _int, _int, _int, _u64, _vp, _vp, _vp]),
+    "brt_p2p_land": (_int, [_vp, _vp, _vp, _int, _int, _int, _int, _i64, _i64, _i64, _vp, _u64,
+                            _vp, _vp, _vp, _vp, _vp, _vp, _u64, _vp]),
+    "brt_p2p_wait": (_int, [_vp, _int, _int, _u64, _vp, _vp, _u64, _vp]),
+    "brt_p2p_control_bytes": (_sz, []),
     "brt_p2p_ctx_create": (_int, [_int, _int, _vp, _vp, _sz, _vp]),
     "brt_p2p_ctx_destroy": (None, [_vp]),
-    "brt_p2p_ctx_slot_bytes": (_sz, [_vp]),
-    "brt_p2p_forward_begin": (_int, [_vp, _vp, _vp, _int, _i64, _i64, _vp, _vp]),
-    "brt_p2p_forward_sizes": (_int, [_vp, _vp, _vp, _vp, _vp]),
-    "brt_p2p_forward_finish": (_int, [_vp, _vp, _vp, _vp, _vp]),
-    "brt_p2p_backward": (_int, [_vp, _vp, _int, _i64, _i64, _vp, _vp, _vp, _vp]),
-    "brt_p2p_wait": (_int, [_vp, _int, _int, ctypes.c_uint64, _vp, _vp]),
+    "brt_p2p_ctx_set_wait_limit": (_int, [_vp, _u64]),
+    "brt_p2p_ctx_status": (_int, [_vp]),
+    "brt_p2p_ctx_reset_status": (_int, [_vp]),
+    "brt_p2p_ctx_exchanges": (_u64, [_vp]),
+    "brt_p2p_sparse_forward_begin": (_int, [_vp, _vp, _vp, _int, _i64, _i64, _vp, _vp, _int]),
+    "brt_p2p_sparse_forward_sizes": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "brt_p2p_sparse_backward": (_int, [_vp, _u64, _int, _i64, _i64, _vp, _vp, _int, _vp, _vp]),
 }
 
 

@@ -1,21 +1,27 @@
 // Expert-parallel exchange over NVLink peer memory.
 //
 // Every rank owns one "arena": device memory it allocates here and exports to the other
-// ranks of the box through CUDA IPC.  A variable-size all-to-all is then
+// ranks of the box through CUDA IPC.  The arena holds a control block (flags, size boards,
+// saved size matrices) and two landing halves.  A variable-size all-to-all is then
 //
-//   push    : one kernel copies each of my buckets with 16-byte stores straight to its final
-//             row offset inside the destination rank's arena (plain peer stores; no TMA, no
-//             multicast), my own bucket included;
-//   arrive  : when the last CTA of the push has finished, the kernel raises my flag in every
-//             peer's arena (system-scope release);
-//   wait    : a second, tiny kernel waits until all peers have raised theirs.  The wait is
-//             bounded: after the limit it records a timeout in a status word and returns,
-//             it never hangs the GPU.
+//   post   : a one-CTA kernel writes my bucket sizes into every rank's size board and raises
+//            my "ready" flag there.  The flag also tells the peers that everything I enqueued
+//            before this exchange has finished, i.e. that the landing half of this exchange
+//            may be overwritten;
+//   land   : one kernel waits (bounded) for the ready flags, derives from the size matrix
+//            where each of my buckets lands in its destination's OUTPUT layout and copies it
+//            there with 16-byte stores (plain peer stores; no TMA, no multicast), my own
+//            buckets included.  The last CTA to finish raises my arrival flag at every rank;
+//   wait   : a tiny kernel waits (bounded) until all peers have raised theirs.
 //
-// The arena is used in two halves that alternate from one exchange to the next, which is
-// what makes a single arrive/wait per exchange sufficient: a peer can only start writing a
-// half again after I have signalled the exchange in between, and that signal is enqueued on
-// my stream behind my copy out of that half.
+// Rows therefore cross each HBM once on the way out and once on the way in: the receiver reads
+// its output straight from the landing half, nothing is packed, staged or copied out.  The
+// halves alternate from one exchange to the next, so the output of an exchange stays valid
+// until its owner enters the second exchange after it.
+//
+// Every wait is bounded by a wall-clock limit: when it runs out the kernel records
+// BRT_ERR_TIMEOUT in the arena's status word and in a host-mapped word, skips its copies
+// and returns; it never blocks the GPU.
 #include <cstdlib>
 
 #include "common.cuh"
@@ -25,8 +31,8 @@ namespace {
 
 constexpr int kMaxRanks = 32;
 constexpr int kMaxCopies = 96;
+constexpr int kMaxBuckets = 1024;
 constexpr int kThreads = 256;
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
 
 struct CopyList {
   int count;
@@ -55,6 +61,61 @@ __device__ __forceinline__ unsigned long long load_acquire_sys(const unsigned lo
   asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Where a bounded wait reports that it ran out: the arena's status word and a word of
+// host-mapped memory that the host can read without synchronising with the device.
+struct StatusSink {
+  int* device_word;
+  int* host_word;
+};
+__device__ __forceinline__ void report_timeout(const StatusSink& s) {
+  if (s.device_word != nullptr) atomicExch(s.device_word, BRT_ERR_TIMEOUT);
+  if (s.host_word != nullptr) {
+    *reinterpret_cast<volatile int*>(s.host_word) = BRT_ERR_TIMEOUT;
+    __threadfence_system();
+  }
+}
+
+// Thread r of the CTA (r < world_size, r != skip) polls flags[r] until it holds a value
+// >= epoch or `limit_ns` has passed.  Returns true (to every thread) when all flags came.
+__device__ __forceinline__ bool wait_for_flags(const unsigned long long* flags, int world_size,
+                                               int skip, unsigned long long epoch,
+                                               unsigned long long limit_ns) {
+  bool ok = true;
+  const int r = threadIdx.x;
+  if (r < world_size && r != skip) {
+    const unsigned long long start = global_timer_ns();
+    unsigned int spins = 0;
+    while (load_acquire_sys(flags + r) < epoch) {
+      __nanosleep(100);
+      if ((++spins & 63u) == 0 && global_timer_ns() - start > limit_ns) {
+        ok = false;
+        break;
+      }
+    }
+  }
+  return __syncthreads_and(ok) != 0;
+}
+
+// One 32 KB chunk: the whole chunk is in flight (8 loads per thread) before the first store.
+__device__ __forceinline__ void copy_chunk(const char* s_bytes, char* d_bytes, long long n) {
+  const uint4* s = reinterpret_cast<const uint4*>(s_bytes);
+  uint4* d = reinterpret_cast<uint4*>(d_bytes);
+  const int vecs = (int)(n >> 4);
+  constexpr int kPer = (int)(kChunkBytes / 16 / kThreads);
+  uint4 r[kPer];
+#pragma unroll
+  for (int i = 0; i < kPer; i++)
+    if (threadIdx.x + i * kThreads < vecs) r[i] = __ldcs(s + threadIdx.x + i * kThreads);
+#pragma unroll
+  for (int i = 0; i < kPer; i++)
+    if (threadIdx.x + i * kThreads < vecs) d[threadIdx.x + i * kThreads] = r[i];
+}
 
 __global__ void __launch_bounds__(kThreads)
 p2p_push_kernel(const char* __restrict__ src, const __grid_constant__ CopyList list,
@@ -76,17 +137,7 @@ p2p_push_kernel(const char* __restrict__ src, const __grid_constant__ CopyList l
     const long long at = (chunk - list.first_chunk[c]) * kChunkBytes;
     long long n = list.bytes[c] - at;
     if (n > kChunkBytes) n = kChunkBytes;
-    const uint4* s = reinterpret_cast<const uint4*>(src + list.src_offset[c] + at);
-    uint4* d = reinterpret_cast<uint4*>(list.dst[c] + at);
-    const int vecs = (int)(n >> 4);
-    constexpr int kPer = (int)(kChunkBytes / 16 / kThreads);  // 8: the whole chunk in flight
-    uint4 r[kPer];
-#pragma unroll
-    for (int i = 0; i < kPer; i++)
-      if (threadIdx.x + i * kThreads < vecs) r[i] = __ldcs(s + threadIdx.x + i * kThreads);
-#pragma unroll
-    for (int i = 0; i < kPer; i++)
-      if (threadIdx.x + i * kThreads < vecs) d[threadIdx.x + i * kThreads] = r[i];
+    copy_chunk(src + list.src_offset[c] + at, list.dst[c] + at, n);
   }
   if (sig.world_size == 0) return;  // plain multi-range copy, nobody to tell
   // arrive: the last CTA to finish raises my flag at every rank
@@ -103,78 +154,176 @@ p2p_push_kernel(const char* __restrict__ src, const __grid_constant__ CopyList l
   }
 }
 
-// Device-planned push: the bucket sizes are still on the device (the host has not seen them
-// yet), so every CTA derives the copy list itself.  Bucket b = (destination rank i, local
-// expert j), b = i * group + j, holds sizes[b] rows of `grain` bytes.  The buckets bound for
-// rank i are packed back to back at plan.slot[i], the region of rank i's arena that belongs
-// to this rank, so no rank needs anybody else's sizes to place its data.  A destination whose
-// buckets would not fit its slot, or whose slot pointer is null (this rank itself), is left
-// out; the host takes the same decision from the gathered size matrix.
-constexpr int kMaxBuckets = 1024;
-
-struct BucketPlan {
+// ------------------------------------------------------------------------------- landing
+// The size matrix S[s][b] holds the rows rank s sends to global bucket b = i * G + j
+// (destination rank i, its local expert j).  Two layouts of rows exist:
+//   rank-major   (what a sender holds before the forward exchange and gets back from the
+//                 inverse one): bucket b of rank s starts at row sum_{b' < b} S[s][b'];
+//   expert-major (what a receiver holds after the forward exchange): at rank i, the rows of
+//                 (expert j, source s) start at sum_{j' < j} sum_{s'} S[s'][i*G+j'] +
+//                 sum_{s' < s} S[s'][i*G+j].
+// With stride_rows != 0 buckets are stride_rows apart instead of back to back.
+// forward != 0: my rows are rank-major and land expert-major at their destinations;
+// forward == 0: my rows are expert-major and land rank-major at their owners.
+struct LandArgs {
   int world_size;
+  int my_rank;
   int group_size;
+  int forward;
   long long grain;        // bytes per row, multiple of 16
-  long long stride_rows;  // source layout: 0 = packed, else bucket b starts at row b * stride
-  long long slot_bytes;
-  int expert_begin;  // only buckets whose local expert j is in [expert_begin, expert_end) move
-  int expert_end;
-  char* slot[kMaxRanks];
+  long long stride_rows;  // 0: packed
+  long long half_bytes;   // capacity of a landing half
+  unsigned long long epoch;
+  unsigned long long limit_ns;
+  const int* sizes;                         // the matrix [world][world * group] (device)
+  int* keep;                                // forward: copy of the matrix kept for the inverse
+  const unsigned long long* ready_flags;    // my ready flags (slot r: raised by rank r)
+  char* land[kMaxRanks];                    // landing half of every rank for this exchange
+  unsigned long long* arrive_flags[kMaxRanks];
+  unsigned int* done_counter;
+  unsigned int* abort_word;  // set by a CTA whose wait ran out; cleared by the last CTA
+  StatusSink status;
 };
 
-__global__ void __launch_bounds__(kThreads)
-p2p_push_buckets_kernel(const char* __restrict__ src, const int* __restrict__ sizes,
-                        const __grid_constant__ BucketPlan plan,
-                        const __grid_constant__ SignalList sig) {
-  __shared__ long long s_rows[kMaxBuckets + 1];   // exclusive prefix of the bucket rows
-  __shared__ long long s_first[kMaxBuckets + 1];  // exclusive prefix of the bucket chunks
-  __shared__ long long s_warp[kThreads / 32];
-  const int n = plan.world_size * plan.group_size;
-  const int lane = threadIdx.x & 31;
-  const int warp = threadIdx.x >> 5;
-
-  // two block-wide exclusive scans over strips of kThreads buckets
-  for (int pass = 0; pass < 2; pass++) {
-    long long carry = 0;
-    for (int b0 = 0; b0 < n; b0 += kThreads) {
-      const int b = b0 + threadIdx.x;
-      long long v = 0;
-      if (b < n) {
-        if (pass == 0) {
-          v = sizes[b] > 0 ? sizes[b] : 0;
-        } else {
-          const int i = b / plan.group_size;
-          const long long dest_rows = s_rows[(i + 1) * plan.group_size] - s_rows[i * plan.group_size];
-          const int j = b - i * plan.group_size;
-          const bool send = plan.slot[i] != nullptr && dest_rows * plan.grain <= plan.slot_bytes &&
-                            j >= plan.expert_begin && j < plan.expert_end;
-          const long long bytes = (s_rows[b + 1] - s_rows[b]) * plan.grain;
-          v = send ? (bytes + kChunkBytes - 1) / kChunkBytes : 0;
-        }
-      }
-      long long incl = v;
+// In-place exclusive prefix sum of a[0 .. n) in shared memory (n <= kMaxBuckets), total at
+// a[n].  All threads of the CTA call it; it opens and closes with a barrier.
+__device__ __forceinline__ void block_exclusive_scan(int* a, int n, int* s_warp) {
+  __syncthreads();
+  const int tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5;
+  const int per = (n + kThreads - 1) / kThreads;
+  const int begin = tid * per < n ? tid * per : n;
+  const int end = begin + per < n ? begin + per : n;
+  int local = 0;
+  for (int i = begin; i < end; i++) local += a[i];
+  int incl = local;
 #pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        const long long up = __shfl_up_sync(0xffffffffu, incl, d);
-        if (lane >= d) incl += up;
-      }
-      if (lane == 31) s_warp[warp] = incl;
-      __syncthreads();
-      long long before = carry;
-      for (int w = 0; w < warp; w++) before += s_warp[w];
-      long long strip = 0;
-      for (int w = 0; w < kThreads / 32; w++) strip += s_warp[w];
-      long long* out = pass == 0 ? s_rows : s_first;
-      if (b < n) out[b] = before + incl - v;
-      carry += strip;
-      __syncthreads();
+  for (int d = 1; d < 32; d <<= 1) {
+    const int up = __shfl_up_sync(0xffffffffu, incl, d);
+    if (lane >= d) incl += up;
+  }
+  if (lane == 31) s_warp[warp] = incl;
+  __syncthreads();
+  int before = 0, total = 0;
+  for (int w = 0; w < kThreads / 32; w++) {
+    if (w < warp) before += s_warp[w];
+    total += s_warp[w];
+  }
+  int run = before + incl - local;
+  for (int i = begin; i < end; i++) {
+    const int v = a[i];
+    a[i] = run;
+    run += v;
+  }
+  if (tid == 0) a[n] = total;
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(kThreads)
+p2p_land_kernel(const char* __restrict__ src, const __grid_constant__ LandArgs a) {
+  __shared__ int s_rows[kMaxBuckets];       // rows of my bucket p (p: position in my buffer)
+  __shared__ int s_src[kMaxBuckets + 1];    // source row of bucket p
+  __shared__ int s_dst[kMaxBuckets];        // landing row of bucket p at its destination
+  __shared__ int s_aux[kMaxBuckets + 1];
+  __shared__ int s_first[kMaxBuckets + 1];  // exclusive prefix of the chunk counts
+  __shared__ int s_base[kMaxRanks];
+  __shared__ int s_warp[kThreads / 32];
+  const int tid = threadIdx.x;
+  const int W = a.world_size, G = a.group_size, me = a.my_rank;
+  const int n = W * G;
+
+  // every rank has entered this exchange: the sizes are on my board and the landing halves
+  // may be written
+  bool go = wait_for_flags(a.ready_flags, W, -1, a.epoch, a.limit_ns);
+  if (!go) {
+    if (tid == 0) {
+      report_timeout(a.status);
+      atomicExch(a.abort_word, 1u);
     }
-    if (threadIdx.x == 0) (pass == 0 ? s_rows : s_first)[n] = carry;
-    __syncthreads();
   }
 
-  const long long total_chunks = s_first[n];
+  const int* S = a.sizes;
+  auto rows_of = [&](int s, int b) -> int {
+    const int v = __ldcg(S + s * n + b);
+    return v > 0 ? v : 0;
+  };
+  bool fits = true;
+  if (go && a.forward) {
+    // position p == global bucket b = i * G + j
+    for (int b = tid; b < n; b += kThreads) {
+      int column = 0, below = 0;
+      for (int s = 0; s < W; s++) {
+        const int v = rows_of(s, b);
+        column += v;
+        if (s < me) below += v;
+        if (a.keep != nullptr && blockIdx.x == 0) a.keep[s * n + b] = __ldcg(S + s * n + b);
+      }
+      const int mine = rows_of(me, b);
+      s_aux[b] = column;
+      s_dst[b] = below;
+      s_rows[b] = mine;
+      s_src[b] = mine;
+    }
+    block_exclusive_scan(s_aux, n, s_warp);
+    block_exclusive_scan(s_src, n, s_warp);
+    bool ok = true;
+    if (tid < W) {
+      const long long landed = a.stride_rows ? (long long)n * a.stride_rows
+                                             : (long long)(s_aux[(tid + 1) * G] - s_aux[tid * G]);
+      ok = landed * a.grain <= a.half_bytes;
+    }
+    fits = __syncthreads_and(ok) != 0;
+    for (int b = tid; b < n; b += kThreads) {
+      const int i = b / G, j = b - i * G;
+      if (a.stride_rows) {
+        s_dst[b] = (int)((long long)(j * W + me) * a.stride_rows);
+        s_src[b] = (int)((long long)b * a.stride_rows);
+      } else {
+        s_dst[b] = s_aux[b] - s_aux[i * G] + s_dst[b];
+      }
+    }
+  } else if (go) {
+    // position p = j * W + i: the rows of my expert j that came from rank i
+    for (int r = tid >> 5; r < W; r += kThreads / 32) {  // rows rank r sent to ranks below me
+      int acc = 0;
+      for (int b = tid & 31; b < me * G; b += 32) acc += rows_of(r, b);
+#pragma unroll
+      for (int d = 16; d != 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+      if ((tid & 31) == 0) s_base[r] = acc;
+    }
+    for (int p = tid; p < n; p += kThreads) {
+      const int j = p / W, i = p - j * W;
+      const int v = rows_of(i, me * G + j);
+      s_rows[p] = v;
+      s_src[p] = v;
+      s_aux[i * G + j] = v;
+    }
+    block_exclusive_scan(s_aux, n, s_warp);
+    block_exclusive_scan(s_src, n, s_warp);
+    for (int p = tid; p < n; p += kThreads) {
+      const int j = p / W, i = p - j * W;
+      if (a.stride_rows) {
+        s_dst[p] = (int)((long long)(me * G + j) * a.stride_rows);
+        s_src[p] = (int)((long long)p * a.stride_rows);
+      } else {
+        s_dst[p] = s_base[i] + s_aux[i * G + j] - s_aux[i * G];
+      }
+    }
+  }
+  __syncthreads();
+  const bool move = go && fits;
+  for (int p = tid; p < n; p += kThreads) {
+    const long long bytes = (long long)s_rows[p] * a.grain;
+    s_first[p] = move ? (int)((bytes + kChunkBytes - 1) / kChunkBytes) : 0;
+  }
+  if (!go) {
+    for (int p = tid; p <= n; p += kThreads) s_first[p] = 0;
+    __syncthreads();
+  } else {
+    block_exclusive_scan(s_first, n, s_warp);
+  }
+
+  const long long total_chunks = go ? s_first[n] : 0;
   const long long run = (total_chunks + kWays - 1) / kWays;
   for (long long k = blockIdx.x; k < run * kWays; k += gridDim.x) {
     const long long chunk = (k % kWays) * run + k / kWays;
@@ -184,40 +333,32 @@ p2p_push_buckets_kernel(const char* __restrict__ src, const int* __restrict__ si
       const int mid = (lo + hi + 1) >> 1;
       if (s_first[mid] <= chunk) lo = mid; else hi = mid - 1;
     }
-    const int b = lo;
-    const int i = b / plan.group_size;
-    const long long at = (chunk - s_first[b]) * kChunkBytes;
-    long long bytes = (s_rows[b + 1] - s_rows[b]) * plan.grain - at;
+    const int p = lo;
+    const int dest = a.forward ? p / G : p % W;
+    const long long at = (chunk - s_first[p]) * kChunkBytes;
+    long long bytes = (long long)s_rows[p] * a.grain - at;
     if (bytes > kChunkBytes) bytes = kChunkBytes;
-    const long long src_row = plan.stride_rows ? (long long)b * plan.stride_rows : s_rows[b];
-    const long long dst_row = s_rows[b] - s_rows[i * plan.group_size];
-    const uint4* s = reinterpret_cast<const uint4*>(src + src_row * plan.grain + at);
-    uint4* d = reinterpret_cast<uint4*>(plan.slot[i] + dst_row * plan.grain + at);
-    const int vecs = (int)(bytes >> 4);
-    constexpr int kPer = (int)(kChunkBytes / 16 / kThreads);
-    uint4 r[kPer];
-#pragma unroll
-    for (int u = 0; u < kPer; u++)
-      if (threadIdx.x + u * kThreads < vecs) r[u] = __ldcs(s + threadIdx.x + u * kThreads);
-#pragma unroll
-    for (int u = 0; u < kPer; u++)
-      if (threadIdx.x + u * kThreads < vecs) d[threadIdx.x + u * kThreads] = r[u];
+    copy_chunk(src + (long long)s_src[p] * a.grain + at,
+               a.land[dest] + (long long)s_dst[p] * a.grain + at, bytes);
   }
+
+  // arrive: the last CTA to finish raises my flag at every rank, unless a wait ran out
   __threadfence_system();
   __syncthreads();
-  if (threadIdx.x == 0) {
-    const unsigned int prev = atomicAdd(sig.done_counter, 1u);
+  if (tid == 0) {
+    const unsigned int prev = atomicAdd(a.done_counter, 1u);
     if (prev == gridDim.x - 1) {
-      *sig.done_counter = 0;
+      *a.done_counter = 0;  // ready for the next exchange (stream-ordered)
+      const unsigned int aborted = atomicExch(a.abort_word, 0u);
       __threadfence_system();
-      for (int r = 0; r < sig.world_size; r++)
-        store_release_sys(sig.peer_flags[r] + sig.my_rank, sig.epoch);
+      if (aborted == 0u)
+        for (int r = 0; r < W; r++) store_release_sys(a.arrive_flags[r] + me, a.epoch);
     }
   }
 }
 
-// Post `n` int32 values (my bucket sizes) into row `my_rank` of every rank's size board and
-// raise my flag there.  One CTA.
+// Post `n` int32 values (my bucket sizes; n may be 0) into row `my_rank` of every rank's size
+// board and raise my flag there.  One CTA.
 struct PostList {
   int world_size;
   int my_rank;
@@ -239,25 +380,11 @@ p2p_post_kernel(const int* __restrict__ values, const __grid_constant__ PostList
       store_release_sys(post.peer_flags[r] + post.my_rank, post.epoch);
 }
 
-__global__ void p2p_wait_kernel(const unsigned long long* __restrict__ my_flags, int world_size,
-                                int skip_rank, unsigned long long epoch,
-                                int* __restrict__ status) {
-  const int r = threadIdx.x;
-  if (r >= world_size || r == skip_rank) return;
-  unsigned long long start = 0;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
-  unsigned int spins = 0;
-  while (load_acquire_sys(my_flags + r) < epoch) {
-    __nanosleep(200);
-    if ((++spins & 255u) == 0) {
-      unsigned long long now = 0;
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-      if (now - start > kWaitLimitNs) {
-        atomicExch(status, BRT_ERR_TIMEOUT);
-        return;
-      }
-    }
-  }
+__global__ void __launch_bounds__(32)
+p2p_wait_kernel(const unsigned long long* __restrict__ my_flags, int world_size, int skip_rank,
+                unsigned long long epoch, unsigned long long limit_ns, const StatusSink status) {
+  if (!wait_for_flags(my_flags, world_size, skip_rank, epoch, limit_ns) && threadIdx.x == 0)
+    report_timeout(status);
 }
 
 }  // namespace
@@ -267,12 +394,15 @@ using namespace brt_b200;
 
 namespace {
 // CTAs per SM of the push kernels.  One per SM already saturates an NVLink direction (about
-// 655 GB/s measured at 1, 2, 4 and 8); two leave room for the copy-out kernels that run beside
-// a push on the side stream.  BRT_P2P_CTAS_PER_SM overrides it.
+// 655 GB/s measured at 1, 2, 4 and 8); two leave room for kernels that run beside a push on
+// another stream.  BRT_P2P_CTAS_PER_SM overrides it (read once).
 int push_ctas_per_sm() {
-  const char* v = getenv("BRT_P2P_CTAS_PER_SM");
-  const int n = v != nullptr ? atoi(v) : 0;
-  return n >= 1 && n <= 8 ? n : 2;
+  static const int chosen = [] {
+    const char* v = getenv("BRT_P2P_CTAS_PER_SM");
+    const int n = v != nullptr ? atoi(v) : 0;
+    return n >= 1 && n <= 8 ? n : 2;
+  }();
+  return chosen;
 }
 }  // namespace
 
@@ -355,7 +485,7 @@ BRT_API int brt_p2p_push(const void* src, int copy_count, const int64_t* src_off
   sig.done_counter = static_cast<unsigned int*>(my_done_counter);
   long long grid = chunks;
   // a flag-less call is a local copy, bound by HBM rather than by a link; it gets more CTAs
-  // than a push, but not the whole SM: the next push has to find room beside it
+  // than a push, but not the whole SM
   const long long cap = (long long)sm_count() * (world_size == 0 ? 4 : push_ctas_per_sm());
   if (grid > cap) grid = cap;
   if (grid < 1) grid = 1;
@@ -367,47 +497,57 @@ BRT_API int brt_p2p_push(const void* src, int copy_count, const int64_t* src_off
   return BRT_OK;
 }
 
-BRT_API int brt_p2p_push_buckets(const void* src, const int32_t* sizes, int world_size,
-                                 int group_size, int my_rank, int64_t grain_bytes,
-                                 int64_t stride_rows, void* const* slot_ptrs, int64_t slot_bytes,
-                                 int expert_begin, int expert_end, uint64_t epoch,
-                                 void* const* peer_flag_arrays, void* my_done_counter,
-                                 void* stream) {
+BRT_API int brt_p2p_land(const void* rows, const int32_t* size_matrix, int32_t* keep_matrix,
+                         int world_size, int group_size, int my_rank, int forward,
+                         int64_t grain_bytes, int64_t stride_rows, int64_t half_bytes,
+                         void* const* landing_ptrs, uint64_t epoch, const void* my_ready_flags,
+                         void* const* peer_arrive_flag_arrays, void* my_done_counter,
+                         void* my_abort_word, void* status_word, void* host_status_word,
+                         uint64_t wait_limit_ns, void* stream) {
   clear_error();
-  // src may be null for a rank that holds no rows (all its sizes are zero)
-  BRT_REQUIRE(sizes != nullptr && slot_ptrs != nullptr && peer_flag_arrays != nullptr &&
-                  my_done_counter != nullptr,
+  // rows may be null for a rank that holds no rows (all its sizes are zero)
+  BRT_REQUIRE(size_matrix != nullptr && landing_ptrs != nullptr && my_ready_flags != nullptr &&
+                  peer_arrive_flag_arrays != nullptr && my_done_counter != nullptr &&
+                  my_abort_word != nullptr && status_word != nullptr,
               "null pointers");
   BRT_REQUIRE(world_size >= 1 && world_size <= kMaxRanks && my_rank >= 0 && my_rank < world_size,
               "bad rank %d of %d", my_rank, world_size);
   BRT_REQUIRE(group_size >= 1 && (long long)world_size * group_size <= kMaxBuckets,
-              "at most %d buckets per device-planned push", kMaxBuckets);
-  BRT_REQUIRE(grain_bytes > 0 && grain_bytes % 16 == 0 && aligned_to(src, 16),
+              "at most %d buckets per exchange", kMaxBuckets);
+  BRT_REQUIRE(grain_bytes > 0 && grain_bytes % 16 == 0 && aligned_to(rows, 16),
               "rows must be 16-byte multiples and the source 16-byte aligned");
-  BRT_REQUIRE(stride_rows >= 0 && slot_bytes >= 0, "negative stride or slot size");
-  BucketPlan plan;
-  plan.world_size = world_size;
-  plan.group_size = group_size;
-  plan.grain = grain_bytes;
-  plan.stride_rows = stride_rows;
-  plan.slot_bytes = slot_bytes;
-  plan.expert_begin = expert_begin;
-  plan.expert_end = expert_end;
-  SignalList sig;
-  sig.world_size = world_size;
-  sig.my_rank = my_rank;
-  sig.epoch = epoch;
+  BRT_REQUIRE(stride_rows >= 0 && half_bytes >= 0, "negative stride or half size");
+  BRT_REQUIRE(stride_rows * (int64_t)world_size * group_size <= 0x7fffffffLL,
+              "more than 2^31-1 rows per rank");
+  LandArgs a;
+  a.world_size = world_size;
+  a.my_rank = my_rank;
+  a.group_size = group_size;
+  a.forward = forward != 0;
+  a.grain = grain_bytes;
+  a.stride_rows = stride_rows;
+  a.half_bytes = half_bytes;
+  a.epoch = epoch;
+  a.limit_ns = wait_limit_ns;
+  a.sizes = size_matrix;
+  a.keep = keep_matrix;
+  a.ready_flags = static_cast<const unsigned long long*>(my_ready_flags);
   for (int r = 0; r < world_size; r++) {
-    BRT_REQUIRE(aligned_to(slot_ptrs[r], 16), "slot %d is not 16-byte aligned", r);
-    plan.slot[r] = static_cast<char*>(slot_ptrs[r]);
-    sig.peer_flags[r] = static_cast<unsigned long long*>(peer_flag_arrays[r]);
+    BRT_REQUIRE(landing_ptrs[r] != nullptr && aligned_to(landing_ptrs[r], 16),
+                "landing half %d is null or not 16-byte aligned", r);
+    a.land[r] = static_cast<char*>(landing_ptrs[r]);
+    a.arrive_flags[r] = static_cast<unsigned long long*>(peer_arrive_flag_arrays[r]);
   }
-  sig.done_counter = static_cast<unsigned int*>(my_done_counter);
-  const KernelTimer timer("p2p_push_buckets_kernel", static_cast<cudaStream_t>(stream));
-  p2p_push_buckets_kernel<<<(unsigned)(sm_count() * push_ctas_per_sm()), kThreads, 0,
-                            static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const char*>(src), sizes, plan, sig), note_launch();
-  BRT_LAUNCH_CHECK("p2p_push_buckets_kernel");
+  a.done_counter = static_cast<unsigned int*>(my_done_counter);
+  a.abort_word = static_cast<unsigned int*>(my_abort_word);
+  a.status.device_word = static_cast<int*>(status_word);
+  a.status.host_word = static_cast<int*>(host_status_word);
+  const KernelTimer timer(forward ? "p2p_land_forward_kernel" : "p2p_land_backward_kernel",
+                          static_cast<cudaStream_t>(stream));
+  p2p_land_kernel<<<(unsigned)(sm_count() * push_ctas_per_sm()), kThreads, 0,
+                    static_cast<cudaStream_t>(stream)>>>(static_cast<const char*>(rows), a),
+      note_launch();
+  BRT_LAUNCH_CHECK("p2p_land_kernel");
   return BRT_OK;
 }
 
@@ -415,7 +555,8 @@ BRT_API int brt_p2p_post(const int32_t* values, int n, int world_size, int my_ra
                          uint64_t epoch, void* const* peer_boards, void* const* peer_flag_arrays,
                          void* stream) {
   clear_error();
-  BRT_REQUIRE(values != nullptr && n > 0 && peer_boards != nullptr && peer_flag_arrays != nullptr,
+  BRT_REQUIRE(n >= 0 && (n == 0 || (values != nullptr && peer_boards != nullptr)) &&
+                  peer_flag_arrays != nullptr,
               "bad arguments");
   BRT_REQUIRE(world_size >= 1 && world_size <= kMaxRanks && my_rank >= 0 && my_rank < world_size,
               "bad rank %d of %d", my_rank, world_size);
@@ -425,40 +566,28 @@ BRT_API int brt_p2p_post(const int32_t* values, int n, int world_size, int my_ra
   post.n = n;
   post.epoch = epoch;
   for (int r = 0; r < world_size; r++) {
-    post.peer_board[r] = static_cast<int*>(peer_boards[r]);
+    post.peer_board[r] = n > 0 ? static_cast<int*>(peer_boards[r]) : nullptr;
     post.peer_flags[r] = static_cast<unsigned long long*>(peer_flag_arrays[r]);
   }
+  const KernelTimer timer("p2p_post_kernel", static_cast<cudaStream_t>(stream));
   p2p_post_kernel<<<1, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(values, post), note_launch();
   BRT_LAUNCH_CHECK("p2p_post_kernel");
   return BRT_OK;
 }
 
-BRT_API int brt_p2p_exchange_sizes(const int32_t* values, int n, int world_size, int my_rank,
-                                   uint64_t epoch, void* const* peer_boards,
-                                   void* const* peer_flag_arrays, const void* my_flag_array,
-                                   const void* my_board, void* status_word, int32_t* host_out,
-                                   void* stream) {
-  if (int rc = brt_p2p_post(values, n, world_size, my_rank, epoch, peer_boards, peer_flag_arrays,
-                            stream))
-    return rc;
-  if (int rc = brt_p2p_wait(my_flag_array, world_size, -1, epoch, status_word, stream)) return rc;
-  BRT_REQUIRE(my_board != nullptr && host_out != nullptr, "null board or host buffer");
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  BRT_CUDA_TRY(cudaMemcpyAsync(host_out, status_word, 4, cudaMemcpyDeviceToHost, st));
-  BRT_CUDA_TRY(cudaMemcpyAsync(host_out + 1, my_board, (size_t)world_size * n * 4,
-                               cudaMemcpyDeviceToHost, st));
-  return BRT_OK;
-}
-
 BRT_API int brt_p2p_wait(const void* my_flag_array, int world_size, int skip_rank,
-                         uint64_t epoch, void* status_word, void* stream) {
+                         uint64_t epoch, void* status_word, void* host_status_word,
+                         uint64_t wait_limit_ns, void* stream) {
   clear_error();
   BRT_REQUIRE(my_flag_array != nullptr && status_word != nullptr, "null control pointers");
   BRT_REQUIRE(world_size >= 1 && world_size <= kMaxRanks, "bad world size %d", world_size);
+  StatusSink sink;
+  sink.device_word = static_cast<int*>(status_word);
+  sink.host_word = static_cast<int*>(host_status_word);
   const KernelTimer timer("p2p_wait_kernel", static_cast<cudaStream_t>(stream));
   p2p_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const unsigned long long*>(my_flag_array), world_size, skip_rank, epoch,
-      static_cast<int*>(status_word)), note_launch();
+      wait_limit_ns, sink), note_launch();
   BRT_LAUNCH_CHECK("p2p_wait_kernel");
   return BRT_OK;
 }

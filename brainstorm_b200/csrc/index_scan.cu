@@ -32,6 +32,7 @@
 //     earlier) and expands its tiles from shared memory;
 //   * the strip path (any path_num / alignment): a thread walks 32 cells of V paths.
 
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 #include <map>
@@ -1129,13 +1130,16 @@ struct ChainArgs {
   GateArgs gate;
   unsigned long long* status;  // [ranges][path_num]: (1 << 32) | column sum once published
   int* ticket;
-  int* error;  // set to 1 when a wait ran out
+  int* error;       // set to 1 when a wait ran out
+  int* host_error;  // host-mapped word that receives BRT_ERR_TIMEOUT then (may be null)
+  int spin_limit;   // polls (each followed by a short sleep) before a wait gives up
+  int first_ticket; // 0; a test passes 1 so that the first run is never published
   int tiles_per_cta;
   int ranges;
 };
 
 constexpr int kChainFly = 16;            // status words a thread keeps in flight
-constexpr int kChainSpinLimit = 1 << 20;  // polls (each followed by a short sleep)
+constexpr int kChainSpinLimit = 1 << 20;  // default number of polls
 
 __device__ __forceinline__ void status_publish(unsigned long long* p, int value) {
   const unsigned long long w = (1ull << 32) | static_cast<unsigned>(value);
@@ -1158,8 +1162,9 @@ __global__ void __launch_bounds__(kTileThreads, 2) index_chain_kernel(const Chai
   int* bits_all = s_dyn + tile_smem_ints(a.ec, a.rg, a.pitch, true);
   for (int i = tid; i < 2 * a.ec + 1; i += kTileThreads) sm.sum[i] = 0;
   __syncthreads();
-  const int ticket = s_ticket;
+  const int ticket = s_ticket + c.first_ticket;
   const int range = ticket / a.chunks;
+  if (range >= c.ranges) return;  // only with first_ticket != 0: nothing left to own
   TileCtx x;
   x.cell_num = a.cell_num;
   x.path_num = a.path_num;
@@ -1238,8 +1243,12 @@ __global__ void __launch_bounds__(kTileThreads, 2) index_chain_kernel(const Chai
 #pragma unroll
           for (int u = 0; u < kChainFly; u++) ready = ready && (w[u] >> 32) != 0;
           if (ready) break;
-          if (++spins > kChainSpinLimit) {  // give up: flag it and carry on with what is there
+          if (++spins > c.spin_limit) {  // give up: report it and carry on with what is there
             *c.error = 1;
+            if (c.host_error != nullptr) {
+              *reinterpret_cast<volatile int*>(c.host_error) = BRT_ERR_TIMEOUT;
+              __threadfence_system();
+            }
             break;
           }
           __nanosleep(64);
@@ -1288,6 +1297,45 @@ size_t tiled_scratch_bytes(int64_t cell_num, int path_num) {
 constexpr int kChainCtasPerSm = 2;
 constexpr size_t kChainSmemLimit = 110 * 1024;
 
+// A run-out look-back wait is reported through one word of host-mapped memory per process:
+// kernels write it, the host reads it without synchronising (brt_index_status).  The word is
+// created by the first call that may allocate; the entry point that must not allocate only
+// uses it when it exists already.
+struct HostStatus {
+  std::mutex mu;
+  int* host = nullptr;
+  int* device = nullptr;
+};
+HostStatus& index_status() {
+  static HostStatus s;
+  return s;
+}
+int* index_status_word(bool may_allocate) {
+  HostStatus& s = index_status();
+  std::lock_guard<std::mutex> lock(s.mu);
+  if (s.host == nullptr && may_allocate) {
+    int* h = nullptr;
+    void* d = nullptr;
+    if (cudaHostAlloc(reinterpret_cast<void**>(&h), 64,
+                      cudaHostAllocMapped | cudaHostAllocPortable) == cudaSuccess) {
+      memset(h, 0, 64);
+      if (cudaHostGetDevicePointer(&d, h, 0) == cudaSuccess) {
+        s.host = h;
+        s.device = static_cast<int*>(d);
+      } else {
+        cudaFreeHost(h);
+      }
+    }
+    cudaGetLastError();
+  }
+  return s.device;
+}
+
+// Test hooks (brt_index_set_test_hooks): a shorter wait and a first run that nobody owns.
+std::atomic<int> g_spin_limit{kChainSpinLimit};
+std::atomic<int> g_first_ticket{0};
+thread_local bool t_may_allocate = true;  // false inside the entry point that must not
+
 template <Mode MODE, bool GATED>
 int launch_chain_mode(const ChainArgs& c, unsigned grid, size_t smem, cudaStream_t stream) {
   static thread_local std::map<int, size_t> configured;  // device -> opted-in bytes
@@ -1321,6 +1369,9 @@ int launch_chain(Mode mode, const TileGeom& g, int tiles_per_cta, int ranges, si
   c.t.flags = reinterpret_cast<int*>(p);
   c.error = c.t.flags + 1;
   c.ticket = c.t.flags + 2;
+  c.host_error = index_status_word(t_may_allocate);
+  c.spin_limit = g_spin_limit.load(std::memory_order_relaxed);
+  c.first_ticket = g_first_ticket.load(std::memory_order_relaxed);
   c.status = reinterpret_cast<unsigned long long*>(p + 256);
   c.tiles_per_cta = tiles_per_cta;
   c.ranges = ranges;
@@ -1371,8 +1422,11 @@ int launch_tiled(Mode mode, const int32_t* mask, int32_t* out, int32_t* loads, i
               path_num);
   // One chained launch when the bit words of a CTA's tiles fit in shared memory, else three
   // launches (pack, scan, expand).  BRT_INDEX_PATH=split forces the latter (for tests).
-  const char* const forced = getenv("BRT_INDEX_PATH");
-  if (gate != nullptr || forced == nullptr || strcmp(forced, "split") != 0) {
+  static const bool forced_split = [] {
+    const char* const forced = getenv("BRT_INDEX_PATH");
+    return forced != nullptr && strcmp(forced, "split") == 0;
+  }();
+  if (gate != nullptr || !forced_split) {
     int64_t target = (int64_t)sm_count() * kChainCtasPerSm / g.col_chunks;
     if (target < 1) target = 1;
     const int64_t ranges0 = g.num_tiles < target ? g.num_tiles : target;
@@ -1635,8 +1689,13 @@ BRT_API int brt_route_scores(const float* scores, int64_t cell_num, int path_num
   BRT_REQUIRE(output == BRT_ROUTE_THROTTLED_MASK || loads != nullptr, "loads is null");
   BRT_REQUIRE(capacity_num >= 0 && (capacity_num == 0 || capacities != nullptr),
               "capacities missing");
-  BRT_REQUIRE(!path_wise_padding || capacity_num == path_num,
-              "path-wise padding needs one capacity per path");
+  // the same rules as brt_generate_indices_and_loads: padding needs a capacity to pad to, and
+  // path-wise padding only exists inside capacity padding
+  BRT_REQUIRE(!capacity_padding || capacity_num >= 1,
+              "capacity_padding needs at least one supported capacity");
+  path_wise_padding = (capacity_padding && path_wise_padding) ? 1 : 0;
+  BRT_REQUIRE(!path_wise_padding || capacity_num >= path_num,
+              "path_wise_padding needs one capacity per path (%d < %d)", capacity_num, path_num);
   if (cell_num == 0) {
     if (output != BRT_ROUTE_THROTTLED_MASK)
       BRT_CUDA_TRY(cudaMemsetAsync(loads, 0, (size_t)path_num * 4, static_cast<cudaStream_t>(stream)));
@@ -1710,10 +1769,30 @@ BRT_API int brt_generate_indices_and_loads_static(const int32_t* hot_mask, int32
   void* scratch = nullptr;
   const int rc = static_scratch_address(&scratch);
   if (rc != BRT_OK) return rc;
-  return brt_generate_indices_and_loads(hot_mask, indices, loads, cell_num, path_num,
-                                        supported_capacities, supported_capacity_num,
-                                        capacity_padding, path_wise_padding, is_tag_index,
-                                        scratch, kStaticScratchBytes, stream);
+  t_may_allocate = false;  // the status word of brt_index_status is used only if it exists
+  const int out = brt_generate_indices_and_loads(hot_mask, indices, loads, cell_num, path_num,
+                                                 supported_capacities, supported_capacity_num,
+                                                 capacity_padding, path_wise_padding,
+                                                 is_tag_index, scratch, kStaticScratchBytes,
+                                                 stream);
+  t_may_allocate = true;
+  return out;
+}
+
+BRT_API int brt_index_status(void) {
+  index_status_word(true);
+  HostStatus& s = index_status();
+  return s.host != nullptr ? *reinterpret_cast<volatile int*>(s.host) : BRT_OK;
+}
+
+BRT_API void brt_index_status_reset(void) {
+  HostStatus& s = index_status();
+  if (s.host != nullptr) *reinterpret_cast<volatile int*>(s.host) = BRT_OK;
+}
+
+BRT_API void brt_index_set_test_hooks(int spin_limit, int skip_first_run) {
+  g_spin_limit.store(spin_limit > 0 ? spin_limit : kChainSpinLimit);
+  g_first_ticket.store(skip_first_run ? 1 : 0);
 }
 
 }  // extern "C"

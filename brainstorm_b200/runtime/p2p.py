@@ -1,11 +1,15 @@
-"""Set-up of the NVLink peer-memory exchange (kernels: csrc/exchange_p2p.cu, planning:
+"""Set-up of the NVLink peer-memory exchange (kernels: csrc/exchange_p2p.cu, host side:
 csrc/exchange_plan.cu).
 
-One arena per process: a control block (arrival flags, a completion counter, a status word,
-size boards) followed by two data halves that alternate from one exchange to the next.  The
-arena is exported through CUDA IPC; handles travel between the ranks of the box through
-``torch.distributed``.  Everything an exchange enqueues is planned and issued by the
-library's exchange context; this module creates it and forwards four calls.
+One arena per process: a control block (flags, size boards, kept size matrices) followed by
+two landing halves that alternate from one exchange to the next.  The arena is exported
+through CUDA IPC; handles travel between the ranks of the box through ``torch.distributed``.
+An exchange lands every bucket straight at its place in the receiver's output layout, and
+the output tensor handed to the caller is a view of the landing half (no copy-out):
+
+* it stays valid until this rank enters the SECOND exchange after the one that produced it
+  (peers only write into a half once its owner has entered the exchange that uses it);
+* ``BRT_P2P_ZERO_COPY=0`` makes every exchange return a private copy instead.
 """
 import ctypes
 import os
@@ -17,8 +21,14 @@ import torch.distributed as dist
 
 from .. import _lib
 
-CONTROL_BYTES = 65536     # control block in front of the two data halves (laid out by the
-STATUS_OFFSET = 1024      # library: flags, completion counter, status word, size boards)
+STATUS_OFFSET = 1024      # status word of the bounded waits inside the control block
+ZERO_COPY = os.environ.get("BRT_P2P_ZERO_COPY", "1") != "0"
+MAX_BUCKETS = 1024        # world * group of one exchange (device planner)
+BOARD_INTS = 7936         # world * world * group: the size matrix must fit a board
+
+
+def buckets_supported(world: int, group_size: int) -> bool:
+    return world * group_size <= MAX_BUCKETS and world * world * group_size <= BOARD_INTS
 
 
 class _DeviceBytes:
@@ -29,76 +39,90 @@ class _DeviceBytes:
                                          "data": (ptr, False), "version": 2}
 
 
+def _row_bytes(x: torch.Tensor) -> int:
+    n = x.element_size()
+    for extent in x.shape[1:]:
+        n *= int(extent)
+    return n
+
+
 class PeerArena:
-    def __init__(self, group, rank: int, world: int, half_bytes: int):
+    """This rank's arena, its peers' arenas as mapped here, and the library's exchange
+    context on top of them."""
+
+    def __init__(self, rank: int, world: int, half_bytes: int, base: int, peer_base: List[int]):
         self.rank, self.world, self.half_bytes = rank, world, int(half_bytes)
-        self.total = CONTROL_BYTES + 2 * self.half_bytes
-        ptr = ctypes.c_void_p()
-        handle = (ctypes.c_ubyte * 64)()
-        _lib.call("brt_p2p_alloc", self.total, ctypes.byref(ptr), handle)
-        self.base = ptr.value
-        handles: List[Optional[bytes]] = [None] * world
-        dist.all_gather_object(handles, bytes(handle), group=group)
-        self.peer_base: List[int] = []
-        for r in range(world):
-            if r == rank:
-                self.peer_base.append(self.base)
-                continue
-            buf = (ctypes.c_ubyte * 64).from_buffer_copy(handles[r])
-            p = ctypes.c_void_p()
-            _lib.call("brt_p2p_open", buf, ctypes.byref(p))
-            self.peer_base.append(p.value)
+        self.control_bytes = int(_lib.query("brt_p2p_control_bytes"))
+        self.total = self.control_bytes + 2 * self.half_bytes
+        self.base = base
+        self.peer_base = list(peer_base)
         self._view = torch.as_tensor(_DeviceBytes(self.base, self.total), device="cuda")
-        self.status = self._view[STATUS_OFFSET:STATUS_OFFSET + 4].view(torch.int32)
-        # copy-outs and the size exchange run on this stream, beside the pushes
+        # the size matrix comes down on this stream, beside the rows
         self.side = torch.cuda.Stream()
-        self._pending = None
-        # host-side planning of the sparse exchanges lives in the library
         ctx = ctypes.c_void_p()
         arenas = (ctypes.c_void_p * world)(*self.peer_base)
         _lib.call("brt_p2p_ctx_create", world, rank, self.base, arenas, self.half_bytes,
                   ctypes.byref(ctx))
         self.ctx = ctx
-        self.slot_bytes = int(_lib.query("brt_p2p_ctx_slot_bytes", self.ctx))
 
-    def forward_begin(self, rows: torch.Tensor, sizes: torch.Tensor, group_size: int,
-                      grain: int, stride_rows: int) -> None:
-        """Enqueue the pushes of a forward sparse exchange on the current stream and its size
-        exchange on the side stream (``brt_p2p_forward_begin``)."""
-        self._pending = (group_size, sizes)  # keeps the device vector alive
-        _lib.call("brt_p2p_forward_begin", self.ctx, rows.data_ptr(), sizes.data_ptr(),
-                  group_size, grain, stride_rows, torch.cuda.current_stream().cuda_stream,
-                  self.side.cuda_stream)
+    # ---- views of the landing halves -------------------------------------------------------
+    def view(self, ptr: int, rows: int, like: torch.Tensor) -> torch.Tensor:
+        """``rows`` rows shaped and typed like the rows of ``like``, at device address ``ptr``
+        inside this arena (no copy)."""
+        off = ptr - self.base
+        nbytes = rows * _row_bytes(like)
+        flat = self._view[off:off + nbytes].view(like.dtype)
+        return flat.view((rows,) + tuple(like.shape[1:]))
 
-    def forward_sizes(self):
-        """Wait for the size exchange: ([world, world * group] int32 matrix, my output rows,
-        whether every rank-to-rank share fits its slot)."""
-        group_size, _ = self._pending
-        self._pending = None
+    def _half_of_next_exchange(self):
+        nxt = int(_lib.query("brt_p2p_ctx_exchanges", self.ctx)) + 1
+        lo = self.base + self.control_bytes + (nxt & 1) * self.half_bytes
+        return lo, lo + self.half_bytes
+
+    def safe_source(self, x: torch.Tensor) -> torch.Tensor:
+        """``x`` itself unless it lives in the half the next exchange lands in (an output held
+        for too long): then a private copy, taken before any peer may write there."""
+        lo, hi = self._half_of_next_exchange()
+        return x.clone() if lo <= x.data_ptr() < hi else x
+
+    # ---- the two exchanges -----------------------------------------------------------------
+    def sparse_forward(self, rows: torch.Tensor, sizes: torch.Tensor, group_size: int,
+                       grain: int, stride_rows: int):
+        """Enqueue a forward sparse exchange on the current stream and wait for its size
+        matrix only.  Returns (matrix [world, world * group] int32, my output rows, whether it
+        fits the landing halves, device address of my output, exchange id)."""
+        main = torch.cuda.current_stream().cuda_stream
+        _lib.call("brt_p2p_sparse_forward_begin", self.ctx, rows.data_ptr(), sizes.data_ptr(),
+                  group_size, grain, stride_rows, main, self.side.cuda_stream, 0)
         matrix = ctypes.POINTER(ctypes.c_int32)()
-        rows = ctypes.c_int64()
-        fits = ctypes.c_int()
-        _lib.call("brt_p2p_forward_sizes", self.ctx, self.side.cuda_stream, ctypes.byref(matrix),
-                  ctypes.byref(rows), ctypes.byref(fits))
-        n = self.world * group_size
-        S = np.ctypeslib.as_array(matrix, shape=(self.world, n)).copy()
-        return S, int(rows.value), bool(fits.value)
+        n_rows, fits = ctypes.c_int64(), ctypes.c_int()
+        out, xid = ctypes.c_void_p(), ctypes.c_uint64()
+        _lib.call("brt_p2p_sparse_forward_sizes", self.ctx, self.side.cuda_stream,
+                  ctypes.byref(matrix), ctypes.byref(n_rows), ctypes.byref(fits),
+                  ctypes.byref(out), ctypes.byref(xid))
+        S = np.ctypeslib.as_array(matrix, shape=(self.world, self.world * group_size)).copy()
+        return S, int(n_rows.value), bool(fits.value), int(out.value), int(xid.value)
 
-    def forward_finish(self, rows: torch.Tensor, out: torch.Tensor) -> None:
-        _lib.call("brt_p2p_forward_finish", self.ctx, rows.data_ptr(), out.data_ptr(),
-                  torch.cuda.current_stream().cuda_stream, self.side.cuda_stream)
+    def sparse_backward(self, exchange_id: int, group_size: int, grain: int, stride_rows: int,
+                        rows: torch.Tensor):
+        """Enqueue the inverse of forward exchange ``exchange_id`` on the current stream.
+        Returns (device address of my output, its rows).  Raises ``_lib.BrtError`` with status
+        BRT_ERR_UNSUPPORTED (on every rank alike) when the exchange cannot take this path."""
+        out, n_rows = ctypes.c_void_p(), ctypes.c_int64()
+        _lib.call("brt_p2p_sparse_backward", self.ctx, exchange_id, group_size, grain,
+                  stride_rows, rows.data_ptr(), torch.cuda.current_stream().cuda_stream, 0,
+                  ctypes.byref(out), ctypes.byref(n_rows))
+        return int(out.value), int(n_rows.value)
 
-    def backward(self, size_matrix: np.ndarray, group_size: int, grain: int, stride_rows: int,
-                 rows: torch.Tensor, out: torch.Tensor) -> None:
-        """Inverse sparse exchange for the int32 size matrix of the matching forward one."""
-        _lib.call("brt_p2p_backward", self.ctx, size_matrix.ctypes.data, group_size, grain,
-                  stride_rows, rows.data_ptr(), out.data_ptr(),
-                  torch.cuda.current_stream().cuda_stream, self.side.cuda_stream)
+    def status(self) -> int:
+        return int(_lib.query("brt_p2p_ctx_status", self.ctx))
+
+    def set_wait_limit(self, seconds: float) -> None:
+        _lib.call("brt_p2p_ctx_set_wait_limit", self.ctx, int(seconds * 1e9))
 
 
 _arena: Optional[PeerArena] = None
 _disabled_reason: Optional[str] = None
-MAX_COPIES = 96
 
 
 def arena() -> Optional[PeerArena]:
@@ -106,7 +130,9 @@ def arena() -> Optional[PeerArena]:
 
 
 def setup(group, rank: int, world: int) -> Optional[PeerArena]:
-    """Create the arena on every rank, or on none: the outcome is agreed by all ranks."""
+    """Create the arena on every rank, or on none.  Every rank takes part in every
+    collective of this function whatever happens to it locally, so a rank that cannot
+    allocate or map makes all ranks fall back to the NCCL transport instead of hanging."""
     global _arena, _disabled_reason
     if _arena is not None or _disabled_reason is not None:
         return _arena
@@ -114,25 +140,64 @@ def setup(group, rank: int, world: int) -> Optional[PeerArena]:
         _disabled_reason = "BRT_P2P=0"
         return None
     half = int(os.environ.get("BRT_P2P_ARENA_MB", "2048")) << 20
-    ok, made, err = 1, None, ""
+    base, handle, err = None, None, ""
     try:
         if dist.get_world_size(group) != torch.cuda.device_count() and \
                 int(os.environ.get("LOCAL_WORLD_SIZE", world)) != world:
             raise RuntimeError("ranks span more than one box")
-        made = PeerArena(group, rank, world, half)
+        ptr = ctypes.c_void_p()
+        buf = (ctypes.c_ubyte * 64)()
+        total = int(_lib.query("brt_p2p_control_bytes")) + 2 * half
+        _lib.call("brt_p2p_alloc", total, ctypes.byref(ptr), buf)
+        base, handle = ptr.value, bytes(buf)
     except Exception as exc:  # IPC not permitted, out of memory, ...
-        ok, err = 0, str(exc)
-    flag = torch.tensor([ok], device="cuda")
+        err = str(exc)
+    handles: List[Optional[bytes]] = [None] * world
+    dist.all_gather_object(handles, handle, group=group)
+    opened: List[int] = []
+    peer_base: List[int] = []
+    ok = all(h is not None for h in handles)
+    if ok:
+        try:
+            for r in range(world):
+                if r == rank:
+                    peer_base.append(base)
+                    continue
+                p = ctypes.c_void_p()
+                _lib.call("brt_p2p_open", (ctypes.c_ubyte * 64).from_buffer_copy(handles[r]),
+                          ctypes.byref(p))
+                opened.append(p.value)
+                peer_base.append(p.value)
+        except Exception as exc:
+            ok, err = False, str(exc)
+    made = None
+    if ok:
+        try:
+            made = PeerArena(rank, world, half, base, peer_base)
+        except Exception as exc:
+            ok, err = False, str(exc)
+    flag = torch.tensor([1 if ok else 0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
     if int(flag.item()) == 1:
         _arena = made
-    else:
-        _disabled_reason = err or "a peer could not map the arena"
-    return _arena
+        return _arena
+    for p in opened:
+        try:
+            _lib.call("brt_p2p_close", p)
+        except Exception:
+            pass
+    if base is not None:
+        try:
+            _lib.call("brt_p2p_free", base)
+        except Exception:
+            pass
+    _disabled_reason = err or "another rank could not allocate or map the arena"
+    return None
 
 
 def check_status() -> None:
-    """Raise if a bounded wait of an earlier exchange ran out (reads one device word)."""
-    if _arena is not None and int(_arena.status.item()) != 0:
-        raise RuntimeError("peer exchange timed out waiting for another rank "
-                           "(brt_p2p_wait, 2 s limit)")
+    """Raise if a bounded wait of an earlier exchange ran out.  Reads a word of host memory
+    that the kernels write; no device synchronisation."""
+    if _arena is not None and _arena.status() != 0:
+        raise RuntimeError("peer exchange timed out waiting for another rank (the bound is "
+                           "PeerArena.set_wait_limit, 2 s by default)")

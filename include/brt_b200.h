@@ -117,6 +117,28 @@ BRT_API int brt_generate_indices_and_loads_static(const int32_t* hot_mask, int32
                                                   int is_tag_index, void* stream);
 
 /*
+ * Bounded waits of the index kernels.  The single-launch scan lets a CTA wait for the column
+ * sums of CTAs that started before it; the wait gives up after a fixed number of polls, the
+ * kernel finishes with what it has (its outputs are then wrong) and records BRT_ERR_TIMEOUT
+ * in a word of host-mapped memory.  No counterpart in the reference (its kernels have no
+ * inter-CTA waits).
+ *
+ * brt_index_status        BRT_OK, or BRT_ERR_TIMEOUT once a scan of this process has given up;
+ *                         read from host memory, no synchronisation.  Results of scans that
+ *                         completed before the call are covered (synchronise first to cover
+ *                         one that is still running).  The first call creates the word
+ *                         (a set-up time allocation); brt_generate_indices_and_loads_static
+ *                         reports through it only once it exists.
+ * brt_index_status_reset  clears the word.
+ * brt_index_set_test_hooks  for tests of the above: `spin_limit` polls per wait (<= 0: the
+ *                         default) and, when `skip_first_run` != 0, a first run of tiles that
+ *                         no CTA owns, so that the waits for its sums run out.
+ */
+BRT_API int brt_index_status(void);
+BRT_API void brt_index_status_reset(void);
+BRT_API void brt_index_set_test_hooks(int spin_limit, int skip_first_run);
+
+/*
  * Replaces brt::router::ThrottleHotmask
  * (include/brt/router/location.h:13-19, src/router/location.cu:59-130,304-315).
  *
@@ -331,10 +353,9 @@ BRT_API int brt_group_sparse_all_to_all(const void* send_buffer, void* recv_buff
 #define BRT_P2P_HANDLE_BYTES 64
 
 /*
- * Same exchange patterns as brt_group_sparse_all_to_all / brt_group_asymmetry_all_to_all
- * (src/distributed/collective.cc:90-224 in the reference), moved by this library's own
- * kernels over NVLink peer memory instead of NCCL send/recv.  No counterpart in the
- * reference for the mechanism.
+ * Same exchange patterns as brt_group_sparse_all_to_all (src/distributed/collective.cc:
+ * 142-224 in the reference), moved by this library's own kernels over NVLink peer memory
+ * instead of NCCL send/recv.  No counterpart in the reference for the mechanism.
  *
  * brt_p2p_alloc   allocates an arena on the current device, zero-fills it and exports it as a
  *                 CUDA IPC handle (BRT_P2P_HANDLE_BYTES bytes) that the caller moves to the
@@ -346,35 +367,35 @@ BRT_API int brt_group_sparse_all_to_all(const void* send_buffer, void* recv_buff
  *                 sized) and then stores `epoch` into slot `my_rank` of every rank's flag
  *                 array.  `my_done_counter` is a zero-initialised 4-byte word in local memory.
  *                 world_size == 0: no flag is raised (a plain multi-range copy).
- * brt_p2p_push_buckets
- *                 the same push planned on the device, for a sender whose bucket sizes are not
- *                 on the host yet: `sizes` is the DEVICE vector of world_size * group_size
- *                 row counts (bucket b = destination rank b / group_size), rows are
- *                 `grain_bytes` long and bucket b starts at source row b * stride_rows
- *                 (stride_rows == 0: buckets are packed).  The buckets of destination i are
- *                 written back to back at slot_ptrs[i]; a destination whose slot pointer is
- *                 null, or whose buckets exceed `slot_bytes`, is left out (the caller sees
- *                 the same sizes later and moves that share another way).  Only buckets whose
- *                 local expert index (b % group_size) lies in [expert_begin, expert_end) are
- *                 moved, so that an exchange can be issued as a few pushes whose arrival is
- *                 signalled one after the other; the packing inside a slot does not depend
- *                 on that range.  At most 1024 buckets.  Raises the flags like brt_p2p_push.
- * brt_p2p_post    writes `n` int32 values (this rank's bucket sizes) into row `my_rank` of the
- *                 size board in every rank's arena and raises slot `my_rank` of the given flag
- *                 arrays; together with brt_p2p_wait this is the size exchange that precedes
- *                 a data exchange (the reference does it with an NCCL all-to-all,
- *                 src/backend/torch/distributed.cc:777-783).
- * brt_p2p_exchange_sizes
- *                 brt_p2p_post + brt_p2p_wait + an asynchronous copy of the status word
- *                 (host_out[0]) and of this rank's board `my_board` (host_out[1 ..
- *                 world_size * n]) into pinned host memory, all on `stream`: the whole size
- *                 exchange in one call.  The caller synchronises the stream before reading.
+ * brt_p2p_post    writes `n` int32 values (this rank's bucket sizes; n may be 0) into row
+ *                 `my_rank` of the size board in every rank's arena and raises slot `my_rank`
+ *                 of the given flag arrays: the size exchange that precedes a data exchange
+ *                 (the reference does it with an NCCL all-to-all,
+ *                 src/backend/torch/distributed.cc:777-783) and, at the same time, the signal
+ *                 that this rank has finished everything it enqueued before the exchange.
+ * brt_p2p_land    one exchange of variable-size buckets planned on the device: waits (bounded)
+ *                 until every slot of `my_ready_flags` holds a value >= epoch, reads the size
+ *                 matrix [sender][destination * group_size + expert] from device memory and
+ *                 copies every bucket this rank holds straight to its row offset in the
+ *                 destination's OUTPUT layout inside landing_ptrs[destination] (peers' arenas
+ *                 and the local one), then stores `epoch` into slot `my_rank` of every rank's
+ *                 arrival flag array.  forward != 0: this rank's rows are ordered
+ *                 [destination rank][its local expert] and land ordered
+ *                 [local expert][source rank] (GroupSparseAllToAllForward); forward == 0: the
+ *                 inverse (GroupSparseAllToAllBackward).  stride_rows != 0: buckets sit
+ *                 stride_rows rows apart on both sides.  If some rank's landed rows exceed
+ *                 half_bytes nothing is copied (every rank takes the same decision from the
+ *                 same matrix) but the flags are still raised.  `keep_matrix` (may be null)
+ *                 receives a copy of the matrix.  At most 1024 buckets.  When the wait runs out
+ *                 the kernel writes BRT_ERR_TIMEOUT to `status_word` (device) and
+ *                 `host_status_word` (device address of host-mapped memory, may be null),
+ *                 copies nothing, raises no flag and returns.
  * brt_p2p_wait    enqueues a kernel that returns once every slot of `my_flag_array` (except
- *                 slot `skip_rank`, -1 for none) holds a value >= epoch.  A wait enqueued on
- *                 another stream than this rank's own push passes its own rank as skip_rank,
- *                 so that it only ever waits for kernels running on other GPUs.  The wait is bounded (2 s): on expiry it writes
- *                 BRT_ERR_TIMEOUT into `status_word` (a 4-byte device word the caller reads
- *                 back when convenient) and returns; it never blocks the GPU indefinitely.
+ *                 slot `skip_rank`, -1 for none) holds a value >= epoch.  A wait for this
+ *                 rank's own landing kernel passes its own rank as skip_rank, so that it only
+ *                 ever waits for kernels running on other GPUs.  The wait is bounded by
+ *                 `wait_limit_ns`: on expiry it reports like brt_p2p_land and returns; it
+ *                 never blocks the GPU indefinitely.
  */
 BRT_API int brt_p2p_alloc(size_t bytes, void** dev_ptr, void* ipc_handle_out);
 BRT_API int brt_p2p_open(const void* ipc_handle, void** peer_ptr);
@@ -384,65 +405,88 @@ BRT_API int brt_p2p_push(const void* src, int copy_count, const int64_t* src_off
                          void* const* dst_ptrs, const int64_t* bytes, int world_size,
                          int my_rank, uint64_t epoch, void* const* peer_flag_arrays,
                          void* my_done_counter, void* stream);
-BRT_API int brt_p2p_push_buckets(const void* src, const int32_t* sizes, int world_size,
-                                 int group_size, int my_rank, int64_t grain_bytes,
-                                 int64_t stride_rows, void* const* slot_ptrs, int64_t slot_bytes,
-                                 int expert_begin, int expert_end, uint64_t epoch,
-                                 void* const* peer_flag_arrays, void* my_done_counter,
-                                 void* stream);
 BRT_API int brt_p2p_post(const int32_t* values, int n, int world_size, int my_rank,
                          uint64_t epoch, void* const* peer_boards, void* const* peer_flag_arrays,
                          void* stream);
-BRT_API int brt_p2p_exchange_sizes(const int32_t* values, int n, int world_size, int my_rank,
-                                   uint64_t epoch, void* const* peer_boards,
-                                   void* const* peer_flag_arrays, const void* my_flag_array,
-                                   const void* my_board, void* status_word, int32_t* host_out,
-                                   void* stream);
+BRT_API int brt_p2p_land(const void* rows, const int32_t* size_matrix, int32_t* keep_matrix,
+                         int world_size, int group_size, int my_rank, int forward,
+                         int64_t grain_bytes, int64_t stride_rows, int64_t half_bytes,
+                         void* const* landing_ptrs, uint64_t epoch, const void* my_ready_flags,
+                         void* const* peer_arrive_flag_arrays, void* my_done_counter,
+                         void* my_abort_word, void* status_word, void* host_status_word,
+                         uint64_t wait_limit_ns, void* stream);
 BRT_API int brt_p2p_wait(const void* my_flag_array, int world_size, int skip_rank,
-                         uint64_t epoch, void* status_word, void* stream);
+                         uint64_t epoch, void* status_word, void* host_status_word,
+                         uint64_t wait_limit_ns, void* stream);
 
 /*
- * Exchange context: the host-side planning of the two sparse exchanges on top of the calls
- * above, so that a forward or an inverse exchange costs the host a few calls.  It owns the
- * arena bookkeeping (flag epochs, which half is current, the per-source slots of a half, a
- * pinned buffer for the size matrix) for an arena whose control block it lays out itself
- * (flags at 0 and 256, completion counter at 512, status word at 1024, two size boards from
- * 2048, data halves from 65536).  `arenas[r]` is rank r's arena as mapped in this process
- * (`my_arena` for r == my_rank).
+ * Exchange context: the host side of the two sparse exchanges on top of the calls above.  It
+ * owns the bookkeeping of one arena (the exchange counter that serves as flag epoch, which
+ * landing half is current, the size matrices kept for the inverse exchanges, a pinned buffer
+ * for the sizes, a host-mapped status word).  The arena is brt_p2p_control_bytes() of control
+ * block followed by two landing halves of `half_bytes` each; `arenas[r]` is rank r's arena as
+ * mapped in this process (`my_arena` for r == my_rank).  Every rank must issue the same
+ * exchanges in the same order.
  *
- * brt_p2p_forward_begin   group_sparse_all_to_all, part 1 (src/distributed/collective.cc:
- *                 142-185 in the reference): enqueues the device-planned pushes of this
- *                 rank's buckets on `main_stream` and the size exchange on `side_stream`
- *                 (ordered behind what `main_stream` holds so far).  BRT_ERR_UNSUPPORTED: too
- *                 many buckets, nothing enqueued.
- * brt_p2p_forward_sizes   waits for the size exchange; returns the gathered matrix
- *                 ([sender][destination * group_size + expert] int32, valid until the next
- *                 begin), this rank's output row count and whether every rank-to-rank share
- *                 fits its slot (if not, every rank sees the same and the caller moves the
- *                 rows another way).
- * brt_p2p_forward_finish  enqueues on `side_stream` the copy of this rank's own buckets and,
- *                 push by push behind a bounded wait, the expert-major copy-out of what the
- *                 peers sent into `out`; `main_stream` then waits for `side_stream`.
- * brt_p2p_backward        size_known_group_sparse_all_to_all (collective.cc:187-224): given
- *                 the size matrix of the matching forward exchange, pushes every bucket back
- *                 to its final offset at its owner (own buckets straight into `out`) and
- *                 copies out what comes back, with the same stream discipline.
+ * The output of an exchange is NOT copied anywhere: `out_data` points into this rank's
+ * landing half of that exchange.  The halves alternate, and a peer only writes into a half
+ * after this rank has entered the exchange that uses it, so an output stays valid until this
+ * rank's stream reaches the second exchange after the one that produced it; work that reads
+ * it must be enqueued (on the same stream) before that exchange.
+ *
+ * `stages` selects which parts of an exchange a call enqueues (0 = all).  A rank of a real
+ * job always passes 0.  Separate stages exist so that several ranks can be driven from ONE
+ * stream of one GPU (tests): all posts first, then all landings, then all waits, so that no
+ * kernel ever waits for a kernel enqueued behind it.
+ *
+ * brt_p2p_sparse_forward_begin   group_sparse_all_to_all, part 1 (collective.cc:142-185):
+ *                 post of `sizes` (DEVICE vector of world_size * group_size row counts), the
+ *                 landing kernel and the wait for the peers' rows on `main_stream`; the copy
+ *                 of the gathered size matrix to the host on `side_stream`, ordered behind the
+ *                 post.  BRT_ERR_UNSUPPORTED: too many buckets, nothing enqueued.
+ * brt_p2p_sparse_forward_sizes   part 2: waits for the size matrix only (the rows are still
+ *                 moving); returns the matrix ([sender][destination * group_size + expert],
+ *                 valid until the next begin), the identifier under which it is kept for the
+ *                 inverse exchange, this rank's output (rows ordered [local expert][source],
+ *                 row count) and whether every rank's rows fit its landing half: if not,
+ *                 nothing was moved, every rank sees the same and moves its rows another way.
+ * brt_p2p_sparse_backward        size_known_group_sparse_all_to_all (collective.cc:187-224) of
+ *                 the forward exchange `exchange_id`: every bucket goes back to its offset in
+ *                 its owner's original layout.  BRT_ERR_UNSUPPORTED (nothing enqueued, same on
+ *                 every rank): the matrix is no longer kept (32 are) or some rank's rows do
+ *                 not fit a landing half.
+ * brt_p2p_ctx_status             BRT_OK, or BRT_ERR_TIMEOUT once a bounded wait of an exchange
+ *                 of this context has run out (read from host memory, no synchronisation);
+ *                 later exchanges are then refused until brt_p2p_ctx_reset_status.
+ * brt_p2p_ctx_set_wait_limit     the bound of every wait (default 2 s: the largest skew
+ *                 between ranks that an exchange tolerates).
  */
+#define BRT_P2P_STAGE_POST 1
+#define BRT_P2P_STAGE_SIZES 2
+#define BRT_P2P_STAGE_PUSH 4
+#define BRT_P2P_STAGE_WAIT 8
+#define BRT_P2P_STAGE_ALL 15
+
 typedef struct brt_p2p_ctx brt_p2p_ctx;
+BRT_API size_t brt_p2p_control_bytes(void);
 BRT_API int brt_p2p_ctx_create(int world_size, int my_rank, void* my_arena,
                                void* const* arenas, size_t half_bytes, brt_p2p_ctx** out);
 BRT_API void brt_p2p_ctx_destroy(brt_p2p_ctx* ctx);
-BRT_API size_t brt_p2p_ctx_slot_bytes(const brt_p2p_ctx* ctx);
-BRT_API int brt_p2p_forward_begin(brt_p2p_ctx* ctx, const void* rows, const int32_t* sizes,
-                                  int group_size, int64_t grain_bytes, int64_t stride_rows,
-                                  void* main_stream, void* side_stream);
-BRT_API int brt_p2p_forward_sizes(brt_p2p_ctx* ctx, void* side_stream,
-                                  const int32_t** size_matrix, int64_t* out_rows, int* fits);
-BRT_API int brt_p2p_forward_finish(brt_p2p_ctx* ctx, const void* rows, void* out,
-                                   void* main_stream, void* side_stream);
-BRT_API int brt_p2p_backward(brt_p2p_ctx* ctx, const int32_t* size_matrix, int group_size,
-                             int64_t grain_bytes, int64_t stride_rows, const void* rows,
-                             void* out, void* main_stream, void* side_stream);
+BRT_API int brt_p2p_ctx_set_wait_limit(brt_p2p_ctx* ctx, uint64_t nanoseconds);
+BRT_API int brt_p2p_ctx_status(const brt_p2p_ctx* ctx);
+BRT_API int brt_p2p_ctx_reset_status(brt_p2p_ctx* ctx);
+BRT_API uint64_t brt_p2p_ctx_exchanges(const brt_p2p_ctx* ctx);
+BRT_API int brt_p2p_sparse_forward_begin(brt_p2p_ctx* ctx, const void* rows,
+                                         const int32_t* sizes, int group_size,
+                                         int64_t grain_bytes, int64_t stride_rows,
+                                         void* main_stream, void* side_stream, int stages);
+BRT_API int brt_p2p_sparse_forward_sizes(brt_p2p_ctx* ctx, void* side_stream,
+                                         const int32_t** size_matrix, int64_t* out_rows,
+                                         int* fits, void** out_data, uint64_t* exchange_id);
+BRT_API int brt_p2p_sparse_backward(brt_p2p_ctx* ctx, uint64_t exchange_id, int group_size,
+                                    int64_t grain_bytes, int64_t stride_rows, const void* rows,
+                                    void* main_stream, int stages, void** out_data,
+                                    int64_t* out_rows);
 
 #ifdef __cplusplus
 }

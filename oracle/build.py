@@ -49,7 +49,10 @@ def build_oracle(force: bool = False) -> Path:
 
 
 def reference_root() -> Path:
-    return Path(os.environ.get("BRT_REFERENCE_ROOT", "/root/reference"))
+    """The reference checkout: BRT_REFERENCE_ROOT, else a directory named ``reference``
+    beside this repository."""
+    default = Path(__file__).resolve().parents[2] / "reference"
+    return Path(os.environ.get("BRT_REFERENCE_ROOT", str(default)))
 
 
 def build_reference(force: bool = False):

@@ -47,7 +47,10 @@ def main():
 
     # ---- packed (sparse) exchange, forward and back, for G local experts
     # (d = 5 floats is not a 16-byte multiple: that case takes the NCCL transport either way)
-    for G, d, hi in ((1, 8, 40), (2, 16, 30), (4, 5, 12), (4, 8, 12), (3, 4, 20), (5, 12, 7)):
+    # (G = 64: more buckets than a host-planned copy list ever held; d = 1024 with up to 200
+    # rows per bucket overflows a 1 MB landing half, which must send every rank to NCCL)
+    for G, d, hi in ((1, 8, 40), (2, 16, 30), (4, 5, 12), (4, 8, 12), (3, 4, 20), (5, 12, 7),
+                     (64, 4, 5), (2, 1024, 200)):
         all_in = [rank_inputs(r, W, G, d, hi) for r in range(W)]
         fwd = oracle.sim_group_sparse_all_to_all([a[0] for a in all_in], [a[1] for a in all_in])
         x, sizes = all_in[rank]
@@ -59,6 +62,28 @@ def main():
         assert np.array_equal(out.cpu().numpy(), fwd[rank][0]), f"rank {rank} forward G={G}"
         back = brt_dist.size_known_group_sparse_a2a(out, out_loads, in_loads)
         assert np.array_equal(back.cpu().numpy(), x), f"rank {rank} round trip G={G}"
+    # two forward exchanges before their inverses, the inverses in reverse order, and one
+    # rank whose send sizes are the same in both: each inverse must pick its own size matrix
+    G, d = 2, 8
+    first = [rank_inputs(r, W, G, d, 20) for r in range(W)]
+    second = [rank_inputs(r + 50, W, G, d, 20) for r in range(W)]
+    second[W - 1] = (np.random.default_rng(77).standard_normal(first[W - 1][0].shape)
+                     .astype(np.float32), first[W - 1][1].copy())
+    xa, sa = first[rank]
+    xb, sb = second[rank]
+    out_a, ol_a, il_a = brt_dist.group_sparse_a2a(torch.from_numpy(xa).to(dev),
+                                                  torch.from_numpy(sa).to(dev))
+    out_a = out_a.clone()  # held across two more exchanges: keep a private copy
+    out_b, ol_b, il_b = brt_dist.group_sparse_a2a(torch.from_numpy(xb).to(dev),
+                                                  torch.from_numpy(sb).to(dev))
+    back_b = brt_dist.size_known_group_sparse_a2a(out_b, ol_b, il_b)
+    assert np.array_equal(back_b.cpu().numpy(), xb), f"rank {rank}: nested inverse (second)"
+    back_a = brt_dist.size_known_group_sparse_a2a(out_a, ol_a, il_a)
+    assert np.array_equal(back_a.cpu().numpy(), xa), f"rank {rank}: nested inverse (first)"
+    # size tensors rebuilt by the caller name no exchange: the inverse goes over NCCL
+    back_a2 = brt_dist.size_known_group_sparse_a2a(out_a, ol_a.clone(), il_a.clone())
+    assert np.array_equal(back_a2.cpu().numpy(), xa), f"rank {rank}: inverse by sizes only"
+
     # padded buckets
     for G, d, stride in ((2, 4, 16), (3, 8, 10), (1, 4, 7)):
         all_in = [rank_inputs(r, W, G, d, stride + 1, stride) for r in range(W)]

@@ -28,7 +28,7 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 REPO = HERE.parent.parent
-REF = Path(os.environ.get("BRT_REFERENCE_ROOT", "/root/reference"))
+REF = Path(os.environ.get("BRT_REFERENCE_ROOT", str(REPO.parent / "reference")))
 
 
 def _tensor_literals(text):

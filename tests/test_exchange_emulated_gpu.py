@@ -1,0 +1,240 @@
+"""The peer-memory sparse exchange with all ranks emulated on ONE GPU.
+
+Each emulated rank has its own arena and its own exchange context; all of them enqueue on one
+stream, stage by stage (every rank's post, then every rank's landing kernel, then every
+rank's wait), so that each kernel finds the flags it needs already raised by a kernel that
+ran before it: nothing ever waits for a kernel enqueued behind it.  The landing kernels, the
+device-side planning and the host bookkeeping are exactly those of a real multi-GPU job; the
+"peer" pointers simply point into arenas of the same device.  Outputs are compared bit for
+bit with the CPU restatement of the reference's walk (src/distributed/collective.cc:142-224).
+
+The last test makes a bounded wait run out on purpose (a rank that never posts) and checks
+that the kernels return, that the status says so and that the device keeps working.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from brainstorm_b200 import _lib
+
+pytestmark = pytest.mark.gpu
+
+POST, SIZES, PUSH, WAIT = 1, 2, 4, 8
+HALF = 8 << 20
+
+
+class Ranks:
+    """W arenas and contexts on the current device."""
+
+    def __init__(self, world, half=HALF):
+        self.world, self.half = world, half
+        self.control = int(_lib.query("brt_p2p_control_bytes"))
+        self.arenas, self.ctxs = [], []
+        for _ in range(world):
+            p, h = ctypes.c_void_p(), (ctypes.c_ubyte * 64)()
+            _lib.call("brt_p2p_alloc", self.control + 2 * half, ctypes.byref(p), h)
+            self.arenas.append(p.value)
+        table = (ctypes.c_void_p * world)(*self.arenas)
+        for r in range(world):
+            c = ctypes.c_void_p()
+            _lib.call("brt_p2p_ctx_create", world, r, self.arenas[r], table, half,
+                      ctypes.byref(c))
+            self.ctxs.append(c)
+
+    def close(self):
+        torch.cuda.synchronize()
+        for c in self.ctxs:
+            _lib.query("brt_p2p_ctx_destroy", c)
+        for a in self.arenas:
+            _lib.call("brt_p2p_free", a)
+
+    def rows_at(self, ptr, rows, cols, dtype=torch.float32):
+        nbytes = rows * cols * torch.empty((), dtype=dtype).element_size()
+
+        class Raw:
+            __cuda_array_interface__ = {"shape": (max(nbytes, 1),), "typestr": "|u1",
+                                        "data": (ptr, False), "version": 2}
+        flat = torch.as_tensor(Raw(), device="cuda")[:nbytes]
+        return flat.view(dtype).view(rows, cols)
+
+    def forward(self, xs, sizes, group, stride=0):
+        st = torch.cuda.current_stream().cuda_stream
+        grain = xs[0].size(1) * xs[0].element_size()
+        for stage in (POST, SIZES, PUSH, WAIT):
+            for r in range(self.world):
+                _lib.call("brt_p2p_sparse_forward_begin", self.ctxs[r], xs[r].data_ptr(),
+                          sizes[r].data_ptr(), group, grain, stride, st, st, stage)
+        outs, ids, fit = [], [], []
+        for r in range(self.world):
+            m = ctypes.POINTER(ctypes.c_int32)()
+            n_rows, fits = ctypes.c_int64(), ctypes.c_int()
+            out, xid = ctypes.c_void_p(), ctypes.c_uint64()
+            _lib.call("brt_p2p_sparse_forward_sizes", self.ctxs[r], st, ctypes.byref(m),
+                      ctypes.byref(n_rows), ctypes.byref(fits), ctypes.byref(out),
+                      ctypes.byref(xid))
+            S = np.ctypeslib.as_array(m, shape=(self.world, self.world * group)).copy()
+            outs.append((out.value, n_rows.value, S))
+            ids.append(xid.value)
+            fit.append(bool(fits.value))
+        return outs, ids, fit
+
+    def backward(self, ids, xs, group, stride=0):
+        st = torch.cuda.current_stream().cuda_stream
+        grain = xs[0].size(1) * xs[0].element_size()
+        res = [None] * self.world
+        for stage in (POST, PUSH, WAIT):
+            for r in range(self.world):
+                out, n_rows = ctypes.c_void_p(), ctypes.c_int64()
+                _lib.call("brt_p2p_sparse_backward", self.ctxs[r], ids[r], group, grain, stride,
+                          xs[r].data_ptr(), st, stage, ctypes.byref(out), ctypes.byref(n_rows))
+                res[r] = (out.value, n_rows.value)
+        return res
+
+
+def make_inputs(world, group, cols, hi, stride, seed):
+    rng = np.random.default_rng(seed)
+    xs, sizes = [], []
+    for _ in range(world):
+        s = rng.integers(0, hi, size=world * group).astype(np.int32)
+        if rng.random() < 0.3:
+            s[rng.integers(0, s.size)] = 0
+        rows = stride * world * group if stride else int(s.sum())
+        xs.append(rng.standard_normal((rows, cols)).astype(np.float32))
+        sizes.append(s)
+    return xs, sizes
+
+
+CASES = [
+    # world, group, cols (fp32), largest bucket, stride
+    (2, 1, 4, 40, 0), (2, 4, 8, 30, 0), (4, 2, 16, 25, 0), (4, 5, 12, 9, 0),
+    (8, 8, 64, 200, 0), (8, 16, 4, 6, 0), (3, 7, 8, 11, 0), (8, 32, 4, 5, 0),
+    (2, 2, 4, 17, 16), (4, 3, 8, 11, 10), (8, 4, 4, 8, 7), (2, 128, 4, 3, 0),
+]
+
+
+@pytest.mark.parametrize("world,group,cols,hi,stride", CASES)
+def test_forward_and_back(world, group, cols, hi, stride):
+    dev = torch.device("cuda", 0)
+    xs_np, sizes_np = make_inputs(world, group, cols, hi if not stride else stride + 1, stride,
+                                  seed=world * 1000 + group)
+    sim = oracle.sim_group_sparse_all_to_all(xs_np, sizes_np, bool(stride), stride)
+    ranks = Ranks(world)
+    try:
+        xs = [torch.from_numpy(x).to(dev) for x in xs_np]
+        sizes = [torch.from_numpy(s).to(dev) for s in sizes_np]
+        for repeat in range(3):  # both landing halves, and a half that is reused
+            outs, ids, fit = ranks.forward(xs, sizes, group, stride)
+            assert all(fit)
+            landed = []
+            for r in range(world):
+                ptr, rows, S = outs[r]
+                assert rows == sim[r][0].shape[0]
+                assert np.array_equal(S, np.stack(sizes_np)), "size matrix differs"
+                got = ranks.rows_at(ptr, rows, cols)
+                landed.append(got)
+                want = sim[r][0]
+                g = got.cpu().numpy()
+                if stride:
+                    for b, n in enumerate(sim[r][1]):
+                        assert np.array_equal(g[b * stride:b * stride + n],
+                                              want[b * stride:b * stride + n]), (r, b)
+                else:
+                    assert np.array_equal(g, want), f"rank {r}: forward rows differ"
+            back = ranks.backward(ids, landed, group, stride)
+            for r in range(world):
+                ptr, rows = back[r]
+                assert rows == xs_np[r].shape[0]
+                g = ranks.rows_at(ptr, rows, cols).cpu().numpy()
+                if stride:
+                    for b, n in enumerate(sizes_np[r]):
+                        assert np.array_equal(g[b * stride:b * stride + n],
+                                              xs_np[r][b * stride:b * stride + n]), (r, b)
+                else:
+                    assert np.array_equal(g, xs_np[r]), f"rank {r}: round trip differs"
+        for c in ranks.ctxs:
+            assert _lib.query("brt_p2p_ctx_status", c) == 0
+    finally:
+        ranks.close()
+
+
+def test_nested_forwards_then_inverses():
+    """Two forward exchanges whose inverses come in reverse order (layer 1, layer 2, back 2,
+    back 1), with one rank sending the same sizes in both: each inverse must use the matrix
+    of its own forward exchange."""
+    dev = torch.device("cuda", 0)
+    world, group, cols = 4, 2, 8
+    a_np, sa_np = make_inputs(world, group, cols, 20, 0, seed=1)
+    b_np, sb_np = make_inputs(world, group, cols, 20, 0, seed=2)
+    sb_np[1] = sa_np[1].copy()  # rank 1 sends the same sizes in both exchanges
+    b_np[1] = np.random.default_rng(3).standard_normal(a_np[1].shape).astype(np.float32)
+    ranks = Ranks(world)
+    try:
+        to = lambda arrs: [torch.from_numpy(a).to(dev) for a in arrs]
+        a, sa, b, sb = to(a_np), to(sa_np), to(b_np), to(sb_np)
+        outs_a, ids_a, _ = ranks.forward(a, sa, group)
+        kept_a = [ranks.rows_at(p, n, cols).clone() for p, n, _ in outs_a]
+        outs_b, ids_b, _ = ranks.forward(b, sb, group)
+        kept_b = [ranks.rows_at(p, n, cols).clone() for p, n, _ in outs_b]
+        back_b = ranks.backward(ids_b, kept_b, group)
+        for r in range(world):
+            assert np.array_equal(ranks.rows_at(*back_b[r], cols).cpu().numpy(), b_np[r])
+        back_a = ranks.backward(ids_a, kept_a, group)
+        for r in range(world):
+            assert np.array_equal(ranks.rows_at(*back_a[r], cols).cpu().numpy(), a_np[r])
+    finally:
+        ranks.close()
+
+
+def test_rows_that_do_not_fit_are_left_alone():
+    dev = torch.device("cuda", 0)
+    world, group, cols = 2, 1, 1024
+    ranks = Ranks(world, half=1 << 16)  # 64 KB halves, 4 KB rows
+    try:
+        sizes_np = [np.array([10, 30], dtype=np.int32), np.array([5, 2], dtype=np.int32)]
+        xs = [torch.zeros((int(s.sum()), cols), device=dev) for s in sizes_np]
+        sizes = [torch.from_numpy(s).to(dev) for s in sizes_np]
+        outs, ids, fit = ranks.forward(xs, sizes, group)
+        assert fit == [False, False]  # rank 1 would receive 32 rows = 128 KB
+        with pytest.raises(_lib.BrtError) as err:  # 40 rows go back to rank 0: too many as well
+            ranks.backward(ids, xs, group)
+        assert err.value.status == 4
+    finally:
+        ranks.close()
+
+
+def test_wait_runs_out_and_is_reported():
+    """Rank 1 never enters the exchange: rank 0's kernels give up after the (shortened)
+    limit, copy nothing, and both the call that reads the sizes and the status query say so."""
+    dev = torch.device("cuda", 0)
+    ranks = Ranks(2)
+    try:
+        _lib.call("brt_p2p_ctx_set_wait_limit", ranks.ctxs[0], 20_000_000)  # 20 ms
+        x = torch.ones((8, 4), device=dev)
+        sizes = torch.tensor([3, 5], dtype=torch.int32, device=dev)
+        st = torch.cuda.current_stream().cuda_stream
+        _lib.call("brt_p2p_sparse_forward_begin", ranks.ctxs[0], x.data_ptr(), sizes.data_ptr(),
+                  1, 16, 0, st, st, 0)
+        m = ctypes.POINTER(ctypes.c_int32)()
+        n_rows, fits = ctypes.c_int64(), ctypes.c_int()
+        out, xid = ctypes.c_void_p(), ctypes.c_uint64()
+        with pytest.raises(_lib.BrtError) as err:
+            _lib.call("brt_p2p_sparse_forward_sizes", ranks.ctxs[0], st, ctypes.byref(m),
+                      ctypes.byref(n_rows), ctypes.byref(fits), ctypes.byref(out),
+                      ctypes.byref(xid))
+        assert err.value.status == 7  # BRT_ERR_TIMEOUT
+        torch.cuda.synchronize()  # every kernel of the exchange has returned
+        assert _lib.query("brt_p2p_ctx_status", ranks.ctxs[0]) == 7
+        with pytest.raises(_lib.BrtError):  # refused until the status is cleared
+            _lib.call("brt_p2p_sparse_forward_begin", ranks.ctxs[0], x.data_ptr(),
+                      sizes.data_ptr(), 1, 16, 0, st, st, 0)
+        _lib.call("brt_p2p_ctx_reset_status", ranks.ctxs[0])
+        assert _lib.query("brt_p2p_ctx_status", ranks.ctxs[0]) == 0
+        # nothing landed in rank 1's arena and the device still answers
+        landing = ranks.rows_at(ranks.arenas[1] + ranks.control + ranks.half, 8, 4)  # exchange 1: half 1
+        assert float(landing.abs().sum()) == 0.0
+        assert float((x * 2).sum()) == 64.0
+    finally:
+        ranks.close()

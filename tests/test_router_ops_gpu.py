@@ -296,6 +296,52 @@ def test_dispatch_with_tag_indices(R, weighted):
         assert np.array_equal(host(got[0]), exp[0]) and np.array_equal(host(got[1]), exp[1])
 
 
+def test_dispatch_2d_with_tag_indices(R):
+    """Tag-index routing of a [cell, path, ...] input: row i of path e pulls cell tag-1 from
+    that path's own slice (src/router/route.cu:161-206)."""
+    rng = np.random.default_rng(8)
+    T, E = 640, 8
+    mask = rand_mask(rng, T, E, 3)
+    tag, loads = oracle.generate_indices_and_loads(mask, None, False, False, True)
+    for cell in (1, 6):
+        x = rng.standard_normal((T, E, cell)).astype(np.float32)
+        for kw in ({}, dict(max_path_padding=True, max_path_load=400)):
+            exp = oracle.dispatch_with_indices_and_loads(x, tag, loads, None, True, None,
+                                                         is_1d_routing=False, is_tag_index=True,
+                                                         **kw)
+            got = R.dispatch_with_indices_and_loads(
+                dev(x), dev(tag), dev(loads), None, True, None,
+                kw.get("max_path_padding", False), kw.get("max_path_load", 0), False, True)
+            assert got[0].shape == exp[0].shape
+            assert np.array_equal(host(got[0]), exp[0]), (cell, kw)
+            assert np.array_equal(host(got[1]), exp[1]), (cell, kw)
+
+
+def test_index_scan_reports_a_wait_that_ran_out(R):
+    """The single-launch scan lets a CTA wait for the column sums of earlier CTAs.  With the
+    test hooks the first run of tiles has no owner and a wait gives up after 50 polls: the
+    kernel must return (no hang), and the status word, then the next index op, must say so."""
+    from brainstorm_b200 import _lib
+
+    rng = np.random.default_rng(11)
+    mask = dev(rand_mask(rng, 150000, 32, 2))
+    good = R.generate_indices_and_loads(mask)
+    torch.cuda.synchronize()
+    assert _lib.query("brt_index_status") == 0
+    _lib.query("brt_index_set_test_hooks", 50, 1)
+    try:
+        R.generate_indices_and_loads(mask)
+        torch.cuda.synchronize()  # returns: every wait is bounded
+        assert _lib.query("brt_index_status") == 7  # BRT_ERR_TIMEOUT
+    finally:
+        _lib.query("brt_index_set_test_hooks", 0, 0)
+    with pytest.raises(_lib.BrtError) as err:
+        R.generate_indices_and_loads(mask)
+    assert err.value.status == 7
+    again = R.generate_indices_and_loads(mask)  # reported once; the library keeps working
+    assert torch.equal(again[0], good[0]) and torch.equal(again[1], good[1])
+
+
 def test_dispatch_empty_and_single(R):
     x = torch.zeros((0, 5), device="cuda")
     idx = torch.zeros((0, 3), dtype=torch.int32, device="cuda")

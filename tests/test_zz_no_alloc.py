@@ -16,6 +16,8 @@ import numpy as np
 import pytest
 import torch
 
+import oracle
+
 pytestmark = pytest.mark.gpu
 
 
@@ -68,6 +70,12 @@ def test_static_scratch_entry_point_matches_regular_one():
         torch.cuda.synchronize()
         assert torch.equal(got_l, want_l)
         assert torch.equal(got_i, want_i)
+        # and against the CPU restatement of the reference's kernel
+        ref_i, ref_l = oracle.generate_indices_and_loads(
+            mask.cpu().numpy(), None if c is None else c.cpu().numpy().tolist(), cpad, False,
+            tag)
+        assert np.array_equal(got_i.cpu().numpy(), ref_i)
+        assert np.array_equal(got_l.cpu().numpy(), ref_l)
     # back to back on one stream without a sync in between
     a = _static(_lib, calls[0][0], caps, True, False)
     b = _static(_lib, calls[1][0], None, False, True)
