@@ -69,11 +69,15 @@ def check_index_status() -> None:
     loads are wrong.  Reads a word of host memory that the kernels write, no device
     synchronisation; every index op calls it on entry, so the error surfaces at the next
     index op at the latest."""
-    if _lib.query("brt_index_status") != 0:
+    code = _lib.query("brt_index_status")
+    if code != 0:
         _lib.query("brt_index_status_reset")
+        if code == 1:
+            raise _lib.BrtError("a fused throttle + index scan was given a mask with values "
+                                "other than 0/1; the indices it returned are zero", 1)
         raise _lib.BrtError("an index scan gave up waiting for the column sums of an earlier "
                             "CTA (BRT_ERR_TIMEOUT); the indices and loads it returned are "
-                            "not valid", 7)
+                            "not valid", code)
 
 
 def throttle_hotmask(hotmask: torch.Tensor, prefix: torch.Tensor, threshold: torch.Tensor):
@@ -132,8 +136,60 @@ def generate_indices_and_loads(
     return indices, loads
 
 
+def throttle_and_generate_indices(
+    hot_mask: torch.Tensor,
+    prefix: torch.Tensor,
+    threshold: torch.Tensor,
+    supported_capacities: Optional[torch.Tensor] = None,
+    capacity_padding: bool = False,
+    path_wise_padding: bool = False,
+    with_mask: bool = False,
+):
+    """``throttle_hotmask`` followed by ``generate_indices_and_loads`` (seat indices) of the
+    throttled 0/1 mask, as one pass over the mask (no counterpart in the reference's
+    extension: python/brt/router/protocol/swin_moe.py:112-140 and
+    python/brt/router/fabric/generic.py:83-89 call the two ops one after the other).
+    Returns (indices, loads, prefix), plus the throttled mask with ``with_mask``; ``prefix``
+    is updated in place.  Masks the single-launch scan cannot take go through the two ops."""
+    _check_cuda(hot_mask, "hot_mask")
+    _check_cuda(prefix, "prefix")
+    _check_cuda(threshold, "threshold")
+    check_index_status()
+    if hot_mask.size(1) != prefix.size(0) or hot_mask.size(1) != threshold.size(0):
+        raise RuntimeError("CHECK_EQ fails.")
+    hot_mask = _int32c(hot_mask, "hot_mask")
+    threshold = _int32c(threshold, "threshold")
+    if prefix.dtype != torch.int32 or not prefix.is_contiguous():
+        raise RuntimeError("prefix must be a contiguous int32 tensor (it is updated in place)")
+    T, E = hot_mask.shape
+    dev = hot_mask.device
+    with torch.cuda.device(dev):
+        caps, ncap = None, 0
+        if supported_capacities is not None:
+            _check_cuda(supported_capacities, "supported_capacities.value()")
+            caps = _int32c(supported_capacities, "supported_capacities")
+            ncap = caps.size(0)
+        indices = torch.empty_like(hot_mask)
+        loads = torch.empty((E,), dtype=torch.int32, device=dev)
+        throttled = torch.empty_like(hot_mask) if with_mask else None
+        nbytes = _lib.query("brt_index_scratch_bytes", T, E)
+        scratch = _scratch.get("index", dev, nbytes)
+        try:
+            _lib.call("brt_throttle_and_generate_indices", _ptr(hot_mask), _ptr(indices),
+                      _ptr(loads), _ptr(prefix), _ptr(threshold), _ptr(throttled), T, E,
+                      _ptr(caps), ncap, int(bool(capacity_padding)),
+                      int(bool(path_wise_padding)), _ptr(scratch), scratch.numel(), _stream(dev))
+        except _lib.BrtError as exc:
+            if exc.status != 4:  # BRT_ERR_UNSUPPORTED: the two-step route takes every shape
+                raise
+            throttled, prefix = throttle_hotmask(hot_mask, prefix, threshold)
+            indices, loads = generate_indices_and_loads(throttled, supported_capacities,
+                                                        capacity_padding, path_wise_padding)
+    return (indices, loads, prefix, throttled) if with_mask else (indices, loads, prefix)
+
+
 _GATE = {"topk": 0, "threshold": 1}
-_ROUTE_OUT = {"mask": 0, "throttled_mask": 1, "seat_indices": 2}
+_ROUTE_OUT = {"mask": 0, "throttled_mask": 1, "seat_indices": 2, "throttled_seat_indices": 3}
 
 
 def route_scores_supported(score: torch.Tensor) -> bool:
@@ -157,6 +213,7 @@ def route_scores(
     prefix: Optional[torch.Tensor] = None,
     throttle_capacity: Optional[torch.Tensor] = None,
     with_gates: bool = False,
+    with_mask: bool = False,
 ):
     """Route decision and index scan in one launch, straight from the gate's scores (no
     counterpart in the reference's extension: it fuses a protocol of
@@ -164,7 +221,9 @@ def route_scores(
 
     ``output`` = "mask": (hot_mask, cells per path); "throttled_mask": (hot_mask cut at
     ``throttle_capacity`` on top of ``prefix``, prefix) with ``prefix`` updated in place;
-    "seat_indices": (indices, loads) as ``generate_indices_and_loads`` of the hot mask.
+    "seat_indices": (indices, loads) as ``generate_indices_and_loads`` of the hot mask;
+    "throttled_seat_indices": (indices, loads, prefix) of the throttled hot mask
+    (``with_mask`` appends that mask).
     ``with_gates`` appends the picked scores renormalised to sum 1 per cell.  Raises
     ``NotImplementedError`` when the scores do not fit the single-launch kernel; callers then
     route in two steps."""
@@ -181,6 +240,9 @@ def route_scores(
         out = torch.empty((T, E), dtype=torch.int32, device=dev)
         loads = torch.empty((E,), dtype=torch.int32, device=dev)
         gates = torch.empty((T, E), dtype=torch.float32, device=dev) if with_gates else None
+        if with_mask and output != "throttled_seat_indices":
+            raise RuntimeError("with_mask goes with output='throttled_seat_indices'")
+        mask_out = torch.empty((T, E), dtype=torch.int32, device=dev) if with_mask else None
         caps, ncap = None, 0
         if supported_capacities is not None:
             _check_cuda(supported_capacities, "supported_capacities")
@@ -189,9 +251,9 @@ def route_scores(
         if capacity_padding and ncap < 1:
             raise RuntimeError("capacity_padding needs at least one supported capacity")
         thr = None
-        if output == "throttled_mask":
+        if output in ("throttled_mask", "throttled_seat_indices"):
             if prefix is None or throttle_capacity is None:
-                raise RuntimeError("a throttled mask needs prefix and throttle_capacity")
+                raise RuntimeError("a throttled output needs prefix and throttle_capacity")
             _check_cuda(prefix, "prefix")
             _check_cuda(throttle_capacity, "throttle_capacity")
             if prefix.dtype != torch.int32 or not prefix.is_contiguous() or prefix.numel() != E:
@@ -207,11 +269,18 @@ def route_scores(
                       float(threshold), int(residual_path), _ROUTE_OUT[output], _ptr(out),
                       _ptr(loads), _ptr(caps), ncap, int(bool(capacity_padding)),
                       int(bool(path_wise_padding)), _ptr(prefix), _ptr(thr), _ptr(gates),
-                      _ptr(scratch), scratch.numel(), _stream(dev))
+                      _ptr(mask_out), _ptr(scratch), scratch.numel(), _stream(dev))
         except _lib.BrtError as exc:
             if exc.status == 4:  # BRT_ERR_UNSUPPORTED: too many scores for one launch
                 raise NotImplementedError(str(exc)) from None
             raise
+    if output == "throttled_seat_indices":
+        res = (out, loads, prefix)
+        if with_gates:
+            res += (gates,)
+        if with_mask:
+            res += (mask_out,)
+        return res
     second = prefix if output == "throttled_mask" else loads
     return (out, second, gates) if with_gates else (out, second)
 

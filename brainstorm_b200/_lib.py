@@ -37,8 +37,10 @@ SIGNATURES = {
     "brt_index_set_test_hooks": (None, [_int, _int]),
     "brt_route_scores": (
         _int, [_vp, _i64, _int, _int, _int, ctypes.c_float, _int, _int, _vp, _vp, _vp, _int, _int,
-               _int, _vp, _vp, _vp, _vp, _sz, _vp]),
+               _int, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "brt_throttle_hotmask": (_int, [_vp, _vp, _vp, _vp, _i64, _int, _vp, _sz, _vp]),
+    "brt_throttle_and_generate_indices": (
+        _int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _int, _vp, _int, _int, _int, _vp, _sz, _vp]),
     "brt_convert_index_format": (_int, [_vp, _vp, _vp, _i64, _int, _int, _vp]),
     "brt_dispatch_scratch_bytes": (_sz, [_i64, _int]),
     "brt_dispatch_with_indices_and_loads": (

@@ -47,7 +47,10 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kGroupRows = 32;  // cells per bit word
 
-enum class Mode { kSeat, kTag, kThrottle, kMask };  // kMask: write the 0/1 mask itself
+// kMask: write the 0/1 mask itself.  kThrottleSeat: seat indices and loads of the throttled
+// mask in one pass (the seat of a kept cell is its seat in the unthrottled mask; a cell is
+// kept while prefix + seat <= threshold); single-launch path and 0/1 masks only.
+enum class Mode { kSeat, kTag, kThrottle, kMask, kThrottleSeat };
 
 // How a [cell, path] int32 matrix is cut into CTA tiles.
 struct Tiling {
@@ -820,6 +823,8 @@ __device__ __forceinline__ void expand_general(const TileCtx& x, const int* __re
     run += m;
     if constexpr (MODE == Mode::kThrottle) {
       out[at] = (m == 1 && run <= thr) ? 1 : 0;
+    } else if constexpr (MODE == Mode::kThrottleSeat) {
+      out[at] = 0;  // not defined for masks with values other than 0/1 (reported by the caller)
     } else if constexpr (MODE == Mode::kSeat) {
       out[at] = run * m;
     } else if constexpr (MODE == Mode::kMask) {
@@ -838,7 +843,8 @@ __device__ __forceinline__ void expand_general(const TileCtx& x, const int* __re
 // of an earlier tile is no longer read.
 template <Mode MODE>
 __device__ __forceinline__ void expand_binary(const TileCtx& x, const TileSmem& sm, int& run,
-                                              int* __restrict__ out) {
+                                              int* __restrict__ out,
+                                              int* __restrict__ mask_out = nullptr) {
   const int tid = threadIdx.x;
   const int col0 = x.chunk * x.ec;
   const int cols = (x.path_num - col0) < x.ec ? (x.path_num - col0) : x.ec;
@@ -875,6 +881,8 @@ __device__ __forceinline__ void expand_binary(const TileCtx& x, const TileSmem& 
       const int seat = b[j] + __popc(w[j] & low);
       if constexpr (MODE == Mode::kThrottle)
         v[j] = (bit && seat <= sm.thr[4 * q + j]) ? 1 : 0;
+      else if constexpr (MODE == Mode::kThrottleSeat)
+        v[j] = (bit && seat <= sm.thr[4 * q + j]) ? seat : 0;
       else if constexpr (MODE == Mode::kMask)
         v[j] = bit;
       else
@@ -890,6 +898,11 @@ __device__ __forceinline__ void expand_binary(const TileCtx& x, const TileSmem& 
     } else {
       __stcs(reinterpret_cast<int4*>(out + row * x.path_num + col0 + 4 * q),
              make_int4(v[0], v[1], v[2], v[3]));
+      if constexpr (MODE == Mode::kThrottleSeat) {
+        if (mask_out != nullptr)  // the throttled 0/1 mask itself, for callers that want both
+          __stcs(reinterpret_cast<int4*>(mask_out + row * x.path_num + col0 + 4 * q),
+                 make_int4(v[0] != 0, v[1] != 0, v[2] != 0, v[3] != 0));
+      }
     }
     r += step_r;
     q += step_q;
@@ -935,6 +948,7 @@ __device__ __forceinline__ void expand_tile(const TileCtx& x, const TileSmem& sm
 struct TiledArgs {
   const int* mask;
   int* out;
+  int* mask_out;  // kThrottleSeat only, may be null: the throttled mask beside the indices
   uint32_t* bits;
   int* tile_sums;
   int* tile_flags;
@@ -1182,10 +1196,14 @@ __global__ void __launch_bounds__(kTileThreads, 2) index_chain_kernel(const Chai
 
   // read before this CTA publishes anything: the last ticket overwrites prefix[] only after
   // it has seen every publication
+  // (kThrottleSeat counts seats from 1 within this call, so its limit is what is left of the
+  // threshold after the prefix)
+  constexpr bool kThrottles = MODE == Mode::kThrottle || MODE == Mode::kThrottleSeat;
   int start = 0;
-  if (MODE == Mode::kThrottle && tid < cols) {
+  if (kThrottles && tid < cols) {
     start = a.prefix[col0 + tid];
-    sm.thr[tid] = a.threshold[col0 + tid];
+    const int thr = a.threshold[col0 + tid];
+    sm.thr[tid] = MODE == Mode::kThrottleSeat ? thr - start : thr;
   }
 
   // two staging buffers: the copy of tile t + 1 is in flight while tile t is packed
@@ -1260,18 +1278,31 @@ __global__ void __launch_bounds__(kTileThreads, 2) index_chain_kernel(const Chai
     }
   }
   __syncthreads();
-  int run = tid < cols ? s_before[tid] + start : 0;
+  int run = tid < cols ? s_before[tid] + (MODE == Mode::kThrottle ? start : 0) : 0;
 
   if (range == c.ranges - 1 && tid < cols) {
-    const int total = run - start + own;
+    const int total = s_before[tid] + own;
     __threadfence();
-    if constexpr (MODE == Mode::kThrottle) {
-      const int thr = sm.thr[tid];
+    if constexpr (kThrottles) {
+      const int thr = MODE == Mode::kThrottleSeat ? sm.thr[tid] + start : sm.thr[tid];
       const int p = start + total;
       a.prefix[col0 + tid] = p >= thr ? thr : p;
-    } else {
+    }
+    if constexpr (MODE == Mode::kThrottleSeat) {
+      const int room = sm.thr[tid] > 0 ? sm.thr[tid] : 0;
+      a.loads[col0 + tid] = map_load(total < room ? total : room, col0 + tid, a.caps, a.ncap,
+                                     a.capacity_padding != 0, a.path_wise != 0);
+    } else if constexpr (!kThrottles) {
       a.loads[col0 + tid] = map_load(total, col0 + tid, a.caps, a.ncap, a.capacity_padding != 0,
                                      a.path_wise != 0);
+    }
+  }
+  if (MODE == Mode::kThrottleSeat && general && tid == 0) {
+    // the fused pass is only defined for 0/1 masks: say so instead of inventing indices
+    *c.error = 2;
+    if (c.host_error != nullptr) {
+      *reinterpret_cast<volatile int*>(c.host_error) = BRT_ERR_INVALID_ARGUMENT;
+      __threadfence_system();
     }
   }
 
@@ -1282,7 +1313,7 @@ __global__ void __launch_bounds__(kTileThreads, 2) index_chain_kernel(const Chai
     } else {
       TileSmem cur = sm;
       cur.bits = bits_all + (t - tile0) * words_per_tile;
-      expand_binary<MODE>(x, cur, run, a.out);
+      expand_binary<MODE>(x, cur, run, a.out, a.mask_out);
     }
   }
 }
@@ -1351,7 +1382,8 @@ int launch_chain_mode(const ChainArgs& c, unsigned grid, size_t smem, cudaStream
   }
   const KernelTimer timer(GATED ? "route_scores_kernel"
                                 : MODE == Mode::kThrottle ? "throttle_chain_kernel"
-                                                          : "index_chain_kernel",
+                                : MODE == Mode::kThrottleSeat ? "throttle_index_chain_kernel"
+                                                              : "index_chain_kernel",
                           stream);
   index_chain_kernel<MODE, GATED><<<grid, kTileThreads, smem, stream>>>(c), note_launch();
   BRT_LAUNCH_CHECK("index_chain_kernel");
@@ -1362,7 +1394,8 @@ int launch_chain(Mode mode, const TileGeom& g, int tiles_per_cta, int ranges, si
                  const int32_t* mask, int32_t* out, int32_t* loads, int64_t cell_num,
                  int path_num, const int32_t* caps, int ncap, int capacity_padding,
                  int path_wise, int32_t* prefix, const int32_t* threshold, void* scratch,
-                 cudaStream_t stream, const GateArgs* gate = nullptr) {
+                 cudaStream_t stream, const GateArgs* gate = nullptr,
+                 int32_t* mask_out = nullptr) {
   ChainArgs c;
   c.gate = gate != nullptr ? *gate : GateArgs{0, 0, 0.f, -1, nullptr};
   char* p = static_cast<char*>(scratch);
@@ -1380,6 +1413,7 @@ int launch_chain(Mode mode, const TileGeom& g, int tiles_per_cta, int ranges, si
   c.t.bits = nullptr;
   c.t.mask = mask;
   c.t.out = out;
+  c.t.mask_out = mask_out;
   c.t.loads = loads;
   c.t.caps = caps;
   c.t.ncap = ncap;
@@ -1402,12 +1436,16 @@ int launch_chain(Mode mode, const TileGeom& g, int tiles_per_cta, int ranges, si
     switch (mode) {
       case Mode::kSeat: return launch_chain_mode<Mode::kSeat, true>(c, grid, smem, stream);
       case Mode::kMask: return launch_chain_mode<Mode::kMask, true>(c, grid, smem, stream);
+      case Mode::kThrottleSeat:
+        return launch_chain_mode<Mode::kThrottleSeat, true>(c, grid, smem, stream);
       default: return launch_chain_mode<Mode::kThrottle, true>(c, grid, smem, stream);
     }
   }
   switch (mode) {
     case Mode::kSeat: return launch_chain_mode<Mode::kSeat, false>(c, grid, smem, stream);
     case Mode::kTag: return launch_chain_mode<Mode::kTag, false>(c, grid, smem, stream);
+    case Mode::kThrottleSeat:
+      return launch_chain_mode<Mode::kThrottleSeat, false>(c, grid, smem, stream);
     default: return launch_chain_mode<Mode::kThrottle, false>(c, grid, smem, stream);
   }
 }
@@ -1415,7 +1453,8 @@ int launch_chain(Mode mode, const TileGeom& g, int tiles_per_cta, int ranges, si
 int launch_tiled(Mode mode, const int32_t* mask, int32_t* out, int32_t* loads, int64_t cell_num,
                  int path_num, const int32_t* caps, int ncap, int capacity_padding,
                  int path_wise, int32_t* prefix, const int32_t* threshold, void* scratch,
-                 cudaStream_t stream, const GateArgs* gate = nullptr) {
+                 cudaStream_t stream, const GateArgs* gate = nullptr,
+                 int32_t* mask_out = nullptr) {
   TileGeom g = make_tile_geom(cell_num, path_num);
   BRT_REQUIRE(g.num_tiles <= 0x7fffffffLL && g.col_chunks <= 65535,
               "mask of %lld x %d cells is too large for one launch", (long long)cell_num,
@@ -1426,7 +1465,7 @@ int launch_tiled(Mode mode, const int32_t* mask, int32_t* out, int32_t* loads, i
     const char* const forced = getenv("BRT_INDEX_PATH");
     return forced != nullptr && strcmp(forced, "split") == 0;
   }();
-  if (gate != nullptr || !forced_split) {
+  if (gate != nullptr || !forced_split || mode == Mode::kThrottleSeat) {
     int64_t target = (int64_t)sm_count() * kChainCtasPerSm / g.col_chunks;
     if (target < 1) target = 1;
     const int64_t ranges0 = g.num_tiles < target ? g.num_tiles : target;
@@ -1439,12 +1478,16 @@ int launch_tiled(Mode mode, const int32_t* mask, int32_t* out, int32_t* loads, i
     if (smem <= kChainSmemLimit)
       return launch_chain(mode, g, (int)tiles_per_cta, (int)ranges, smem, mask, out, loads,
                           cell_num, path_num, caps, ncap, capacity_padding, path_wise, prefix,
-                          threshold, scratch, stream, gate);
+                          threshold, scratch, stream, gate, mask_out);
   }
   if (gate != nullptr)
     return set_error(BRT_ERR_UNSUPPORTED,
                      "%lld x %d scores do not fit the single-launch gate; route in two steps",
                      (long long)cell_num, path_num);
+  if (mode == Mode::kThrottleSeat)
+    return set_error(BRT_ERR_UNSUPPORTED,
+                     "a %lld x %d mask does not fit the single-launch scan; throttle and index "
+                     "it in two steps", (long long)cell_num, path_num);
   TiledArgs a;
   char* p = static_cast<char*>(scratch);
   a.flags = reinterpret_cast<int*>(p);
@@ -1456,6 +1499,7 @@ int launch_tiled(Mode mode, const int32_t* mask, int32_t* out, int32_t* loads, i
   a.bits = reinterpret_cast<uint32_t*>(p);
   a.mask = mask;
   a.out = out;
+  a.mask_out = nullptr;
   a.loads = loads;
   a.caps = caps;
   a.ncap = ncap;
@@ -1666,12 +1710,55 @@ BRT_API int brt_throttle_hotmask(const int32_t* hotmask, int32_t* throttled, int
                   static_cast<cudaStream_t>(stream));
 }
 
+BRT_API int brt_throttle_and_generate_indices(
+    const int32_t* hot_mask, int32_t* indices, int32_t* loads, int32_t* prefix,
+    const int32_t* threshold, int32_t* throttled_mask, int64_t cell_num, int path_num,
+    const int32_t* supported_capacities, int supported_capacity_num, int capacity_padding,
+    int path_wise_padding, void* scratch, size_t scratch_bytes, void* stream) {
+  clear_error();
+  BRT_REQUIRE(cell_num >= 0 && path_num > 0, "bad shape: cell_num=%lld path_num=%d",
+              (long long)cell_num, path_num);
+  BRT_REQUIRE(loads != nullptr && prefix != nullptr && threshold != nullptr,
+              "loads, prefix or threshold is null");
+  BRT_REQUIRE(supported_capacity_num >= 0 &&
+                  (supported_capacity_num == 0 || supported_capacities != nullptr),
+              "supported_capacities is null but supported_capacity_num=%d",
+              supported_capacity_num);
+  BRT_REQUIRE(!capacity_padding || supported_capacity_num >= 1,
+              "capacity_padding needs at least one supported capacity");
+  const int path_wise = (capacity_padding && path_wise_padding) ? 1 : 0;
+  BRT_REQUIRE(!path_wise || supported_capacity_num >= path_num,
+              "path_wise_padding needs one capacity per path (%d < %d)", supported_capacity_num,
+              path_num);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cell_num == 0) {  // as the two ops it stands for: prefix untouched, loads zero
+    BRT_CUDA_TRY(cudaMemsetAsync(loads, 0, (size_t)path_num * 4, st));
+    return BRT_OK;
+  }
+  BRT_REQUIRE(hot_mask != nullptr && indices != nullptr, "hot_mask or indices is null");
+  if (path_num % 4 != 0 || !aligned_to(hot_mask, 16) || !aligned_to(indices, 16) ||
+      !aligned_to(throttled_mask, 16))
+    return set_error(BRT_ERR_UNSUPPORTED,
+                     "the fused scan needs path_num %% 4 == 0 and 16-byte aligned arrays; "
+                     "throttle and index in two steps");
+  BRT_REQUIRE(scratch != nullptr && aligned_to(scratch, 256),
+              "scratch must be a 256-byte aligned device buffer");
+  const size_t need = scratch_bytes_for(cell_num, path_num);
+  if (scratch_bytes < need)
+    return set_error(BRT_ERR_SCRATCH_TOO_SMALL, "scratch holds %zu bytes, %zu needed",
+                     scratch_bytes, need);
+  return launch_tiled(Mode::kThrottleSeat, hot_mask, indices, loads, cell_num, path_num,
+                      supported_capacities, supported_capacity_num, capacity_padding, path_wise,
+                      prefix, threshold, scratch, st, nullptr, throttled_mask);
+}
+
 BRT_API int brt_route_scores(const float* scores, int64_t cell_num, int path_num, int decision,
                              int top_k, float threshold, int residual_path, int output,
                              int32_t* out, int32_t* loads, const int32_t* capacities,
                              int capacity_num, int capacity_padding, int path_wise_padding,
                              int32_t* prefix, const int32_t* throttle_capacity, float* gates_out,
-                             void* scratch, size_t scratch_bytes, void* stream) {
+                             int32_t* mask_out, void* scratch, size_t scratch_bytes,
+                             void* stream) {
   clear_error();
   BRT_REQUIRE(cell_num >= 0 && path_num > 0, "bad shape: cell_num=%lld path_num=%d",
               (long long)cell_num, path_num);
@@ -1682,10 +1769,12 @@ BRT_API int brt_route_scores(const float* scores, int64_t cell_num, int path_num
   BRT_REQUIRE(residual_path < path_num, "residual_path=%d outside the %d paths", residual_path,
               path_num);
   BRT_REQUIRE(output == BRT_ROUTE_MASK || output == BRT_ROUTE_THROTTLED_MASK ||
-                  output == BRT_ROUTE_SEAT_INDICES,
+                  output == BRT_ROUTE_SEAT_INDICES || output == BRT_ROUTE_THROTTLED_SEAT_INDICES,
               "unknown output %d", output);
-  BRT_REQUIRE(output != BRT_ROUTE_THROTTLED_MASK || (prefix != nullptr && throttle_capacity != nullptr),
-              "a throttled mask needs prefix and throttle_capacity");
+  const bool throttles =
+      output == BRT_ROUTE_THROTTLED_MASK || output == BRT_ROUTE_THROTTLED_SEAT_INDICES;
+  BRT_REQUIRE(!throttles || (prefix != nullptr && throttle_capacity != nullptr),
+              "a throttled output needs prefix and throttle_capacity");
   BRT_REQUIRE(output == BRT_ROUTE_THROTTLED_MASK || loads != nullptr, "loads is null");
   BRT_REQUIRE(capacity_num >= 0 && (capacity_num == 0 || capacities != nullptr),
               "capacities missing");
@@ -1702,8 +1791,10 @@ BRT_API int brt_route_scores(const float* scores, int64_t cell_num, int path_num
     return BRT_OK;
   }
   BRT_REQUIRE(scores != nullptr && out != nullptr, "scores or out is null");
+  BRT_REQUIRE(mask_out == nullptr || output == BRT_ROUTE_THROTTLED_SEAT_INDICES,
+              "mask_out goes with BRT_ROUTE_THROTTLED_SEAT_INDICES only");
   if (path_num % 4 != 0 || path_num > 256 || !aligned_to(scores, 16) || !aligned_to(out, 16) ||
-      (gates_out != nullptr && !aligned_to(gates_out, 4)))
+      !aligned_to(mask_out, 16) || (gates_out != nullptr && !aligned_to(gates_out, 4)))
     return set_error(BRT_ERR_UNSUPPORTED,
                      "the single-launch gate needs path_num %% 4 == 0, path_num <= 256 and "
                      "16-byte aligned arrays; route in two steps");
@@ -1716,10 +1807,12 @@ BRT_API int brt_route_scores(const float* scores, int64_t cell_num, int path_num
   const GateArgs gate{decision == BRT_GATE_TOPK ? 1 : 2, top_k, threshold, residual_path, gates_out};
   const Mode mode = output == BRT_ROUTE_MASK ? Mode::kMask
                     : output == BRT_ROUTE_THROTTLED_MASK ? Mode::kThrottle
-                                                         : Mode::kSeat;
+                    : output == BRT_ROUTE_THROTTLED_SEAT_INDICES ? Mode::kThrottleSeat
+                                                                 : Mode::kSeat;
   return launch_tiled(mode, reinterpret_cast<const int32_t*>(scores), out, loads, cell_num,
                       path_num, capacities, capacity_num, capacity_padding, path_wise_padding,
-                      prefix, throttle_capacity, scratch, static_cast<cudaStream_t>(stream), &gate);
+                      prefix, throttle_capacity, scratch, static_cast<cudaStream_t>(stream), &gate,
+                      mask_out);
 }
 
 BRT_API int brt_convert_index_format(const int32_t* origin_indices, int32_t* new_indices,

@@ -61,9 +61,16 @@ class DispatchFabric(FabricBase):
                 score: torch.Tensor = None):
         capacities = runtime_capacities if runtime_capacities is not None \
             else self.supported_capacities
-        route_indices, loads = c_router.generate_indices_and_loads(
-            hot_mask, supported_capacities=capacities, capacity_padding=self.capacity_padding,
-            path_wise_padding=self.path_wise_padding, is_tag_index=False)
+        routes = getattr(hot_mask, "_brt_routes", None)
+        if routes is not None and routes[2] is capacities and \
+                routes[3:] == (self.capacity_padding, self.path_wise_padding):
+            # the gate kernel that made this mask already scanned it under the same rules
+            route_indices, loads = routes[0], routes[1]
+        else:
+            route_indices, loads = c_router.generate_indices_and_loads(
+                hot_mask, supported_capacities=capacities,
+                capacity_padding=self.capacity_padding,
+                path_wise_padding=self.path_wise_padding, is_tag_index=False)
         in_flows = [in_flow] if self.flow_num == 1 else in_flow
         self.capture_flow_stats(in_flows, route_indices, loads)
         all_out_flows, score = self.dispatch(in_flows, route_indices, loads, score)

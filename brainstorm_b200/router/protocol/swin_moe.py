@@ -62,6 +62,10 @@ class SwinMoEProtocol(ProtocolBase):
         self.normalize_gate = normalize_gate
         self.is_gshard_loss = is_gshard_loss
         self.alignment = alignment
+        # (capacity_padding, path_wise_padding) of the dispatch fabric that follows, set by the
+        # router that owns both: the gate kernel then hands the fabric its seat indices and
+        # loads along with the hot mask, and the fabric skips its own index scan
+        self.index_rules = None
 
     def runtime_capacity(self, cell_num: int, path_num: int) -> int:
         if self.capacity_factor <= 0:
@@ -77,9 +81,19 @@ class SwinMoEProtocol(ProtocolBase):
             runtime_capacities = torch.full((E,), cap, dtype=torch.int32, device=score.device)
             prefix = torch.zeros((E,), dtype=torch.int32, device=score.device)
             try:
-                hot_mask, _ = c_router.route_scores(score, "topk", 1, output="throttled_mask",
-                                                    prefix=prefix,
-                                                    throttle_capacity=runtime_capacities)
+                if self.index_rules is not None:
+                    # gate, throttle and index scan in one launch; the mask comes with it
+                    cpad, pwise = self.index_rules
+                    indices, loads, _, hot_mask = c_router.route_scores(
+                        score, "topk", 1, output="throttled_seat_indices", prefix=prefix,
+                        throttle_capacity=runtime_capacities,
+                        supported_capacities=runtime_capacities, capacity_padding=cpad,
+                        path_wise_padding=pwise, with_mask=True)
+                    hot_mask._brt_routes = (indices, loads, runtime_capacities, cpad, pwise)
+                else:
+                    hot_mask, _ = c_router.route_scores(score, "topk", 1,
+                                                        output="throttled_mask", prefix=prefix,
+                                                        throttle_capacity=runtime_capacities)
                 loss = self.generate_auxiliary(score, logits_wo_noise, logits, None)
                 return hot_mask, runtime_capacities, score, loss
             except NotImplementedError:

@@ -87,6 +87,9 @@ class SwinMoEScatterRouter(RouterBase):
         self.fabric_kwargs = {"flow_num": 1, "route_logic": ["1d"], "transform": [False]}
         self.fabric_kwargs.update(fabric_kwargs or {})
         self.fabric = make_fabric(fabric_type, self.fabric_kwargs)
+        if hasattr(self.fabric, "capacity_padding"):
+            self.protocol.index_rules = (bool(self.fabric.capacity_padding),
+                                         bool(self.fabric.path_wise_padding))
 
     def forward(self, in_flows, score, logits_wo_noise=None, logits=None):
         hot_mask, runtime_capacities, new_score, _loss = self.protocol(score, logits_wo_noise,

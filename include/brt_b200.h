@@ -151,6 +151,32 @@ BRT_API int brt_throttle_hotmask(const int32_t* hotmask, int32_t* throttled, int
                                  void* scratch, size_t scratch_bytes, void* stream);
 
 /*
+ * brt_throttle_hotmask followed by brt_generate_indices_and_loads (seat indices) of the
+ * throttled mask, in one pass over the mask and without the throttled mask ever reaching
+ * memory: what python/brt/router/protocol/swin_moe.py:112-140 and
+ * python/brt/router/fabric/generic.py:83-89 do in two operator calls
+ * (src/router/location.cu:304-315 then :335-379).  The seat of a kept cell is its seat in the
+ * unthrottled mask, and a cell is kept while prefix[e] + seat <= threshold[e], so one scan
+ * yields both.
+ *
+ * indices[t,e] = seat if hot_mask[t,e] != 0 and prefix_in[e] + seat <= threshold[e], else 0;
+ * loads[e] = the capacity rules of brt_generate_indices_and_loads applied to the number of
+ * kept cells; prefix[e] <- min(prefix[e] + sum(hot_mask[:, e]), threshold[e]) in place.
+ * throttled_mask (optional, [cell_num, path_num]) receives the throttled 0/1 mask as well.
+ *
+ * hot_mask must hold only 0 and 1 (what the protocols produce).  Another value makes the
+ * kernel write zero indices and report BRT_ERR_INVALID_ARGUMENT through brt_index_status.
+ * Returns BRT_ERR_UNSUPPORTED (nothing launched) when path_num is not a multiple of 4, an
+ * array is not 16-byte aligned or the mask is too large for the single-launch scan; the
+ * caller then uses the two entry points above.
+ */
+BRT_API int brt_throttle_and_generate_indices(
+    const int32_t* hot_mask, int32_t* indices, int32_t* loads, int32_t* prefix,
+    const int32_t* threshold, int32_t* throttled_mask, int64_t cell_num, int path_num,
+    const int32_t* supported_capacities, int supported_capacity_num, int capacity_padding,
+    int path_wise_padding, void* scratch, size_t scratch_bytes, void* stream);
+
+/*
  * Replaces brt::router::ConvertIndexFormat
  * (include/brt/router/location.h:21-27, src/router/location.cu:259-333).
  * tag_to_seat != 0: new[tag-1, e] = r+1 for rows r < loads[e] with a non-zero tag;
@@ -167,7 +193,10 @@ typedef enum brt_gate_decision { BRT_GATE_TOPK = 0, BRT_GATE_THRESHOLD = 1 } brt
 typedef enum brt_route_output {
   BRT_ROUTE_MASK = 0,           /* out = hot mask, loads = cells routed to every path */
   BRT_ROUTE_THROTTLED_MASK = 1, /* out = hot mask cut at throttle_capacity, prefix updated */
-  BRT_ROUTE_SEAT_INDICES = 2    /* out = seat indices, loads as brt_generate_indices_and_loads */
+  BRT_ROUTE_SEAT_INDICES = 2,   /* out = seat indices, loads as brt_generate_indices_and_loads */
+  BRT_ROUTE_THROTTLED_SEAT_INDICES = 3 /* both: seat indices and loads of the hot mask cut at
+                                          throttle_capacity, prefix updated
+                                          (brt_throttle_and_generate_indices from scores) */
 } brt_route_output;
 
 /*
@@ -185,10 +214,12 @@ typedef enum brt_route_output {
  *            BRT_GATE_THRESHOLD: ones where score > threshold, and residual_path (>= 0) for
  *            a cell that would otherwise go nowhere
  *   output   see brt_route_output; capacities / capacity_padding / path_wise_padding as in
- *            brt_generate_indices_and_loads (BRT_ROUTE_SEAT_INDICES only); prefix and
- *            throttle_capacity as in brt_throttle_hotmask (BRT_ROUTE_THROTTLED_MASK only)
+ *            brt_generate_indices_and_loads (the two SEAT_INDICES outputs); prefix and
+ *            throttle_capacity as in brt_throttle_hotmask (the two THROTTLED outputs)
  *   gates_out optional fp32 [cell_num, path_num]: picked scores divided by their sum
  *            (clamped at FLT_EPSILON), zero elsewhere (protocol/swin_moe.py:193-204)
+ *   mask_out optional int32 [cell_num, path_num], BRT_ROUTE_THROTTLED_SEAT_INDICES only: the
+ *            throttled hot mask beside its seat indices
  *   scratch  brt_index_scratch_bytes(cell_num, path_num) bytes
  *
  * Returns BRT_ERR_UNSUPPORTED (nothing launched) when path_num is not a multiple of 4 or
@@ -200,7 +231,8 @@ BRT_API int brt_route_scores(const float* scores, int64_t cell_num, int path_num
                              int32_t* out, int32_t* loads, const int32_t* capacities,
                              int capacity_num, int capacity_padding, int path_wise_padding,
                              int32_t* prefix, const int32_t* throttle_capacity, float* gates_out,
-                             void* scratch, size_t scratch_bytes, void* stream);
+                             int32_t* mask_out, void* scratch, size_t scratch_bytes,
+                             void* stream);
 
 /* ------------------------------------------------------------------ router: data movement */
 

@@ -75,6 +75,32 @@ def test_topk_throttled_mask(R, T, E, k):
     assert np.array_equal(got_m.cpu().numpy(), exp_m)
 
 
+@pytest.mark.parametrize("T,E,k", [(33, 8, 1), (5000, 32, 1), (32768, 32, 2), (262144, 128, 1),
+                                   (65536, 64, 2)])
+def test_topk_throttled_seat_indices(R, T, E, k):
+    """Scores straight to the seat indices and loads of the throttled mask: gate, throttle
+    and index scan in one launch."""
+    s = scores(T, E, 5 * T + E)
+    rng = np.random.default_rng(T + 1)
+    prefix = rng.integers(0, 5, size=E).astype(np.int32)
+    cap = np.full(E, k * ((T + E - 1) // E), dtype=np.int32)
+    exp_p = prefix.copy()
+    exp_m, _ = oracle.route_scores(s, "topk", k, output="throttled_mask", prefix=exp_p,
+                                   throttle_capacity=cap)
+    for caps, cpad in ((None, False), ([64, 1024, 16384], True)):
+        exp_i, exp_l = oracle.generate_indices_and_loads(exp_m, caps, cpad)
+        p = cuda(prefix)
+        got_i, got_l, got_p = R.route_scores(
+            cuda(s), "topk", k, output="throttled_seat_indices", prefix=p,
+            throttle_capacity=cuda(cap),
+            supported_capacities=None if caps is None else cuda(np.array(caps, dtype=np.int32)),
+            capacity_padding=cpad)
+        assert got_p is p
+        assert np.array_equal(got_p.cpu().numpy(), exp_p)
+        assert np.array_equal(got_l.cpu().numpy(), exp_l)
+        assert np.array_equal(got_i.cpu().numpy(), exp_i)
+
+
 @pytest.mark.parametrize("T,E,thr,res", [(64, 8, 0.5, -1), (5000, 8, 0.5, -1), (5000, 8, 0.8, 3),
                                          (70000, 64, 0.9, 40), (3000, 128, 0.2, 0)])
 def test_threshold(R, T, E, thr, res):

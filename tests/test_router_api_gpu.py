@@ -177,6 +177,33 @@ def test_swin_moe_scatter(api):
     assert torch.allclose(out.data, x * best.values[:, None], rtol=1e-6, atol=1e-6)
 
 
+@pytest.mark.parametrize("cpad", [False, True])
+def test_swin_moe_gate_hands_its_indices_to_the_fabric(api, cpad):
+    """The router's protocol computes the seat indices and loads along with the throttled mask
+    (one launch); the fabric must route exactly as when it scans the mask itself."""
+    from brainstorm_b200.router import SwinMoEScatterRouter
+
+    Annotator, _, _ = api
+    torch.manual_seed(3)
+    T, E = 5000, 16
+    x = torch.randn(T, 24, device="cuda")
+    score = torch.softmax(torch.randn(T, E, device="cuda") * 3, dim=1)
+
+    def make():
+        return SwinMoEScatterRouter(
+            fabric_type="fused_dispatch",
+            protocol_kwargs={"top_k": 1, "capacity_factor": 0.5},
+            fabric_kwargs={"max_path_padding": True, "capacity_padding": cpad})
+    fused, plain = make(), make()
+    assert fused.protocol.index_rules == (cpad, False)
+    plain.protocol.index_rules = None  # the fabric scans the mask itself
+    a, _ = fused(Annotator([0])(x), score)
+    b, _ = plain(Annotator([0])(x), score)
+    assert torch.equal(a.data, b.data)
+    assert torch.equal(a.tag_stack[-1], b.tag_stack[-1])
+    assert torch.equal(a.load_stack[-1], b.load_stack[-1])
+
+
 def test_install_as_brt(api):
     import brainstorm_b200
 

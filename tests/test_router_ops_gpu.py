@@ -176,6 +176,68 @@ def test_throttle(R, T, E, k, index_path):
     assert np.array_equal(host(got_p), exp_p)
 
 
+FUSED_CASES = [(16, 4, 2), (1037, 8, 2), (5000, 32, 2), (3000, 128, 1), (40000, 8, 2),
+               (200000, 64, 2), (32768, 32, 2), (262144, 128, 1), (777, 12, 3), (50, 6, 2)]
+
+
+@pytest.mark.parametrize("T,E,k", FUSED_CASES)
+@pytest.mark.parametrize("caps_mode", ["none", "list", "padding", "path_wise"])
+def test_throttle_and_generate_indices(R, T, E, k, caps_mode):
+    """One pass = throttle_hotmask then generate_indices_and_loads of the throttled mask
+    (E = 6 is not a multiple of 4: the wrapper takes the two ops there)."""
+    rng = np.random.default_rng(3 * T + E)
+    mask = rand_mask(rng, T, E, k)
+    prefix = rng.integers(0, 20, size=E).astype(np.int32)
+    thr = rng.integers(0, max(2, 2 * T * k // E), size=E).astype(np.int32)
+    if caps_mode == "none":
+        caps, cpad, pwise = None, False, False
+    elif caps_mode == "list":
+        caps, cpad, pwise = [8, 64, 512, 4096], False, False
+    elif caps_mode == "padding":
+        caps, cpad, pwise = [8, 64, 512, 4096], True, False
+    else:
+        caps, cpad, pwise = list(rng.integers(1, 5000, size=E)), True, True
+    exp_p = prefix.copy()
+    exp_m, _ = oracle.throttle_hotmask(mask, exp_p, thr)
+    exp_i, exp_l = oracle.generate_indices_and_loads(exp_m, caps, cpad, pwise)
+    p = dev(prefix)
+    got_i, got_l, got_p = R.throttle_and_generate_indices(
+        dev(mask), p, dev(thr), None if caps is None else dev(np.array(caps, dtype=np.int32)),
+        cpad, pwise)
+    assert got_p is p
+    assert np.array_equal(host(got_p), exp_p)
+    assert np.array_equal(host(got_l), exp_l)
+    assert np.array_equal(host(got_i), exp_i)
+
+
+def test_throttle_and_generate_indices_golden(R, golden_dir):
+    import json
+
+    v = json.load(open(golden_dir / "notebook_vectors.json"))["throttle"]
+    prefix = dev(np.array(v["prefix_in"], dtype=np.int32))
+    idx, loads, p2 = R.throttle_and_generate_indices(
+        dev(np.array(v["hot_mask"], dtype=np.int32)), prefix,
+        dev(np.array(v["threshold"], dtype=np.int32)))
+    want_i, want_l = oracle.generate_indices_and_loads(
+        np.array(v["throttled_mask"], dtype=np.int32))
+    assert host(prefix).tolist() == v["prefix_out"]
+    assert np.array_equal(host(idx), want_i) and np.array_equal(host(loads), want_l)
+
+
+def test_fused_scan_refuses_other_mask_values(R):
+    """The fused pass is defined for 0/1 masks; another value is reported, not guessed at."""
+    from brainstorm_b200 import _lib
+
+    mask = torch.zeros((4096, 8), dtype=torch.int32, device="cuda")
+    mask[17, 3] = 5
+    E = 8
+    R.throttle_and_generate_indices(mask, torch.zeros(E, dtype=torch.int32, device="cuda"),
+                                    torch.full((E,), 9, dtype=torch.int32, device="cuda"))
+    torch.cuda.synchronize()
+    assert _lib.query("brt_index_status") == 1  # BRT_ERR_INVALID_ARGUMENT
+    _lib.query("brt_index_status_reset")
+
+
 def test_convert_index_format(R):
     rng = np.random.default_rng(11)
     mask = rand_mask(rng, 3000, 6, 2)
