@@ -126,7 +126,7 @@ def algorithmic_bytes(w, idx: np.ndarray, loads: np.ndarray, total_rows: int):
     Tr = int(kept.any(axis=1).sum())
     return {
         "throttle": 8 * T * E + 12 * E,
-        "indices": 8 * T * E + 4 * E,
+        "indices": 8 * T * E + (16 * E if w["cap"] != "none" else 4 * E),
         "dispatch": Tr * d * s + total_rows * d * s + 4 * T * E,
         "combine": R * d * s + T * d * s + 8 * T * E,
         # the two kernels of a dispatch: rows moved to their routes, rows nobody landed on
@@ -142,7 +142,8 @@ def config_of(name: str, world: int) -> dict:
     s = 4 if w["dtype"] == "f32" else 2
     distributed = world > 1
     return {"workload": f"{name}: {w['desc']}",
-            "step": "throttle + seat indices/loads + dispatch + "
+            "step": "throttle + seat indices/loads (one fused scan when a capacity applies) + "
+                    "dispatch + "
                     + ("sparse all-to-all forward and back + " if distributed else "")
                     + "weighted combine",
             "l2": "inputs and outputs of a step exceed the 126 MB L2"
@@ -247,12 +248,13 @@ def run_gpu(args):
     def step(i=None):
         rec = (lambda j: ev[i][j].record()) if i is not None else (lambda j: None)
         rec(0)
-        m = mask
-        if padded:
-            prefix = zeros_e.clone()
-            m, _ = R.throttle_hotmask(mask, prefix, caps)
         rec(1)
-        idx, loads = R.generate_indices_and_loads(m, caps)
+        if padded:
+            # throttle_hotmask + generate_indices_and_loads of the throttled mask, one pass
+            prefix = torch.zeros_like(zeros_e)
+            idx, loads, _ = R.throttle_and_generate_indices(mask, prefix, caps, caps)
+        else:
+            idx, loads = R.generate_indices_and_loads(mask, caps)
         rec(2)
         (routed,) = R.dispatch_with_indices_and_loads(x, idx, loads, None, False, None, padded,
                                                       cap)
@@ -384,8 +386,8 @@ def run_gpu(args):
     peak = float(peaks.get("hbm_gbs", 6650.0))
     peak_kind = "measured" if "hbm_gbs" in peaks else "fallback"
     kernels = {}
-    for n in ("throttle", "indices", "dispatch", "combine"):
-        if op_ms[n] > 0 and (n != "throttle" or padded):
+    for n in ("indices", "dispatch", "combine"):
+        if op_ms[n] > 0:
             gbs = ab[n] / (op_ms[n] * 1e-3) / 1e9
             kernels[n] = {"ms": round(op_ms[n], 5), "algorithmic_bytes": ab[n],
                           "achieved_gbs": round(gbs, 1), "frac": round(gbs / peak, 4)}
@@ -393,6 +395,8 @@ def run_gpu(args):
     # which algorithmic byte count belongs to which timed kernel
     kernel_bytes = {"throttle_chain_kernel": ab["throttle"], "throttle_split_kernels": ab["throttle"],
                     "index_chain_kernel": ab["indices"], "index_split_kernels": ab["indices"],
+                    "throttle_index_chain_kernel": ab["indices"],
+                    "dispatch_kernel": ab["dispatch"],
                     "dispatch_move_kernel": ab["dispatch_move"],
                     "dispatch_zero_fill_kernel": ab["dispatch_zero_fill"],
                     "combine_kernel": ab["combine"]}
@@ -414,6 +418,7 @@ def run_gpu(args):
     dominant = max((n for n in device_kernels if not n.startswith("p2p_")),
                    key=lambda n: device_kernels[n]["ms"])
     dominant_op = {"dispatch_move_kernel": "dispatch", "dispatch_zero_fill_kernel": "dispatch",
+                   "dispatch_kernel": "dispatch",
                    "combine_kernel": "combine"}.get(dominant, "indices")
 
     # ---- the gate in front of the path: scores -> mask (-> indices), torch ops of the
@@ -700,11 +705,11 @@ def measure_gate(wl, dev, w, R, padded, caps):
         return R.generate_indices_and_loads(mask, caps)
 
     def gate_kernel():
-        if padded:  # decision + throttle in one launch, then the index scan
-            mask, _ = R.route_scores(score, output="throttled_mask",
+        if padded:  # decision, throttle and index scan in one launch
+            i, l, _ = R.route_scores(score, output="throttled_seat_indices",
                                      prefix=torch.zeros(E, dtype=torch.int32, device=dev),
-                                     throttle_capacity=caps, **decide)
-            return R.generate_indices_and_loads(mask, caps)
+                                     throttle_capacity=caps, supported_capacities=caps, **decide)
+            return i, l
         return R.route_scores(score, output="seat_indices", **decide)
 
     def timed(fn):
@@ -734,7 +739,7 @@ def measure_gate(wl, dev, w, R, padded, caps):
             "launches": {"torch_protocol_then_index_ops":
                          ("compare, cast" if threshold is not None else "topk, zeros, scatter_")
                          + (", throttle, indices" if padded else ", indices"),
-                         "gate_kernel": "route_scores(throttled mask), indices" if padded
+                         "gate_kernel": "route_scores(throttled seat indices)" if padded
                          else "route_scores(seat indices)"}}
 
 

@@ -64,6 +64,18 @@ class _ScratchPool:
 _scratch = _ScratchPool()
 
 
+_DENSE = "_brt_dense_counts"
+
+
+def _mark_dense(indices: torch.Tensor, counts: torch.Tensor) -> None:
+    """Remember, on the tensor itself, that ``indices`` came out of an index kernel: column e
+    holds every seat 1 .. counts[e] exactly once.  ``dispatch_with_indices_and_loads`` then
+    knows which output rows stay empty without scanning for them and runs as one launch.
+    The note does not survive slicing, cloning or any other op; code that edits such a tensor
+    IN PLACE must delete the attribute."""
+    setattr(indices, _DENSE, counts)
+
+
 def check_index_status() -> None:
     """Raise (once) if an index scan enqueued earlier gave up a bounded wait: its indices and
     loads are wrong.  Reads a word of host memory that the kernels write, no device
@@ -126,13 +138,17 @@ def generate_indices_and_loads(
             caps = _int32c(supported_capacities, "supported_capacities")
             ncap = caps.size(0)
         indices = torch.empty_like(hot_mask)
-        loads = torch.empty((E,), dtype=torch.int32, device=hot_mask.device)
+        both = torch.empty((2, E), dtype=torch.int32, device=hot_mask.device)
+        loads, counts = both[0], both[1]
         nbytes = _lib.query("brt_index_scratch_bytes", T, E)
         scratch = _scratch.get("index", hot_mask.device, nbytes)
         _lib.call("brt_generate_indices_and_loads", _ptr(hot_mask), _ptr(indices), _ptr(loads),
-                  T, E, _ptr(caps), ncap, int(bool(capacity_padding)),
-                  int(bool(path_wise_padding)), int(bool(is_tag_index)), _ptr(scratch),
-                  scratch.numel(), _stream(hot_mask.device))
+                  None if is_tag_index else _ptr(counts), T, E, _ptr(caps), ncap,
+                  int(bool(capacity_padding)), int(bool(path_wise_padding)),
+                  int(bool(is_tag_index)), _ptr(scratch), scratch.numel(),
+                  _stream(hot_mask.device))
+        if not is_tag_index:
+            _mark_dense(indices, counts)
     return indices, loads
 
 
@@ -170,15 +186,17 @@ def throttle_and_generate_indices(
             caps = _int32c(supported_capacities, "supported_capacities")
             ncap = caps.size(0)
         indices = torch.empty_like(hot_mask)
-        loads = torch.empty((E,), dtype=torch.int32, device=dev)
+        both = torch.empty((2, E), dtype=torch.int32, device=dev)
+        loads, counts = both[0], both[1]
         throttled = torch.empty_like(hot_mask) if with_mask else None
         nbytes = _lib.query("brt_index_scratch_bytes", T, E)
         scratch = _scratch.get("index", dev, nbytes)
         try:
             _lib.call("brt_throttle_and_generate_indices", _ptr(hot_mask), _ptr(indices),
-                      _ptr(loads), _ptr(prefix), _ptr(threshold), _ptr(throttled), T, E,
-                      _ptr(caps), ncap, int(bool(capacity_padding)),
+                      _ptr(loads), _ptr(counts), _ptr(prefix), _ptr(threshold), _ptr(throttled),
+                      T, E, _ptr(caps), ncap, int(bool(capacity_padding)),
                       int(bool(path_wise_padding)), _ptr(scratch), scratch.numel(), _stream(dev))
+            _mark_dense(indices, counts)
         except _lib.BrtError as exc:
             if exc.status != 4:  # BRT_ERR_UNSUPPORTED: the two-step route takes every shape
                 raise
@@ -238,7 +256,9 @@ def route_scores(
     dev = score.device
     with torch.cuda.device(dev):
         out = torch.empty((T, E), dtype=torch.int32, device=dev)
-        loads = torch.empty((E,), dtype=torch.int32, device=dev)
+        both = torch.empty((2, E), dtype=torch.int32, device=dev)
+        loads, counts = both[0], both[1]
+        seats = output in ("seat_indices", "throttled_seat_indices")
         gates = torch.empty((T, E), dtype=torch.float32, device=dev) if with_gates else None
         if with_mask and output != "throttled_seat_indices":
             raise RuntimeError("with_mask goes with output='throttled_seat_indices'")
@@ -267,13 +287,16 @@ def route_scores(
         try:
             _lib.call("brt_route_scores", _ptr(score), T, E, _GATE[decision], int(top_k),
                       float(threshold), int(residual_path), _ROUTE_OUT[output], _ptr(out),
-                      _ptr(loads), _ptr(caps), ncap, int(bool(capacity_padding)),
+                      _ptr(loads), _ptr(counts) if seats else None, _ptr(caps), ncap,
+                      int(bool(capacity_padding)),
                       int(bool(path_wise_padding)), _ptr(prefix), _ptr(thr), _ptr(gates),
                       _ptr(mask_out), _ptr(scratch), scratch.numel(), _stream(dev))
         except _lib.BrtError as exc:
             if exc.status == 4:  # BRT_ERR_UNSUPPORTED: too many scores for one launch
                 raise NotImplementedError(str(exc)) from None
             raise
+        if seats:
+            _mark_dense(out, counts)
     if output == "throttled_seat_indices":
         res = (out, loads, prefix)
         if with_gates:
@@ -384,13 +407,22 @@ def dispatch_with_indices_and_loads(
                     raise RuntimeError("CHECK_EQ fails.")
                 old_tags = tags if tags.is_contiguous() else tags.contiguous()
             new_tags = torch.empty((total,), dtype=route_indices.dtype, device=dev)
-        nbytes = _lib.query("brt_dispatch_scratch_bytes", total, path_num)
-        scratch = _scratch.get("dispatch", dev, nbytes)
+        # indices that came straight out of an index kernel are known to be dense: one launch,
+        # no scratch; any other index tensor takes the general two-launch route
+        dense = None if is_tag_index else getattr(route_indices, _DENSE, None)
+        if dense is not None and (dense.device != dev or dense.numel() != path_num
+                                  or path_num > 2048):
+            dense = None
+        scratch, nscratch = None, 0
+        if dense is None and not is_tag_index:
+            nscratch = _lib.query("brt_dispatch_scratch_bytes", total, path_num)
+            scratch = _scratch.get("dispatch", dev, nscratch)
+            nscratch = scratch.numel()
         _lib.call("brt_dispatch_with_indices_and_loads", _ptr(src), _ptr(out), _ptr(g),
                   _ptr(route_indices), _ptr(cuda_loads), _ptr(old_tags), _ptr(new_tags),
                   cell_num, cell_size, path_num, mpl, total, int(bool(is_1d_routing)),
-                  int(bool(is_tag_index)), _DT[in_data.dtype], _ptr(scratch), scratch.numel(),
-                  _stream(dev))
+                  int(bool(is_tag_index)), _DT[in_data.dtype], _ptr(dense), _ptr(scratch),
+                  nscratch, _stream(dev))
     if tag_generating:
         return [out, new_tags]
     return [out]

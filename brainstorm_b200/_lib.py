@@ -28,7 +28,7 @@ SIGNATURES = {
     "brt_profile_report": (_int, [_vp, _sz]),
     "brt_index_scratch_bytes": (_sz, [_i64, _int]),
     "brt_generate_indices_and_loads": (
-        _int, [_vp, _vp, _vp, _i64, _int, _vp, _int, _int, _int, _int, _vp, _sz, _vp]),
+        _int, [_vp, _vp, _vp, _vp, _i64, _int, _vp, _int, _int, _int, _int, _vp, _sz, _vp]),
     "brt_static_index_scratch_bytes": (_sz, []),
     "brt_generate_indices_and_loads_static": (
         _int, [_vp, _vp, _vp, _i64, _int, _vp, _int, _int, _int, _int, _vp]),
@@ -36,16 +36,17 @@ SIGNATURES = {
     "brt_index_status_reset": (None, []),
     "brt_index_set_test_hooks": (None, [_int, _int]),
     "brt_route_scores": (
-        _int, [_vp, _i64, _int, _int, _int, ctypes.c_float, _int, _int, _vp, _vp, _vp, _int, _int,
-               _int, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+        _int, [_vp, _i64, _int, _int, _int, ctypes.c_float, _int, _int, _vp, _vp, _vp, _vp, _int,
+               _int, _int, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "brt_throttle_hotmask": (_int, [_vp, _vp, _vp, _vp, _i64, _int, _vp, _sz, _vp]),
     "brt_throttle_and_generate_indices": (
-        _int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _int, _vp, _int, _int, _int, _vp, _sz, _vp]),
+        _int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _int, _vp, _int, _int, _int, _vp, _sz,
+               _vp]),
     "brt_convert_index_format": (_int, [_vp, _vp, _vp, _i64, _int, _int, _vp]),
     "brt_dispatch_scratch_bytes": (_sz, [_i64, _int]),
     "brt_dispatch_with_indices_and_loads": (
         _int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _i32, _i64, _int, _int,
-               _int, _vp, _sz, _vp]),
+               _int, _vp, _vp, _sz, _vp]),
     "brt_combine_with_indices_and_loads": (
         _int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _i32, _int, _int, _int, _vp]),
     "brt_sum_rows_scratch_bytes": (_sz, [_i64, _i64]),

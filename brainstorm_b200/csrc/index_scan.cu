@@ -47,6 +47,14 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kGroupRows = 32;  // cells per bit word
 
+// Where the launch under way writes the per-path cell counts of the indices it produces
+// (null: nowhere).  Set by the entry points around their call into the launch helpers.
+thread_local int32_t* t_counts_out = nullptr;
+struct CountsScope {
+  explicit CountsScope(int32_t* p) { t_counts_out = p; }
+  ~CountsScope() { t_counts_out = nullptr; }
+};
+
 // kMask: write the 0/1 mask itself.  kThrottleSeat: seat indices and loads of the throttled
 // mask in one pass (the seat of a kept cell is its seat in the unthrottled mask; a cell is
 // kept while prefix + seat <= threshold); single-launch path and 0/1 masks only.
@@ -257,7 +265,7 @@ __global__ void __launch_bounds__(1024)
 tile_scan_kernel(int* __restrict__ tile_sums, int64_t num_tiles, int path_num,
                  int* __restrict__ loads, const int* __restrict__ caps, int ncap,
                  int capacity_padding, int path_wise, int* __restrict__ prefix,
-                 const int* __restrict__ threshold) {
+                 const int* __restrict__ threshold, int* __restrict__ counts) {
   __shared__ int s_part[32][33];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -291,6 +299,7 @@ tile_scan_kernel(int* __restrict__ tile_sums, int64_t num_tiles, int path_num,
       prefix[col] = p >= thr ? thr : p;
     } else {
       loads[col] = map_load(run, col, caps, ncap, capacity_padding != 0, path_wise != 0);
+      if (counts != nullptr) counts[col] = run;
     }
   }
 }
@@ -707,7 +716,7 @@ __device__ __forceinline__ void scan_tiles(int col_block, int* __restrict__ tile
                                            int capacity_padding, int path_wise,
                                            int* __restrict__ prefix,
                                            const int* __restrict__ threshold,
-                                           int (*s_warp)[4]) {
+                                           int (*s_warp)[4], int* __restrict__ counts) {
   constexpr int kSegs = THREADS / 4;
   constexpr int kWarpsHere = THREADS / 32;
   const int tid = threadIdx.x;
@@ -797,6 +806,7 @@ __device__ __forceinline__ void scan_tiles(int col_block, int* __restrict__ tile
         prefix[col] = p >= thr ? thr : p;
       } else {
         loads[col] = map_load(total, col, caps, ncap, capacity_padding != 0, path_wise != 0);
+        if (counts != nullptr) counts[col] = total;
       }
     }
   }
@@ -954,6 +964,8 @@ struct TiledArgs {
   int* tile_flags;
   int* flags;
   int* loads;
+  int* counts;  // may be null: cells per path that the written indices hold (before the
+                // capacity rules turn them into loads)
   const int* caps;
   int ncap;
   int capacity_padding;
@@ -991,7 +1003,8 @@ __global__ void __launch_bounds__(1024) tile_scan_wide_kernel(const TiledArgs a)
   __shared__ int s_warp[32][4];
   scan_tiles<THROTTLE, 1024>(blockIdx.x, a.tile_sums, a.num_tiles, a.path_num, a.tile_flags,
                              a.num_tiles * a.chunks, a.flags, a.loads, a.caps, a.ncap,
-                             a.capacity_padding, a.path_wise, a.prefix, a.threshold, s_warp);
+                             a.capacity_padding, a.path_wise, a.prefix, a.threshold, s_warp,
+                             a.counts);
 }
 
 template <Mode MODE>
@@ -1290,11 +1303,14 @@ __global__ void __launch_bounds__(kTileThreads, 2) index_chain_kernel(const Chai
     }
     if constexpr (MODE == Mode::kThrottleSeat) {
       const int room = sm.thr[tid] > 0 ? sm.thr[tid] : 0;
-      a.loads[col0 + tid] = map_load(total < room ? total : room, col0 + tid, a.caps, a.ncap,
-                                     a.capacity_padding != 0, a.path_wise != 0);
+      const int kept = total < room ? total : room;
+      a.loads[col0 + tid] = map_load(kept, col0 + tid, a.caps, a.ncap, a.capacity_padding != 0,
+                                     a.path_wise != 0);
+      if (a.counts != nullptr) a.counts[col0 + tid] = kept;
     } else if constexpr (!kThrottles) {
       a.loads[col0 + tid] = map_load(total, col0 + tid, a.caps, a.ncap, a.capacity_padding != 0,
                                      a.path_wise != 0);
+      if (a.counts != nullptr) a.counts[col0 + tid] = total;
     }
   }
   if (MODE == Mode::kThrottleSeat && general && tid == 0) {
@@ -1415,6 +1431,7 @@ int launch_chain(Mode mode, const TileGeom& g, int tiles_per_cta, int ranges, si
   c.t.out = out;
   c.t.mask_out = mask_out;
   c.t.loads = loads;
+  c.t.counts = t_counts_out;
   c.t.caps = caps;
   c.t.ncap = ncap;
   c.t.capacity_padding = capacity_padding;
@@ -1501,6 +1518,7 @@ int launch_tiled(Mode mode, const int32_t* mask, int32_t* out, int32_t* loads, i
   a.out = out;
   a.mask_out = nullptr;
   a.loads = loads;
+  a.counts = t_counts_out;
   a.caps = caps;
   a.ncap = ncap;
   a.capacity_padding = capacity_padding;
@@ -1560,11 +1578,12 @@ int launch_scan(Mode mode, const Tiling& tl, const Scratch& sc, const int32_t* m
   const unsigned scan_grid = (unsigned)((path_num + 31) / 32);
   if (mode == Mode::kThrottle) {
     tile_scan_kernel<true><<<scan_grid, 1024, 0, stream>>>(
-        sc.tile_sums, tl.num_tiles, path_num, nullptr, nullptr, 0, 0, 0, prefix, threshold), note_launch();
+        sc.tile_sums, tl.num_tiles, path_num, nullptr, nullptr, 0, 0, 0, prefix, threshold,
+        nullptr), note_launch();
   } else {
     tile_scan_kernel<false><<<scan_grid, 1024, 0, stream>>>(
         sc.tile_sums, tl.num_tiles, path_num, loads, caps, ncap, capacity_padding, path_wise,
-        nullptr, nullptr), note_launch();
+        nullptr, nullptr, t_counts_out), note_launch();
   }
   BRT_LAUNCH_CHECK("tile_scan_kernel");
   switch (mode) {
@@ -1664,7 +1683,8 @@ BRT_API size_t brt_index_scratch_bytes(int64_t cell_num, int path_num) {
 }
 
 BRT_API int brt_generate_indices_and_loads(const int32_t* hot_mask, int32_t* indices,
-                                           int32_t* loads, int64_t cell_num, int path_num,
+                                           int32_t* loads, int32_t* path_counts,
+                                           int64_t cell_num, int path_num,
                                            const int32_t* supported_capacities,
                                            int supported_capacity_num, int capacity_padding,
                                            int path_wise_padding, int is_tag_index,
@@ -1688,9 +1708,12 @@ BRT_API int brt_generate_indices_and_loads(const int32_t* hot_mask, int32_t* ind
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (cell_num == 0) {
     BRT_CUDA_TRY(cudaMemsetAsync(loads, 0, (size_t)path_num * 4, st));
+    if (path_counts != nullptr)
+      BRT_CUDA_TRY(cudaMemsetAsync(path_counts, 0, (size_t)path_num * 4, st));
     return BRT_OK;
   }
   BRT_REQUIRE(hot_mask != nullptr && indices != nullptr, "hot_mask or indices is null");
+  const CountsScope counts(path_counts);
   return run_scan(is_tag_index ? Mode::kTag : Mode::kSeat, hot_mask, indices, loads, cell_num,
                   path_num, supported_capacities, supported_capacity_num, capacity_padding,
                   path_wise, nullptr, nullptr, scratch, scratch_bytes, st);
@@ -1711,8 +1734,9 @@ BRT_API int brt_throttle_hotmask(const int32_t* hotmask, int32_t* throttled, int
 }
 
 BRT_API int brt_throttle_and_generate_indices(
-    const int32_t* hot_mask, int32_t* indices, int32_t* loads, int32_t* prefix,
-    const int32_t* threshold, int32_t* throttled_mask, int64_t cell_num, int path_num,
+    const int32_t* hot_mask, int32_t* indices, int32_t* loads, int32_t* path_counts,
+    int32_t* prefix, const int32_t* threshold, int32_t* throttled_mask, int64_t cell_num,
+    int path_num,
     const int32_t* supported_capacities, int supported_capacity_num, int capacity_padding,
     int path_wise_padding, void* scratch, size_t scratch_bytes, void* stream) {
   clear_error();
@@ -1733,6 +1757,8 @@ BRT_API int brt_throttle_and_generate_indices(
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (cell_num == 0) {  // as the two ops it stands for: prefix untouched, loads zero
     BRT_CUDA_TRY(cudaMemsetAsync(loads, 0, (size_t)path_num * 4, st));
+    if (path_counts != nullptr)
+      BRT_CUDA_TRY(cudaMemsetAsync(path_counts, 0, (size_t)path_num * 4, st));
     return BRT_OK;
   }
   BRT_REQUIRE(hot_mask != nullptr && indices != nullptr, "hot_mask or indices is null");
@@ -1747,6 +1773,7 @@ BRT_API int brt_throttle_and_generate_indices(
   if (scratch_bytes < need)
     return set_error(BRT_ERR_SCRATCH_TOO_SMALL, "scratch holds %zu bytes, %zu needed",
                      scratch_bytes, need);
+  const CountsScope counts(path_counts);
   return launch_tiled(Mode::kThrottleSeat, hot_mask, indices, loads, cell_num, path_num,
                       supported_capacities, supported_capacity_num, capacity_padding, path_wise,
                       prefix, threshold, scratch, st, nullptr, throttled_mask);
@@ -1754,7 +1781,8 @@ BRT_API int brt_throttle_and_generate_indices(
 
 BRT_API int brt_route_scores(const float* scores, int64_t cell_num, int path_num, int decision,
                              int top_k, float threshold, int residual_path, int output,
-                             int32_t* out, int32_t* loads, const int32_t* capacities,
+                             int32_t* out, int32_t* loads, int32_t* path_counts,
+                             const int32_t* capacities,
                              int capacity_num, int capacity_padding, int path_wise_padding,
                              int32_t* prefix, const int32_t* throttle_capacity, float* gates_out,
                              int32_t* mask_out, void* scratch, size_t scratch_bytes,
@@ -1785,9 +1813,15 @@ BRT_API int brt_route_scores(const float* scores, int64_t cell_num, int path_num
   path_wise_padding = (capacity_padding && path_wise_padding) ? 1 : 0;
   BRT_REQUIRE(!path_wise_padding || capacity_num >= path_num,
               "path_wise_padding needs one capacity per path (%d < %d)", capacity_num, path_num);
+  BRT_REQUIRE(path_counts == nullptr || output == BRT_ROUTE_SEAT_INDICES ||
+                  output == BRT_ROUTE_THROTTLED_SEAT_INDICES,
+              "path_counts goes with the seat-index outputs only");
   if (cell_num == 0) {
     if (output != BRT_ROUTE_THROTTLED_MASK)
       BRT_CUDA_TRY(cudaMemsetAsync(loads, 0, (size_t)path_num * 4, static_cast<cudaStream_t>(stream)));
+    if (path_counts != nullptr)
+      BRT_CUDA_TRY(cudaMemsetAsync(path_counts, 0, (size_t)path_num * 4,
+                                   static_cast<cudaStream_t>(stream)));
     return BRT_OK;
   }
   BRT_REQUIRE(scores != nullptr && out != nullptr, "scores or out is null");
@@ -1809,6 +1843,7 @@ BRT_API int brt_route_scores(const float* scores, int64_t cell_num, int path_num
                     : output == BRT_ROUTE_THROTTLED_MASK ? Mode::kThrottle
                     : output == BRT_ROUTE_THROTTLED_SEAT_INDICES ? Mode::kThrottleSeat
                                                                  : Mode::kSeat;
+  const CountsScope counts(path_counts);
   return launch_tiled(mode, reinterpret_cast<const int32_t*>(scores), out, loads, cell_num,
                       path_num, capacities, capacity_num, capacity_padding, path_wise_padding,
                       prefix, throttle_capacity, scratch, static_cast<cudaStream_t>(stream), &gate,
@@ -1863,7 +1898,8 @@ BRT_API int brt_generate_indices_and_loads_static(const int32_t* hot_mask, int32
   const int rc = static_scratch_address(&scratch);
   if (rc != BRT_OK) return rc;
   t_may_allocate = false;  // the status word of brt_index_status is used only if it exists
-  const int out = brt_generate_indices_and_loads(hot_mask, indices, loads, cell_num, path_num,
+  const int out = brt_generate_indices_and_loads(hot_mask, indices, loads, nullptr, cell_num,
+                                                 path_num,
                                                  supported_capacities, supported_capacity_num,
                                                  capacity_padding, path_wise_padding,
                                                  is_tag_index, scratch, kStaticScratchBytes,

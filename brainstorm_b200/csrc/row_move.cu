@@ -126,6 +126,45 @@ __device__ __forceinline__ void setup_paths(const int* __restrict__ loads, int p
   __syncthreads();
 }
 
+// Dense seat columns (what the index kernels write): column e holds every seat
+// 1 .. counts[e] exactly once, so the rows of path e that receive a cell are exactly the first
+// min(counts[e], loads[e]) of its slot and the rest of the slot is known to stay empty
+// without looking at the indices.  s_written[e] = rows of path e that get a cell,
+// s_fill[e] = exclusive prefix of the empty rows per path (s_fill[path_num] = their total).
+// Called by all threads of the CTA after setup_paths.
+__device__ __forceinline__ void setup_fill(const int* __restrict__ counts, int path_num,
+                                           int max_path_load, const int* s_loads,
+                                           int* s_written, int* s_fill) {
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    int carry = 0;
+    for (int p = 0; p < path_num; p += 32) {
+      const int e = p + lane;
+      int written = 0, empty = 0;
+      if (e < path_num) {
+        const int load = s_loads[e] > 0 ? s_loads[e] : 0;
+        const int have = counts[e] > 0 ? counts[e] : 0;
+        written = have < load ? have : load;
+        const int slot = max_path_load != 0 ? max_path_load : load;
+        empty = slot > written ? slot - written : 0;
+      }
+      int incl = empty;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += n;
+      }
+      if (e < path_num) {
+        s_written[e] = written;
+        s_fill[e] = carry + incl - empty;
+      }
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) s_fill[path_num] = carry;
+  }
+  __syncthreads();
+}
+
 template <int VB, int DT>
 struct Lanes {
   using V = typename Chunk<VB>::type;
@@ -209,7 +248,8 @@ struct MoveArgs {
   const int* loads;
   const int* old_tags;       // dispatch only
   int* new_tags;             // dispatch only
-  unsigned char* row_marks;  // dispatch only
+  unsigned char* row_marks;  // dispatch only (general index tensors)
+  const int* dense_counts;   // dispatch only: seat columns are dense, see setup_fill
   int64_t cell_num;
   int64_t row_vecs;  // vectors per row
   int64_t pieces_per_row;
@@ -306,6 +346,55 @@ __device__ __forceinline__ int build_routes(const MoveArgs& a, int64_t cell,
   return count;
 }
 
+// Zero one (empty row, 2 KB piece) of a dense dispatch; `item` counts the pieces of the empty
+// rows in path order.  Called by a whole warp.
+template <int VB>
+__device__ __forceinline__ void fill_item(const MoveArgs& a, const int* s_base,
+                                          const int* s_written, const int* s_fill, int64_t item,
+                                          int lane) {
+  using V = typename Chunk<VB>::type;
+  const int64_t nth = item / a.pieces_per_row;
+  const int piece = (int)(item - nth * a.pieces_per_row);
+  int lo = 0, hi = a.path_num - 1;  // last path whose first empty row is <= nth
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if ((int64_t)s_fill[mid] <= nth) lo = mid; else hi = mid - 1;
+  }
+  const int64_t row = (int64_t)s_base[lo] + s_written[lo] + (nth - s_fill[lo]);
+  V* dp = static_cast<V*>(a.dst) + row * a.row_vecs;
+  const V zero = zero_chunk<V>();
+  const int64_t v0 = (int64_t)piece * kPieceVecs + lane;
+#pragma unroll
+  for (int u = 0; u < kCopyUnroll; u++) {
+    const int64_t v = v0 + u * 32;
+    if (v < a.row_vecs) store_stream(dp + v, zero);
+  }
+  if (piece == 0 && lane == 0 && a.new_tags != nullptr) a.new_tags[row] = 0;
+}
+
+// A warp's share of the empty-row pieces, spread evenly between its move items so that the
+// writes of zeros mix with the row traffic instead of trailing it.
+struct FillPacer {
+  int64_t next, end, stride;  // items next, next + stride, ... < end
+  int64_t moves, fills, acc;
+  __device__ __forceinline__ FillPacer(int64_t move_items, int64_t fill_items, int64_t warp,
+                                       int64_t warps) {
+    next = warp;
+    end = fill_items;
+    stride = warps;
+    moves = move_items > warp ? (move_items - warp + warps - 1) / warps : 0;
+    fills = fill_items > warp ? (fill_items - warp + warps - 1) / warps : 0;
+    acc = 0;
+  }
+  // how many fill items are due after one more move item
+  __device__ __forceinline__ int due() {
+    acc += fills;
+    int n = 0;
+    while (acc >= moves && moves > 0) { acc -= moves; n++; }
+    return n;
+  }
+};
+
 // ---------------------------------------------------------------------------------- dispatch
 template <int VB, int DT, bool WEIGHTED, bool IS_1D, int IV>
 __global__ void __launch_bounds__(kThreads, 4) dispatch_seat_kernel(const MoveArgs a) {
@@ -315,7 +404,11 @@ __global__ void __launch_bounds__(kThreads, 4) dispatch_seat_kernel(const MoveAr
   extern __shared__ int s_mem[];
   int* s_loads = s_mem;
   int* s_base = s_mem + a.path_num;
+  int* s_written = s_base + a.path_num;
+  int* s_fill = s_written + a.path_num;
   setup_paths(a.loads, a.path_num, a.max_path_load, s_loads, s_base);
+  const bool dense = a.dense_counts != nullptr;
+  if (dense) setup_fill(a.dense_counts, a.path_num, a.max_path_load, s_loads, s_written, s_fill);
 
   const int lane = threadIdx.x & 31;
   const int64_t warp = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
@@ -325,6 +418,7 @@ __global__ void __launch_bounds__(kThreads, 4) dispatch_seat_kernel(const MoveAr
   V* __restrict__ dst = static_cast<V*>(a.dst);
   const int E = a.path_num;
   const int chunks = (E + 32 * IV - 1) / (32 * IV);
+  FillPacer pace(items, dense ? (int64_t)s_fill[E] * a.pieces_per_row : 0, warp, warps);
 
   const ItemStep step = step_of(warps, a.pieces_per_row);
   ItemCursor at = cursor_at(warp < items ? warp : 0, a.pieces_per_row);
@@ -404,18 +498,23 @@ __global__ void __launch_bounds__(kThreads, 4) dispatch_seat_kernel(const MoveAr
               }
             }
             if (piece == 0 && lane == 0) {
-              a.row_marks[row] = 1;
+              if (!dense) a.row_marks[row] = 1;
               if (a.new_tags != nullptr) a.new_tags[row] = a.old_tags[cell];
             }
           }
         }
       }
     }
+    if (dense)
+      for (int n = pace.due(); n > 0 && pace.next < pace.end; n--, pace.next += pace.stride)
+        fill_item<VB>(a, s_base, s_written, s_fill, pace.next, lane);
 #pragma unroll
     for (int j = 0; j < IV; j++) cur[j] = nxt[j];
     at = ahead;
     ahead = advance(ahead, step);
   }
+  for (; pace.next < pace.end; pace.next += pace.stride)
+    fill_item<VB>(a, s_base, s_written, s_fill, pace.next, lane);
 }
 
 // Writes zeros to every row (and tag) the move pass did not mark.  A warp owns the items
@@ -731,7 +830,11 @@ __global__ void __launch_bounds__(kThreads, WEIGHTED ? 3 : 4) dispatch_seat_asyn
   CopyStage* s_stage = reinterpret_cast<CopyStage*>(s_raw);  // [kWarps][kStages]
   int* s_loads = reinterpret_cast<int*>(s_raw + sizeof(CopyStage) * kWarps * kStages);
   int* s_base = s_loads + a.path_num;
+  int* s_written = s_base + a.path_num;
+  int* s_fill = s_written + a.path_num;
   setup_paths(a.loads, a.path_num, a.max_path_load, s_loads, s_base);
+  const bool dense = a.dense_counts != nullptr;
+  if (dense) setup_fill(a.dense_counts, a.path_num, a.max_path_load, s_loads, s_written, s_fill);
 
   const int lane = threadIdx.x & 31;
   const int warp_in_cta = threadIdx.x >> 5;
@@ -742,6 +845,7 @@ __global__ void __launch_bounds__(kThreads, WEIGHTED ? 3 : 4) dispatch_seat_asyn
   V* __restrict__ dst = static_cast<V*>(a.dst);
   const int E = a.path_num;
   CopyStage* my = s_stage + warp_in_cta * kStages;
+  FillPacer pace(items, dense ? (int64_t)s_fill[E] * a.pieces_per_row : 0, warp, warps);
 
   int seat[IV];
   float gate[IV];
@@ -808,7 +912,7 @@ __global__ void __launch_bounds__(kThreads, WEIGHTED ? 3 : 4) dispatch_seat_asyn
             store_stream(dp + u * 32, regs[u]);
         }
         if (at.piece == 0 && lane == 0) {
-          a.row_marks[slot.row] = 1;
+          if (!dense) a.row_marks[slot.row] = 1;
           if (a.new_tags != nullptr) a.new_tags[slot.row] = a.old_tags[cell];
         }
       }
@@ -832,12 +936,15 @@ __global__ void __launch_bounds__(kThreads, WEIGHTED ? 3 : 4) dispatch_seat_asyn
               store_stream(dp + u * 32, regs[u]);
           }
           if (at.piece == 0 && lane == 0) {
-            a.row_marks[row] = 1;
+            if (!dense) a.row_marks[row] = 1;
             if (a.new_tags != nullptr) a.new_tags[row] = a.old_tags[cell];
           }
         }
       }
     }
+    if (dense)
+      for (int n = pace.due(); n > 0 && pace.next < pace.end; n--, pace.next += pace.stride)
+        fill_item<VB>(a, s_base, s_written, s_fill, pace.next, lane);
     __syncwarp();
     at = ahead;
     ahead = ahead2;
@@ -845,6 +952,8 @@ __global__ void __launch_bounds__(kThreads, WEIGHTED ? 3 : 4) dispatch_seat_asyn
     stage ^= 1;
   }
   cp_async_wait<0>();
+  for (; pace.next < pace.end; pace.next += pace.stride)
+    fill_item<VB>(a, s_base, s_written, s_fill, pace.next, lane);
 }
 
 // Register-only combine for rows that cannot be moved 16 bytes at a time.
@@ -951,21 +1060,27 @@ void configure_smem(size_t stage_bytes) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || configured_device == dev) return;
   cudaFuncSetAttribute(kKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                       (int)(stage_bytes + (size_t)kMaxPaths * 2 * sizeof(int)));
+                       (int)(stage_bytes + ((size_t)kMaxPaths * 4 + 4) * sizeof(int)));
   configured_device = dev;
 }
 
 template <int VB, int DT, bool WEIGHTED, bool IS_1D>
 void launch_dispatch(const MoveArgs& a, bool is_tag, cudaStream_t st) {
-  const KernelTimer timer(is_tag ? "dispatch_tag_kernel" : "dispatch_move_kernel", st);
-  const size_t smem = (size_t)a.path_num * 2 * sizeof(int);
+  const KernelTimer timer(is_tag ? "dispatch_tag_kernel"
+                                 : a.dense_counts != nullptr ? "dispatch_kernel"
+                                                             : "dispatch_move_kernel",
+                          st);
+  const size_t smem = (a.dense_counts != nullptr ? (size_t)a.path_num * 4 + 4
+                                                 : (size_t)a.path_num * 2) * sizeof(int);
   if (is_tag) {
     dispatch_tag_kernel<VB, DT, WEIGHTED, IS_1D>
         <<<grid_for_items(a.total_rows * a.pieces_per_row), kThreads, smem, st>>>(a), note_launch();
   } else if (VB == 16 && IS_1D) {
     if constexpr (VB == 16 && IS_1D) {
       const size_t smem_async = sizeof(CopyStage) * kWarps * kStages + smem;
-      const unsigned grid = grid_for_resident(a.cell_num * a.pieces_per_row, WEIGHTED ? 3 : 4);
+      const int64_t work = (a.cell_num + (a.dense_counts != nullptr ? a.total_rows : 0)) *
+                           a.pieces_per_row;
+      const unsigned grid = grid_for_resident(work, WEIGHTED ? 3 : 4);
       if (wide_rows(a.indices, a.gates, dtype_size(DT), a.path_num)) {
         configure_smem<dispatch_seat_async_kernel<DT, WEIGHTED, 4>>(sizeof(CopyStage) * kWarps *
                                                                     kStages);
@@ -976,12 +1091,15 @@ void launch_dispatch(const MoveArgs& a, bool is_tag, cudaStream_t st) {
         dispatch_seat_async_kernel<DT, WEIGHTED, 1><<<grid, kThreads, smem_async, st>>>(a), note_launch();
       }
     }
-  } else if (wide_rows(a.indices, a.gates, dtype_size(DT), a.path_num)) {
-    dispatch_seat_kernel<VB, DT, WEIGHTED, IS_1D, 4>
-        <<<grid_for_items(a.cell_num * a.pieces_per_row), kThreads, smem, st>>>(a), note_launch();
   } else {
-    dispatch_seat_kernel<VB, DT, WEIGHTED, IS_1D, 1>
-        <<<grid_for_items(a.cell_num * a.pieces_per_row), kThreads, smem, st>>>(a), note_launch();
+    const int64_t work = (a.cell_num + (a.dense_counts != nullptr ? a.total_rows : 0)) *
+                         a.pieces_per_row;
+    if (wide_rows(a.indices, a.gates, dtype_size(DT), a.path_num))
+      dispatch_seat_kernel<VB, DT, WEIGHTED, IS_1D, 4>
+          <<<grid_for_items(work), kThreads, smem, st>>>(a), note_launch();
+    else
+      dispatch_seat_kernel<VB, DT, WEIGHTED, IS_1D, 1>
+          <<<grid_for_items(work), kThreads, smem, st>>>(a), note_launch();
   }
 }
 
@@ -1086,8 +1204,8 @@ BRT_API int brt_dispatch_with_indices_and_loads(
     const void* src_data, void* dst_data, const void* gates, const int32_t* route_indices,
     const int32_t* loads, const int32_t* old_tags, int32_t* new_tags, int64_t cell_num,
     int64_t cell_size, int path_num, int32_t max_path_load, int64_t total_rows,
-    int is_1d_routing, int is_tag_index, int dtype, void* scratch, size_t scratch_bytes,
-    void* stream) {
+    int is_1d_routing, int is_tag_index, int dtype, const int32_t* dense_counts, void* scratch,
+    size_t scratch_bytes, void* stream) {
   clear_error();
   BRT_REQUIRE(dtype == BRT_F32 || dtype == BRT_F16 || dtype == BRT_BF16, "bad dtype %d", dtype);
   BRT_REQUIRE(cell_num >= 0 && cell_size >= 0 && total_rows >= 0, "negative size");
@@ -1119,6 +1237,9 @@ BRT_API int brt_dispatch_with_indices_and_loads(
   a.old_tags = old_tags;
   a.new_tags = new_tags;
   a.row_marks = static_cast<unsigned char*>(scratch);
+  // the one-launch path for dense seat columns (its per-path tables live in shared memory)
+  const bool dense = dense_counts != nullptr && !is_tag_index && path_num <= 2048;
+  a.dense_counts = dense ? dense_counts : nullptr;
   a.cell_num = cell_num;
   a.row_vecs = row_bytes / vb;
   a.pieces_per_row = (a.row_vecs + kPieceVecs - 1) / kPieceVecs;
@@ -1128,7 +1249,7 @@ BRT_API int brt_dispatch_with_indices_and_loads(
   a.is_residual = 0;
 
   const bool is_tag = is_tag_index != 0;
-  if (!is_tag) {
+  if (!is_tag && !dense) {
     const size_t need = brt_dispatch_scratch_bytes(total_rows, path_num);
     BRT_REQUIRE(scratch != nullptr, "scratch is null");
     if (scratch_bytes < need)
@@ -1137,7 +1258,7 @@ BRT_API int brt_dispatch_with_indices_and_loads(
     BRT_CUDA_TRY(cudaMemsetAsync(scratch, 0, (size_t)total_rows, st));
   }
   int rc = BRT_OK;
-  if (cell_num > 0 || is_tag) {
+  if (cell_num > 0 || is_tag || dense) {
     switch (vb) {
       case 16: rc = dispatch_by_flags<16>(a, dtype, gates != nullptr, is_1d_routing != 0, is_tag, st); break;
       case 8: rc = dispatch_by_flags<8>(a, dtype, gates != nullptr, is_1d_routing != 0, is_tag, st); break;
@@ -1147,7 +1268,7 @@ BRT_API int brt_dispatch_with_indices_and_loads(
     if (rc != BRT_OK) return rc;
     BRT_LAUNCH_CHECK("dispatch kernel");
   }
-  if (!is_tag) {
+  if (!is_tag && !dense) {
     switch (vb) {
       case 16: launch_zero_fill<16>(a, st); break;
       case 8: launch_zero_fill<8>(a, st); break;
@@ -1189,6 +1310,7 @@ BRT_API int brt_combine_with_indices_and_loads(
   a.old_tags = nullptr;
   a.new_tags = nullptr;
   a.row_marks = nullptr;
+  a.dense_counts = nullptr;
   a.cell_num = cell_num;
   a.row_vecs = row_bytes / vb;
   a.pieces_per_row = (a.row_vecs + kFoldVecs - 1) / kFoldVecs;

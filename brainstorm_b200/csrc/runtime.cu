@@ -83,7 +83,7 @@ int sm_count() {
 
 extern "C" {
 
-BRT_API int brt_abi_version(void) { return 2; }
+BRT_API int brt_abi_version(void) { return 3; }
 
 BRT_API const char* brt_last_error(void) { return brt_b200::error_buffer(); }
 

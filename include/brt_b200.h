@@ -78,9 +78,13 @@ BRT_API size_t brt_index_scratch_bytes(int64_t cell_num, int path_num);
  * loads follow the reference's capacity rules (path_wise_padding only with
  * capacity_padding; capacity_padding needs supported_capacity_num >= 1).
  * `indices` is fully written (it does not have to be zeroed by the caller).
+ * path_counts (optional, [path_num]) receives the cells per path that the indices hold, i.e.
+ * the column sums of the mask before the capacity rules turn them into loads: what
+ * brt_dispatch_with_indices_and_loads takes as `dense_counts`.
  */
 BRT_API int brt_generate_indices_and_loads(const int32_t* hot_mask, int32_t* indices,
-                                           int32_t* loads, int64_t cell_num, int path_num,
+                                           int32_t* loads, int32_t* path_counts,
+                                           int64_t cell_num, int path_num,
                                            const int32_t* supported_capacities,
                                            int supported_capacity_num, int capacity_padding,
                                            int path_wise_padding, int is_tag_index,
@@ -171,8 +175,9 @@ BRT_API int brt_throttle_hotmask(const int32_t* hotmask, int32_t* throttled, int
  * caller then uses the two entry points above.
  */
 BRT_API int brt_throttle_and_generate_indices(
-    const int32_t* hot_mask, int32_t* indices, int32_t* loads, int32_t* prefix,
-    const int32_t* threshold, int32_t* throttled_mask, int64_t cell_num, int path_num,
+    const int32_t* hot_mask, int32_t* indices, int32_t* loads, int32_t* path_counts,
+    int32_t* prefix, const int32_t* threshold, int32_t* throttled_mask, int64_t cell_num,
+    int path_num,
     const int32_t* supported_capacities, int supported_capacity_num, int capacity_padding,
     int path_wise_padding, void* scratch, size_t scratch_bytes, void* stream);
 
@@ -228,7 +233,8 @@ typedef enum brt_route_output {
  */
 BRT_API int brt_route_scores(const float* scores, int64_t cell_num, int path_num, int decision,
                              int top_k, float threshold, int residual_path, int output,
-                             int32_t* out, int32_t* loads, const int32_t* capacities,
+                             int32_t* out, int32_t* loads, int32_t* path_counts,
+                             const int32_t* capacities,
                              int capacity_num, int capacity_padding, int path_wise_padding,
                              int32_t* prefix, const int32_t* throttle_capacity, float* gates_out,
                              int32_t* mask_out, void* scratch, size_t scratch_bytes,
@@ -252,13 +258,20 @@ BRT_API size_t brt_dispatch_scratch_bytes(int64_t total_rows, int path_num);
  * the data's dtype and scales the copied row; old_tags/new_tags (optional, both or
  * neither) carry the cell tags.  is_tag_index != 0 reads route_indices as tag indices
  * (row i < loads[e] of path e pulls cell tag-1; a zero tag leaves the row zero).
+ *
+ * dense_counts (optional, seat indices only): the caller vouches that column e of
+ * route_indices holds every seat 1 .. dense_counts[e] exactly once and zeros elsewhere, which
+ * is what the index entry points write and report as `path_counts`.  The rows that stay empty
+ * are then known without looking at the indices and the whole dispatch is ONE launch that
+ * needs no scratch; without it (any index tensor) the call marks the rows it writes in
+ * `scratch` (brt_dispatch_scratch_bytes) and zeroes the others with a second launch.
  */
 BRT_API int brt_dispatch_with_indices_and_loads(
     const void* src_data, void* dst_data, const void* gates, const int32_t* route_indices,
     const int32_t* loads, const int32_t* old_tags, int32_t* new_tags, int64_t cell_num,
     int64_t cell_size, int path_num, int32_t max_path_load, int64_t total_rows,
-    int is_1d_routing, int is_tag_index, int dtype, void* scratch, size_t scratch_bytes,
-    void* stream);
+    int is_1d_routing, int is_tag_index, int dtype, const int32_t* dense_counts, void* scratch,
+    size_t scratch_bytes, void* stream);
 
 /*
  * Replaces brt::router::CombineWithIndicesAndLoads<T>

@@ -52,18 +52,18 @@ def test_status_codes_without_gpu():
     from brainstorm_b200 import _lib
 
     with pytest.raises(_lib.BrtError, match="bad shape"):
-        _lib.call("brt_generate_indices_and_loads", None, None, None, 4, 0, None, 0, 0, 0, 0,
-                  None, 0, None)
+        _lib.call("brt_generate_indices_and_loads", None, None, None, None, 4, 0, None, 0, 0, 0,
+                  0, None, 0, None)
     with pytest.raises(_lib.BrtError, match="capacity_padding needs"):
-        _lib.call("brt_generate_indices_and_loads", 16, 16, 16, 4, 4, None, 0, 1, 0, 0, None, 0,
-                  None)
+        _lib.call("brt_generate_indices_and_loads", 16, 16, 16, None, 4, 4, None, 0, 1, 0, 0,
+                  None, 0, None)
     # the gate entry point applies the same capacity rules before it touches anything
     with pytest.raises(_lib.BrtError, match="capacity_padding needs"):
-        _lib.call("brt_route_scores", 16, 64, 8, 0, 1, 0.0, -1, 2, 16, 16, None, 0, 1, 0, None,
-                  None, None, None, None, 0, None)
+        _lib.call("brt_route_scores", 16, 64, 8, 0, 1, 0.0, -1, 2, 16, 16, None, None, 0, 1, 0,
+                  None, None, None, None, None, 0, None)
     with pytest.raises(_lib.BrtError, match="path_wise_padding needs"):
-        _lib.call("brt_route_scores", 16, 64, 8, 0, 1, 0.0, -1, 2, 16, 16, 16, 3, 1, 1, None,
-                  None, None, None, None, 0, None)
+        _lib.call("brt_route_scores", 16, 64, 8, 0, 1, 0.0, -1, 2, 16, 16, None, 16, 3, 1, 1,
+                  None, None, None, None, None, 0, None)
     with pytest.raises(_lib.BrtError, match="has not been called"):
         _lib.call("brt_all_to_all", None, None, 0, None)
     with pytest.raises(_lib.BrtError, match="world_size"):

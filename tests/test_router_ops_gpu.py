@@ -310,6 +310,71 @@ def test_dispatch_and_combine(R, dtype, T, E, k, cell, variant):
     assert np.array_equal(host(res_d), exp_res)
 
 
+def poison_allocator(nbytes):
+    """Fill a block with a NaN pattern and hand it back to torch's allocator, so that an output
+    the next call leaves partly unwritten shows up as garbage, not as stale zeros."""
+    junk = torch.full((max(nbytes, 1024) // 4 + 64,), float("nan"), device="cuda")
+    del junk
+
+
+DENSE_VARIANTS = ["plain", "padded", "padded_capacity", "capped", "throttled", "weighted",
+                  "tags", "2d"]
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("T,E,k,cell", DISPATCH_CASES + [(3000, 32, 2, (1024,)),
+                                                         (2000, 8, 1, (2600,))])
+@pytest.mark.parametrize("variant", DENSE_VARIANTS)
+def test_dispatch_of_library_made_indices(R, dtype, T, E, k, cell, variant):
+    """Indices that come straight out of the index kernels carry the per-path cell counts, and
+    the dispatch runs as one launch that zeroes the empty rows from those counts alone.  The
+    result must equal the checker's whatever the relation between counts, loads and slot size:
+    loads above the counts (capacity padding), below them (capped), slots above the loads."""
+    from brainstorm_b200._C.router import _DENSE
+
+    rng = np.random.default_rng(T * 5 + E + len(variant))
+    mask = rand_mask(rng, T, E, k)
+    caps, cpad, kw = None, False, {}
+    per_path = max(1, T * k // E)
+    if variant == "padded_capacity":
+        caps, cpad = [per_path // 2, 2 * per_path, 8 * per_path], True
+    elif variant == "capped":
+        caps, cpad = [max(1, per_path // 2)], False  # loads capped below the counts: drops
+    mask_d = dev(mask)
+    if variant == "throttled":
+        thr = rng.integers(0, 2 * per_path, size=E).astype(np.int32)
+        m_np, _ = oracle.throttle_hotmask(mask, np.zeros(E, dtype=np.int32), thr)
+        idx_np, loads_np = oracle.generate_indices_and_loads(m_np)
+        idx, loads, _ = R.throttle_and_generate_indices(
+            mask_d, torch.zeros(E, dtype=torch.int32, device="cuda"), dev(thr))
+    else:
+        idx_np, loads_np = oracle.generate_indices_and_loads(mask, caps, cpad)
+        idx, loads = R.generate_indices_and_loads(
+            mask_d, None if caps is None else dev(np.array(caps, dtype=np.int32)), cpad)
+    assert getattr(idx, _DENSE, None) is not None
+    if variant in ("padded", "padded_capacity", "throttled"):
+        kw = dict(max_path_padding=True, max_path_load=int(loads_np.max()) + 5)
+    is_1d = variant != "2d"
+    x = make_data(rng, (T,) + cell if is_1d else (T, E) + cell[:1], dtype)
+    gates = make_data(rng, (T, E), dtype) if variant == "weighted" else None
+    tagging = variant == "tags"
+    exp = oracle.dispatch_with_indices_and_loads(x, idx_np, loads_np, gates, tagging, None,
+                                                 is_1d_routing=is_1d, dtype=dtype, **kw)
+    poison_allocator(exp[0].size * exp[0].itemsize)
+    got = R.dispatch_with_indices_and_loads(
+        dev(x, dtype), idx, loads, None if gates is None else dev(gates, dtype), tagging, None,
+        kw.get("max_path_padding", False), kw.get("max_path_load", 0), is_1d)
+    assert got[0].shape == exp[0].shape
+    assert np.array_equal(host(got[0]), exp[0])
+    if tagging:
+        assert np.array_equal(host(got[1]), exp[1])
+    # an index tensor that lost the note (a clone) takes the general route: same rows
+    again = R.dispatch_with_indices_and_loads(
+        dev(x, dtype), idx.clone(), loads, None if gates is None else dev(gates, dtype), tagging,
+        None, kw.get("max_path_padding", False), kw.get("max_path_load", 0), is_1d)
+    assert np.array_equal(host(again[0]), exp[0])
+
+
 @pytest.mark.parametrize("dtype", ["f16", "bf16"])
 def test_combine_gates_in_data_dtype(R, dtype):
     rng = np.random.default_rng(2)

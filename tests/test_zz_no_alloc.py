@@ -34,7 +34,7 @@ def _regular(lib, mask, caps, cpad, tag):
     n = lib.query("brt_index_scratch_bytes", T, E)
     scratch = torch.empty(n, dtype=torch.uint8, device="cuda")
     lib.call("brt_generate_indices_and_loads", mask.data_ptr(), idx.data_ptr(), loads.data_ptr(),
-             T, E, None if caps is None else caps.data_ptr(), 0 if caps is None else caps.numel(),
+             None, T, E, None if caps is None else caps.data_ptr(), 0 if caps is None else caps.numel(),
              int(cpad), 0, int(tag), scratch.data_ptr(), n,
              torch.cuda.current_stream().cuda_stream)
     return idx, loads
