@@ -11,6 +11,7 @@ deliberate:
   identical when the current stream is the default one);
 * outputs are never pre-zeroed by a separate memset: the kernels write every byte.
 """
+import os
 from typing import List, Optional
 
 import torch
@@ -65,6 +66,7 @@ _scratch = _ScratchPool()
 
 
 _DENSE = "_brt_dense_counts"
+_USE_DENSE = os.environ.get("BRT_DISPATCH_DENSE", "1") != "0"  # 0: always the general route
 
 
 def _mark_dense(indices: torch.Tensor, counts: torch.Tensor) -> None:
@@ -411,7 +413,7 @@ def dispatch_with_indices_and_loads(
         # no scratch; any other index tensor takes the general two-launch route
         dense = None if is_tag_index else getattr(route_indices, _DENSE, None)
         if dense is not None and (dense.device != dev or dense.numel() != path_num
-                                  or path_num > 2048):
+                                  or path_num > 2048 or not _USE_DENSE):
             dense = None
         scratch, nscratch = None, 0
         if dense is None and not is_tag_index:

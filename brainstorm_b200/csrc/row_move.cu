@@ -27,6 +27,8 @@
 // through a slower serial walk of the index row, so any number of routes is correct.
 #include "common.cuh"
 
+#include <cstdlib>
+#include <cstring>
 #include <initializer_list>
 
 namespace brt_b200 {
@@ -250,6 +252,11 @@ struct MoveArgs {
   int* new_tags;             // dispatch only
   unsigned char* row_marks;  // dispatch only (general index tensors)
   const int* dense_counts;   // dispatch only: seat columns are dense, see setup_fill
+  int keep_rows_cached;      // dispatch: write rows with the default cache policy (the next
+                             // op reads them) instead of evict-first
+  int loads_evict_first;     // dispatch: source rows leave L2 first (they are read once)
+  int newest_first;          // combine: visit the cells from the last to the first, so that
+                             // the rows written most recently are read while still in L2
   int64_t cell_num;
   int64_t row_vecs;  // vectors per row
   int64_t pieces_per_row;
@@ -631,6 +638,9 @@ __global__ void __launch_bounds__(kThreads) dispatch_tag_kernel(const MoveArgs a
 }
 
 // ---------------------------------------------------------------------------------- combine
+// (The packed fp32 instructions of sm_100, mul.rn.f32x2 / add.rn.f32x2, were tried here: the
+// results differed from the scalar sequence in the last bit and the kernel ran slower, so the
+// fold stays scalar.)
 template <int VB, int DT, int GMODE>
 __device__ __forceinline__ void fold_chunk(float (&acc)[Lanes<VB, DT>::N],
                                            const typename Chunk<VB>::type& row, float g) {
@@ -685,20 +695,22 @@ __global__ void __launch_bounds__(kThreads, 3) combine_seat_async_kernel(const M
 
   int seat[IV];
   float gate[IV];
+  // the cell an item position stands for (positions are walked upwards either way)
+  auto cell_at = [&](int64_t pos) { return a.newest_first ? a.cell_num - 1 - pos : pos; };
   auto fetch = [&](const ItemCursor& c) {
 #pragma unroll
     for (int j = 0; j < IV; j++) { seat[j] = 0; gate[j] = 1.f; }
     if (c.cell < a.cell_num) {
-      load_index_chunk<IV>(a.indices, c.cell, E, 0, lane, seat);
-      load_gate_chunk<IV, GMODE, DT>(a.gates, c.cell, E, 0, lane, gate);
+      load_index_chunk<IV>(a.indices, cell_at(c.cell), E, 0, lane, seat);
+      load_gate_chunk<IV, GMODE, DT>(a.gates, cell_at(c.cell), E, 0, lane, gate);
     }
   };
   // Build the route table of an item from the registers fetched for it and start the
   // asynchronous copies of its rows; always closes exactly one copy group.
   auto issue = [&](FoldStage& st, const ItemCursor& c) {
     if (c.cell < a.cell_num) {
-      const int count = build_routes<IV, GMODE, DT, false>(a, c.cell, seat, gate, s_loads,
-                                                           s_base, st.route, lane);
+      const int count = build_routes<IV, GMODE, DT, false>(a, cell_at(c.cell), seat, gate,
+                                                           s_loads, s_base, st.route, lane);
       if (lane == 0) st.count = count;
       __syncwarp();
       const int staged = count < kMaxRoutes ? count : kMaxRoutes;
@@ -731,7 +743,7 @@ __global__ void __launch_bounds__(kThreads, 3) combine_seat_async_kernel(const M
     __syncwarp();
 
     const FoldStage& st = my[stage];
-    const int64_t cell = at.cell;
+    const int64_t cell = cell_at(at.cell);
     const int64_t first = (int64_t)at.piece * kFoldVecs;
     const int count = st.count;
     V* dp = dst + cell * a.row_vecs + first + lane;
@@ -845,6 +857,7 @@ __global__ void __launch_bounds__(kThreads, WEIGHTED ? 3 : 4) dispatch_seat_asyn
   V* __restrict__ dst = static_cast<V*>(a.dst);
   const int E = a.path_num;
   CopyStage* my = s_stage + warp_in_cta * kStages;
+  const unsigned long long evict_first = l2_evict_first_policy();
   FillPacer pace(items, dense ? (int64_t)s_fill[E] * a.pieces_per_row : 0, warp, warps);
 
   int seat[IV];
@@ -868,7 +881,12 @@ __global__ void __launch_bounds__(kThreads, WEIGHTED ? 3 : 4) dispatch_seat_asyn
 #pragma unroll
         for (int u = 0; u < kCopyUnroll; u++) {
           const int v = u * 32 + lane;
-          if (first + v < a.row_vecs) cp_async_16(&st.row[v], sp + v);
+          if (first + v < a.row_vecs) {
+            if (a.loads_evict_first)
+              cp_async_16_hint(&st.row[v], sp + v, evict_first);
+            else
+              cp_async_16(&st.row[v], sp + v);
+          }
         }
       }
     }
@@ -906,10 +924,12 @@ __global__ void __launch_bounds__(kThreads, WEIGHTED ? 3 : 4) dispatch_seat_asyn
 #pragma unroll
         for (int u = 0; u < kCopyUnroll; u++) {
           if (!full && first + u * 32 + lane >= a.row_vecs) continue;
-          if constexpr (WEIGHTED)
-            store_stream(dp + u * 32, scale_chunk<VB, DT>(regs[u], slot.gate));
+          V out = regs[u];
+          if constexpr (WEIGHTED) out = scale_chunk<VB, DT>(regs[u], slot.gate);
+          if (a.keep_rows_cached)
+            dp[u * 32] = out;
           else
-            store_stream(dp + u * 32, regs[u]);
+            store_stream(dp + u * 32, out);
         }
         if (at.piece == 0 && lane == 0) {
           if (!dense) a.row_marks[slot.row] = 1;
@@ -1017,6 +1037,41 @@ __global__ void __launch_bounds__(kThreads) combine_seat_kernel(const MoveArgs a
 }
 
 // ---------------------------------------------------------------------------------- launch
+// Cache behaviour of the two big kernels (read once; the defaults are what measured best on
+// the routing step, the variables exist for experiments):
+//   BRT_DISPATCH_STORES = cached | stream   rows written with the default policy or evict-first
+//   BRT_COMBINE_ORDER   = newest | oldest   cells visited last-to-first or first-to-last
+//   BRT_DISPATCH_LOADS  = evict_first | normal   L2 policy of the source rows of a dispatch
+bool env_is(const char* name, const char* value, bool otherwise) {
+  const char* v = getenv(name);
+  return v == nullptr ? otherwise : strcmp(v, value) == 0;
+}
+int64_t l2_bytes() {
+  static thread_local int cached_dev = -1;
+  static thread_local int64_t cached = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (dev != cached_dev) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrL2CacheSize, dev) != cudaSuccess) n = 0;
+    cached = n;
+    cached_dev = dev;
+  }
+  return cached;
+}
+bool dispatch_keeps_rows_cached() {
+  static const bool on = env_is("BRT_DISPATCH_STORES", "cached", true);
+  return on;
+}
+bool dispatch_loads_evict_first() {
+  static const bool on = env_is("BRT_DISPATCH_LOADS", "evict_first", true);
+  return on;
+}
+bool combine_newest_first() {
+  static const bool on = env_is("BRT_COMBINE_ORDER", "newest", true);
+  return on;
+}
+
 int pick_vec_bytes(int64_t row_bytes, std::initializer_list<const void*> ptrs, int min_bytes) {
   for (int vb : {16, 8, 4, 2}) {
     if (vb < min_bytes) break;
@@ -1240,6 +1295,12 @@ BRT_API int brt_dispatch_with_indices_and_loads(
   // the one-launch path for dense seat columns (its per-path tables live in shared memory)
   const bool dense = dense_counts != nullptr && !is_tag_index && path_num <= 2048;
   a.dense_counts = dense ? dense_counts : nullptr;
+  // rows stay in L2 for the op that reads them next only when the output is of L2's order of
+  // size; a larger output is streamed (measured: cached stores of a 512 MB output cost 30 %)
+  a.keep_rows_cached =
+      dispatch_keeps_rows_cached() && total_rows * row_bytes <= (int64_t)l2_bytes() * 5 / 4;
+  a.loads_evict_first = dispatch_loads_evict_first() ? 1 : 0;
+  a.newest_first = 0;
   a.cell_num = cell_num;
   a.row_vecs = row_bytes / vb;
   a.pieces_per_row = (a.row_vecs + kPieceVecs - 1) / kPieceVecs;
@@ -1311,6 +1372,9 @@ BRT_API int brt_combine_with_indices_and_loads(
   a.new_tags = nullptr;
   a.row_marks = nullptr;
   a.dense_counts = nullptr;
+  a.keep_rows_cached = 0;
+  a.loads_evict_first = 0;
+  a.newest_first = combine_newest_first() ? 1 : 0;
   a.cell_num = cell_num;
   a.row_vecs = row_bytes / vb;
   a.pieces_per_row = (a.row_vecs + kFoldVecs - 1) / kFoldVecs;
