@@ -26,6 +26,7 @@ _ALIASES = (
     "router.protocol.swin_moe", "router.fabric", "router.fabric.base", "router.fabric.generic",
     "router.fabric.fused", "router.fabric.distributed", "runtime", "runtime.grid_tensor",
     "runtime.annotate", "runtime.registry", "runtime.distributed", "runtime.log",
+    "runtime.placement",
 )
 
 
