@@ -130,6 +130,21 @@ def test_renormalised_gates(R, T, E, k):
     np.testing.assert_allclose(g, ref.numpy(), rtol=1e-6, atol=0)
 
 
+def test_switch_top1_capacity_mask():
+    """The Switch gate's capacity mask (argmax -> one-hot -> cumsum -> <= capacity, per group)
+    from the gate kernel, against the torch formula of the reference's model code."""
+    from brainstorm_b200.router.protocol.switch import switch_top1_capacity_mask
+
+    torch.manual_seed(5)
+    for shape, cap in (((3, 700, 8), 60), ((4096, 32), 100), ((2, 513, 6), 40)):
+        probs = torch.softmax(torch.randn(shape, device="cuda") * 2, dim=-1)
+        one_hot = torch.nn.functional.one_hot(torch.argmax(probs, dim=-1), num_classes=shape[-1])
+        want = one_hot * (torch.cumsum(one_hot, dim=-2) <= cap)
+        got = switch_top1_capacity_mask(probs, cap)
+        assert got.dtype == torch.int32 and got.shape == probs.shape
+        assert torch.equal(got, want.to(torch.int32))
+
+
 def test_ties_go_to_the_lower_path(R):
     s = np.zeros((40, 8), dtype=np.float32)
     s[:, 5] = 1.0
