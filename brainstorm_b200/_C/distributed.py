@@ -190,15 +190,44 @@ def _locality_tail(recv_sizes: torch.Tensor, group_size: int):
     return reordered, reorder_indices
 
 
+def _slots_p2p(x: torch.Tensor, send_sizes: torch.Tensor, group_size: int):
+    """The padded-slot exchange over peer memory: (out, recv_sizes on the device) or None when
+    this exchange cannot take that path (decided from facts every rank shares)."""
+    rank, W = _world()
+    n = W * group_size
+    if not _p2p_usable(x, W, group_size) or x.size(0) == 0 or x.size(0) % n != 0:
+        return None
+    arena = p2p.arena()
+    stride = x.size(0) // n
+    x = arena.safe_source(x)
+    sizes32 = send_sizes.to(torch.int32).contiguous()
+    S, out_rows, fits, ptr, xid = arena.sparse_forward(x, sizes32, group_size, _row_bytes(x),
+                                                       stride, p2p.SLOTS)
+    # slot (i, j) of my output holds what rank i sent from its slot (me, j)
+    recv_np = np.ascontiguousarray(S[:, rank * group_size:(rank + 1) * group_size].reshape(-1))
+    recv = torch.from_numpy(recv_np).to(x.device)
+    if fits:
+        out = _landed(arena, ptr, out_rows, x)
+    else:
+        send_np = np.ascontiguousarray(S[rank])
+        out = _slot_a2a(x, send_np, recv_np, group_size, False)
+    setattr(recv, _TAG, (xid, group_size))
+    return out, recv
+
+
 def _asymmetry(in_data, send_sizes, locality_aware, zero_fill=False):
     _check_cuda(in_data, "in_data")
     _check_cuda(send_sizes, "send_sizes")
     _, W = _world()
     group_size = send_sizes.numel() // W
     with torch.cuda.device(in_data.device):
-        recv_sizes = _exchange_sizes(send_sizes)
-        send_np, recv_np = _host_sizes(send_sizes, recv_sizes)
-        out = _slot_a2a(in_data, send_np, recv_np, group_size, zero_fill)
+        moved = _slots_p2p(_contig(in_data), send_sizes, group_size)
+        if moved is not None:
+            out, recv_sizes = moved
+        else:
+            recv_sizes = _exchange_sizes(send_sizes)
+            send_np, recv_np = _host_sizes(send_sizes, recv_sizes)
+            out = _slot_a2a(in_data, send_np, recv_np, group_size, zero_fill)
         if locality_aware:
             reordered, reorder_indices = _locality_tail(recv_sizes, group_size)
             return [out, reordered, reorder_indices]
@@ -235,11 +264,30 @@ def batched_group_asymmetry_all_to_all(in_datas: List[torch.Tensor], send_sizes:
 
 def size_known_group_asymmetry_all_to_all(in_data: torch.Tensor, send_sizes: torch.Tensor,
                                           recv_sizes: torch.Tensor) -> torch.Tensor:
+    """The way back of ``group_asymmetry_all_to_all``: ``send_sizes`` is what that call
+    returned as received sizes.  Handed that very tensor, the rows travel over peer memory
+    (it names the exchange whose size matrix every rank kept); rows beyond a slot's size come
+    back as zeros, as in the reference (src/backend/torch/distributed.cc:523)."""
     _check_cuda(in_data, "in_data")
     _, W = _world()
-    send_np, recv_np = _host_sizes(send_sizes, recv_sizes)
+    group_size = send_sizes.numel() // W
     with torch.cuda.device(in_data.device):
-        return _slot_a2a(in_data, send_np, recv_np, send_sizes.numel() // W, True)
+        x = _contig(in_data)
+        n = W * group_size
+        tag = getattr(send_sizes, _TAG, None)
+        if tag is not None and tag[1] == group_size and x.size(0) and x.size(0) % n == 0 \
+                and _p2p_usable(x, W, group_size):
+            arena = p2p.arena()
+            x = arena.safe_source(x)
+            try:
+                ptr, rows = arena.sparse_backward(tag[0], group_size, _row_bytes(x),
+                                                  x.size(0) // n, x, p2p.SLOTS_BACK, True)
+                return _landed(arena, ptr, rows, x)
+            except _lib.BrtError as exc:
+                if exc.status != 4:  # BRT_ERR_UNSUPPORTED is the same verdict on every rank
+                    raise
+        send_np, recv_np = _host_sizes(send_sizes, recv_sizes)
+        return _slot_a2a(x, send_np, recv_np, group_size, True)
 
 
 def batched_size_known_group_asymmetry_all_to_all(in_datas: List[torch.Tensor],

@@ -24,7 +24,7 @@ _ALIASES = (
     "router.gather", "router.utils", "router.protocol", "router.protocol.base",
     "router.protocol.topk", "router.protocol.threshold", "router.protocol.switch",
     "router.protocol.swin_moe", "router.fabric", "router.fabric.base", "router.fabric.generic",
-    "router.fabric.fused", "router.fabric.distributed", "runtime", "runtime.grid_tensor",
+    "router.fabric.fused", "router.fabric.distributed", "router.fabric.distributed_slots", "runtime", "runtime.grid_tensor",
     "runtime.annotate", "runtime.registry", "runtime.distributed", "runtime.log",
     "runtime.placement",
 )

@@ -71,7 +71,7 @@ SIGNATURES = {
     "brt_p2p_free": (_int, [_vp]),
     "brt_p2p_push": (_int, [_vp, _int, _vp, _vp, _vp, _int, _int, _u64, _vp, _vp, _vp]),
     "brt_p2p_post": (_int, [_vp, _int, _int, _int, _u64, _vp, _vp, _vp]),
-    "brt_p2p_land": (_int, [_vp, _vp, _vp, _int, _int, _int, _int, _i64, _i64, _i64, _vp, _u64,
+    "brt_p2p_land": (_int, [_vp, _vp, _vp, _int, _int, _int, _int, _int, _i64, _i64, _i64, _vp, _u64,
                             _vp, _vp, _vp, _vp, _vp, _vp, _u64, _vp]),
     "brt_p2p_wait": (_int, [_vp, _int, _int, _u64, _vp, _vp, _u64, _vp]),
     "brt_p2p_control_bytes": (_sz, []),
@@ -81,9 +81,11 @@ SIGNATURES = {
     "brt_p2p_ctx_status": (_int, [_vp]),
     "brt_p2p_ctx_reset_status": (_int, [_vp]),
     "brt_p2p_ctx_exchanges": (_u64, [_vp]),
-    "brt_p2p_sparse_forward_begin": (_int, [_vp, _vp, _vp, _int, _i64, _i64, _vp, _vp, _int]),
+    "brt_p2p_sparse_forward_begin": (_int, [_vp, _vp, _vp, _int, _i64, _i64, _int, _vp, _vp,
+                                            _int]),
     "brt_p2p_sparse_forward_sizes": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp]),
-    "brt_p2p_sparse_backward": (_int, [_vp, _u64, _int, _i64, _i64, _vp, _vp, _int, _vp, _vp]),
+    "brt_p2p_sparse_backward": (_int, [_vp, _u64, _int, _i64, _i64, _int, _int, _vp, _vp, _int,
+                                       _vp, _vp]),
 }
 
 

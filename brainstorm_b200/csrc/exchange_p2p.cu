@@ -163,13 +163,20 @@ p2p_push_kernel(const char* __restrict__ src, const __grid_constant__ CopyList l
 //                 (expert j, source s) start at sum_{j' < j} sum_{s'} S[s'][i*G+j'] +
 //                 sum_{s' < s} S[s'][i*G+j].
 // With stride_rows != 0 buckets are stride_rows apart instead of back to back.
-// forward != 0: my rows are rank-major and land expert-major at their destinations;
-// forward == 0: my rows are expert-major and land rank-major at their owners.
+// layout 1 (sparse forward): my rows are rank-major and land expert-major at their destinations;
+// layout 0 (sparse inverse): my rows are expert-major and land rank-major at their owners;
+// layout 2 (slots): the padded-slot exchange, an involution: my slot (i, j) lands in rank i's
+//          slot (me, j); rows per slot from S[me][i*G+j], stride_rows = the slot size;
+// layout 3 (slots back): the same move with the sizes this rank RECEIVED in the slot exchange
+//          the matrix belongs to, S[i][me*G+j].
+// zero_tails (slot layouts): this rank also zeroes, in its own landing half, the rows of every
+// slot beyond what the slot receives.
 struct LandArgs {
   int world_size;
   int my_rank;
   int group_size;
-  int forward;
+  int layout;
+  int zero_tails;
   long long grain;        // bytes per row, multiple of 16
   long long stride_rows;  // 0: packed
   long long half_bytes;   // capacity of a landing half
@@ -248,7 +255,24 @@ p2p_land_kernel(const char* __restrict__ src, const __grid_constant__ LandArgs a
     return v > 0 ? v : 0;
   };
   bool fits = true;
-  if (go && a.forward) {
+  if (go && a.layout >= 2) {
+    // slots: position p == global bucket b = i * G + j, fixed slot size
+    for (int b = tid; b < n; b += kThreads) {
+      const int i = b / G, j = b - i * G;
+      if (a.keep != nullptr && blockIdx.x == 0)
+        for (int s = 0; s < W; s++) a.keep[s * n + b] = __ldcg(S + s * n + b);
+      int v = a.layout == 2 ? rows_of(me, b) : rows_of(i, me * G + j);
+      if (v > a.stride_rows) v = (int)a.stride_rows;
+      s_rows[b] = v;
+      s_src[b] = (int)((long long)b * a.stride_rows);
+      s_dst[b] = (int)((long long)(me * G + j) * a.stride_rows);
+      // rows slot b of MY half receives (for the tails): from rank i, its slot (me, j)
+      int got = a.layout == 2 ? rows_of(i, me * G + j) : rows_of(me, b);
+      if (got > a.stride_rows) got = (int)a.stride_rows;
+      s_aux[b] = got;
+    }
+    fits = (long long)n * a.stride_rows * a.grain <= a.half_bytes;
+  } else if (go && a.layout == 1) {
     // position p == global bucket b = i * G + j
     for (int b = tid; b < n; b += kThreads) {
       int column = 0, below = 0;
@@ -334,12 +358,38 @@ p2p_land_kernel(const char* __restrict__ src, const __grid_constant__ LandArgs a
       if (s_first[mid] <= chunk) lo = mid; else hi = mid - 1;
     }
     const int p = lo;
-    const int dest = a.forward ? p / G : p % W;
+    const int dest = a.layout == 0 ? p % W : p / G;
     const long long at = (chunk - s_first[p]) * kChunkBytes;
     long long bytes = (long long)s_rows[p] * a.grain - at;
     if (bytes > kChunkBytes) bytes = kChunkBytes;
     copy_chunk(src + (long long)s_src[p] * a.grain + at,
                a.land[dest] + (long long)s_dst[p] * a.grain + at, bytes);
+  }
+
+  if (move && a.layout >= 2 && a.zero_tails) {
+    // the rows of my own slots that nobody writes (the peers only write rows below s_aux[b])
+    __syncthreads();
+    for (int b = tid; b < n; b += kThreads) {
+      const long long bytes = (a.stride_rows - s_aux[b]) * a.grain;
+      s_first[b] = (int)((bytes + kChunkBytes - 1) / kChunkBytes);
+    }
+    block_exclusive_scan(s_first, n, s_warp);
+    const long long tail_chunks = s_first[n];
+    for (long long chunk = blockIdx.x; chunk < tail_chunks; chunk += gridDim.x) {
+      int lo = 0, hi = n - 1;
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (s_first[mid] <= chunk) lo = mid; else hi = mid - 1;
+      }
+      const int b = lo;
+      const long long at = (chunk - s_first[b]) * kChunkBytes;
+      long long bytes = (a.stride_rows - s_aux[b]) * a.grain - at;
+      if (bytes > kChunkBytes) bytes = kChunkBytes;
+      uint4* d = reinterpret_cast<uint4*>(a.land[me] +
+                                          ((long long)b * a.stride_rows + s_aux[b]) * a.grain + at);
+      const int vecs = (int)(bytes >> 4);
+      for (int v = tid; v < vecs; v += kThreads) d[v] = make_uint4(0u, 0u, 0u, 0u);
+    }
   }
 
   // arrive: the last CTA to finish raises my flag at every rank, unless a wait ran out
@@ -498,8 +548,9 @@ BRT_API int brt_p2p_push(const void* src, int copy_count, const int64_t* src_off
 }
 
 BRT_API int brt_p2p_land(const void* rows, const int32_t* size_matrix, int32_t* keep_matrix,
-                         int world_size, int group_size, int my_rank, int forward,
-                         int64_t grain_bytes, int64_t stride_rows, int64_t half_bytes,
+                         int world_size, int group_size, int my_rank, int layout,
+                         int zero_tails, int64_t grain_bytes, int64_t stride_rows,
+                         int64_t half_bytes,
                          void* const* landing_ptrs, uint64_t epoch, const void* my_ready_flags,
                          void* const* peer_arrive_flag_arrays, void* my_done_counter,
                          void* my_abort_word, void* status_word, void* host_status_word,
@@ -517,13 +568,17 @@ BRT_API int brt_p2p_land(const void* rows, const int32_t* size_matrix, int32_t* 
   BRT_REQUIRE(grain_bytes > 0 && grain_bytes % 16 == 0 && aligned_to(rows, 16),
               "rows must be 16-byte multiples and the source 16-byte aligned");
   BRT_REQUIRE(stride_rows >= 0 && half_bytes >= 0, "negative stride or half size");
+  BRT_REQUIRE(layout >= BRT_P2P_SPARSE_INVERSE && layout <= BRT_P2P_SLOTS_BACK,
+              "unknown layout %d", layout);
+  BRT_REQUIRE(layout < BRT_P2P_SLOTS || stride_rows > 0, "the slot layouts need a slot size");
   BRT_REQUIRE(stride_rows * (int64_t)world_size * group_size <= 0x7fffffffLL,
               "more than 2^31-1 rows per rank");
   LandArgs a;
   a.world_size = world_size;
   a.my_rank = my_rank;
   a.group_size = group_size;
-  a.forward = forward != 0;
+  a.layout = layout;
+  a.zero_tails = zero_tails != 0;
   a.grain = grain_bytes;
   a.stride_rows = stride_rows;
   a.half_bytes = half_bytes;
@@ -542,7 +597,9 @@ BRT_API int brt_p2p_land(const void* rows, const int32_t* size_matrix, int32_t* 
   a.abort_word = static_cast<unsigned int*>(my_abort_word);
   a.status.device_word = static_cast<int*>(status_word);
   a.status.host_word = static_cast<int*>(host_status_word);
-  const KernelTimer timer(forward ? "p2p_land_forward_kernel" : "p2p_land_backward_kernel",
+  const KernelTimer timer(layout == BRT_P2P_SPARSE_INVERSE ? "p2p_land_backward_kernel"
+                          : layout == BRT_P2P_SPARSE_FORWARD ? "p2p_land_forward_kernel"
+                                                             : "p2p_land_slots_kernel",
                           static_cast<cudaStream_t>(stream));
   p2p_land_kernel<<<(unsigned)(sm_count() * push_ctas_per_sm()), kThreads, 0,
                     static_cast<cudaStream_t>(stream)>>>(static_cast<const char*>(rows), a),

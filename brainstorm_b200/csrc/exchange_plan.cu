@@ -64,7 +64,7 @@ struct brt_p2p_ctx {
   brt_b200::KeptMatrix kept[brt_b200::kKept];
   // forward exchange whose sizes have not been read yet
   uint64_t pending = 0;
-  int group = 0;
+  int group = 0, layout = 0;
   int64_t grain = 0, stride = 0;
 };
 
@@ -84,10 +84,12 @@ int check_alive(const brt_p2p_ctx* c) {
 }
 
 int land(brt_p2p_ctx* c, const void* rows, const int32_t* matrix, int32_t* keep, int group,
-         int forward, int64_t grain, int64_t stride, uint64_t exchange, void* stream) {
+         int layout, int zero_tails, int64_t grain, int64_t stride, uint64_t exchange,
+         void* stream) {
   void* halves[kMaxRanks];
   for (int r = 0; r < c->world; r++) halves[r] = half_of(c, r, exchange);
-  return brt_p2p_land(rows, matrix, keep, c->world, group, c->rank, forward, grain, stride,
+  return brt_p2p_land(rows, matrix, keep, c->world, group, c->rank, layout, zero_tails, grain,
+                      stride,
                       (int64_t)c->half_bytes, halves, exchange, c->base + kReadyOffset,
                       c->arrive_flags, c->base + kCounterOffset, c->base + kAbortOffset,
                       c->base + kStatusOffset, c->host_status_dev, c->wait_ns, stream);
@@ -177,10 +179,12 @@ BRT_API uint64_t brt_p2p_ctx_exchanges(const brt_p2p_ctx* c) { return c ? c->exc
 
 BRT_API int brt_p2p_sparse_forward_begin(brt_p2p_ctx* c, const void* rows, const int32_t* sizes,
                                          int group_size, int64_t grain_bytes,
-                                         int64_t stride_rows, void* main_stream,
+                                         int64_t stride_rows, int layout, void* main_stream,
                                          void* side_stream, int stages) {
   clear_error();
   BRT_REQUIRE(c != nullptr && sizes != nullptr, "null context or sizes");
+  BRT_REQUIRE(layout == BRT_P2P_SPARSE_FORWARD || (layout == BRT_P2P_SLOTS && stride_rows > 0),
+              "layout must be the sparse forward one or slots with a slot size");
   const int n = c->world * group_size;
   BRT_REQUIRE(group_size >= 1 && grain_bytes > 0 && grain_bytes % 16 == 0 && stride_rows >= 0,
               "bad bucket geometry");
@@ -193,6 +197,7 @@ BRT_API int brt_p2p_sparse_forward_begin(brt_p2p_ctx* c, const void* rows, const
     c->exchanges++;
     c->pending = c->exchanges;
     c->group = group_size;
+    c->layout = layout;
     c->grain = grain_bytes;
     c->stride = stride_rows;
     const size_t board = kBoardOffset + 4 * (c->exchanges & 1) * kBoardInts;
@@ -207,7 +212,7 @@ BRT_API int brt_p2p_sparse_forward_begin(brt_p2p_ctx* c, const void* rows, const
     }
   }
   BRT_REQUIRE(c->pending != 0 && c->group == group_size && c->grain == grain_bytes &&
-                  c->stride == stride_rows,
+                  c->stride == stride_rows && c->layout == layout,
               "stages of one exchange must be issued with the same geometry");
   const uint64_t x = c->pending;
   const size_t board = kBoardOffset + 4 * (x & 1) * kBoardInts;
@@ -226,7 +231,7 @@ BRT_API int brt_p2p_sparse_forward_begin(brt_p2p_ctx* c, const void* rows, const
   if (stages & BRT_P2P_STAGE_PUSH) {
     int32_t* keep = reinterpret_cast<int32_t*>(c->base + kKeptOffset) + (x % kKept) * kBoardInts;
     if (int rc = land(c, rows, reinterpret_cast<const int32_t*>(c->base + board), keep,
-                      group_size, 1, grain_bytes, stride_rows, x, main_stream))
+                      group_size, layout, 0, grain_bytes, stride_rows, x, main_stream))
       return rc;
   }
   if (stages & BRT_P2P_STAGE_WAIT)
@@ -272,11 +277,13 @@ BRT_API int brt_p2p_sparse_forward_sizes(brt_p2p_ctx* c, void* side_stream,
 }
 
 BRT_API int brt_p2p_sparse_backward(brt_p2p_ctx* c, uint64_t exchange_id, int group_size,
-                                    int64_t grain_bytes, int64_t stride_rows, const void* rows,
-                                    void* main_stream, int stages, void** out_data,
-                                    int64_t* out_rows) {
+                                    int64_t grain_bytes, int64_t stride_rows, int layout,
+                                    int zero_tails, const void* rows, void* main_stream,
+                                    int stages, void** out_data, int64_t* out_rows) {
   clear_error();
   BRT_REQUIRE(c != nullptr && out_data != nullptr && out_rows != nullptr, "null pointers");
+  BRT_REQUIRE(layout == BRT_P2P_SPARSE_INVERSE || (layout == BRT_P2P_SLOTS_BACK && stride_rows > 0),
+              "layout must be the sparse inverse one or slots-back with a slot size");
   BRT_REQUIRE(group_size >= 1 && grain_bytes > 0 && grain_bytes % 16 == 0 && stride_rows >= 0,
               "bad bucket geometry");
   if (stages == 0) stages = BRT_P2P_STAGE_ALL;
@@ -308,7 +315,8 @@ BRT_API int brt_p2p_sparse_backward(brt_p2p_ctx* c, uint64_t exchange_id, int gr
   if (stages & BRT_P2P_STAGE_PUSH) {
     const int32_t* kept =
         reinterpret_cast<const int32_t*>(c->base + kKeptOffset) + (exchange_id % kKept) * kBoardInts;
-    if (int rc = land(c, rows, kept, nullptr, G, 0, grain_bytes, stride_rows, x, main_stream))
+    if (int rc = land(c, rows, kept, nullptr, G, layout, zero_tails, grain_bytes, stride_rows, x,
+                      main_stream))
       return rc;
   }
   if (stages & BRT_P2P_STAGE_WAIT)

@@ -23,6 +23,7 @@ from .. import _lib
 
 STATUS_OFFSET = 1024      # status word of the bounded waits inside the control block
 ZERO_COPY = os.environ.get("BRT_P2P_ZERO_COPY", "1") != "0"
+SPARSE_INVERSE, SPARSE_FORWARD, SLOTS, SLOTS_BACK = 0, 1, 2, 3   # layouts of an exchange
 MAX_BUCKETS = 1024        # world * group of one exchange (device planner)
 BOARD_INTS = 7936         # world * world * group: the size matrix must fit a board
 
@@ -87,13 +88,14 @@ class PeerArena:
 
     # ---- the two exchanges -----------------------------------------------------------------
     def sparse_forward(self, rows: torch.Tensor, sizes: torch.Tensor, group_size: int,
-                       grain: int, stride_rows: int):
-        """Enqueue a forward sparse exchange on the current stream and wait for its size
-        matrix only.  Returns (matrix [world, world * group] int32, my output rows, whether it
-        fits the landing halves, device address of my output, exchange id)."""
+                       grain: int, stride_rows: int, layout: int = SPARSE_FORWARD):
+        """Enqueue a forward exchange (packed buckets, or padded slots with ``layout=SLOTS``)
+        on the current stream and wait for its size matrix only.  Returns (matrix
+        [world, world * group] int32, my output rows, whether it fits the landing halves,
+        device address of my output, exchange id)."""
         main = torch.cuda.current_stream().cuda_stream
         _lib.call("brt_p2p_sparse_forward_begin", self.ctx, rows.data_ptr(), sizes.data_ptr(),
-                  group_size, grain, stride_rows, main, self.side.cuda_stream, 0)
+                  group_size, grain, stride_rows, layout, main, self.side.cuda_stream, 0)
         matrix = ctypes.POINTER(ctypes.c_int32)()
         n_rows, fits = ctypes.c_int64(), ctypes.c_int()
         out, xid = ctypes.c_void_p(), ctypes.c_uint64()
@@ -104,14 +106,16 @@ class PeerArena:
         return S, int(n_rows.value), bool(fits.value), int(out.value), int(xid.value)
 
     def sparse_backward(self, exchange_id: int, group_size: int, grain: int, stride_rows: int,
-                        rows: torch.Tensor):
+                        rows: torch.Tensor, layout: int = SPARSE_INVERSE,
+                        zero_tails: bool = False):
         """Enqueue the inverse of forward exchange ``exchange_id`` on the current stream.
         Returns (device address of my output, its rows).  Raises ``_lib.BrtError`` with status
         BRT_ERR_UNSUPPORTED (on every rank alike) when the exchange cannot take this path."""
         out, n_rows = ctypes.c_void_p(), ctypes.c_int64()
         _lib.call("brt_p2p_sparse_backward", self.ctx, exchange_id, group_size, grain,
-                  stride_rows, rows.data_ptr(), torch.cuda.current_stream().cuda_stream, 0,
-                  ctypes.byref(out), ctypes.byref(n_rows))
+                  stride_rows, layout, int(zero_tails), rows.data_ptr(),
+                  torch.cuda.current_stream().cuda_stream, 0, ctypes.byref(out),
+                  ctypes.byref(n_rows))
         return int(out.value), int(n_rows.value)
 
     def status(self) -> int:

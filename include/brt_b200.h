@@ -424,11 +424,17 @@ BRT_API int brt_group_sparse_all_to_all(const void* send_buffer, void* recv_buff
  *                 copies every bucket this rank holds straight to its row offset in the
  *                 destination's OUTPUT layout inside landing_ptrs[destination] (peers' arenas
  *                 and the local one), then stores `epoch` into slot `my_rank` of every rank's
- *                 arrival flag array.  forward != 0: this rank's rows are ordered
- *                 [destination rank][its local expert] and land ordered
- *                 [local expert][source rank] (GroupSparseAllToAllForward); forward == 0: the
- *                 inverse (GroupSparseAllToAllBackward).  stride_rows != 0: buckets sit
- *                 stride_rows rows apart on both sides.  If some rank's landed rows exceed
+ *                 arrival flag array.  layout BRT_P2P_SPARSE_FORWARD: this rank's rows are
+ *                 ordered [destination rank][its local expert] and land ordered
+ *                 [local expert][source rank] (GroupSparseAllToAllForward);
+ *                 BRT_P2P_SPARSE_INVERSE: the inverse (GroupSparseAllToAllBackward);
+ *                 stride_rows != 0: buckets sit stride_rows rows apart on both sides.
+ *                 BRT_P2P_SLOTS: the padded-slot exchange (GroupAsymmetryAllToAll,
+ *                 collective.cc:108-140): slot (i, j) of stride_rows rows sends its first
+ *                 S[me][i*G+j] rows into slot (me, j) of rank i; BRT_P2P_SLOTS_BACK: the same
+ *                 move with the sizes this rank received in the slot exchange the matrix
+ *                 belongs to.  zero_tails (slot layouts): the rows of this rank's own slots
+ *                 beyond what they receive are zeroed (the reference's zeros_like outputs).  If some rank's landed rows exceed
  *                 half_bytes nothing is copied (every rank takes the same decision from the
  *                 same matrix) but the flags are still raised.  `keep_matrix` (may be null)
  *                 receives a copy of the matrix.  At most 1024 buckets.  When the wait runs out
@@ -442,6 +448,11 @@ BRT_API int brt_group_sparse_all_to_all(const void* send_buffer, void* recv_buff
  *                 `wait_limit_ns`: on expiry it reports like brt_p2p_land and returns; it
  *                 never blocks the GPU indefinitely.
  */
+#define BRT_P2P_SPARSE_INVERSE 0
+#define BRT_P2P_SPARSE_FORWARD 1
+#define BRT_P2P_SLOTS 2
+#define BRT_P2P_SLOTS_BACK 3
+
 BRT_API int brt_p2p_alloc(size_t bytes, void** dev_ptr, void* ipc_handle_out);
 BRT_API int brt_p2p_open(const void* ipc_handle, void** peer_ptr);
 BRT_API int brt_p2p_close(void* peer_ptr);
@@ -454,8 +465,9 @@ BRT_API int brt_p2p_post(const int32_t* values, int n, int world_size, int my_ra
                          uint64_t epoch, void* const* peer_boards, void* const* peer_flag_arrays,
                          void* stream);
 BRT_API int brt_p2p_land(const void* rows, const int32_t* size_matrix, int32_t* keep_matrix,
-                         int world_size, int group_size, int my_rank, int forward,
-                         int64_t grain_bytes, int64_t stride_rows, int64_t half_bytes,
+                         int world_size, int group_size, int my_rank, int layout,
+                         int zero_tails, int64_t grain_bytes, int64_t stride_rows,
+                         int64_t half_bytes,
                          void* const* landing_ptrs, uint64_t epoch, const void* my_ready_flags,
                          void* const* peer_arrive_flag_arrays, void* my_done_counter,
                          void* my_abort_word, void* status_word, void* host_status_word,
@@ -483,6 +495,11 @@ BRT_API int brt_p2p_wait(const void* my_flag_array, int world_size, int skip_ran
  * job always passes 0.  Separate stages exist so that several ranks can be driven from ONE
  * stream of one GPU (tests): all posts first, then all landings, then all waits, so that no
  * kernel ever waits for a kernel enqueued behind it.
+ *
+ * `layout` is BRT_P2P_SPARSE_FORWARD / BRT_P2P_SPARSE_INVERSE for the packed exchange and
+ * BRT_P2P_SLOTS / BRT_P2P_SLOTS_BACK for the padded-slot one (asymmetry_all_to_all and
+ * size_known_group_asymmetry_all_to_all, src/backend/torch/distributed.cc:339-753), whose
+ * buffers are world_size * group_size slots of `stride_rows` rows on both sides.
  *
  * brt_p2p_sparse_forward_begin   group_sparse_all_to_all, part 1 (collective.cc:142-185):
  *                 post of `sizes` (DEVICE vector of world_size * group_size row counts), the
@@ -523,15 +540,15 @@ BRT_API int brt_p2p_ctx_reset_status(brt_p2p_ctx* ctx);
 BRT_API uint64_t brt_p2p_ctx_exchanges(const brt_p2p_ctx* ctx);
 BRT_API int brt_p2p_sparse_forward_begin(brt_p2p_ctx* ctx, const void* rows,
                                          const int32_t* sizes, int group_size,
-                                         int64_t grain_bytes, int64_t stride_rows,
+                                         int64_t grain_bytes, int64_t stride_rows, int layout,
                                          void* main_stream, void* side_stream, int stages);
 BRT_API int brt_p2p_sparse_forward_sizes(brt_p2p_ctx* ctx, void* side_stream,
                                          const int32_t** size_matrix, int64_t* out_rows,
                                          int* fits, void** out_data, uint64_t* exchange_id);
 BRT_API int brt_p2p_sparse_backward(brt_p2p_ctx* ctx, uint64_t exchange_id, int group_size,
-                                    int64_t grain_bytes, int64_t stride_rows, const void* rows,
-                                    void* main_stream, int stages, void** out_data,
-                                    int64_t* out_rows);
+                                    int64_t grain_bytes, int64_t stride_rows, int layout,
+                                    int zero_tails, const void* rows, void* main_stream,
+                                    int stages, void** out_data, int64_t* out_rows);
 
 #ifdef __cplusplus
 }

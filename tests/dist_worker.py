@@ -153,6 +153,32 @@ def main():
     ep = GatherRouter("distributed_fused_combine", {"transform": True})(routed, None, score)
     assert torch.equal(ep.data, local.data), f"rank {rank}: expert-parallel route differs"
 
+    # ---- padded-slot fabrics: plain, and with the locality matching (the cells of rank
+    # reorder[k] come out on rank k)
+    cap = 2 * T // E * 3
+    fkw = {"max_path_load": cap}
+    local_p = GatherRouter("fused_combine", {"transform": True, "max_path_padding": True})(
+        ScatterRouter(protocol_type="topk", fabric_type="fused_dispatch",
+                      protocol_kwargs={"top_k": 2},
+                      fabric_kwargs={"max_path_padding": True, "max_path_load": cap})(
+            Annotator([0])(x), score), None, score)
+    slots = GatherRouter("distributed_slot_combine", {"transform": True})(
+        ScatterRouter(protocol_type="topk", fabric_type="distributed_slot_dispatch",
+                      protocol_kwargs={"top_k": 2}, fabric_kwargs=fkw)(Annotator([0])(x), score),
+        None, score)
+    assert torch.equal(slots.data, local_p.data), f"rank {rank}: padded-slot route differs"
+    matched = GatherRouter("distributed_slot_combine",
+                           {"transform": True, "locality_aware": True})(
+        ScatterRouter(protocol_type="topk", fabric_type="distributed_slot_dispatch",
+                      protocol_kwargs={"top_k": 2},
+                      fabric_kwargs=dict(fkw, locality_aware=True))(Annotator([0])(x), score),
+        None, score)
+    reorder = brt_dist.get_reorder_indices()
+    everyone = [torch.empty_like(local_p.data) for _ in range(W)]
+    dist.all_gather(everyone, local_p.data.contiguous())
+    assert torch.equal(matched.data, everyone[int(reorder[rank])]), \
+        f"rank {rank}: locality-matched route differs"
+
     p2p.check_status()
     dist.barrier()
     if rank == 0:

@@ -60,13 +60,13 @@ class Ranks:
         flat = torch.as_tensor(Raw(), device="cuda")[:nbytes]
         return flat.view(dtype).view(rows, cols)
 
-    def forward(self, xs, sizes, group, stride=0):
+    def forward(self, xs, sizes, group, stride=0, layout=1):
         st = torch.cuda.current_stream().cuda_stream
         grain = xs[0].size(1) * xs[0].element_size()
         for stage in (POST, SIZES, PUSH, WAIT):
             for r in range(self.world):
                 _lib.call("brt_p2p_sparse_forward_begin", self.ctxs[r], xs[r].data_ptr(),
-                          sizes[r].data_ptr(), group, grain, stride, st, st, stage)
+                          sizes[r].data_ptr(), group, grain, stride, layout, st, st, stage)
         outs, ids, fit = [], [], []
         for r in range(self.world):
             m = ctypes.POINTER(ctypes.c_int32)()
@@ -81,7 +81,7 @@ class Ranks:
             fit.append(bool(fits.value))
         return outs, ids, fit
 
-    def backward(self, ids, xs, group, stride=0):
+    def backward(self, ids, xs, group, stride=0, layout=0, zero_tails=0):
         st = torch.cuda.current_stream().cuda_stream
         grain = xs[0].size(1) * xs[0].element_size()
         res = [None] * self.world
@@ -89,7 +89,8 @@ class Ranks:
             for r in range(self.world):
                 out, n_rows = ctypes.c_void_p(), ctypes.c_int64()
                 _lib.call("brt_p2p_sparse_backward", self.ctxs[r], ids[r], group, grain, stride,
-                          xs[r].data_ptr(), st, stage, ctypes.byref(out), ctypes.byref(n_rows))
+                          layout, zero_tails, xs[r].data_ptr(), st, stage, ctypes.byref(out),
+                          ctypes.byref(n_rows))
                 res[r] = (out.value, n_rows.value)
         return res
 
@@ -160,6 +161,46 @@ def test_forward_and_back(world, group, cols, hi, stride):
         ranks.close()
 
 
+@pytest.mark.parametrize("world,group,cols,slot", [(2, 1, 4, 9), (4, 2, 8, 12), (8, 4, 4, 6),
+                                                   (3, 5, 16, 7)])
+def test_padded_slot_exchange_and_back(world, group, cols, slot):
+    """group_asymmetry_all_to_all and its size-known inverse (src/distributed/collective.cc:
+    108-140): slot (i, j) of rank s lands in slot (s, j) of rank i; on the way back the rows
+    beyond a slot's size come back as zeros."""
+    dev = torch.device("cuda", 0)
+    n = world * group
+    rng = np.random.default_rng(40 + world + group)
+    xs_np = [rng.standard_normal((slot * n, cols)).astype(np.float32) for _ in range(world)]
+    sizes_np = [rng.integers(0, slot + 1, size=n).astype(np.int32) for _ in range(world)]
+    sim = oracle.sim_group_asymmetry_all_to_all(xs_np, sizes_np)
+    ranks = Ranks(world)
+    try:
+        xs = [torch.from_numpy(x).to(dev) for x in xs_np]
+        sizes = [torch.from_numpy(s).to(dev) for s in sizes_np]
+        for repeat in range(2):
+            outs, ids, fit = ranks.forward(xs, sizes, group, slot, layout=2)
+            assert all(fit)
+            landed = []
+            for r in range(world):
+                ptr, rows, _ = outs[r]
+                assert rows == slot * n
+                got = ranks.rows_at(ptr, rows, cols)
+                landed.append(got)
+                g = got.cpu().numpy()
+                for b, cnt in enumerate(sim[r][1]):
+                    assert np.array_equal(g[b * slot:b * slot + cnt],
+                                          sim[r][0][b * slot:b * slot + cnt]), (r, b)
+            back = ranks.backward(ids, landed, group, slot, layout=3, zero_tails=1)
+            for r in range(world):
+                g = ranks.rows_at(back[r][0], back[r][1], cols).cpu().numpy()
+                for b, cnt in enumerate(sizes_np[r]):
+                    assert np.array_equal(g[b * slot:b * slot + cnt],
+                                          xs_np[r][b * slot:b * slot + cnt]), (r, b)
+                    assert not g[b * slot + cnt:(b + 1) * slot].any(), (r, b)
+    finally:
+        ranks.close()
+
+
 def test_nested_forwards_then_inverses():
     """Two forward exchanges whose inverses come in reverse order (layer 1, layer 2, back 2,
     back 1), with one rank sending the same sizes in both: each inverse must use the matrix
@@ -216,7 +257,7 @@ def test_wait_runs_out_and_is_reported():
         sizes = torch.tensor([3, 5], dtype=torch.int32, device=dev)
         st = torch.cuda.current_stream().cuda_stream
         _lib.call("brt_p2p_sparse_forward_begin", ranks.ctxs[0], x.data_ptr(), sizes.data_ptr(),
-                  1, 16, 0, st, st, 0)
+                  1, 16, 0, 1, st, st, 0)
         m = ctypes.POINTER(ctypes.c_int32)()
         n_rows, fits = ctypes.c_int64(), ctypes.c_int()
         out, xid = ctypes.c_void_p(), ctypes.c_uint64()
@@ -229,7 +270,7 @@ def test_wait_runs_out_and_is_reported():
         assert _lib.query("brt_p2p_ctx_status", ranks.ctxs[0]) == 7
         with pytest.raises(_lib.BrtError):  # refused until the status is cleared
             _lib.call("brt_p2p_sparse_forward_begin", ranks.ctxs[0], x.data_ptr(),
-                      sizes.data_ptr(), 1, 16, 0, st, st, 0)
+                      sizes.data_ptr(), 1, 16, 0, 1, st, st, 0)
         _lib.call("brt_p2p_ctx_reset_status", ranks.ctxs[0])
         assert _lib.query("brt_p2p_ctx_status", ranks.ctxs[0]) == 0
         # nothing landed in rank 1's arena and the device still answers

@@ -155,6 +155,34 @@ def test_fused_topk_round_trip(api):
     assert torch.equal(out_d.data, out.data)
 
 
+def test_slot_fabrics_without_a_process_group(api):
+    """Without torch.distributed the padded-slot fabrics are the local fused fabrics."""
+    Annotator, ScatterRouter, GatherRouter = api
+    torch.manual_seed(2)
+    T, E, cap = 600, 8, 200
+    x = torch.randn(T, 48, device="cuda")
+    score = torch.softmax(torch.randn(T, E, device="cuda"), dim=1)
+    local = GatherRouter("fused_combine", {"transform": True, "max_path_padding": True})(
+        ScatterRouter(protocol_type="topk", fabric_type="fused_dispatch",
+                      protocol_kwargs={"top_k": 2},
+                      fabric_kwargs={"max_path_padding": True, "max_path_load": cap})(
+            Annotator([0])(x), score), None, score)
+    routed = ScatterRouter(protocol_type="topk", fabric_type="distributed_slot_dispatch",
+                           protocol_kwargs={"top_k": 2},
+                           fabric_kwargs={"max_path_load": cap})(Annotator([0])(x), score)
+    assert routed.shape == (E * cap, 48)
+    out = GatherRouter("distributed_slot_combine", {"transform": True})(routed, None, score)
+    assert torch.equal(out.data, local.data)
+    # the placement fabrics are the packed-bucket ones under another name
+    packed = GatherRouter("distributed_placement_combine", {"transform": True})(
+        ScatterRouter(protocol_type="topk", fabric_type="distributed_placement_dispatch",
+                      protocol_kwargs={"top_k": 2})(Annotator([0])(x), score), None, score)
+    ref = GatherRouter("fused_combine", {"transform": True})(
+        ScatterRouter(protocol_type="topk", fabric_type="fused_dispatch",
+                      protocol_kwargs={"top_k": 2})(Annotator([0])(x), score), None, score)
+    assert torch.equal(packed.data, ref.data)
+
+
 def test_swin_moe_scatter(api):
     from brainstorm_b200.router import SwinMoEScatterRouter
 
