@@ -494,6 +494,8 @@ def run_gpu(args):
                          if __import__("brainstorm_b200.runtime.p2p", fromlist=["arena"]).arena()
                          is not None else "nccl send/recv",
         }
+    if world == 1:
+        result["expert_gemm"] = measure_expert_gemm(wl, dev, loads, cap, peaks)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         result["cpu_baseline"] = cpu_baseline(wl, budget_s=args.cpu_seconds)
     if rank == 0:
@@ -741,6 +743,48 @@ def measure_gate(wl, dev, w, R, padded, caps):
                          + (", throttle, indices" if padded else ", indices"),
                          "gate_kernel": "route_scores(throttled seat indices)" if padded
                          else "route_scores(seat indices)"}}
+
+
+def measure_expert_gemm(wl, dev, idx_loads, cap, peaks):
+    """The expert side of the dispatched layout (not part of the routing step): a grouped
+    linear layer [d -> 4d] over the rows this workload dispatches, on the tensor cores, with
+    the per-expert loads staying on the device.  CUDA events, median of 7, against the measured
+    sustained bf16 GEMM rate of this pool's B200s."""
+    from brainstorm_b200._C import expert as X
+
+    w = wl["spec"]
+    if w["dtype"] != "bf16" or w["d"] % 128 != 0 or w["E"] > 1024:
+        return None
+    E, d = w["E"], w["d"]
+    loads = idx_loads
+    padded = cap > 0
+    L = cap * E if padded else int(loads.sum().item())
+    if L * 4 * d * 2 > 8e9:
+        return None
+    rows = torch.empty((L, d), dtype=torch.bfloat16, device=dev).normal_()
+    weights = torch.empty((E, 4 * d, d), dtype=torch.bfloat16, device=dev).normal_(0, d ** -0.5)
+    for _ in range(3):
+        X.grouped_expert_linear(rows, weights, loads, padded, cap, True)
+    X.check_status()
+    ts = []
+    for _ in range(7):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        X.grouped_expert_linear(rows, weights, loads, padded, cap, True)
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    ms = sorted(ts)[3]
+    kept = loads.clamp(max=cap) if padded else loads
+    flops = 2.0 * float(kept.sum().item()) * d * 4 * d
+    tf = flops / (ms * 1e-3) / 1e12
+    peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    return {"op": f"grouped expert linear {d} -> {4 * d} with ReLU over the dispatched rows "
+                  f"({int(kept.sum().item())} rows in {E} experts)",
+            "ms": round(ms, 4), "tflops": round(tf, 1), "peak_tflops": peak,
+            "peak_kind": "measured sustained cuBLAS bf16" if "bf16_tflops_sustained" in peaks
+                         else "fallback",
+            "frac": round(tf / peak, 4), "kernel": "expert_gemm_kernel (tcgen05.mma, TMA, TMEM)"}
 
 
 def measure_e2e(wl, dev, args, ScatterRouter, GatherRouter, distributed, world):

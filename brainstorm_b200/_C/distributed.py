@@ -396,6 +396,57 @@ def group_sparse_all_to_all(in_data: torch.Tensor, send_sizes: torch.Tensor,
     return [out, torch.from_numpy(recv_np.copy()), torch.from_numpy(send_np.copy())]
 
 
+def dispatch_group_sparse_all_to_all(in_data: torch.Tensor, route_indices: torch.Tensor,
+                                     loads: torch.Tensor, max_path_padding: bool = False,
+                                     max_path_load: int = 0):
+    """``dispatch_with_indices_and_loads`` (unweighted, 1-D) followed by
+    ``group_sparse_all_to_all``, as ONE kernel over peer memory: the sequence of the reference's
+    expert-parallel dispatch fabric (python/brt/router/fabric/distributed.py:35-97) without the
+    dispatched buffer in between — every kept copy of a cell is stored straight into the
+    destination rank's output.  Returns what ``group_sparse_all_to_all`` returns, or ``None``
+    when this call cannot take the fused route (no peer arena, rows that are not 16-byte
+    multiples, index tensors that did not come from this library's index ops); the caller then
+    runs the two ops.  The verdict depends on the program, not on the data, except for "the
+    rows do not fit the landing halves", which every rank sees alike: the op then runs the two
+    steps itself, with the sizes it already knows."""
+    from . import router as c_router
+
+    _check_cuda(in_data, "in_data")
+    _check_cuda(route_indices, "route_indices")
+    rank, W = _world()
+    E = route_indices.size(1)
+    counts = getattr(route_indices, c_router._DENSE, None)
+    if counts is None or E % W != 0 or in_data.dim() < 2 or in_data.size(0) == 0 or \
+            loads.numel() != E or not loads.is_cuda or route_indices.dtype != torch.int32 or \
+            not route_indices.is_contiguous() or (max_path_padding and not max_path_load):
+        return None
+    group_size = E // W
+    with torch.cuda.device(in_data.device):
+        x = _contig(in_data)
+        if not _p2p_usable(x, W, group_size):
+            return None
+        arena = p2p.arena()
+        stride = int(max_path_load) if max_path_padding else 0
+        x = arena.safe_source(x)
+        loads32 = loads.to(torch.int32).contiguous()
+        S, out_rows, fits, ptr, xid = arena.dispatch_forward(
+            x, route_indices, loads32, counts, group_size, _row_bytes(x), stride)
+        S3 = S.reshape(W, W, group_size)
+        send_np = np.ascontiguousarray(S3[rank].reshape(-1))
+        recv_np = np.ascontiguousarray(S3[:, rank, :].T.reshape(-1))
+        if fits:
+            out = _landed(arena, ptr, out_rows, x)
+        else:
+            (routed,) = c_router.dispatch_with_indices_and_loads(
+                x, route_indices, loads, None, False, None, max_path_padding, max_path_load)
+            rows = a2a_plan.total_rows(recv_np, stride)
+            out = _sparse_a2a(routed, send_np, recv_np, stride, rows, group_size, True)
+        recv_t, send_t = torch.from_numpy(recv_np), torch.from_numpy(send_np)
+        setattr(recv_t, _TAG, (xid, group_size))
+        setattr(send_t, _TAG, (xid, group_size))
+        return [out, recv_t, send_t]
+
+
 def size_known_group_sparse_all_to_all(in_data: torch.Tensor, send_sizes: torch.Tensor,
                                        recv_sizes: torch.Tensor,
                                        max_path_padding: bool = False) -> torch.Tensor:

@@ -51,6 +51,8 @@ SIGNATURES = {
         _int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _i32, _int, _int, _int, _vp]),
     "brt_sum_rows_scratch_bytes": (_sz, [_i64, _i64]),
     "brt_sum_rows_by_index": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
+    "brt_grouped_expert_gemm": (_int, [_vp, _vp, _vp, _vp, _int, _i64, _i32, _i64, _i64, _int,
+                                       _vp, _vp]),
     "brt_locality_reorder": (_int, [_vp, _int, _vp, _vp, _vp]),
     "brt_group_locality_reorder": (_int, [_vp, _int, _int, _vp, _vp, _vp]),
     "brt_nccl_get_unique_id": (_int, [_vp]),
@@ -83,6 +85,10 @@ SIGNATURES = {
     "brt_p2p_ctx_exchanges": (_u64, [_vp]),
     "brt_p2p_sparse_forward_begin": (_int, [_vp, _vp, _vp, _int, _i64, _i64, _int, _vp, _vp,
                                             _int]),
+    "brt_p2p_dispatch_forward_begin": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _i64,
+                                              _vp, _vp, _int]),
+    "brt_p2p_dispatch_land": (_int, [_vp, _vp, _vp, _i64, _i64, _vp, _vp, _int, _int, _int, _i64,
+                                     _i64, _vp, _u64, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _vp]),
     "brt_p2p_sparse_forward_sizes": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "brt_p2p_sparse_backward": (_int, [_vp, _u64, _int, _i64, _i64, _int, _int, _vp, _vp, _int,
                                        _vp, _vp]),

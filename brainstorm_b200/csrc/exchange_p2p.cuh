@@ -1,0 +1,101 @@
+// Device-side building blocks of the peer-memory exchange kernels: system-scope flag
+// accesses, bounded waits that report to the host, and a block-wide scan.
+#pragma once
+
+#include "common.cuh"
+
+namespace brt_b200 {
+namespace p2p {
+
+constexpr int kMaxRanks = 32;
+constexpr int kMaxCopies = 96;
+constexpr int kMaxBuckets = 1024;
+constexpr int kThreads = 256;
+constexpr long long kChunkBytes = 32768;
+constexpr int kWays = 32;  // interleaved runs of the copy list (>= any world size)
+
+__device__ __forceinline__ void store_release_sys(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long load_acquire_sys(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Where a bounded wait reports that it ran out: the arena's status word and a word of
+// host-mapped memory that the host can read without synchronising with the device.
+struct StatusSink {
+  int* device_word;
+  int* host_word;
+};
+__device__ __forceinline__ void report_timeout(const StatusSink& s) {
+  if (s.device_word != nullptr) atomicExch(s.device_word, BRT_ERR_TIMEOUT);
+  if (s.host_word != nullptr) {
+    *reinterpret_cast<volatile int*>(s.host_word) = BRT_ERR_TIMEOUT;
+    __threadfence_system();
+  }
+}
+
+// Thread r of the CTA (r < world_size, r != skip) polls flags[r] until it holds a value
+// >= epoch or `limit_ns` has passed.  Returns true (to every thread) when all flags came.
+__device__ __forceinline__ bool wait_for_flags(const unsigned long long* flags, int world_size,
+                                               int skip, unsigned long long epoch,
+                                               unsigned long long limit_ns) {
+  bool ok = true;
+  const int r = threadIdx.x;
+  if (r < world_size && r != skip) {
+    const unsigned long long start = global_timer_ns();
+    unsigned int spins = 0;
+    while (load_acquire_sys(flags + r) < epoch) {
+      __nanosleep(100);
+      if ((++spins & 63u) == 0 && global_timer_ns() - start > limit_ns) {
+        ok = false;
+        break;
+      }
+    }
+  }
+  return __syncthreads_and(ok) != 0;
+}
+
+// In-place exclusive prefix sum of a[0 .. n) in shared memory (n <= kMaxBuckets), total at
+// a[n].  All threads of the CTA call it; it opens and closes with a barrier.
+__device__ __forceinline__ void block_exclusive_scan(int* a, int n, int* s_warp) {
+  __syncthreads();
+  const int tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5;
+  const int per = (n + kThreads - 1) / kThreads;
+  const int begin = tid * per < n ? tid * per : n;
+  const int end = begin + per < n ? begin + per : n;
+  int local = 0;
+  for (int i = begin; i < end; i++) local += a[i];
+  int incl = local;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int up = __shfl_up_sync(0xffffffffu, incl, d);
+    if (lane >= d) incl += up;
+  }
+  if (lane == 31) s_warp[warp] = incl;
+  __syncthreads();
+  int before = 0, total = 0;
+  for (int w = 0; w < kThreads / 32; w++) {
+    if (w < warp) before += s_warp[w];
+    total += s_warp[w];
+  }
+  int run = before + incl - local;
+  for (int i = begin; i < end; i++) {
+    const int v = a[i];
+    a[i] = run;
+    run += v;
+  }
+  if (tid == 0) a[n] = total;
+  __syncthreads();
+}
+
+}  // namespace p2p
+}  // namespace brt_b200

@@ -177,11 +177,19 @@ BRT_API int brt_p2p_ctx_reset_status(brt_p2p_ctx* c) {
 
 BRT_API uint64_t brt_p2p_ctx_exchanges(const brt_p2p_ctx* c) { return c ? c->exchanges : 0; }
 
-BRT_API int brt_p2p_sparse_forward_begin(brt_p2p_ctx* c, const void* rows, const int32_t* sizes,
-                                         int group_size, int64_t grain_bytes,
-                                         int64_t stride_rows, int layout, void* main_stream,
-                                         void* side_stream, int stages) {
-  clear_error();
+namespace {
+// What the PUSH stage of a forward exchange launches: the landing kernel over rows that are
+// already laid out by destination, or the dispatch that lands its rows itself.
+struct FusedDispatch {
+  const void* src;
+  const int32_t* indices;
+  const int32_t* dense_counts;
+  int64_t cell_num;
+};
+
+int forward_begin(brt_p2p_ctx* c, const void* rows, const FusedDispatch* fused,
+                  const int32_t* sizes, int group_size, int64_t grain_bytes, int64_t stride_rows,
+                  int layout, void* main_stream, void* side_stream, int stages) {
   BRT_REQUIRE(c != nullptr && sizes != nullptr, "null context or sizes");
   BRT_REQUIRE(layout == BRT_P2P_SPARSE_FORWARD || (layout == BRT_P2P_SLOTS && stride_rows > 0),
               "layout must be the sparse forward one or slots with a slot size");
@@ -230,13 +238,50 @@ BRT_API int brt_p2p_sparse_forward_begin(brt_p2p_ctx* c, const void* rows, const
   }
   if (stages & BRT_P2P_STAGE_PUSH) {
     int32_t* keep = reinterpret_cast<int32_t*>(c->base + kKeptOffset) + (x % kKept) * kBoardInts;
-    if (int rc = land(c, rows, reinterpret_cast<const int32_t*>(c->base + board), keep,
-                      group_size, layout, 0, grain_bytes, stride_rows, x, main_stream))
-      return rc;
+    const int32_t* matrix = reinterpret_cast<const int32_t*>(c->base + board);
+    if (fused == nullptr) {
+      if (int rc = land(c, rows, matrix, keep, group_size, layout, 0, grain_bytes, stride_rows, x,
+                        main_stream))
+        return rc;
+    } else {
+      void* halves[kMaxRanks];
+      for (int r = 0; r < c->world; r++) halves[r] = half_of(c, r, x);
+      if (int rc = brt_p2p_dispatch_land(
+              fused->src, fused->indices, fused->dense_counts, fused->cell_num, grain_bytes,
+              matrix, keep, c->world, group_size, c->rank, stride_rows, (int64_t)c->half_bytes,
+              halves, x, c->base + kReadyOffset, c->arrive_flags, c->base + kCounterOffset,
+              c->base + kAbortOffset, c->base + kStatusOffset, c->host_status_dev, c->wait_ns,
+              main_stream))
+        return rc;
+    }
   }
   if (stages & BRT_P2P_STAGE_WAIT)
     if (int rc = wait_arrivals(c, x, main_stream)) return rc;
   return BRT_OK;
+}
+}  // namespace
+
+BRT_API int brt_p2p_sparse_forward_begin(brt_p2p_ctx* c, const void* rows, const int32_t* sizes,
+                                         int group_size, int64_t grain_bytes,
+                                         int64_t stride_rows, int layout, void* main_stream,
+                                         void* side_stream, int stages) {
+  clear_error();
+  return forward_begin(c, rows, nullptr, sizes, group_size, grain_bytes, stride_rows, layout,
+                       main_stream, side_stream, stages);
+}
+
+BRT_API int brt_p2p_dispatch_forward_begin(brt_p2p_ctx* c, const void* src_data,
+                                           const int32_t* route_indices, const int32_t* loads,
+                                           const int32_t* dense_counts, int64_t cell_num,
+                                           int64_t row_bytes, int group_size,
+                                           int64_t stride_rows, void* main_stream,
+                                           void* side_stream, int stages) {
+  clear_error();
+  BRT_REQUIRE(route_indices != nullptr && dense_counts != nullptr && cell_num >= 0,
+              "null indices or counts");
+  const FusedDispatch fused{src_data, route_indices, dense_counts, cell_num};
+  return forward_begin(c, nullptr, &fused, loads, group_size, row_bytes, stride_rows,
+                       BRT_P2P_SPARSE_FORWARD, main_stream, side_stream, stages);
 }
 
 BRT_API int brt_p2p_sparse_forward_sizes(brt_p2p_ctx* c, void* side_stream,

@@ -35,9 +35,17 @@ class DistributedFusedDispatchFabric(FusedDispatchFabric):
         for flow_idx in range(self.flow_num):
             data, tag_stack, load_stack, extra = to_torch_tensor(in_flows[flow_idx],
                                                                  retrieve_attr=True)
-            (routed,) = self._route(data, route_indices, loads, score, flow_idx, None)
-            out_data, out_loads, in_loads = brt_dist.group_sparse_a2a(
-                routed, loads, self.max_path_padding, self.max_path_load)
+            fused = None
+            if not self.transforms[flow_idx] and self.route_logics[flow_idx] == "1d":
+                # dispatch and exchange as one kernel over peer memory when that is possible
+                fused = brt_dist.dispatch_group_sparse_a2a(
+                    data, route_indices, loads, self.max_path_padding, self.max_path_load)
+            if fused is not None:
+                out_data, out_loads, in_loads = fused
+            else:
+                (routed,) = self._route(data, route_indices, loads, score, flow_idx, None)
+                out_data, out_loads, in_loads = brt_dist.group_sparse_a2a(
+                    routed, loads, self.max_path_padding, self.max_path_load)
             if self.task_locality:
                 # hand back, per received row, the global id of the local expert ("task") it
                 # belongs to, in place of the score

@@ -116,6 +116,16 @@ def group_sparse_a2a(in_data: torch.Tensor, in_loads: torch.Tensor, max_path_pad
     return in_data, in_loads, in_loads
 
 
+def dispatch_group_sparse_a2a(in_data: torch.Tensor, route_indices: torch.Tensor,
+                              loads: torch.Tensor, max_path_padding=False, max_path_load=0):
+    """Unweighted dispatch + ``group_sparse_a2a`` as one kernel when the peer-memory transport
+    can take it, else ``None`` (the caller runs the two steps)."""
+    if is_nccl_activated():
+        return C_dist.dispatch_group_sparse_all_to_all(in_data, route_indices, loads,
+                                                       max_path_padding, max_path_load)
+    return None
+
+
 def size_known_group_sparse_a2a(in_data: torch.Tensor, in_loads: torch.Tensor,
                                 out_loads: torch.Tensor, max_path_padding=False):
     if is_nccl_activated():

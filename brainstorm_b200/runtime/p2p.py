@@ -96,6 +96,9 @@ class PeerArena:
         main = torch.cuda.current_stream().cuda_stream
         _lib.call("brt_p2p_sparse_forward_begin", self.ctx, rows.data_ptr(), sizes.data_ptr(),
                   group_size, grain, stride_rows, layout, main, self.side.cuda_stream, 0)
+        return self._forward_sizes(group_size)
+
+    def _forward_sizes(self, group_size: int):
         matrix = ctypes.POINTER(ctypes.c_int32)()
         n_rows, fits = ctypes.c_int64(), ctypes.c_int()
         out, xid = ctypes.c_void_p(), ctypes.c_uint64()
@@ -104,6 +107,18 @@ class PeerArena:
                   ctypes.byref(out), ctypes.byref(xid))
         S = np.ctypeslib.as_array(matrix, shape=(self.world, self.world * group_size)).copy()
         return S, int(n_rows.value), bool(fits.value), int(out.value), int(xid.value)
+
+    def dispatch_forward(self, cells: torch.Tensor, route_indices: torch.Tensor,
+                         loads: torch.Tensor, counts: torch.Tensor, group_size: int, grain: int,
+                         stride_rows: int):
+        """Dispatch fused with the forward packed exchange: every kept copy of a cell goes
+        straight to its row in the destination rank's landing half.  Same results as
+        ``sparse_forward`` of the dispatched rows."""
+        main = torch.cuda.current_stream().cuda_stream
+        _lib.call("brt_p2p_dispatch_forward_begin", self.ctx, cells.data_ptr(),
+                  route_indices.data_ptr(), loads.data_ptr(), counts.data_ptr(), cells.size(0),
+                  grain, group_size, stride_rows, main, self.side.cuda_stream, 0)
+        return self._forward_sizes(group_size)
 
     def sparse_backward(self, exchange_id: int, group_size: int, grain: int, stride_rows: int,
                         rows: torch.Tensor, layout: int = SPARSE_INVERSE,

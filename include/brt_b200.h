@@ -305,6 +305,34 @@ BRT_API int brt_sum_rows_by_index(const void* in_rows, const int32_t* row_index,
                                   int64_t rows_in, int64_t rows_out, int64_t cell_size,
                                   int dtype, void* scratch, size_t scratch_bytes, void* stream);
 
+/* ------------------------------------------------------------------ experts: grouped GEMM */
+
+/*
+ * The expert side of the dispatched layout: one linear layer per expert over the rows that
+ * dispatch wrote for it, on the 5th-generation tensor cores (tcgen05.mma with accumulators in
+ * tensor memory, operands staged by TMA).  Stands where the reference launches its
+ * horizontally fused "homo" expert kernel on the dispatched buffer with the per-expert loads
+ * (src/backend/torch/jit.cc:54-75, benchmark/switch_moe/switch_expert.py:62-99).
+ *
+ *   out[r, :] = act(rows[r, :] x weights[e]^T)   for the first loads[e] rows r of expert e
+ *
+ * rows [total_rows, in_features] bf16 as dispatch leaves them (expert e starts at row
+ * e * max_path_load when max_path_load != 0, else at sum(loads[0..e)); weights
+ * [path_num, out_features, in_features] bf16; out [total_rows, out_features] bf16; loads
+ * [path_num] int32 ON THE DEVICE (nothing is read back to the host; with max_path_load != 0
+ * loads above it are cut).  Rows of `out` beyond an expert's load are not written.
+ * relu != 0 applies max(x, 0) before the rounding to bf16.
+ * error_word: a zero-initialised 4-byte device word; a bounded wait inside the kernel that
+ * runs out stores BRT_ERR_TIMEOUT there (the kernel then returns with `out` incomplete).
+ * Returns BRT_ERR_UNSUPPORTED (nothing launched) unless in_features % 64 == 0 and
+ * out_features % 128 == 0.
+ */
+BRT_API int brt_grouped_expert_gemm(const void* rows, const void* weights, void* out,
+                                    const int32_t* loads, int path_num, int64_t total_rows,
+                                    int32_t max_path_load, int64_t in_features,
+                                    int64_t out_features, int relu, void* error_word,
+                                    void* stream);
+
 /* ------------------------------------------------------------------ distributed: rank reorder */
 
 /*
@@ -475,6 +503,17 @@ BRT_API int brt_p2p_land(const void* rows, const int32_t* size_matrix, int32_t* 
 BRT_API int brt_p2p_wait(const void* my_flag_array, int world_size, int skip_rank,
                          uint64_t epoch, void* status_word, void* host_status_word,
                          uint64_t wait_limit_ns, void* stream);
+/* brt_p2p_land with the dispatch in front of it folded in (see
+ * brt_p2p_dispatch_forward_begin): cells `src_data[cell_num, row_bytes]` go, by dense seat
+ * indices `route_indices[cell_num, world_size * group_size]`, straight to their rows in the
+ * destinations' landing halves; the size matrix row of this rank holds the loads. */
+BRT_API int brt_p2p_dispatch_land(
+    const void* src_data, const int32_t* route_indices, const int32_t* dense_counts,
+    int64_t cell_num, int64_t row_bytes, const int32_t* size_matrix, int32_t* keep_matrix,
+    int world_size, int group_size, int my_rank, int64_t stride_rows, int64_t half_bytes,
+    void* const* landing_ptrs, uint64_t epoch, const void* my_ready_flags,
+    void* const* peer_arrive_flag_arrays, void* my_done_counter, void* my_abort_word,
+    void* status_word, void* host_status_word, uint64_t wait_limit_ns, void* stream);
 
 /*
  * Exchange context: the host side of the two sparse exchanges on top of the calls above.  It
@@ -506,6 +545,15 @@ BRT_API int brt_p2p_wait(const void* my_flag_array, int world_size, int skip_ran
  *                 landing kernel and the wait for the peers' rows on `main_stream`; the copy
  *                 of the gathered size matrix to the host on `side_stream`, ordered behind the
  *                 post.  BRT_ERR_UNSUPPORTED: too many buckets, nothing enqueued.
+ * brt_p2p_dispatch_forward_begin the same exchange FUSED with the dispatch in front of it
+ *                 (python/brt/router/fabric/distributed.py:35-97 in the reference runs
+ *                 dispatch_with_indices_and_loads, then group_sparse_all_to_all): the landing
+ *                 kernel is replaced by a dispatch kernel that reads the cells
+ *                 `src_data[cell_num, row_bytes]` and stores every kept copy straight into the
+ *                 destination rank's landing half; the bucket sizes are `loads` (DEVICE,
+ *                 world_size * group_size).  Unweighted 1-D routing with dense seat indices
+ *                 (`dense_counts` as for brt_dispatch_with_indices_and_loads).  Followed by
+ *                 brt_p2p_sparse_forward_sizes like the unfused call.
  * brt_p2p_sparse_forward_sizes   part 2: waits for the size matrix only (the rows are still
  *                 moving); returns the matrix ([sender][destination * group_size + expert],
  *                 valid until the next begin), the identifier under which it is kept for the
@@ -542,6 +590,12 @@ BRT_API int brt_p2p_sparse_forward_begin(brt_p2p_ctx* ctx, const void* rows,
                                          const int32_t* sizes, int group_size,
                                          int64_t grain_bytes, int64_t stride_rows, int layout,
                                          void* main_stream, void* side_stream, int stages);
+BRT_API int brt_p2p_dispatch_forward_begin(brt_p2p_ctx* ctx, const void* src_data,
+                                           const int32_t* route_indices, const int32_t* loads,
+                                           const int32_t* dense_counts, int64_t cell_num,
+                                           int64_t row_bytes, int group_size,
+                                           int64_t stride_rows, void* main_stream,
+                                           void* side_stream, int stages);
 BRT_API int brt_p2p_sparse_forward_sizes(brt_p2p_ctx* ctx, void* side_stream,
                                          const int32_t** size_matrix, int64_t* out_rows,
                                          int* fits, void** out_data, uint64_t* exchange_id);

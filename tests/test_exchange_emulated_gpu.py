@@ -201,6 +201,104 @@ def test_padded_slot_exchange_and_back(world, group, cols, slot):
         ranks.close()
 
 
+    # (method of Ranks, bound below)
+def _dispatch_forward(self, xs, idxs, loads, counts, group, stride=0):
+    st = torch.cuda.current_stream().cuda_stream
+    grain = xs[0].size(1) * xs[0].element_size()
+    for stage in (POST, SIZES, PUSH, WAIT):
+        for r in range(self.world):
+            _lib.call("brt_p2p_dispatch_forward_begin", self.ctxs[r], xs[r].data_ptr(),
+                      idxs[r].data_ptr(), loads[r].data_ptr(), counts[r].data_ptr(),
+                      xs[r].size(0), grain, group, stride, st, st, stage)
+    outs = []
+    for r in range(self.world):
+        m = ctypes.POINTER(ctypes.c_int32)()
+        n_rows, fits = ctypes.c_int64(), ctypes.c_int()
+        out, xid = ctypes.c_void_p(), ctypes.c_uint64()
+        _lib.call("brt_p2p_sparse_forward_sizes", self.ctxs[r], st, ctypes.byref(m),
+                  ctypes.byref(n_rows), ctypes.byref(fits), ctypes.byref(out), ctypes.byref(xid))
+        assert fits.value
+        outs.append((out.value, n_rows.value))
+    return outs
+
+
+Ranks.dispatch_forward = _dispatch_forward
+
+
+@pytest.mark.parametrize("world,group,cells,cols,k,mode", [
+    (2, 2, 300, 4, 2, "packed"), (4, 2, 257, 8, 2, "packed"), (8, 4, 500, 1024, 2, "packed"),
+    (2, 4, 640, 600, 1, "packed"), (4, 1, 300, 16, 1, "padded"), (8, 2, 400, 520, 2, "padded"),
+    (2, 3, 200, 4, 2, "capacity"), (4, 4, 900, 12, 3, "capacity"), (8, 8, 1000, 2048, 2, "packed"),
+])
+def test_dispatch_fused_with_the_forward_exchange(world, group, cells, cols, k, mode):
+    """Dispatch that stores its rows straight into the destinations' landing halves equals
+    dispatch followed by the exchange (the checker's dispatch, then its walk of the exchange),
+    bit for bit: packed buckets, padded buckets, and loads padded above the cell counts (rows
+    that must arrive as zeros).  The indices come from the library's index ops, as in the
+    fabrics."""
+    from brainstorm_b200._C import router as R
+
+    dev = torch.device("cuda", 0)
+    E = world * group
+    rng = np.random.default_rng(world * 100 + group * 10 + cells)
+    xs_np, rows_np, sizes_np = [], [], []
+    xs, idxs, loads, counts = [], [], [], []
+    per_path = max(1, cells * k // E)
+    stride = 0
+    for r in range(world):
+        mask = oracle.topk_hot_mask(rng.standard_normal((cells, E)).astype(np.float32), k)
+        x = rng.standard_normal((cells, cols)).astype(np.float32)
+        caps = cpad = None
+        if mode == "padded":
+            stride = 2 * per_path
+            thr = np.full(E, stride, dtype=np.int32)
+            m_np, _ = oracle.throttle_hotmask(mask, np.zeros(E, dtype=np.int32), thr)
+            i_np, l_np = oracle.generate_indices_and_loads(m_np)
+            i_t, l_t, _ = R.throttle_and_generate_indices(
+                torch.from_numpy(mask).to(dev), torch.zeros(E, dtype=torch.int32, device=dev),
+                torch.from_numpy(thr).to(dev))
+        else:
+            if mode == "capacity":
+                caps, cpad = [per_path // 2 + 1, 2 * per_path, 16 * per_path], True
+            i_np, l_np = oracle.generate_indices_and_loads(mask, caps, bool(cpad))
+            i_t, l_t = R.generate_indices_and_loads(
+                torch.from_numpy(mask).to(dev),
+                None if caps is None else torch.tensor(caps, dtype=torch.int32, device=dev),
+                bool(cpad))
+        assert np.array_equal(i_t.cpu().numpy(), i_np)
+        (routed,) = oracle.dispatch_with_indices_and_loads(
+            x, i_np, l_np, max_path_padding=bool(stride), max_path_load=stride)
+        xs_np.append(x)
+        rows_np.append(routed)
+        sizes_np.append(l_np)
+        xs.append(torch.from_numpy(x).to(dev))
+        idxs.append(i_t)
+        loads.append(l_t.contiguous())
+        counts.append(getattr(i_t, R._DENSE))
+    sim = oracle.sim_group_sparse_all_to_all(rows_np, sizes_np, bool(stride), stride)
+    ranks = Ranks(world, half=32 << 20)
+    try:
+        for repeat in range(2):
+            # NaN in the landing halves first: rows the kernel must write show if it does not
+            for r in range(world):
+                ranks.rows_at(ranks.arenas[r] + ranks.control, 2 * ranks.half // 4, 1).fill_(
+                    float("nan"))
+            outs = ranks.dispatch_forward(xs, idxs, loads, counts, group, stride)
+            for r in range(world):
+                ptr, rows = outs[r]
+                want = sim[r][0]
+                assert rows == want.shape[0]
+                g = ranks.rows_at(ptr, rows, cols).cpu().numpy()
+                if stride:
+                    for b, cnt in enumerate(sim[r][1]):
+                        assert np.array_equal(g[b * stride:b * stride + cnt],
+                                              want[b * stride:b * stride + cnt]), (r, b)
+                else:
+                    assert np.array_equal(g, want), f"rank {r}: landed rows differ"
+    finally:
+        ranks.close()
+
+
 def test_nested_forwards_then_inverses():
     """Two forward exchanges whose inverses come in reverse order (layer 1, layer 2, back 2,
     back 1), with one rank sending the same sizes in both: each inverse must use the matrix
