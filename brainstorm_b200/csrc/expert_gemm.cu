@@ -8,13 +8,13 @@
 // out     [L, N] bf16
 // loads   [E] int32 ON THE DEVICE: the kernel never needs them on the host.
 //
-// One persistent CTA per SM walks the list of (expert, 128-row tile, 128-column tile) work
+// One persistent CTA per SM walks the list of (expert, 128-row tile, BN-column tile) work
 // items that it derives from `loads` itself.  Roles inside a CTA (192 threads):
 //   warp 0     one elected lane issues the TMA loads (cp.async.bulk.tensor, 128B swizzle, no
-//              multicast) of the A tile [128 x 64] and the B tile [128 x 64] of every k-block
+//              multicast) of the A tile [128 x 64] and the B tile [BN x 64] of every k-block
 //              into a 4-stage shared-memory ring, completion on mbarriers;
-//   warp 1     allocates tensor memory (2 accumulators of 128 lanes x 128 fp32 columns), and
-//              one elected lane issues tcgen05.mma (M = 128, N = 128, K = 16, bf16 -> fp32)
+//   warp 1     allocates tensor memory (2 accumulators of 128 lanes x BN fp32 columns), and
+//              one elected lane issues tcgen05.mma (M = 128, N = BN, K = 16, bf16 -> fp32)
 //              four times per k-block, releasing ring slots and publishing finished
 //              accumulators with tcgen05.commit;
 //   warps 2-5  epilogue: tcgen05.ld of the accumulator quarter their warp id selects, optional
@@ -29,13 +29,14 @@
 namespace brt_b200 {
 namespace {
 
-constexpr int kBM = 128, kBN = 128, kBK = 64;  // tile; kBK bf16 = one 128-byte swizzle row
+constexpr int kBM = 128, kBK = 64;  // tile rows; kBK bf16 = one 128-byte swizzle row
+// Tile columns BN are 256 when out_features allows it (the A tile is then used by twice as many
+// multiply-accumulates, which is what keeps the tensor pipe fed from shared memory), else 128.
 constexpr int kStages = 4;
 constexpr int kUmmaK = 16;
 constexpr int kThreads = 192;
 constexpr int kMaxExperts = 1024;
-constexpr uint32_t kTileBytes = kBM * kBK * 2;  // 16 KB, A and B alike
-constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kTileBytes = kBM * kBK * 2;  // 16 KB: an A tile, or 128 columns of a B tile
 constexpr int kSpinLimit = 1 << 22;
 
 struct GemmArgs {
@@ -44,7 +45,7 @@ struct GemmArgs {
   int* error;
   int experts;
   int max_path_load;  // 0: packed
-  int n_tiles;        // N / kBN
+  int n_tiles;        // N / BN
   int k_blocks;       // K / kBK
   long long N;
   long long total_rows;
@@ -114,8 +115,9 @@ __device__ __forceinline__ uint64_t umma_desc(const void* tile) {
   return d;
 }
 // kind::f16 instruction descriptor: fp32 accumulate, bf16 x bf16, both operands K-major.
+template <int BN>
 __device__ __forceinline__ uint32_t umma_idesc() {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) |
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
          ((uint32_t)(kBM >> 4) << 24);
 }
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc,
@@ -148,9 +150,10 @@ __device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&r)[32]) 
       : "memory");
 }
 
+template <int BN>
 struct alignas(1024) GemmSmem {
   unsigned char a[kStages][kTileBytes];
-  unsigned char b[kStages][kTileBytes];
+  unsigned char b[kStages][kTileBytes * (BN / 128)];
   uint64_t full[kStages];
   uint64_t empty[kStages];
   uint64_t acc_full[2];
@@ -163,7 +166,8 @@ struct alignas(1024) GemmSmem {
 struct TileAt {
   int expert, m_tile, n_tile;
 };
-__device__ __forceinline__ TileAt tile_at(const GemmSmem& s, int experts, int n_tiles, int t) {
+template <int BN>
+__device__ __forceinline__ TileAt tile_at(const GemmSmem<BN>& s, int experts, int n_tiles, int t) {
   int lo = 0, hi = experts - 1;  // last expert whose first tile is <= t (empty ones skipped)
   while (lo < hi) {
     const int mid = (lo + hi + 1) >> 1;
@@ -177,11 +181,14 @@ __device__ __forceinline__ TileAt tile_at(const GemmSmem& s, int experts, int n_
   return at;
 }
 
+template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 expert_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                    const __grid_constant__ CUtensorMap map_b, const GemmArgs g) {
+  constexpr uint32_t kTmemCols = 2 * BN;
+  constexpr uint32_t kStageBytes = kTileBytes + kTileBytes * (BN / 128);
   extern __shared__ __align__(1024) unsigned char s_raw[];
-  GemmSmem& s = *reinterpret_cast<GemmSmem*>(
+  GemmSmem<BN>& s = *reinterpret_cast<GemmSmem<BN>*>(
       (reinterpret_cast<uintptr_t>(s_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -233,16 +240,16 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         const int row0 = s.row_base[at.expert] + at.m_tile * kBM;
         for (int kb = 0; kb < g.k_blocks; kb++) {
           if (!mbar_wait(&s.empty[slot], phase ^ 1)) { failed = true; break; }
-          mbar_expect_tx(&s.full[slot], 2 * kTileBytes);
+          mbar_expect_tx(&s.full[slot], kStageBytes);
           tma_load_2d(s.a[slot], &map_a, &s.full[slot], kb * kBK, row0);
-          tma_load_3d(s.b[slot], &map_b, &s.full[slot], kb * kBK, at.n_tile * kBN, at.expert);
+          tma_load_3d(s.b[slot], &map_b, &s.full[slot], kb * kBK, at.n_tile * BN, at.expert);
           if (++slot == kStages) { slot = 0; phase ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc = umma_idesc();
+      const uint32_t idesc = umma_idesc<BN>();
       int slot = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -250,7 +257,7 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       for (int t = blockIdx.x; t < total_tiles && !failed; t += gridDim.x) {
         if (!mbar_wait(&s.acc_empty[acc], acc_phase ^ 1)) { failed = true; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t d = tmem + (uint32_t)acc * kBN;
+        const uint32_t d = tmem + (uint32_t)acc * BN;
         for (int kb = 0; kb < g.k_blocks; kb++) {
           if (!mbar_wait(&s.full[slot], phase)) { failed = true; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -283,12 +290,12 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       if (!mbar_wait(&s.acc_full[acc], acc_phase)) { failed = true; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
-      for (int c0 = 0; c0 < kBN; c0 += 32) {
+      for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t v[32];
-        tmem_load_32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kBN + c0), v);
+        tmem_load_32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + c0), v);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (row_in_expert < load && row < g.total_rows) {
-          uint4* dst = reinterpret_cast<uint4*>(g.out + row * g.N + (long long)at.n_tile * kBN + c0);
+          uint4* dst = reinterpret_cast<uint4*>(g.out + row * g.N + (long long)at.n_tile * BN + c0);
 #pragma unroll
           for (int q = 0; q < 4; q++) {
             uint32_t w[4];
@@ -362,11 +369,12 @@ BRT_API int brt_grouped_expert_gemm(const void* rows, const void* weights, void*
               kMaxExperts);
   BRT_REQUIRE(total_rows >= 0 && max_path_load >= 0, "negative size");
   BRT_REQUIRE(loads != nullptr && error_word != nullptr, "loads or error_word is null");
-  if (in_features <= 0 || out_features <= 0 || in_features % kBK != 0 || out_features % kBN != 0)
+  if (in_features <= 0 || out_features <= 0 || in_features % kBK != 0 || out_features % 128 != 0)
     return set_error(BRT_ERR_UNSUPPORTED,
                      "the tensor-core expert GEMM needs in_features %% %d == 0 and "
-                     "out_features %% %d == 0 (got %lld, %lld)",
-                     kBK, kBN, (long long)in_features, (long long)out_features);
+                     "out_features %% 128 == 0 (got %lld, %lld)",
+                     kBK, (long long)in_features, (long long)out_features);
+  const int bn = out_features % 256 == 0 ? 256 : 128;
   if (total_rows == 0) return BRT_OK;
   BRT_REQUIRE(rows != nullptr && weights != nullptr && out != nullptr, "null pointer argument");
   BRT_REQUIRE(aligned_to(rows, 16) && aligned_to(weights, 16) && aligned_to(out, 16),
@@ -395,7 +403,7 @@ BRT_API int brt_grouped_expert_gemm(const void* rows, const void* weights, void*
                                 (cuuint64_t)path_num};
     const cuuint64_t strides[2] = {(cuuint64_t)in_features * 2,
                                    (cuuint64_t)in_features * out_features * 2};
-    const cuuint32_t box[3] = {kBK, kBN, 1};
+    const cuuint32_t box[3] = {kBK, (cuuint32_t)bn, 1};
     const cuuint32_t elem[3] = {1, 1, 1};
     const CUresult r = encode(&map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
                               const_cast<void*>(weights), dims, strides, box, elem,
@@ -411,23 +419,36 @@ BRT_API int brt_grouped_expert_gemm(const void* rows, const void* weights, void*
   g.error = static_cast<int*>(error_word);
   g.experts = path_num;
   g.max_path_load = max_path_load;
-  g.n_tiles = (int)(out_features / kBN);
+  g.n_tiles = (int)(out_features / bn);
   g.k_blocks = (int)(in_features / kBK);
   g.N = out_features;
   g.total_rows = total_rows;
   g.relu = relu != 0;
-  const size_t smem = sizeof(GemmSmem) + 1024;
-  static thread_local int configured_device = -1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
   int dev = 0;
   BRT_CUDA_TRY(cudaGetDevice(&dev));
-  if (configured_device != dev) {
-    BRT_CUDA_TRY(cudaFuncSetAttribute(expert_gemm_kernel,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured_device = dev;
-  }
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   const KernelTimer timer("expert_gemm_kernel", st);
-  expert_gemm_kernel<<<(unsigned)sm_count(), kThreads, smem, st>>>(map_a, map_b, g), note_launch();
+  if (bn == 256) {
+    const size_t smem = sizeof(GemmSmem<256>) + 1024;
+    static thread_local int configured_device = -1;
+    if (configured_device != dev) {
+      BRT_CUDA_TRY(cudaFuncSetAttribute(expert_gemm_kernel<256>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      configured_device = dev;
+    }
+    expert_gemm_kernel<256><<<(unsigned)sm_count(), kThreads, smem, st>>>(map_a, map_b, g),
+        note_launch();
+  } else {
+    const size_t smem = sizeof(GemmSmem<128>) + 1024;
+    static thread_local int configured_device = -1;
+    if (configured_device != dev) {
+      BRT_CUDA_TRY(cudaFuncSetAttribute(expert_gemm_kernel<128>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      configured_device = dev;
+    }
+    expert_gemm_kernel<128><<<(unsigned)sm_count(), kThreads, smem, st>>>(map_a, map_b, g),
+        note_launch();
+  }
   BRT_LAUNCH_CHECK("expert_gemm_kernel");
   return BRT_OK;
 }
