@@ -69,13 +69,15 @@ def capacity_of(w) -> int:
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of each timed kernel, from the ncu
-# capture summarised in profiles/ncu_full_cfg2_routing_step_kernels.txt.  Dirty lines that
-# the 126 MB L2 still holds when a kernel ends are not in these counters, so the write-heavy
-# ops read below their algorithmic bytes.
+# captures summarised under profiles/ (ncu_full_cfg2_routing_step_kernels.txt,
+# ncu_counters_cfg3_dispatch_combine.txt, ncu_counters_cfg4_dispatch_combine.txt).  Each
+# kernel alone and cold; dirty lines that the 126 MB L2 still holds when a kernel ends are not
+# in these counters, so the write-heavy ops can read below their algorithmic bytes.
 NCU_DRAM_KERNEL_TRAFFIC = {
-    "cfg2": {"throttle_chain_kernel": 4.24e6, "index_chain_kernel": 4.24e6,
-             "dispatch_move_kernel": 84.5e6, "dispatch_zero_fill_kernel": 1.6e6,
-             "combine_kernel": 110.3e6},
+    "cfg2": {"throttle_index_chain_kernel": 4.24e6, "dispatch_kernel": 132.97e6,
+             "combine_kernel": 117.16e6},
+    "cfg3": {"dispatch_kernel": 935.44e6, "combine_kernel": 673.39e6},
+    "cfg4": {"dispatch_kernel": 763.28e6, "combine_kernel": 800.58e6},
 }
 
 
@@ -456,6 +458,10 @@ def run_gpu(args):
         "timed_region": "CUDA graph replay of the step" if graph is not None
                         else "eager launches of the step",
         "eager_ms_per_step": eager_host_ms, "eager_device_ms_per_step": eager_ms,
+        # one timing mode for a scaling curve: `value` is a graph replay at N = 1 where the
+        # step has no host synchronisation, and eager launches at N > 1 (the forward exchange
+        # returns CPU size tensors); this is the eager figure at every N
+        "value_eager": world * T / (eager_host_ms * 1e-3),
     }
     if distributed:
         result["checks"] = exchange_checks(dev, rank, world, x, mask, gates, caps, cap, padded,

@@ -47,18 +47,25 @@ def _contig_rows(t: torch.Tensor, cell_size: int) -> torch.Tensor:
 
 
 class _ScratchPool:
-    """One reusable scratch buffer per (device, purpose).  Reuse is safe for calls enqueued
-    on the same stream; a different stream gets its own buffer."""
+    """One reusable scratch buffer per (purpose, device, stream).  Reuse is safe for calls
+    enqueued on the same stream; a different stream gets its own buffer.  At most ``LIMIT``
+    buffers are kept: the least recently used one is dropped (torch's allocator keeps its
+    memory alive until the stream it was used on has passed it)."""
+
+    LIMIT = 16
 
     def __init__(self):
         self._bufs = {}
 
     def get(self, purpose: str, device: torch.device, nbytes: int) -> torch.Tensor:
-        key = (purpose, device.index, torch.cuda.current_stream(device).cuda_stream)
-        buf = self._bufs.get(key)
+        stream = torch.cuda.current_stream(device)
+        key = (purpose, device.index, stream.cuda_stream)
+        buf = self._bufs.pop(key, None)
         if buf is None or buf.numel() < nbytes:
             buf = torch.empty(max(nbytes, 1 << 16), dtype=torch.uint8, device=device)
-            self._bufs[key] = buf
+        self._bufs[key] = buf  # most recently used last
+        while len(self._bufs) > self.LIMIT:
+            self._bufs.pop(next(iter(self._bufs)))  # dicts keep insertion order: the oldest
         return buf
 
 
