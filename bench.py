@@ -246,6 +246,7 @@ def run_gpu(args):
 
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(8)] for _ in range(args.steps)]
     a2a_bytes = [0]
+    fused_used = [False]
 
     def step(i=None):
         rec = (lambda j: ev[i][j].record()) if i is not None else (lambda j: None)
@@ -258,17 +259,26 @@ def run_gpu(args):
         else:
             idx, loads = R.generate_indices_and_loads(mask, caps)
         rec(2)
-        (routed,) = R.dispatch_with_indices_and_loads(x, idx, loads, None, False, None, padded,
-                                                      cap)
+        fused = None
+        if distributed and not args.no_fused_exchange:
+            # dispatch and forward exchange as one kernel (what the distributed fabric runs)
+            fused = brt_dist.dispatch_group_sparse_a2a(x, idx, loads, padded, cap)
+        if fused is None:
+            (routed,) = R.dispatch_with_indices_and_loads(x, idx, loads, None, False, None,
+                                                          padded, cap)
         rec(3)
         if distributed:
-            recv, out_loads, in_loads = brt_dist.group_sparse_a2a(routed, loads, padded, cap)
+            if fused is not None:
+                recv, out_loads, in_loads = fused
+            else:
+                recv, out_loads, in_loads = brt_dist.group_sparse_a2a(routed, loads, padded, cap)
             rec(4)
             routed = brt_dist.size_known_group_sparse_a2a(recv, out_loads, in_loads, padded)
             rec(5)
             # rows this rank really sends to OTHER ranks (in_loads: my send sizes, [W, G])
             sent = in_loads.reshape(world, -1)
             a2a_bytes[0] = int(sent.sum() - sent[rank].sum()) * d * x.element_size()
+            fused_used[0] = fused is not None
         else:
             rec(4)
             rec(5)
@@ -389,7 +399,7 @@ def run_gpu(args):
     peak_kind = "measured" if "hbm_gbs" in peaks else "fallback"
     kernels = {}
     for n in ("indices", "dispatch", "combine"):
-        if op_ms[n] > 0:
+        if op_ms[n] > 0 and not (n == "dispatch" and fused_used[0]):
             gbs = ab[n] / (op_ms[n] * 1e-3) / 1e9
             kernels[n] = {"ms": round(op_ms[n], 5), "algorithmic_bytes": ab[n],
                           "achieved_gbs": round(gbs, 1), "frac": round(gbs / peak, 4)}
@@ -406,7 +416,8 @@ def run_gpu(args):
     for name, t in timed.items():
         if t["launches"] == 0:
             continue
-        if name.startswith("p2p_"):  # exchange kernels: bound by NVLink, not by HBM
+        if name.startswith("p2p_") or name == "dispatch_land_kernel":
+            # exchange kernels: bound by NVLink, not by HBM
             device_kernels[name] = {"launches": t["launches"],
                                     "ms": round(t["total_ms"] / t["launches"], 5)}
             continue
@@ -417,7 +428,7 @@ def run_gpu(args):
         device_kernels[name] = {"launches": t["launches"], "ms": round(ms, 5),
                                 "algorithmic_bytes": kernel_bytes[name],
                                 "achieved_gbs": round(gbs, 1), "frac": round(gbs / peak, 4)}
-    dominant = max((n for n in device_kernels if not n.startswith("p2p_")),
+    dominant = max((n for n in device_kernels if "algorithmic_bytes" in device_kernels[n]),
                    key=lambda n: device_kernels[n]["ms"])
     dominant_op = {"dispatch_move_kernel": "dispatch", "dispatch_zero_fill_kernel": "dispatch",
                    "dispatch_kernel": "dispatch",
@@ -477,13 +488,14 @@ def run_gpu(args):
             plain["round_trip_bit_exact"] and skewed["round_trip_bit_exact"])
         result["locality"] = measure_locality(loads, world, dev, brt_dist)
         fwd = a2a_bytes[0]
-        land = device_kernels.get("p2p_land_forward_kernel")
+        land_name = "dispatch_land_kernel" if fused_used[0] else "p2p_land_forward_kernel"
+        land = device_kernels.get(land_name)
         if land is not None and land["ms"] > 0:
             # at N > 1 the step is bound by the exchange: its landing kernel against NVLink
             gbs = fwd / (land["ms"] * 1e-3) / 1e9
             result["roofline_hbm_kernel"] = result["roofline"]
             result["roofline"] = {
-                "bound": "nvlink", "kernel": "p2p_land_forward_kernel", "achieved": round(gbs, 1),
+                "bound": "nvlink", "kernel": land_name, "achieved": round(gbs, 1),
                 "peak": 900.0, "unit": "GB/s", "frac": round(gbs / 900.0, 4), "traffic": None,
                 "peak_kind": "nominal NVLink 5 bandwidth per direction per GPU; a peer copy "
                              "on this pool measures 770 GB/s",
@@ -499,6 +511,7 @@ def run_gpu(args):
             "transport": "peer-memory landing kernels over NVLink"
                          if __import__("brainstorm_b200.runtime.p2p", fromlist=["arena"]).arena()
                          is not None else "nccl send/recv",
+            "forward_includes_dispatch": fused_used[0],
         }
     if world == 1:
         result["expert_gemm"] = measure_expert_gemm(wl, dev, loads, cap, peaks)
@@ -569,11 +582,28 @@ def exchange_checks(dev, rank, world, x, mask, gates, caps, cap, padded, R, brt_
     rows_ok = got.size(0) == (E * cap if padded else cursor)
     layout = bool(rows_ok and torch.equal(got[at, 0], want_rank)
                   and torch.equal(got[at, 1], want_row))
-    verdict = torch.tensor([int(round_trip), int(layout), int(same_as_local)], device=dev)
+    # (4) the dispatch that stores its rows straight into the peers equals the two steps
+    fused = brt_dist.dispatch_group_sparse_a2a(x, idx, loads, padded, cap)
+    fused_same = True
+    if fused is not None:
+        two = brt_dist.group_sparse_a2a(routed, loads, padded, cap)
+        if padded:
+            valid = torch.zeros(two[0].size(0), dtype=torch.bool, device=dev)
+            for b, cnt in enumerate(two[1].tolist()):
+                valid[b * cap:b * cap + min(cnt, cap)] = True
+            fused_same = bool(torch.equal(fused[0][valid], two[0][valid]))
+        else:
+            fused_same = bool(torch.equal(fused[0], two[0]))
+        fused_same = fused_same and bool(torch.equal(fused[1], two[1]))
+    verdict = torch.tensor([int(round_trip), int(layout), int(same_as_local), int(fused_same)],
+                           device=dev)
     dist.all_reduce(verdict, op=dist.ReduceOp.MIN)
     v = verdict.tolist()
     return {"round_trip_bit_exact": bool(v[0]), "forward_layout_matches_reference_walk": bool(v[1]),
-            "step_equals_single_rank_step": bool(v[2]), "ranks": world,
+            "step_equals_single_rank_step": bool(v[2]),
+            "fused_dispatch_exchange_equals_two_steps": bool(v[3]),
+            "fused_dispatch_exchange": "ran" if fused is not None
+            else "not available on this transport (two steps)", "ranks": world,
             "rows_exchanged_per_rank": int(n_rows)}
 
 
@@ -1011,6 +1041,9 @@ def main():
     ap.add_argument("--local-bias", type=float, default=0.0,
                     help="added to the logits of a rank's own experts (N>1): 2.0 sends about "
                          "60%% of the top-2 picks of cfg4 to local experts")
+    ap.add_argument("--no-fused-exchange", action="store_true",
+                    help="at N>1 run dispatch and the forward exchange as two ops instead of the "
+                         "one kernel that stores the dispatched rows straight into the peers")
     ap.add_argument("--no-graph", action="store_true",
                     help="time eager launches instead of a CUDA graph replay")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
