@@ -261,12 +261,17 @@ def run_gpu(args):
         rec(2)
         fused = None
         if distributed and not args.no_fused_exchange:
-            # dispatch and forward exchange as one kernel (what the distributed fabric runs)
+            # dispatch and forward exchange as one kernel (what the distributed fabric runs):
+            # there is no separate dispatch to time, the forward leg includes it
+            rec(3)
             fused = brt_dist.dispatch_group_sparse_a2a(x, idx, loads, padded, cap)
-        if fused is None:
+            if fused is None:
+                (routed,) = R.dispatch_with_indices_and_loads(x, idx, loads, None, False, None,
+                                                              padded, cap)
+        else:
             (routed,) = R.dispatch_with_indices_and_loads(x, idx, loads, None, False, None,
                                                           padded, cap)
-        rec(3)
+            rec(3)
         if distributed:
             if fused is not None:
                 recv, out_loads, in_loads = fused
