@@ -488,6 +488,13 @@ def run_gpu(args):
         skewed = measure_a2a_cfg4(dev, rank, world, R, brt_dist, 2.0)
         skew_loads = skewed.pop("loads_rank")
         skewed["locality"] = measure_locality(skew_loads, world, dev, brt_dist)
+        # the same bias towards the NEXT rank's experts (every rank's favourite experts live
+        # elsewhere, the case of benchmark/micro/distributed/placement_a2a.py:54-64): here the
+        # rank matching has something to find
+        shifted = measure_a2a_cfg4(dev, rank, world, R, brt_dist, 2.0, favour_shift=1,
+                                   loads_only=True)
+        skewed["locality_when_the_favoured_experts_sit_on_the_next_rank"] = measure_locality(
+            shifted["loads_rank"], world, dev, brt_dist)
         result["locality_cfg4"] = skewed
         result["checks"]["a2a_cfg4_round_trip_bit_exact"] = bool(
             plain["round_trip_bit_exact"] and skewed["round_trip_bit_exact"])
@@ -612,7 +619,8 @@ def exchange_checks(dev, rank, world, x, mask, gates, caps, cap, padded, R, brt_
             "rows_exchanged_per_rank": int(n_rows)}
 
 
-def measure_a2a_cfg4(dev, rank, world, R, brt_dist, local_bias: float, iters: int = 10):
+def measure_a2a_cfg4(dev, rank, world, R, brt_dist, local_bias: float, iters: int = 10,
+                     favour_shift: int = 0, loads_only: bool = False):
     """The exchange the metric's all-to-all figure is quoted on (cfg4: T = 65536 tokens per
     rank, d = 2048 bf16, 64 experts, top-2, packed buckets), forward and back, with the timing
     protocol of benchmark/micro/distributed/sparse_a2a.py:53-100: CUDA events around
@@ -630,10 +638,13 @@ def measure_a2a_cfg4(dev, rank, world, R, brt_dist, local_bias: float, iters: in
     gb = torch.Generator(device="cpu").manual_seed(4999)
     logits = torch.randn((T, E), generator=g) + torch.randn((E,), generator=gb)
     if local_bias:
-        logits[:, rank * G:(rank + 1) * G] += local_bias
+        favoured = (rank + favour_shift) % world
+        logits[:, favoured * G:(favoured + 1) * G] += local_bias
     picks = torch.topk(logits, k, dim=1).indices
     mask = torch.zeros((T, E), dtype=torch.int32).scatter_(1, picks, 1).to(dev)
     _, loads = R.generate_indices_and_loads(mask)
+    if loads_only:
+        return {"loads_rank": loads}
     rows = int(loads.sum().item())
     x = torch.empty((rows, d), dtype=torch.bfloat16, device=dev).normal_()
     sent = loads.reshape(world, G).sum(dim=1)
@@ -667,12 +678,21 @@ def measure_a2a_cfg4(dev, rank, world, R, brt_dist, local_bias: float, iters: in
     timed = json.loads(report.value.decode())
     fwd = statistics.mean(e[0].elapsed_time(e[1]) for e in evs)
     bwd = statistics.mean(e[1].elapsed_time(e[2]) for e in evs)
-    stats = torch.tensor([fwd, bwd, -float(remote), float(ok)], device=dev, dtype=torch.float64)
+    # bytes every rank sends to / receives from OTHER ranks in one direction of the exchange
+    _, recv_sizes, _ = brt_dist.group_sparse_a2a(x, loads)
+    got = recv_sizes.reshape(G, world).sum(dim=0)
+    received = int((got.sum() - got[rank]).item()) * d * 2
+    mine = torch.tensor([float(remote), float(received)], device=dev, dtype=torch.float64)
+    everyone = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(everyone, mine)
+    per_rank = torch.stack(everyone).cpu()
+    mean_remote = float(per_rank[:, 0].mean())
+    busiest = float(per_rank.max())
+    stats = torch.tensor([fwd, bwd], device=dev, dtype=torch.float64)
     dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-    fwd, bwd, min_remote, _ = stats.tolist()
+    fwd, bwd = stats.tolist()
     all_ok = torch.tensor([int(ok)], device=dev)
     dist.all_reduce(all_ok, op=dist.ReduceOp.MIN)
-    min_remote = -min_remote
     kernels = {name: round(t["total_ms"] / max(t["launches"], 1), 5)
                for name, t in timed.items() if name.startswith("p2p_")}
     from brainstorm_b200.runtime import p2p
@@ -680,13 +700,22 @@ def measure_a2a_cfg4(dev, rank, world, R, brt_dist, local_bias: float, iters: in
         "workload": "cfg4 exchange: T=65536 per rank, d=2048 bf16, E=64, top-2, packed buckets"
                     + (f", logits of a rank's own experts +{local_bias}" if local_bias else ""),
         "forward_ms": fwd, "backward_ms": bwd, "iterations": iters,
-        "remote_bytes_per_rank_per_direction": remote,
-        "bus_gbs_forward": min_remote / (fwd * 1e-3) / 1e9,
-        "bus_gbs_backward": min_remote / (bwd * 1e-3) / 1e9,
-        "frac_of_900_forward": min_remote / (fwd * 1e-3) / 1e9 / 900.0,
-        "frac_of_900_backward": min_remote / (bwd * 1e-3) / 1e9 / 900.0,
-        "bytes_note": "bus figures use the rank that sends the FEWEST remote bytes and the "
-                      "slowest rank's time",
+        "remote_bytes_per_rank_per_direction": {
+            "mean": mean_remote, "sent_min": float(per_rank[:, 0].min()),
+            "sent_max": float(per_rank[:, 0].max()), "received_max": float(per_rank[:, 1].max())},
+        "bus_gbs_forward": mean_remote / (fwd * 1e-3) / 1e9,
+        "bus_gbs_backward": mean_remote / (bwd * 1e-3) / 1e9,
+        "frac_of_900_forward": mean_remote / (fwd * 1e-3) / 1e9 / 900.0,
+        "frac_of_900_backward": mean_remote / (bwd * 1e-3) / 1e9 / 900.0,
+        "busiest_link_gbs_forward": busiest / (fwd * 1e-3) / 1e9,
+        "busiest_link_gbs_backward": busiest / (bwd * 1e-3) / 1e9,
+        "busiest_link_frac_of_900": busiest / (max(fwd, bwd) * 1e-3) / 1e9 / 900.0,
+        "bytes_note": "bus GB/s = mean over ranks of the bytes a rank sends to OTHER ranks per "
+                      "direction / the slowest rank's time of the op (host work included). "
+                      "The picks are skewed by the per-expert bias of the workload, so some "
+                      "rank receives (forward) and sends back (inverse) more than the mean: "
+                      "busiest_link is that rank's bytes over the same time, the figure the "
+                      "link ceiling applies to",
         "kernel_ms_rank0": kernels,
         "round_trip_bit_exact": bool(all_ok.item()),
         "transport": "peer-memory landing kernels over NVLink" if p2p.arena() is not None
