@@ -485,13 +485,14 @@ def run_gpu(args):
         plain = measure_a2a_cfg4(dev, rank, world, R, brt_dist, 0.0)
         plain.pop("loads_rank")
         result["a2a_cfg4"] = plain
-        skewed = measure_a2a_cfg4(dev, rank, world, R, brt_dist, 2.0)
+        bias = bias_for_local_fraction(world, 0.6)
+        skewed = measure_a2a_cfg4(dev, rank, world, R, brt_dist, bias)
         skew_loads = skewed.pop("loads_rank")
         skewed["locality"] = measure_locality(skew_loads, world, dev, brt_dist)
         # the same bias towards the NEXT rank's experts (every rank's favourite experts live
         # elsewhere, the case of benchmark/micro/distributed/placement_a2a.py:54-64): here the
         # rank matching has something to find
-        shifted = measure_a2a_cfg4(dev, rank, world, R, brt_dist, 2.0, favour_shift=1,
+        shifted = measure_a2a_cfg4(dev, rank, world, R, brt_dist, bias, favour_shift=1,
                                    loads_only=True)
         skewed["locality_when_the_favoured_experts_sit_on_the_next_rank"] = measure_locality(
             shifted["loads_rank"], world, dev, brt_dist)
@@ -617,6 +618,29 @@ def exchange_checks(dev, rank, world, x, mask, gates, caps, cap, padded, R, brt_
             "fused_dispatch_exchange": "ran" if fused is not None
             else "not available on this transport (two steps)", "ranks": world,
             "rows_exchanged_per_rank": int(n_rows)}
+
+
+def bias_for_local_fraction(world: int, target: float = 0.6) -> float:
+    """The value to add to the logits of ONE rank's experts so that about ``target`` of the
+    cfg4 top-2 picks go to them (the workload states 60 %); found by bisection on a sample
+    that every rank draws alike."""
+    w = WORKLOADS["cfg4"]
+    E, k = w["E"], w["k"]
+    G = E // world
+    g = torch.Generator(device="cpu").manual_seed(4242)
+    logits = torch.randn((8192, E), generator=g) + torch.randn(
+        (E,), generator=torch.Generator(device="cpu").manual_seed(4999))
+    lo, hi = 0.0, 8.0
+    for _ in range(24):
+        mid = 0.5 * (lo + hi)
+        biased = logits.clone()
+        biased[:, :G] += mid
+        local = float((torch.topk(biased, k, dim=1).indices < G).float().mean())
+        if local < target:
+            lo = mid
+        else:
+            hi = mid
+    return round(0.5 * (lo + hi), 3)
 
 
 def measure_a2a_cfg4(dev, rank, world, R, brt_dist, local_bias: float, iters: int = 10,
