@@ -21,12 +21,13 @@ def _free_port():
 
 
 @pytest.mark.parametrize("world", [2, 4])
-@pytest.mark.parametrize("transport", ["p2p", "p2p_small_arena", "nccl"])
+@pytest.mark.parametrize("transport", ["p2p", "p2p_small_arena", "p2p_private_copies", "nccl"])
 def test_expert_parallel_exchange(world, transport):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", BRT_P2P="0" if transport == "nccl" else "1",
-               BRT_P2P_ARENA_MB="1" if transport == "p2p_small_arena" else "64")
+               BRT_P2P_ARENA_MB="1" if transport == "p2p_small_arena" else "64",
+               BRT_P2P_ZERO_COPY="0" if transport == "p2p_private_copies" else "1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
            f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(_free_port()), str(HERE / "dist_worker.py")]
