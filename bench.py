@@ -482,9 +482,12 @@ def run_gpu(args):
     if distributed:
         result["checks"] = exchange_checks(dev, rank, world, x, mask, gates, caps, cap, padded,
                                            R, brt_dist)
-        plain = measure_a2a_cfg4(dev, rank, world, R, brt_dist, 0.0)
+        plain = measure_a2a_cfg4(dev, rank, world, R, brt_dist, 0.0, uniform_loads=True)
         plain.pop("loads_rank")
         result["a2a_cfg4"] = plain
+        hot = measure_a2a_cfg4(dev, rank, world, R, brt_dist, 0.0)
+        hot.pop("loads_rank")
+        result["a2a_cfg4_hot_experts"] = hot
         bias = bias_for_local_fraction(world, 0.6)
         skewed = measure_a2a_cfg4(dev, rank, world, R, brt_dist, bias)
         skew_loads = skewed.pop("loads_rank")
@@ -498,7 +501,8 @@ def run_gpu(args):
             shifted["loads_rank"], world, dev, brt_dist)
         result["locality_cfg4"] = skewed
         result["checks"]["a2a_cfg4_round_trip_bit_exact"] = bool(
-            plain["round_trip_bit_exact"] and skewed["round_trip_bit_exact"])
+            plain["round_trip_bit_exact"] and hot["round_trip_bit_exact"]
+            and skewed["round_trip_bit_exact"])
         result["locality"] = measure_locality(loads, world, dev, brt_dist)
         fwd = a2a_bytes[0]
         land_name = "dispatch_land_kernel" if fused_used[0] else "p2p_land_forward_kernel"
@@ -644,12 +648,18 @@ def bias_for_local_fraction(world: int, target: float = 0.6) -> float:
 
 
 def measure_a2a_cfg4(dev, rank, world, R, brt_dist, local_bias: float, iters: int = 10,
-                     favour_shift: int = 0, loads_only: bool = False):
+                     favour_shift: int = 0, loads_only: bool = False,
+                     uniform_loads: bool = False):
     """The exchange the metric's all-to-all figure is quoted on (cfg4: T = 65536 tokens per
     rank, d = 2048 bf16, 64 experts, top-2, packed buckets), forward and back, with the timing
     protocol of benchmark/micro/distributed/sparse_a2a.py:53-100: CUDA events around
     group_sparse_a2a and size_known_group_sparse_a2a, host work of the calls included.
     Bus GB/s = bytes this rank sends to OTHER ranks / time; the slowest rank counts.
+    ``uniform_loads``: the bucket sizes are drawn as that script draws them
+    (``torch.randint(load, (world * local_expert,))`` seeded by the rank, sparse_a2a.py:56-60)
+    with ``load`` = 2 x the mean cfg4 bucket, so a rank holds T * k rows on average; otherwise
+    they come from top-2 picks on gate logits that carry a per-expert bias shared by all
+    ranks (hot experts, so some rank receives well above the mean).
     ``local_bias`` > 0 skews each rank's picks towards its own experts
     (benchmark/micro/distributed/placement_a2a.py:54-80 measures that case)."""
     import torch.distributed as dist
@@ -664,9 +674,13 @@ def measure_a2a_cfg4(dev, rank, world, R, brt_dist, local_bias: float, iters: in
     if local_bias:
         favoured = (rank + favour_shift) % world
         logits[:, favoured * G:(favoured + 1) * G] += local_bias
-    picks = torch.topk(logits, k, dim=1).indices
-    mask = torch.zeros((T, E), dtype=torch.int32).scatter_(1, picks, 1).to(dev)
-    _, loads = R.generate_indices_and_loads(mask)
+    if uniform_loads:
+        gu = torch.Generator(device="cpu").manual_seed(rank)
+        loads = torch.randint(2 * T * k // E, (E,), generator=gu, dtype=torch.int32).to(dev)
+    else:
+        picks = torch.topk(logits, k, dim=1).indices
+        mask = torch.zeros((T, E), dtype=torch.int32).scatter_(1, picks, 1).to(dev)
+        _, loads = R.generate_indices_and_loads(mask)
     if loads_only:
         return {"loads_rank": loads}
     rows = int(loads.sum().item())
@@ -721,7 +735,12 @@ def measure_a2a_cfg4(dev, rank, world, R, brt_dist, local_bias: float, iters: in
                for name, t in timed.items() if name.startswith("p2p_")}
     from brainstorm_b200.runtime import p2p
     return {
-        "workload": "cfg4 exchange: T=65536 per rank, d=2048 bf16, E=64, top-2, packed buckets"
+        "workload": "cfg4 exchange: d=2048 bf16, E=64, packed buckets; "
+                    + ("bucket sizes ~ randint(4096) seeded by the rank (T*k = 131072 rows per "
+                       "rank on average), the draw of the reference's sparse_a2a.py"
+                       if uniform_loads else
+                       "T=65536 per rank, top-2 picks on logits with a per-expert bias shared "
+                       "by all ranks (hot experts)")
                     + (f", logits of a rank's own experts +{local_bias}" if local_bias else ""),
         "forward_ms": fwd, "backward_ms": bwd, "iterations": iters,
         "remote_bytes_per_rank_per_direction": {
@@ -736,10 +755,9 @@ def measure_a2a_cfg4(dev, rank, world, R, brt_dist, local_bias: float, iters: in
         "busiest_link_frac_of_900": busiest / (max(fwd, bwd) * 1e-3) / 1e9 / 900.0,
         "bytes_note": "bus GB/s = mean over ranks of the bytes a rank sends to OTHER ranks per "
                       "direction / the slowest rank's time of the op (host work included). "
-                      "The picks are skewed by the per-expert bias of the workload, so some "
-                      "rank receives (forward) and sends back (inverse) more than the mean: "
-                      "busiest_link is that rank's bytes over the same time, the figure the "
-                      "link ceiling applies to",
+                      "Where the buckets are uneven some rank receives (forward) and sends "
+                      "back (inverse) more than the mean: busiest_link is that rank's bytes "
+                      "over the same time, the figure the link ceiling applies to",
         "kernel_ms_rank0": kernels,
         "round_trip_bit_exact": bool(all_ok.item()),
         "transport": "peer-memory landing kernels over NVLink" if p2p.arena() is not None
@@ -1097,8 +1115,9 @@ def main():
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--local-bias", type=float, default=0.0,
-                    help="added to the logits of a rank's own experts (N>1): 2.0 sends about "
-                         "60%% of the top-2 picks of cfg4 to local experts")
+                    help="added to the logits of a rank's own experts in the timed step's workload "
+                         "(N>1); the locality_cfg4 block calibrates its own bias to 60%% local "
+                         "picks at the world size it runs on")
     ap.add_argument("--no-fused-exchange", action="store_true",
                     help="at N>1 run dispatch and the forward exchange as two ops instead of the "
                          "one kernel that stores the dispatched rows straight into the peers")

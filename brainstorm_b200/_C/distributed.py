@@ -447,6 +447,88 @@ def dispatch_group_sparse_all_to_all(in_data: torch.Tensor, route_indices: torch
         return [out, recv_t, send_t]
 
 
+class replayable_exchanges:
+    """``with replayable_exchanges():`` around ``*_device`` exchanges and their inverses makes
+    the sequence fit for CUDA graph capture: put the ``with`` inside ``torch.cuda.graph(...)``
+    and replay the graph, or run the block again, as often as wanted, with ordinary exchanges
+    in between if need be.  Every rank must do the same (the peers' kernels wait for each
+    other).  A replay overwrites the outputs of the previous one."""
+
+    def __enter__(self):
+        arena = p2p.arena()
+        if arena is None:
+            raise RuntimeError("replayable exchanges need the peer-memory arena")
+        arena.replay_begin()
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        p2p.arena().replay_end()
+        return False
+
+
+def _device_result(arena, x, received, ptr, capacity, xid, group_size, sent):
+    out = arena.view(ptr, capacity, x)
+    setattr(received, _TAG, (xid, group_size))
+    setattr(sent, _TAG, (xid, group_size))
+    return [out, received, sent]
+
+
+def group_sparse_all_to_all_device(in_data: torch.Tensor, send_sizes: torch.Tensor,
+                                   max_path_padding: bool = False, max_path_load: int = 0):
+    """``group_sparse_all_to_all`` without the host synchronisation of the reference's op
+    (src/distributed/collective.cc:157-166): the size tensors stay on the device.  Returns
+    (out_data, recv_sizes [G, W] int32 on the device, send_sizes on the device).  ``out_data``
+    is the whole landing half seen as rows; its first ``recv_sizes.sum()`` rows are the
+    output (with padding: every slot).  Peer-memory transport only; rows that do not fit the
+    landing half are an error reported by ``p2p.check_status()``."""
+    _check_cuda(in_data, "in_data")
+    _check_cuda(send_sizes, "send_sizes")
+    _, W = _world()
+    group_size = send_sizes.numel() // W
+    with torch.cuda.device(in_data.device):
+        x = _contig(in_data)
+        if not _p2p_usable(x, W, group_size) or (max_path_padding and not max_path_load):
+            raise RuntimeError("this exchange cannot use the peer-memory transport")
+        arena = p2p.arena()
+        stride = int(max_path_load) if max_path_padding else 0
+        x = arena.safe_source(x)
+        sizes32 = send_sizes.to(torch.int32).contiguous()
+        received, ptr, capacity, xid = arena.sparse_forward_device(
+            x, sizes32, group_size, _row_bytes(x), stride)
+        return _device_result(arena, x, received, ptr, capacity, xid, group_size, sizes32)
+
+
+def dispatch_group_sparse_all_to_all_device(in_data: torch.Tensor, route_indices: torch.Tensor,
+                                            loads: torch.Tensor, max_path_padding: bool = False,
+                                            max_path_load: int = 0):
+    """``dispatch_group_sparse_all_to_all`` with device-resident sizes (see
+    ``group_sparse_all_to_all_device``).  ``route_indices`` must come from this library's
+    index ops (dense seat columns)."""
+    from . import router as c_router
+
+    _check_cuda(in_data, "in_data")
+    _check_cuda(route_indices, "route_indices")
+    _, W = _world()
+    E = route_indices.size(1)
+    counts = getattr(route_indices, c_router._DENSE, None)
+    if counts is None or E % W != 0 or in_data.dim() < 2 or in_data.size(0) == 0 or \
+            loads.numel() != E or not loads.is_cuda or route_indices.dtype != torch.int32 or \
+            not route_indices.is_contiguous() or (max_path_padding and not max_path_load):
+        raise RuntimeError("this dispatch cannot be fused with the peer-memory exchange")
+    group_size = E // W
+    with torch.cuda.device(in_data.device):
+        x = _contig(in_data)
+        if not _p2p_usable(x, W, group_size):
+            raise RuntimeError("this exchange cannot use the peer-memory transport")
+        arena = p2p.arena()
+        stride = int(max_path_load) if max_path_padding else 0
+        x = arena.safe_source(x)
+        loads32 = loads.to(torch.int32).contiguous()
+        received, ptr, capacity, xid = arena.dispatch_forward_device(
+            x, route_indices, loads32, counts, group_size, _row_bytes(x), stride)
+        return _device_result(arena, x, received, ptr, capacity, xid, group_size, loads32)
+
+
 def size_known_group_sparse_all_to_all(in_data: torch.Tensor, send_sizes: torch.Tensor,
                                        recv_sizes: torch.Tensor,
                                        max_path_padding: bool = False) -> torch.Tensor:
@@ -471,6 +553,8 @@ def size_known_group_sparse_all_to_all(in_data: torch.Tensor, send_sizes: torch.
             x = arena.safe_source(x)
             try:
                 ptr, rows = arena.sparse_backward(tag[0], group_size, _row_bytes(x), stride, x)
+                if send_sizes.is_cuda:  # device-resident sizes: `rows` is the half's capacity
+                    return arena.view(ptr, rows, x)
                 return _landed(arena, ptr, rows, x)
             except _lib.BrtError as exc:
                 if exc.status != 4:  # BRT_ERR_UNSUPPORTED is the same verdict on every rank

@@ -89,6 +89,9 @@ SIGNATURES = {
                                               _vp, _vp, _int]),
     "brt_p2p_dispatch_land": (_int, [_vp, _vp, _vp, _i64, _i64, _vp, _vp, _int, _int, _int, _i64,
                                      _i64, _vp, _u64, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _vp]),
+    "brt_p2p_ctx_replay_begin": (_int, [_vp]),
+    "brt_p2p_ctx_replay_end": (_int, [_vp]),
+    "brt_p2p_forward_device_sizes": (_int, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "brt_p2p_sparse_forward_sizes": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "brt_p2p_sparse_backward": (_int, [_vp, _u64, _int, _i64, _i64, _int, _int, _vp, _vp, _int,
                                        _vp, _vp]),

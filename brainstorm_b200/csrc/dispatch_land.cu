@@ -51,6 +51,8 @@ struct DispatchLandArgs {
   long long stride_rows;   // 0: packed buckets
   long long half_bytes;
   unsigned long long epoch, limit_ns;
+  const unsigned long long* epoch_counter;  // see p2p::effective_epoch()
+  int strict;              // rows that do not fit are reported as an error
   const int* sizes;        // [world][world * group] on my board
   int* keep;
   const unsigned long long* ready_flags;
@@ -87,7 +89,8 @@ dispatch_land_kernel(const __grid_constant__ DispatchLandArgs a) {
   const int tid = threadIdx.x;
   const long long grain = a.row_vecs * 16;
 
-  bool go = p2p::wait_for_flags(a.ready_flags, W, -1, a.epoch, a.limit_ns);
+  const unsigned long long epoch = p2p::effective_epoch(a.epoch, a.epoch_counter);
+  bool go = p2p::wait_for_flags(a.ready_flags, W, -1, epoch, a.limit_ns);
   if (!go && tid == 0) {
     p2p::report_timeout(a.status);
     atomicExch(a.abort_word, 1u);
@@ -129,6 +132,8 @@ dispatch_land_kernel(const __grid_constant__ DispatchLandArgs a) {
     rows::setup_fill(a.dense_counts, n, 0, s_loads, s_written, s_fill);
   }
   const bool move = go && fits;
+  if (go && !fits && a.strict && blockIdx.x == 0 && tid == 0)
+    p2p::report_status(a.status, BRT_ERR_UNSUPPORTED);
 
   if (move) {
     const int lane = tid & 31;
@@ -264,7 +269,7 @@ dispatch_land_kernel(const __grid_constant__ DispatchLandArgs a) {
       const unsigned int aborted = atomicExch(a.abort_word, 0u);
       __threadfence_system();
       if (aborted == 0u)
-        for (int r = 0; r < W; r++) p2p::store_release_sys(a.arrive_flags[r] + me, a.epoch);
+        for (int r = 0; r < W; r++) p2p::store_release_sys(a.arrive_flags[r] + me, epoch);
     }
   }
 }
@@ -303,6 +308,26 @@ BRT_API int brt_p2p_dispatch_land(
     void* const* peer_arrive_flag_arrays, void* my_done_counter, void* my_abort_word,
     void* status_word, void* host_status_word, uint64_t wait_limit_ns, void* stream) {
   clear_error();
+  return p2p_dispatch_land_launch(src_data, route_indices, dense_counts, cell_num, row_bytes,
+                                  size_matrix, keep_matrix, world_size, group_size, my_rank,
+                                  stride_rows, half_bytes, landing_ptrs, epoch, my_ready_flags,
+                                  peer_arrive_flag_arrays, my_done_counter, my_abort_word,
+                                  status_word, host_status_word, wait_limit_ns, P2pReplay{},
+                                  stream);
+}
+
+}  // extern "C"
+
+namespace brt_b200 {
+int p2p_dispatch_land_launch(const void* src_data, const int32_t* route_indices,
+                             const int32_t* dense_counts, int64_t cell_num, int64_t row_bytes,
+                             const int32_t* size_matrix, int32_t* keep_matrix, int world_size,
+                             int group_size, int my_rank, int64_t stride_rows,
+                             int64_t half_bytes, void* const* landing_ptrs, uint64_t epoch,
+                             const void* my_ready_flags, void* const* peer_arrive_flag_arrays,
+                             void* my_done_counter, void* my_abort_word, void* status_word,
+                             void* host_status_word, uint64_t wait_limit_ns,
+                             const P2pReplay& replay, void* stream) {
   BRT_REQUIRE(route_indices != nullptr && dense_counts != nullptr && size_matrix != nullptr &&
                   landing_ptrs != nullptr && my_ready_flags != nullptr &&
                   peer_arrive_flag_arrays != nullptr && my_done_counter != nullptr &&
@@ -330,6 +355,8 @@ BRT_API int brt_p2p_dispatch_land(
   a.stride_rows = stride_rows;
   a.half_bytes = half_bytes;
   a.epoch = epoch;
+  a.epoch_counter = static_cast<const unsigned long long*>(replay.epoch_counter);
+  a.strict = replay.strict;
   a.limit_ns = wait_limit_ns;
   a.sizes = size_matrix;
   a.keep = keep_matrix;
@@ -349,5 +376,4 @@ BRT_API int brt_p2p_dispatch_land(
   if (n % 4 == 0 && aligned_to(route_indices, 16)) return launch<4>(a, st);
   return launch<1>(a, st);
 }
-
-}  // extern "C"
+}  // namespace brt_b200

@@ -129,6 +129,8 @@ struct LandArgs {
   long long stride_rows;  // 0: packed
   long long half_bytes;   // capacity of a landing half
   unsigned long long epoch;
+  const unsigned long long* epoch_counter;  // see effective_epoch()
+  int strict;             // a landing that does not fit is an error (reported), not a verdict
   unsigned long long limit_ns;
   const int* sizes;                         // the matrix [world][world * group] (device)
   int* keep;                                // forward: copy of the matrix kept for the inverse
@@ -153,10 +155,11 @@ p2p_land_kernel(const char* __restrict__ src, const __grid_constant__ LandArgs a
   const int tid = threadIdx.x;
   const int W = a.world_size, G = a.group_size, me = a.my_rank;
   const int n = W * G;
+  const unsigned long long epoch = effective_epoch(a.epoch, a.epoch_counter);
 
   // every rank has entered this exchange: the sizes are on my board and the landing halves
   // may be written
-  bool go = wait_for_flags(a.ready_flags, W, -1, a.epoch, a.limit_ns);
+  bool go = wait_for_flags(a.ready_flags, W, -1, epoch, a.limit_ns);
   if (!go) {
     if (tid == 0) {
       report_timeout(a.status);
@@ -251,6 +254,8 @@ p2p_land_kernel(const char* __restrict__ src, const __grid_constant__ LandArgs a
   }
   __syncthreads();
   const bool move = go && fits;
+  if (go && !fits && a.strict && blockIdx.x == 0 && tid == 0)
+    report_status(a.status, BRT_ERR_UNSUPPORTED);
   for (int p = tid; p < n; p += kThreads) {
     const long long bytes = (long long)s_rows[p] * a.grain;
     s_first[p] = move ? (int)((bytes + kChunkBytes - 1) / kChunkBytes) : 0;
@@ -317,7 +322,7 @@ p2p_land_kernel(const char* __restrict__ src, const __grid_constant__ LandArgs a
       const unsigned int aborted = atomicExch(a.abort_word, 0u);
       __threadfence_system();
       if (aborted == 0u)
-        for (int r = 0; r < W; r++) store_release_sys(a.arrive_flags[r] + me, a.epoch);
+        for (int r = 0; r < W; r++) store_release_sys(a.arrive_flags[r] + me, epoch);
     }
   }
 }
@@ -329,12 +334,20 @@ struct PostList {
   int my_rank;
   int n;
   unsigned long long epoch;
+  unsigned long long* epoch_counter;  // advanced here: this kernel opens the exchange
   int* peer_board[kMaxRanks];
   unsigned long long* peer_flags[kMaxRanks];
 };
 
 __global__ void __launch_bounds__(kThreads)
 p2p_post_kernel(const int* __restrict__ values, const __grid_constant__ PostList post) {
+  unsigned long long epoch = post.epoch;
+  if (post.epoch_counter != nullptr) {  // read by thread 0 only: no other thread needs it
+    if (threadIdx.x == 0) {
+      epoch = *post.epoch_counter + 1;
+      *post.epoch_counter = epoch;
+    }
+  }
   for (int r = 0; r < post.world_size; r++)
     for (int t = threadIdx.x; t < post.n; t += kThreads)
       post.peer_board[r][post.my_rank * post.n + t] = values[t];
@@ -342,15 +355,37 @@ p2p_post_kernel(const int* __restrict__ values, const __grid_constant__ PostList
   __syncthreads();
   if (threadIdx.x == 0)
     for (int r = 0; r < post.world_size; r++)
-      store_release_sys(post.peer_flags[r] + post.my_rank, post.epoch);
+      store_release_sys(post.peer_flags[r] + post.my_rank, epoch);
 }
 
 __global__ void __launch_bounds__(32)
 p2p_wait_kernel(const unsigned long long* __restrict__ my_flags, int world_size, int skip_rank,
-                unsigned long long epoch, unsigned long long limit_ns, const StatusSink status) {
-  if (!wait_for_flags(my_flags, world_size, skip_rank, epoch, limit_ns) && threadIdx.x == 0)
+                unsigned long long epoch, const unsigned long long* epoch_counter,
+                unsigned long long limit_ns, const StatusSink status) {
+  if (!wait_for_flags(my_flags, world_size, skip_rank, effective_epoch(epoch, epoch_counter),
+                      limit_ns) &&
+      threadIdx.x == 0)
     report_timeout(status);
 }
+
+// The rows this rank receives, in the order of its landed output: [expert j][source rank s].
+__global__ void __launch_bounds__(kThreads)
+p2p_received_sizes_kernel(const int* __restrict__ board, int world_size, int group_size,
+                          int my_rank, const unsigned long long* __restrict__ ready_flags,
+                          unsigned long long epoch, const unsigned long long* epoch_counter,
+                          unsigned long long limit_ns, int* __restrict__ out_loads,
+                          const StatusSink status) {
+  const int n = world_size * group_size;
+  const bool go = wait_for_flags(ready_flags, world_size, -1,
+                                 effective_epoch(epoch, epoch_counter), limit_ns);
+  if (!go && threadIdx.x == 0) report_timeout(status);
+  for (int p = threadIdx.x; p < n; p += kThreads) {
+    const int j = p / world_size, s = p - j * world_size;
+    const int v = go ? __ldcg(board + s * n + my_rank * group_size + j) : 0;
+    out_loads[p] = v > 0 ? v : 0;
+  }
+}
+
 
 }  // namespace
 }  // namespace brt_b200
@@ -471,6 +506,22 @@ BRT_API int brt_p2p_land(const void* rows, const int32_t* size_matrix, int32_t* 
                          void* my_abort_word, void* status_word, void* host_status_word,
                          uint64_t wait_limit_ns, void* stream) {
   clear_error();
+  return p2p_land_launch(rows, size_matrix, keep_matrix, world_size, group_size, my_rank, layout,
+                         zero_tails, grain_bytes, stride_rows, half_bytes, landing_ptrs, epoch,
+                         my_ready_flags, peer_arrive_flag_arrays, my_done_counter, my_abort_word,
+                         status_word, host_status_word, wait_limit_ns, P2pReplay{}, stream);
+}
+
+}  // extern "C"
+
+namespace brt_b200 {
+int p2p_land_launch(const void* rows, const int32_t* size_matrix, int32_t* keep_matrix,
+                    int world_size, int group_size, int my_rank, int layout, int zero_tails,
+                    int64_t grain_bytes, int64_t stride_rows, int64_t half_bytes,
+                    void* const* landing_ptrs, uint64_t epoch, const void* my_ready_flags,
+                    void* const* peer_arrive_flag_arrays, void* my_done_counter,
+                    void* my_abort_word, void* status_word, void* host_status_word,
+                    uint64_t wait_limit_ns, const P2pReplay& replay, void* stream) {
   // rows may be null for a rank that holds no rows (all its sizes are zero)
   BRT_REQUIRE(size_matrix != nullptr && landing_ptrs != nullptr && my_ready_flags != nullptr &&
                   peer_arrive_flag_arrays != nullptr && my_done_counter != nullptr &&
@@ -498,6 +549,8 @@ BRT_API int brt_p2p_land(const void* rows, const int32_t* size_matrix, int32_t* 
   a.stride_rows = stride_rows;
   a.half_bytes = half_bytes;
   a.epoch = epoch;
+  a.epoch_counter = static_cast<const unsigned long long*>(replay.epoch_counter);
+  a.strict = replay.strict;
   a.limit_ns = wait_limit_ns;
   a.sizes = size_matrix;
   a.keep = keep_matrix;
@@ -523,10 +576,9 @@ BRT_API int brt_p2p_land(const void* rows, const int32_t* size_matrix, int32_t* 
   return BRT_OK;
 }
 
-BRT_API int brt_p2p_post(const int32_t* values, int n, int world_size, int my_rank,
-                         uint64_t epoch, void* const* peer_boards, void* const* peer_flag_arrays,
-                         void* stream) {
-  clear_error();
+int p2p_post_launch(const int32_t* values, int n, int world_size, int my_rank, uint64_t epoch,
+                    void* const* peer_boards, void* const* peer_flag_arrays,
+                    const P2pReplay& replay, void* stream) {
   BRT_REQUIRE(n >= 0 && (n == 0 || (values != nullptr && peer_boards != nullptr)) &&
                   peer_flag_arrays != nullptr,
               "bad arguments");
@@ -537,6 +589,7 @@ BRT_API int brt_p2p_post(const int32_t* values, int n, int world_size, int my_ra
   post.my_rank = my_rank;
   post.n = n;
   post.epoch = epoch;
+  post.epoch_counter = static_cast<unsigned long long*>(replay.epoch_counter);
   for (int r = 0; r < world_size; r++) {
     post.peer_board[r] = n > 0 ? static_cast<int*>(peer_boards[r]) : nullptr;
     post.peer_flags[r] = static_cast<unsigned long long*>(peer_flag_arrays[r]);
@@ -547,10 +600,9 @@ BRT_API int brt_p2p_post(const int32_t* values, int n, int world_size, int my_ra
   return BRT_OK;
 }
 
-BRT_API int brt_p2p_wait(const void* my_flag_array, int world_size, int skip_rank,
-                         uint64_t epoch, void* status_word, void* host_status_word,
-                         uint64_t wait_limit_ns, void* stream) {
-  clear_error();
+int p2p_wait_launch(const void* my_flag_array, int world_size, int skip_rank, uint64_t epoch,
+                    void* status_word, void* host_status_word, uint64_t wait_limit_ns,
+                    const P2pReplay& replay, void* stream) {
   BRT_REQUIRE(my_flag_array != nullptr && status_word != nullptr, "null control pointers");
   BRT_REQUIRE(world_size >= 1 && world_size <= kMaxRanks, "bad world size %d", world_size);
   StatusSink sink;
@@ -559,9 +611,52 @@ BRT_API int brt_p2p_wait(const void* my_flag_array, int world_size, int skip_ran
   const KernelTimer timer("p2p_wait_kernel", static_cast<cudaStream_t>(stream));
   p2p_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const unsigned long long*>(my_flag_array), world_size, skip_rank, epoch,
-      wait_limit_ns, sink), note_launch();
+      static_cast<const unsigned long long*>(replay.epoch_counter), wait_limit_ns, sink),
+      note_launch();
   BRT_LAUNCH_CHECK("p2p_wait_kernel");
   return BRT_OK;
+}
+
+int p2p_received_sizes_launch(const int32_t* board, int world_size, int group_size, int my_rank,
+                              uint64_t epoch, const void* my_ready_flags, int32_t* out_loads,
+                              void* status_word, void* host_status_word, uint64_t wait_limit_ns,
+                              const P2pReplay& replay, void* stream) {
+  BRT_REQUIRE(board != nullptr && my_ready_flags != nullptr && out_loads != nullptr &&
+                  status_word != nullptr,
+              "null pointers");
+  BRT_REQUIRE(world_size >= 1 && world_size <= kMaxRanks && my_rank >= 0 && my_rank < world_size &&
+                  group_size >= 1 && (long long)world_size * group_size <= kMaxBuckets,
+              "bad geometry");
+  StatusSink sink;
+  sink.device_word = static_cast<int*>(status_word);
+  sink.host_word = static_cast<int*>(host_status_word);
+  const KernelTimer timer("p2p_received_sizes_kernel", static_cast<cudaStream_t>(stream));
+  p2p_received_sizes_kernel<<<1, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      board, world_size, group_size, my_rank,
+      static_cast<const unsigned long long*>(my_ready_flags), epoch,
+      static_cast<const unsigned long long*>(replay.epoch_counter), wait_limit_ns, out_loads,
+      sink), note_launch();
+  BRT_LAUNCH_CHECK("p2p_received_sizes_kernel");
+  return BRT_OK;
+}
+}  // namespace brt_b200
+
+extern "C" {
+
+BRT_API int brt_p2p_post(const int32_t* values, int n, int world_size, int my_rank,
+                         uint64_t epoch, void* const* peer_boards, void* const* peer_flag_arrays,
+                         void* stream) {
+  clear_error();
+  return p2p_post_launch(values, n, world_size, my_rank, epoch, peer_boards, peer_flag_arrays,
+                         P2pReplay{}, stream);
+}
+
+BRT_API int brt_p2p_wait(const void* my_flag_array, int world_size, int skip_rank,
+                         uint64_t epoch, void* status_word, void* host_status_word,
+                         uint64_t wait_limit_ns, void* stream) {
+  clear_error();
+  return p2p_wait_launch(my_flag_array, world_size, skip_rank, epoch, status_word,
+                         host_status_word, wait_limit_ns, P2pReplay{}, stream);
 }
 
 }  // extern "C"

@@ -28,18 +28,30 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
   return t;
 }
 
+// The epoch of an exchange: the `epoch` argument for callers that count exchanges themselves,
+// else the value of a counter in the rank's own arena that the post kernel (the first kernel
+// of every exchange) advances.  A device-side count keeps growing when kernels with fixed
+// arguments run again, i.e. when exchanges are replayed from a CUDA graph.
+__device__ __forceinline__ unsigned long long effective_epoch(unsigned long long epoch,
+                                                              const unsigned long long* counter) {
+  return counter != nullptr ? __ldcg(counter) : epoch;
+}
+
 // Where a bounded wait reports that it ran out: the arena's status word and a word of
 // host-mapped memory that the host can read without synchronising with the device.
 struct StatusSink {
   int* device_word;
   int* host_word;
 };
-__device__ __forceinline__ void report_timeout(const StatusSink& s) {
-  if (s.device_word != nullptr) atomicExch(s.device_word, BRT_ERR_TIMEOUT);
+__device__ __forceinline__ void report_status(const StatusSink& s, int code) {
+  if (s.device_word != nullptr) atomicExch(s.device_word, code);
   if (s.host_word != nullptr) {
-    *reinterpret_cast<volatile int*>(s.host_word) = BRT_ERR_TIMEOUT;
+    *reinterpret_cast<volatile int*>(s.host_word) = code;
     __threadfence_system();
   }
+}
+__device__ __forceinline__ void report_timeout(const StatusSink& s) {
+  report_status(s, BRT_ERR_TIMEOUT);
 }
 
 // Thread r of the CTA (r < world_size, r != skip) polls flags[r] until it holds a value
@@ -98,4 +110,41 @@ __device__ __forceinline__ void block_exclusive_scan(int* a, int n, int* s_warp)
 }
 
 }  // namespace p2p
+
+// What the exchange context adds to the public low-level entry points: the arena's epoch
+// counter (see effective_epoch), and `strict` (a landing that does not fit its half reports
+// BRT_ERR_UNSUPPORTED through the status words instead of leaving the verdict to the host).
+struct P2pReplay {
+  void* epoch_counter = nullptr;
+  int strict = 0;
+};
+int p2p_land_launch(const void* rows, const int32_t* size_matrix, int32_t* keep_matrix,
+                    int world_size, int group_size, int my_rank, int layout, int zero_tails,
+                    int64_t grain_bytes, int64_t stride_rows, int64_t half_bytes,
+                    void* const* landing_ptrs, uint64_t epoch, const void* my_ready_flags,
+                    void* const* peer_arrive_flag_arrays, void* my_done_counter,
+                    void* my_abort_word, void* status_word, void* host_status_word,
+                    uint64_t wait_limit_ns, const P2pReplay& replay, void* stream);
+int p2p_post_launch(const int32_t* values, int n, int world_size, int my_rank, uint64_t epoch,
+                    void* const* peer_boards, void* const* peer_flag_arrays,
+                    const P2pReplay& replay, void* stream);
+int p2p_wait_launch(const void* my_flag_array, int world_size, int skip_rank, uint64_t epoch,
+                    void* status_word, void* host_status_word, uint64_t wait_limit_ns,
+                    const P2pReplay& replay, void* stream);
+int p2p_dispatch_land_launch(const void* src_data, const int32_t* route_indices,
+                             const int32_t* dense_counts, int64_t cell_num, int64_t row_bytes,
+                             const int32_t* size_matrix, int32_t* keep_matrix, int world_size,
+                             int group_size, int my_rank, int64_t stride_rows,
+                             int64_t half_bytes, void* const* landing_ptrs, uint64_t epoch,
+                             const void* my_ready_flags, void* const* peer_arrive_flag_arrays,
+                             void* my_done_counter, void* my_abort_word, void* status_word,
+                             void* host_status_word, uint64_t wait_limit_ns,
+                             const P2pReplay& replay, void* stream);
+// out_loads[j * world + s] = rows rank s sends to my expert j in the exchange whose sizes are
+// on `board`, once every rank's ready flag shows the exchange (bounded wait).
+int p2p_received_sizes_launch(const int32_t* board, int world_size, int group_size, int my_rank,
+                              uint64_t epoch, const void* my_ready_flags, int32_t* out_loads,
+                              void* status_word, void* host_status_word, uint64_t wait_limit_ns,
+                              const P2pReplay& replay, void* stream);
+
 }  // namespace brt_b200

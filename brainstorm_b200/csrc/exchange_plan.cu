@@ -8,19 +8,31 @@
 //   256      32 x uint64  ready flags                  (slot r: last exchange rank r entered)
 //   512      uint32       completion counter of this rank's landing kernel
 //   516      uint32       abort word of this rank's landing kernel
+//   520      uint64       epoch counter: exchanges this rank has opened (device-side count)
 //   1024     int32        status word of the bounded waits
 //   2048     two size boards of kBoardInts int32 each, used alternately
-//   65536    kKept size matrices (kBoardInts int32 each) kept for the inverse exchanges
+//   65536    kKept + kKeptReplay size matrices (kBoardInts int32 each) kept for the inverse
+//            exchanges; the last kKeptReplay belong to exchanges issued for replay
+//   ...      two more size boards, for the exchanges issued for replay
 //   kControlBytes ..      two landing halves of half_bytes each
 //
 // All ranks call the exchanges in the same order, so the exchange counter advances in step
-// on every rank; it is the epoch of the flags, it selects the landing half (counter & 1) and
-// it is the identifier under which a forward exchange's size matrix is kept.
+// on every rank.  The host's count selects the landing half and the size board (count & 1)
+// and is the identifier under which a forward exchange's size matrix is kept; the epoch of
+// the flags is a second count kept on the device, advanced by the kernel that opens an
+// exchange, so that it keeps growing when the same kernels run again from a CUDA graph.
+//
+// Replays.  Between brt_p2p_ctx_replay_begin and _end the caller issues exchanges whose sizes
+// stay on the device (brt_p2p_forward_device_sizes instead of brt_p2p_sparse_forward_sizes),
+// normally while a CUDA graph is being captured.  Such exchanges use size boards and kept
+// matrices of their own, so that replaying them between ordinary exchanges never touches a
+// board or a matrix an ordinary exchange still needs; their landing halves are the ones the
+// host's count named when they were issued, on every replay.
 #include <cstdlib>
 #include <cstring>
 #include <vector>
 
-#include "common.cuh"
+#include "exchange_p2p.cuh"
 
 namespace brt_b200 {
 namespace {
@@ -30,18 +42,24 @@ constexpr size_t kFlagsOffset = 0;
 constexpr size_t kReadyOffset = 256;
 constexpr size_t kCounterOffset = 512;
 constexpr size_t kAbortOffset = 516;
+constexpr size_t kEpochCounter = 520;
 constexpr size_t kStatusOffset = 1024;
 constexpr size_t kBoardOffset = 2048;
 constexpr size_t kBoardInts = (65536 - kBoardOffset) / 8;
 constexpr size_t kKeptOffset = 65536;
 constexpr int kKept = 32;
+constexpr int kKeptReplay = 16;
 constexpr size_t kControlBytes = 2u << 20;
-static_assert(kKeptOffset + kKept * kBoardInts * 4 <= kControlBytes, "control block too small");
+constexpr size_t kReplayBoardOffset = kKeptOffset + (kKept + kKeptReplay) * kBoardInts * 4;
+static_assert(kReplayBoardOffset + 2 * kBoardInts * 4 <= kControlBytes,
+              "control block too small");
 constexpr uint64_t kDefaultWaitNs = 2000000000ull;  // 2 s: a bound on the skew between ranks
 
 struct KeptMatrix {
   uint64_t id = 0;  // 0: empty
   int group = 0;
+  int slot = 0;                // which device copy (see kKeptOffset) holds it
+  bool device_only = false;    // the host never saw the sizes
   std::vector<int32_t> sizes;  // [world][world * group]
 };
 
@@ -64,6 +82,10 @@ struct brt_p2p_ctx {
   brt_b200::KeptMatrix kept[brt_b200::kKept];
   // forward exchange whose sizes have not been read yet
   uint64_t pending = 0;
+  int pending_slot = 0;
+  size_t pending_board = 0;  // byte offset of its size board in every arena
+  bool replaying = false;
+  uint64_t replay_slots = 0;
   int group = 0, layout = 0;
   int64_t grain = 0, stride = 0;
 };
@@ -76,6 +98,10 @@ char* half_of(const brt_p2p_ctx* c, int r, uint64_t exchange) {
 }
 
 int check_alive(const brt_p2p_ctx* c) {
+  if (c->host_status[0] == BRT_ERR_UNSUPPORTED)
+    return set_error(BRT_ERR_UNSUPPORTED,
+                     "an earlier peer exchange with device-resident sizes carried rows that "
+                     "do not fit a landing half (brt_p2p_ctx_reset_status clears this)");
   if (c->host_status[0] != 0)
     return set_error(BRT_ERR_TIMEOUT,
                      "an earlier peer exchange timed out waiting for another rank "
@@ -83,21 +109,33 @@ int check_alive(const brt_p2p_ctx* c) {
   return BRT_OK;
 }
 
+P2pReplay replay_of(const brt_p2p_ctx* c, bool strict) {
+  P2pReplay r;
+  r.epoch_counter = c->base + kEpochCounter;
+  r.strict = strict ? 1 : 0;
+  return r;
+}
+
+int32_t* kept_slot(const brt_p2p_ctx* c, int slot) {
+  return reinterpret_cast<int32_t*>(c->base + kKeptOffset) + (size_t)slot * kBoardInts;
+}
+
 int land(brt_p2p_ctx* c, const void* rows, const int32_t* matrix, int32_t* keep, int group,
          int layout, int zero_tails, int64_t grain, int64_t stride, uint64_t exchange,
-         void* stream) {
+         bool strict, void* stream) {
   void* halves[kMaxRanks];
   for (int r = 0; r < c->world; r++) halves[r] = half_of(c, r, exchange);
-  return brt_p2p_land(rows, matrix, keep, c->world, group, c->rank, layout, zero_tails, grain,
-                      stride,
-                      (int64_t)c->half_bytes, halves, exchange, c->base + kReadyOffset,
-                      c->arrive_flags, c->base + kCounterOffset, c->base + kAbortOffset,
-                      c->base + kStatusOffset, c->host_status_dev, c->wait_ns, stream);
+  return p2p_land_launch(rows, matrix, keep, c->world, group, c->rank, layout, zero_tails, grain,
+                         stride, (int64_t)c->half_bytes, halves, exchange,
+                         c->base + kReadyOffset, c->arrive_flags, c->base + kCounterOffset,
+                         c->base + kAbortOffset, c->base + kStatusOffset, c->host_status_dev,
+                         c->wait_ns, replay_of(c, strict), stream);
 }
 
 int wait_arrivals(brt_p2p_ctx* c, uint64_t exchange, void* stream) {
-  return brt_p2p_wait(c->base + kFlagsOffset, c->world, c->rank, exchange,
-                      c->base + kStatusOffset, c->host_status_dev, c->wait_ns, stream);
+  return p2p_wait_launch(c->base + kFlagsOffset, c->world, c->rank, exchange,
+                         c->base + kStatusOffset, c->host_status_dev, c->wait_ns,
+                         replay_of(c, false), stream);
 }
 
 }  // namespace
@@ -200,19 +238,26 @@ int forward_begin(brt_p2p_ctx* c, const void* rows, const FusedDispatch* fused,
     return set_error(BRT_ERR_UNSUPPORTED, "%d buckets are too many for the peer exchange", n);
   if (stages == 0) stages = BRT_P2P_STAGE_ALL;
   if (int rc = check_alive(c)) return rc;
+  BRT_REQUIRE(!c->replaying || !(stages & BRT_P2P_STAGE_SIZES),
+              "exchanges issued for replay keep their sizes on the device "
+              "(brt_p2p_forward_device_sizes); the SIZES stage brings them to the host");
   if (stages & BRT_P2P_STAGE_POST) {
     BRT_REQUIRE(c->pending == 0, "the sizes of the previous forward exchange were never read");
     c->exchanges++;
     c->pending = c->exchanges;
+    c->pending_slot = c->replaying ? kKept + (int)(c->replay_slots++ % kKeptReplay)
+                                   : (int)(c->exchanges % kKept);
+    c->pending_board = (c->replaying ? kReplayBoardOffset : kBoardOffset) +
+                       4 * (c->exchanges & 1) * kBoardInts;
     c->group = group_size;
     c->layout = layout;
     c->grain = grain_bytes;
     c->stride = stride_rows;
-    const size_t board = kBoardOffset + 4 * (c->exchanges & 1) * kBoardInts;
+    const size_t board = c->pending_board;
     void* boards[kMaxRanks];
     for (int r = 0; r < c->world; r++) boards[r] = c->peer[r] + board;
-    if (int rc = brt_p2p_post(sizes, n, c->world, c->rank, c->exchanges, boards, c->ready_flags,
-                              main_stream))
+    if (int rc = p2p_post_launch(sizes, n, c->world, c->rank, c->exchanges, boards,
+                                 c->ready_flags, replay_of(c, false), main_stream))
       return rc;
     if (main_stream != side_stream) {
       BRT_CUDA_TRY(cudaEventRecord(c->fork, static_cast<cudaStream_t>(main_stream)));
@@ -223,13 +268,14 @@ int forward_begin(brt_p2p_ctx* c, const void* rows, const FusedDispatch* fused,
                   c->stride == stride_rows && c->layout == layout,
               "stages of one exchange must be issued with the same geometry");
   const uint64_t x = c->pending;
-  const size_t board = kBoardOffset + 4 * (x & 1) * kBoardInts;
+  const size_t board = c->pending_board;
   if (stages & BRT_P2P_STAGE_SIZES) {
     // the sizes reach the host beside the data: a wait on the ready flags (raised by kernels
     // of OTHER GPUs and by my post above), then the board and the status word come down
     cudaStream_t side = static_cast<cudaStream_t>(side_stream);
-    if (int rc = brt_p2p_wait(c->base + kReadyOffset, c->world, -1, x, c->base + kStatusOffset,
-                              c->host_status_dev, c->wait_ns, side_stream))
+    if (int rc = p2p_wait_launch(c->base + kReadyOffset, c->world, -1, x,
+                                 c->base + kStatusOffset, c->host_status_dev, c->wait_ns,
+                                 replay_of(c, false), side_stream))
       return rc;
     BRT_CUDA_TRY(cudaMemcpyAsync(c->pinned, c->base + kStatusOffset, 4, cudaMemcpyDeviceToHost,
                                  side));
@@ -237,21 +283,22 @@ int forward_begin(brt_p2p_ctx* c, const void* rows, const FusedDispatch* fused,
                                  cudaMemcpyDeviceToHost, side));
   }
   if (stages & BRT_P2P_STAGE_PUSH) {
-    int32_t* keep = reinterpret_cast<int32_t*>(c->base + kKeptOffset) + (x % kKept) * kBoardInts;
+    int32_t* keep = kept_slot(c, c->pending_slot);
     const int32_t* matrix = reinterpret_cast<const int32_t*>(c->base + board);
+    const bool strict = (stages & BRT_P2P_STAGE_STRICT) != 0;
     if (fused == nullptr) {
       if (int rc = land(c, rows, matrix, keep, group_size, layout, 0, grain_bytes, stride_rows, x,
-                        main_stream))
+                        strict, main_stream))
         return rc;
     } else {
       void* halves[kMaxRanks];
       for (int r = 0; r < c->world; r++) halves[r] = half_of(c, r, x);
-      if (int rc = brt_p2p_dispatch_land(
+      if (int rc = p2p_dispatch_land_launch(
               fused->src, fused->indices, fused->dense_counts, fused->cell_num, grain_bytes,
               matrix, keep, c->world, group_size, c->rank, stride_rows, (int64_t)c->half_bytes,
               halves, x, c->base + kReadyOffset, c->arrive_flags, c->base + kCounterOffset,
               c->base + kAbortOffset, c->base + kStatusOffset, c->host_status_dev, c->wait_ns,
-              main_stream))
+              replay_of(c, strict), main_stream))
         return rc;
     }
   }
@@ -312,12 +359,61 @@ BRT_API int brt_p2p_sparse_forward_sizes(brt_p2p_ctx* c, void* side_stream,
   KeptMatrix& k = c->kept[x % kKept];
   k.id = x;
   k.group = G;
+  k.slot = c->pending_slot;
+  k.device_only = false;
   k.sizes.assign(S, S + (size_t)W * n);
   *size_matrix = S;
   *out_rows = rows;
   *fits = ok;
   *out_data = half_of(c, c->rank, x);
   *exchange_id = x;
+  return BRT_OK;
+}
+
+BRT_API int brt_p2p_forward_device_sizes(brt_p2p_ctx* c, int32_t* received_sizes,
+                                         void* stream, void** out_data,
+                                         int64_t* capacity_rows, uint64_t* exchange_id) {
+  clear_error();
+  BRT_REQUIRE(c != nullptr && received_sizes != nullptr && out_data != nullptr &&
+                  capacity_rows != nullptr && exchange_id != nullptr,
+              "null pointers");
+  BRT_REQUIRE(c->pending != 0, "no forward exchange in flight");
+  const uint64_t x = c->pending;
+  const int W = c->world, G = c->group, n = W * G;
+  const size_t board = c->pending_board;
+  if (int rc = p2p_received_sizes_launch(
+          reinterpret_cast<const int32_t*>(c->base + board), W, G, c->rank, x,
+          c->base + kReadyOffset, received_sizes, c->base + kStatusOffset, c->host_status_dev,
+          c->wait_ns, replay_of(c, false), stream))
+    return rc;
+  c->pending = 0;
+  KeptMatrix& k = c->kept[x % kKept];
+  k.id = x;
+  k.group = G;
+  k.slot = c->pending_slot;
+  k.device_only = true;
+  k.sizes.clear();
+  *out_data = half_of(c, c->rank, x);
+  *capacity_rows = c->stride ? c->stride * n : (int64_t)c->half_bytes / c->grain;
+  *exchange_id = x;
+  return BRT_OK;
+}
+
+BRT_API int brt_p2p_ctx_replay_begin(brt_p2p_ctx* c) {
+  clear_error();
+  BRT_REQUIRE(c != nullptr, "null context");
+  BRT_REQUIRE(!c->replaying, "a replay section is already open");
+  BRT_REQUIRE(c->pending == 0, "the sizes of the previous forward exchange were never read");
+  if (int rc = check_alive(c)) return rc;
+  c->replaying = true;
+  return BRT_OK;
+}
+
+BRT_API int brt_p2p_ctx_replay_end(brt_p2p_ctx* c) {
+  clear_error();
+  BRT_REQUIRE(c != nullptr && c->replaying, "no replay section is open");
+  c->replaying = false;
+  BRT_REQUIRE(c->pending == 0, "the sizes of the last forward exchange were never taken");
   return BRT_OK;
 }
 
@@ -339,8 +435,10 @@ BRT_API int brt_p2p_sparse_backward(brt_p2p_ctx* c, uint64_t exchange_id, int gr
                      (unsigned long long)exchange_id);
   const int W = c->world, G = group_size, n = W * G;
   const int32_t* S = k.sizes.data();
-  int64_t mine = 0;
-  for (int i = 0; i < W; i++) {
+  // sizes that never reached the host: the output is the landing half as far as rows of
+  // this size go, and the landing kernel itself reports rows that do not fit
+  int64_t mine = stride_rows ? stride_rows * n : (int64_t)c->half_bytes / grain_bytes;
+  for (int i = 0; i < W && !k.device_only; i++) {
     int64_t total = 0;
     for (int b = 0; b < n; b++) total += S[i * n + b] > 0 ? S[i * n + b] : 0;
     if (stride_rows) total = stride_rows * n;
@@ -352,16 +450,14 @@ BRT_API int brt_p2p_sparse_backward(brt_p2p_ctx* c, uint64_t exchange_id, int gr
   if (stages & BRT_P2P_STAGE_POST) {
     BRT_REQUIRE(c->pending == 0, "the sizes of the previous forward exchange were never read");
     c->exchanges++;
-    if (int rc = brt_p2p_post(nullptr, 0, c->world, c->rank, c->exchanges, nullptr,
-                              c->ready_flags, main_stream))
+    if (int rc = p2p_post_launch(nullptr, 0, c->world, c->rank, c->exchanges, nullptr,
+                                 c->ready_flags, replay_of(c, false), main_stream))
       return rc;
   }
   const uint64_t x = c->exchanges;
   if (stages & BRT_P2P_STAGE_PUSH) {
-    const int32_t* kept =
-        reinterpret_cast<const int32_t*>(c->base + kKeptOffset) + (exchange_id % kKept) * kBoardInts;
-    if (int rc = land(c, rows, kept, nullptr, G, layout, zero_tails, grain_bytes, stride_rows, x,
-                      main_stream))
+    if (int rc = land(c, rows, kept_slot(c, k.slot), nullptr, G, layout, zero_tails,
+                      grain_bytes, stride_rows, x, k.device_only, main_stream))
       return rc;
   }
   if (stages & BRT_P2P_STAGE_WAIT)

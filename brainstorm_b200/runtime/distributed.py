@@ -126,6 +126,27 @@ def dispatch_group_sparse_a2a(in_data: torch.Tensor, route_indices: torch.Tensor
     return None
 
 
+def group_sparse_a2a_device(in_data: torch.Tensor, in_loads: torch.Tensor,
+                            max_path_padding=False, max_path_load=0):
+    """``group_sparse_a2a`` whose size tensors stay on the device (no host synchronisation;
+    fit for ``replayable_exchanges`` and CUDA graph capture)."""
+    is_nccl_activated()
+    return C_dist.group_sparse_all_to_all_device(in_data, in_loads, max_path_padding,
+                                                 max_path_load)
+
+
+def dispatch_group_sparse_a2a_device(in_data: torch.Tensor, route_indices: torch.Tensor,
+                                     loads: torch.Tensor, max_path_padding=False,
+                                     max_path_load=0):
+    """``dispatch_group_sparse_a2a`` whose size tensors stay on the device."""
+    is_nccl_activated()
+    return C_dist.dispatch_group_sparse_all_to_all_device(in_data, route_indices, loads,
+                                                          max_path_padding, max_path_load)
+
+
+replayable_exchanges = C_dist.replayable_exchanges
+
+
 def size_known_group_sparse_a2a(in_data: torch.Tensor, in_loads: torch.Tensor,
                                 out_loads: torch.Tensor, max_path_padding=False):
     if is_nccl_activated():

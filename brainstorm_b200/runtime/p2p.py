@@ -120,6 +120,48 @@ class PeerArena:
                   grain, group_size, stride_rows, main, self.side.cuda_stream, 0)
         return self._forward_sizes(group_size)
 
+    # ---- exchanges whose sizes stay on the device (CUDA graph capture) ------------------------
+    def replay_begin(self) -> None:
+        """Open a section of exchanges that may be captured in a CUDA graph and replayed:
+        exchanges issued with ``dispatch_forward_device`` / ``sparse_forward_device`` and
+        ``sparse_backward``, closed by ``replay_end``.  Every rank opens, fills, closes and
+        replays its sections alike."""
+        _lib.call("brt_p2p_ctx_replay_begin", self.ctx)
+
+    def replay_end(self) -> None:
+        _lib.call("brt_p2p_ctx_replay_end", self.ctx)
+
+    def _device_sizes(self, group_size: int, device):
+        received = torch.empty((group_size * self.world,), dtype=torch.int32, device=device)
+        out, cap, xid = ctypes.c_void_p(), ctypes.c_int64(), ctypes.c_uint64()
+        _lib.call("brt_p2p_forward_device_sizes", self.ctx, received.data_ptr(),
+                  torch.cuda.current_stream().cuda_stream, ctypes.byref(out), ctypes.byref(cap),
+                  ctypes.byref(xid))
+        return received, int(out.value), int(cap.value), int(xid.value)
+
+    _DEVICE_STAGES = 1 | 4 | 8 | 16  # post, push, wait; rows that do not fit are an error
+
+    def sparse_forward_device(self, rows: torch.Tensor, sizes: torch.Tensor, group_size: int,
+                              grain: int, stride_rows: int, layout: int = SPARSE_FORWARD):
+        """``sparse_forward`` without a host synchronisation.  Returns (rows this rank receives
+        as a device tensor [group, world] flattened, device address of my output, the rows
+        the output can hold, exchange id)."""
+        main = torch.cuda.current_stream().cuda_stream
+        _lib.call("brt_p2p_sparse_forward_begin", self.ctx, rows.data_ptr(), sizes.data_ptr(),
+                  group_size, grain, stride_rows, layout, main, main, self._DEVICE_STAGES)
+        return self._device_sizes(group_size, rows.device)
+
+    def dispatch_forward_device(self, cells: torch.Tensor, route_indices: torch.Tensor,
+                                loads: torch.Tensor, counts: torch.Tensor, group_size: int,
+                                grain: int, stride_rows: int):
+        """``dispatch_forward`` without a host synchronisation; returns what
+        ``sparse_forward_device`` returns."""
+        main = torch.cuda.current_stream().cuda_stream
+        _lib.call("brt_p2p_dispatch_forward_begin", self.ctx, cells.data_ptr(),
+                  route_indices.data_ptr(), loads.data_ptr(), counts.data_ptr(), cells.size(0),
+                  grain, group_size, stride_rows, main, main, self._DEVICE_STAGES)
+        return self._device_sizes(group_size, cells.device)
+
     def sparse_backward(self, exchange_id: int, group_size: int, grain: int, stride_rows: int,
                         rows: torch.Tensor, layout: int = SPARSE_INVERSE,
                         zero_tails: bool = False):

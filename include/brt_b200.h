@@ -570,12 +570,34 @@ BRT_API int brt_p2p_dispatch_land(
  *                 later exchanges are then refused until brt_p2p_ctx_reset_status.
  * brt_p2p_ctx_set_wait_limit     the bound of every wait (default 2 s: the largest skew
  *                 between ranks that an exchange tolerates).
+ *
+ * Exchanges without a host synchronisation, fit for CUDA graph capture.  The reference's
+ * forward exchange hands its size tensors to the host (collective.cc:157-166 synchronises the
+ * stream for them); a layer whose experts read their loads on the device does not need that:
+ * brt_p2p_ctx_replay_begin       opens a section.  Its forward exchanges are issued without
+ *                 BRT_P2P_STAGE_SIZES and with BRT_P2P_STAGE_STRICT, and are completed by
+ * brt_p2p_forward_device_sizes   (in place of brt_p2p_sparse_forward_sizes): writes the rows
+ *                 this rank receives, [local expert][source rank] int32, to device memory
+ *                 (stream-ordered, no synchronisation) and returns this rank's output - the
+ *                 landing half, `capacity_rows` rows of the exchange's row size of which the
+ *                 first sum(received) are the output - and the identifier for
+ *                 brt_p2p_sparse_backward, whose `out_rows` is then a capacity as well.
+ *                 Rows that do not fit a landing half cannot be rerouted without the host:
+ *                 nothing moves and BRT_ERR_UNSUPPORTED appears in brt_p2p_ctx_status.
+ * brt_p2p_ctx_replay_end         closes the section.  Its kernels may be captured in a CUDA
+ *                 graph and replayed, or issued again, any number of times, between
+ *                 ordinary exchanges too: the epoch of the flags is counted on the device
+ *                 (it advances whenever an exchange runs, not when it is issued), and the
+ *                 section has size boards and kept matrices of its own.  A replay lands in
+ *                 the halves named when the section was issued; all ranks must replay alike.
+ *                 The sections alive at one time may hold 16 forward exchanges in all.
  */
 #define BRT_P2P_STAGE_POST 1
 #define BRT_P2P_STAGE_SIZES 2
 #define BRT_P2P_STAGE_PUSH 4
 #define BRT_P2P_STAGE_WAIT 8
 #define BRT_P2P_STAGE_ALL 15
+#define BRT_P2P_STAGE_STRICT 16
 
 typedef struct brt_p2p_ctx brt_p2p_ctx;
 BRT_API size_t brt_p2p_control_bytes(void);
@@ -599,6 +621,11 @@ BRT_API int brt_p2p_dispatch_forward_begin(brt_p2p_ctx* ctx, const void* src_dat
 BRT_API int brt_p2p_sparse_forward_sizes(brt_p2p_ctx* ctx, void* side_stream,
                                          const int32_t** size_matrix, int64_t* out_rows,
                                          int* fits, void** out_data, uint64_t* exchange_id);
+BRT_API int brt_p2p_ctx_replay_begin(brt_p2p_ctx* ctx);
+BRT_API int brt_p2p_ctx_replay_end(brt_p2p_ctx* ctx);
+BRT_API int brt_p2p_forward_device_sizes(brt_p2p_ctx* ctx, int32_t* received_sizes,
+                                         void* stream, void** out_data,
+                                         int64_t* capacity_rows, uint64_t* exchange_id);
 BRT_API int brt_p2p_sparse_backward(brt_p2p_ctx* ctx, uint64_t exchange_id, int group_size,
                                     int64_t grain_bytes, int64_t stride_rows, int layout,
                                     int zero_tails, const void* rows, void* main_stream,

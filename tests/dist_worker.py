@@ -179,6 +179,67 @@ def main():
     assert torch.equal(matched.data, everyone[int(reorder[rank])]), \
         f"rank {rank}: locality-matched route differs"
 
+    # ---- a routing step with both exchanges captured in a CUDA graph and replayed on new
+    # inputs: the sizes never reach the host, the epochs of the flags advance on the device
+    if p2p.arena() is not None and p2p.ZERO_COPY and p2p.arena().half_bytes >= (64 << 20):
+        from brainstorm_b200._C import router as R
+
+        T, E, d = 384, 4 * W, 64
+        cells = torch.zeros((T, d), device=dev)
+        mask = torch.zeros((T, E), dtype=torch.int32, device=dev)
+
+        def step():
+            idx, loads = R.generate_indices_and_loads(mask)
+            with brt_dist.replayable_exchanges():
+                landed, received, sent = brt_dist.dispatch_group_sparse_a2a_device(
+                    cells, idx, loads)
+                back = brt_dist.size_known_group_sparse_a2a(landed, received, sent)
+            (y,) = R.combine_with_indices_and_loads(back, idx, loads, None, None)
+            return y, received, landed
+
+        def fill(seed):
+            gen = torch.Generator().manual_seed(seed * 100 + rank)
+            cells.copy_(torch.randn((T, d), generator=gen))
+            picks = torch.topk(torch.randn((T, E), generator=gen), 2, dim=1).indices
+            mask.copy_(torch.zeros((T, E), dtype=torch.int32).scatter_(1, picks, 1))
+
+        def check(y, received, landed, what):
+            idx, loads = R.generate_indices_and_loads(mask)
+            (routed,) = R.dispatch_with_indices_and_loads(cells, idx, loads)
+            (want,) = R.combine_with_indices_and_loads(routed, idx, loads, None, None)
+            assert torch.equal(y, want), f"rank {rank}: {what}: combined cells differ"
+            want_out, want_recv, _ = brt_dist.group_sparse_a2a(routed, loads)
+            assert torch.equal(received.cpu(), want_recv.reshape(-1).to(torch.int32)), \
+                f"rank {rank}: {what}: received sizes differ"
+            n = int(want_recv.sum())
+            # (the eager exchange above reused a landing half: compare the clone taken before)
+            assert torch.equal(landed[:n], want_out), f"rank {rank}: {what}: landed rows differ"
+
+        fill(1)
+        y, received, landed = step()  # issued eagerly: a section run once
+        check(y, received, landed[:int(received.sum())].clone(), "eager section")
+        fill(2)
+        torch.cuda.synchronize()
+        dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            y, received, landed = step()
+        for seed in (3, 4, 5):
+            fill(seed)
+            graph.replay()
+            torch.cuda.synchronize()
+            check(y.clone(), received.clone(), landed[:int(received.sum())].clone(),
+                  f"replay {seed}")
+        # ordinary exchanges continue after the replays, and another replay after them
+        xs, sizes = rank_inputs(rank, W, 2, 8, 20)
+        o, ol, il = brt_dist.group_sparse_a2a(torch.from_numpy(xs).to(dev),
+                                              torch.from_numpy(sizes).to(dev))
+        assert np.array_equal(brt_dist.size_known_group_sparse_a2a(o, ol, il).cpu().numpy(), xs)
+        fill(6)
+        graph.replay()
+        torch.cuda.synchronize()
+        check(y.clone(), received.clone(), landed[:int(received.sum())].clone(), "late replay")
+
     p2p.check_status()
     dist.barrier()
     if rank == 0:

@@ -377,3 +377,137 @@ def test_wait_runs_out_and_is_reported():
         assert float((x * 2).sum()) == 64.0
     finally:
         ranks.close()
+
+
+STRICT = 16
+
+
+def _section(ranks, xs, sizes, group, cols, expert=None):
+    """One replay section on every emulated rank: forward exchange with device-resident
+    sizes, an optional per-rank transform of the landed rows, the inverse exchange.  Returns
+    (received sizes per rank, landed rows per rank (clones), returned rows per rank)."""
+    st = torch.cuda.current_stream().cuda_stream
+    world = ranks.world
+    grain = cols * 4
+    for c in ranks.ctxs:
+        _lib.call("brt_p2p_ctx_replay_begin", c)
+    for stage in (POST, PUSH | STRICT, WAIT):
+        for r in range(world):
+            _lib.call("brt_p2p_sparse_forward_begin", ranks.ctxs[r], xs[r].data_ptr(),
+                      sizes[r].data_ptr(), group, grain, 0, 1, st, st, stage)
+    received, landed, ids = [], [], []
+    for r in range(world):
+        got = torch.empty((group * world,), dtype=torch.int32, device="cuda")
+        out, cap, xid = ctypes.c_void_p(), ctypes.c_int64(), ctypes.c_uint64()
+        _lib.call("brt_p2p_forward_device_sizes", ranks.ctxs[r], got.data_ptr(), st,
+                  ctypes.byref(out), ctypes.byref(cap), ctypes.byref(xid))
+        assert cap.value == ranks.half // grain
+        received.append(got)
+        landed.append(ranks.rows_at(out.value, cap.value, cols))
+        ids.append(xid.value)
+    sources = [expert(t) if expert else t for t in landed]
+    back = [None] * world
+    for stage in (POST, PUSH, WAIT):
+        for r in range(world):
+            out, n_rows = ctypes.c_void_p(), ctypes.c_int64()
+            _lib.call("brt_p2p_sparse_backward", ranks.ctxs[r], ids[r], group, grain, 0, 0, 0,
+                      sources[r].data_ptr(), st, stage, ctypes.byref(out), ctypes.byref(n_rows))
+            back[r] = ranks.rows_at(out.value, n_rows.value, cols)
+    for c in ranks.ctxs:
+        _lib.call("brt_p2p_ctx_replay_end", c)
+    return received, landed, back
+
+
+@pytest.mark.parametrize("world,group,cols", [(2, 2, 4), (4, 3, 8), (8, 4, 16)])
+def test_replay_sections_with_device_resident_sizes(world, group, cols):
+    """Sections of forward + inverse exchange whose sizes never reach the host, issued again
+    and again with new data (what replaying a captured graph does: the epoch is counted on
+    the device), with ordinary exchanges in between.  Everything is compared
+    with the checker's walk of the exchange."""
+    dev = torch.device("cuda", 0)
+    ranks = Ranks(world)
+    try:
+        # fixed buffers, as under a CUDA graph: new contents are copied into them
+        bound = 40 * world * group
+        xs = [torch.zeros((bound, cols), device=dev) for _ in range(world)]
+        sizes = [torch.zeros((world * group,), dtype=torch.int32, device=dev)
+                 for _ in range(world)]
+        for it in range(5):
+            xs_np, sizes_np = make_inputs(world, group, cols, 40, 0, seed=900 + it)
+            sim = oracle.sim_group_sparse_all_to_all(xs_np, sizes_np, False, 0)
+            for r in range(world):
+                xs[r].zero_()
+                xs[r][:xs_np[r].shape[0]].copy_(torch.from_numpy(xs_np[r]))
+                sizes[r].copy_(torch.from_numpy(sizes_np[r]))
+            if it == 3:
+                # an ordinary exchange between two sections: its epoch continues theirs
+                tx = [torch.from_numpy(x).to(dev) for x in xs_np]
+                outs, ids, fit = ranks.forward(tx, sizes, group)
+                assert all(fit)
+                held = [ranks.rows_at(p, n, cols).clone() for p, n, _ in outs]
+                for r in range(world):
+                    assert np.array_equal(held[r].cpu().numpy(), sim[r][0])
+                back = ranks.backward(ids, held, group)
+                for r in range(world):
+                    assert np.array_equal(ranks.rows_at(*back[r], cols).cpu().numpy(), xs_np[r])
+                continue
+            received, landed, back = _section(ranks, xs, sizes, group, cols)
+            torch.cuda.synchronize()
+            for r in range(world):
+                want_rows, want_sizes = sim[r][0], sim[r][1]
+                assert np.array_equal(received[r].cpu().numpy(), want_sizes.reshape(-1)), \
+                    f"iteration {it}, rank {r}: received sizes differ"
+                n = want_rows.shape[0]
+                assert np.array_equal(landed[r][:n].cpu().numpy(), want_rows), \
+                    f"iteration {it}, rank {r}: landed rows differ"
+                m = xs_np[r].shape[0]
+                assert np.array_equal(back[r][:m].cpu().numpy(), xs_np[r]), \
+                    f"iteration {it}, rank {r}: round trip differs"
+        for c in ranks.ctxs:
+            assert _lib.query("brt_p2p_ctx_status", c) == 0
+    finally:
+        ranks.close()
+
+
+def test_replay_section_rules_and_rows_that_do_not_fit():
+    dev = torch.device("cuda", 0)
+    world, group, cols = 2, 1, 1024
+    ranks = Ranks(world, half=1 << 16)  # 64 KB halves, 4 KB rows
+    st = torch.cuda.current_stream().cuda_stream
+    try:
+        sizes_np = [np.array([10, 30], dtype=np.int32), np.array([5, 2], dtype=np.int32)]
+        xs = [torch.ones((int(s.sum()), cols), device=dev) for s in sizes_np]
+        sizes = [torch.from_numpy(s).to(dev) for s in sizes_np]
+        # the host-size stage is refused inside a section
+        _lib.call("brt_p2p_ctx_replay_begin", ranks.ctxs[0])
+        with pytest.raises(_lib.BrtError):
+            _lib.call("brt_p2p_sparse_forward_begin", ranks.ctxs[0], xs[0].data_ptr(),
+                      sizes[0].data_ptr(), group, cols * 4, 0, 1, st, st, 0)
+        _lib.call("brt_p2p_ctx_replay_end", ranks.ctxs[0])  # empty section: fine
+        with pytest.raises(_lib.BrtError):
+            _lib.call("brt_p2p_ctx_replay_end", ranks.ctxs[0])  # none open
+        # rank 1 would receive 32 rows = 128 KB: nothing moves, and the status says why
+        for c in ranks.ctxs:
+            _lib.call("brt_p2p_ctx_replay_begin", c)
+        for stage in (POST, PUSH | STRICT, WAIT):
+            for r in range(world):
+                _lib.call("brt_p2p_sparse_forward_begin", ranks.ctxs[r], xs[r].data_ptr(),
+                          sizes[r].data_ptr(), group, cols * 4, 0, 1, st, st, stage)
+        landed = []
+        for r in range(world):
+            got = torch.empty((group * world,), dtype=torch.int32, device=dev)
+            out, cap, xid = ctypes.c_void_p(), ctypes.c_int64(), ctypes.c_uint64()
+            _lib.call("brt_p2p_forward_device_sizes", ranks.ctxs[r], got.data_ptr(), st,
+                      ctypes.byref(out), ctypes.byref(cap), ctypes.byref(xid))
+            landed.append(ranks.rows_at(out.value, cap.value, cols))
+        for c in ranks.ctxs:
+            _lib.call("brt_p2p_ctx_replay_end", c)
+        torch.cuda.synchronize()
+        assert [_lib.query("brt_p2p_ctx_status", c) for c in ranks.ctxs] == [4, 4]
+        assert float(landed[1].abs().sum()) == 0.0
+        with pytest.raises(_lib.BrtError) as err:  # refused until the status is cleared
+            _lib.call("brt_p2p_ctx_replay_begin", ranks.ctxs[0])
+        assert err.value.status == 4
+        assert float((xs[0] * 2).sum()) == 2.0 * xs[0].numel()  # the device still answers
+    finally:
+        ranks.close()
