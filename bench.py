@@ -291,6 +291,22 @@ def run_gpu(args):
         rec(6)
         return out, idx, loads, routed
 
+    def step_replayable():
+        """The expert-parallel step without a host synchronisation: the exchange's size
+        tensors stay on the device (an expert would read its loads there), so the whole step
+        can be captured in a CUDA graph, as the single-GPU step is."""
+        if padded:
+            prefix = torch.zeros_like(zeros_e)
+            idx, loads, _ = R.throttle_and_generate_indices(mask, prefix, caps, caps)
+        else:
+            idx, loads = R.generate_indices_and_loads(mask, caps)
+        with brt_dist.replayable_exchanges():
+            recv, out_loads, in_loads = brt_dist.dispatch_group_sparse_a2a_device(
+                x, idx, loads, padded, cap)
+            routed = brt_dist.size_known_group_sparse_a2a(recv, out_loads, in_loads, padded)
+        (out,) = R.combine_with_indices_and_loads(routed, idx, loads, gates, None, padded)
+        return out, idx, loads, routed
+
     def barrier():
         if distributed:
             dist.barrier()
@@ -317,6 +333,72 @@ def run_gpu(args):
         torch.cuda.current_stream().wait_stream(side)
         for _ in range(warmup):
             graph.replay()
+        barrier()
+    graph_note = None
+    if distributed and not args.no_graph and not args.no_fused_exchange:
+        # every rank captures, or none does: a rank that replays cannot meet one that issues
+        from brainstorm_b200.runtime import p2p as brt_p2p
+        eager_out = out.clone()
+        captured, why = None, ""
+        try:
+            if brt_p2p.arena() is None:
+                raise RuntimeError("no peer-memory arena")
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step_replayable()
+                side.synchronize()
+                captured = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(captured, stream=side):
+                    g_out, g_idx, g_loads, g_routed = step_replayable()
+            torch.cuda.current_stream().wait_stream(side)
+        except Exception as exc:  # noqa: BLE001
+            captured, why = None, f"{type(exc).__name__}: {exc}"[:200]
+        agreed = torch.tensor([1 if captured is not None else 0], device=dev)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+        if int(agreed.item()) == 1:
+            graph = captured
+            for _ in range(warmup):
+                graph.replay()
+            barrier()
+            same = torch.tensor([int(torch.equal(g_out, eager_out))], device=dev)
+            dist.all_reduce(same, op=dist.ReduceOp.MIN)
+            graph_note = {"replayed_step_equals_eager_step": bool(same.item())}
+            out, idx, loads = g_out, g_idx, g_loads
+        else:
+            graph_note = {"not_captured": why or "another rank could not capture"}
+            del captured
+        barrier()
+
+    exchange_trace = None
+    if distributed:
+        from brainstorm_b200.runtime import p2p as brt_p2p
+        if brt_p2p.arena() is not None:
+            # where the two landing kernels of a step spend their time: waiting for the other
+            # ranks to enter the exchange (skew) or moving rows (device clock, one step at a
+            # time with a synchronisation after each; outside the timed region)
+            rows_t = []
+            for _ in range(10):
+                if graph is not None:
+                    graph.replay()
+                else:
+                    step()
+                rows_t.append(brt_p2p.arena().trace())
+            mean_t = torch.tensor([statistics.mean(r[k] for r in rows_t) for k in range(10)],
+                                  device=dev, dtype=torch.float64)
+            worst = mean_t.clone()
+            dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+            keys = ("wait", "move", "plan", "first_cta_out", "last_cta_out")
+            exchange_trace = {"unit": "us", "steps": len(rows_t)}
+            for leg, base in (("forward", 0), ("inverse", 5)):
+                exchange_trace["rank0_" + leg] = {k: round(float(mean_t[base + i]), 2)
+                                                  for i, k in enumerate(keys)}
+                exchange_trace["slowest_rank_" + leg + "_move"] = round(float(worst[base + 1]), 2)
+            exchange_trace["note"] = (
+                "wait = CTA 0 of the landing kernel from its start until every rank has "
+                "entered the exchange; the rest counts from that instant: move = until the "
+                "arrival flags are raised, plan = CTA 0 has placed its buckets, first / "
+                "last_cta_out = when the first / last CTA leaves its copy loop")
         barrier()
 
     sampler = ClockSampler(local_rank)
@@ -471,17 +553,27 @@ def run_gpu(args):
         "gpu_launches": int(round(args.steps * launches_per_step)),
         "gpu_launches_per_step": launches_per_step,
         "clocks": clocks, "e2e": e2e,
-        "timed_region": "CUDA graph replay of the step" if graph is not None
+        "timed_region": ("CUDA graph replay of the step" + (
+                             " (exchanges with device-resident sizes, no host synchronisation)"
+                             if distributed else "")) if graph is not None
                         else "eager launches of the step",
         "eager_ms_per_step": eager_host_ms, "eager_device_ms_per_step": eager_ms,
-        # one timing mode for a scaling curve: `value` is a graph replay at N = 1 where the
-        # step has no host synchronisation, and eager launches at N > 1 (the forward exchange
-        # returns CPU size tensors); this is the eager figure at every N
+        # `value` is a graph replay wherever the step can be captured (at N > 1: with the
+        # exchange's size tensors left on the device); this is the figure of the eager
+        # Python API at every N (at N > 1 the forward exchange hands CPU size tensors to the
+        # host, as the reference's op does)
         "value_eager": world * T / (eager_host_ms * 1e-3),
     }
     if distributed:
         result["checks"] = exchange_checks(dev, rank, world, x, mask, gates, caps, cap, padded,
                                            R, brt_dist)
+        if exchange_trace is not None:
+            result["exchange_trace_us"] = exchange_trace
+        if graph_note is not None:
+            if "replayed_step_equals_eager_step" in graph_note:
+                result["checks"].update(graph_note)
+            else:
+                result["graph"] = graph_note
         plain = measure_a2a_cfg4(dev, rank, world, R, brt_dist, 0.0, uniform_loads=True)
         plain.pop("loads_rank")
         result["a2a_cfg4"] = plain

@@ -51,6 +51,7 @@ struct DispatchLandArgs {
   long long stride_rows;   // 0: packed buckets
   long long half_bytes;
   unsigned long long epoch, limit_ns;
+  unsigned long long* trace;                // see P2pReplay
   const unsigned long long* epoch_counter;  // see p2p::effective_epoch()
   int strict;              // rows that do not fit are reported as an error
   const int* sizes;        // [world][world * group] on my board
@@ -90,7 +91,14 @@ dispatch_land_kernel(const __grid_constant__ DispatchLandArgs a) {
   const long long grain = a.row_vecs * 16;
 
   const unsigned long long epoch = p2p::effective_epoch(a.epoch, a.epoch_counter);
+  const bool tracer = a.trace != nullptr && blockIdx.x == 0 && tid == 0;
+  if (tracer) {
+    a.trace[0] = p2p::global_timer_ns();
+    a.trace[4] = ~0ull;
+    a.trace[5] = 0ull;
+  }
   bool go = p2p::wait_for_flags(a.ready_flags, W, -1, epoch, a.limit_ns);
+  if (tracer) a.trace[1] = p2p::global_timer_ns();
   if (!go && tid == 0) {
     p2p::report_timeout(a.status);
     atomicExch(a.abort_word, 1u);
@@ -135,6 +143,7 @@ dispatch_land_kernel(const __grid_constant__ DispatchLandArgs a) {
   if (go && !fits && a.strict && blockIdx.x == 0 && tid == 0)
     p2p::report_status(a.status, BRT_ERR_UNSUPPORTED);
 
+  if (tracer) a.trace[3] = p2p::global_timer_ns();
   if (move) {
     const int lane = tid & 31;
     const int warp_in_cta = tid >> 5;
@@ -260,6 +269,14 @@ dispatch_land_kernel(const __grid_constant__ DispatchLandArgs a) {
   }
 
   // arrive: the last CTA to finish raises my flag at every rank, unless a wait ran out
+  if (a.trace != nullptr) {
+    __syncthreads();
+    if (tid == 0) {
+      const unsigned long long now = p2p::global_timer_ns();
+      atomicMin(a.trace + 4, now);
+      atomicMax(a.trace + 5, now);
+    }
+  }
   __threadfence_system();
   __syncthreads();
   if (tid == 0) {
@@ -270,6 +287,7 @@ dispatch_land_kernel(const __grid_constant__ DispatchLandArgs a) {
       __threadfence_system();
       if (aborted == 0u)
         for (int r = 0; r < W; r++) p2p::store_release_sys(a.arrive_flags[r] + me, epoch);
+      if (a.trace != nullptr) a.trace[2] = p2p::global_timer_ns();
     }
   }
 }
@@ -357,6 +375,7 @@ int p2p_dispatch_land_launch(const void* src_data, const int32_t* route_indices,
   a.epoch = epoch;
   a.epoch_counter = static_cast<const unsigned long long*>(replay.epoch_counter);
   a.strict = replay.strict;
+  a.trace = static_cast<unsigned long long*>(replay.trace);
   a.limit_ns = wait_limit_ns;
   a.sizes = size_matrix;
   a.keep = keep_matrix;

@@ -129,6 +129,7 @@ struct LandArgs {
   long long stride_rows;  // 0: packed
   long long half_bytes;   // capacity of a landing half
   unsigned long long epoch;
+  unsigned long long* trace;                // see P2pReplay
   const unsigned long long* epoch_counter;  // see effective_epoch()
   int strict;             // a landing that does not fit is an error (reported), not a verdict
   unsigned long long limit_ns;
@@ -156,10 +157,17 @@ p2p_land_kernel(const char* __restrict__ src, const __grid_constant__ LandArgs a
   const int W = a.world_size, G = a.group_size, me = a.my_rank;
   const int n = W * G;
   const unsigned long long epoch = effective_epoch(a.epoch, a.epoch_counter);
+  const bool tracer = a.trace != nullptr && blockIdx.x == 0 && tid == 0;
+  if (tracer) {
+    a.trace[0] = global_timer_ns();
+    a.trace[4] = ~0ull;
+    a.trace[5] = 0ull;
+  }
 
   // every rank has entered this exchange: the sizes are on my board and the landing halves
   // may be written
   bool go = wait_for_flags(a.ready_flags, W, -1, epoch, a.limit_ns);
+  if (tracer) a.trace[1] = global_timer_ns();
   if (!go) {
     if (tid == 0) {
       report_timeout(a.status);
@@ -267,6 +275,7 @@ p2p_land_kernel(const char* __restrict__ src, const __grid_constant__ LandArgs a
     block_exclusive_scan(s_first, n, s_warp);
   }
 
+  if (tracer) a.trace[3] = global_timer_ns();
   const long long total_chunks = go ? s_first[n] : 0;
   const long long run = (total_chunks + kWays - 1) / kWays;
   for (long long k = blockIdx.x; k < run * kWays; k += gridDim.x) {
@@ -313,6 +322,14 @@ p2p_land_kernel(const char* __restrict__ src, const __grid_constant__ LandArgs a
   }
 
   // arrive: the last CTA to finish raises my flag at every rank, unless a wait ran out
+  if (a.trace != nullptr) {
+    __syncthreads();
+    if (tid == 0) {
+      const unsigned long long now = global_timer_ns();
+      atomicMin(a.trace + 4, now);
+      atomicMax(a.trace + 5, now);
+    }
+  }
   __threadfence_system();
   __syncthreads();
   if (tid == 0) {
@@ -323,6 +340,7 @@ p2p_land_kernel(const char* __restrict__ src, const __grid_constant__ LandArgs a
       __threadfence_system();
       if (aborted == 0u)
         for (int r = 0; r < W; r++) store_release_sys(a.arrive_flags[r] + me, epoch);
+      if (a.trace != nullptr) a.trace[2] = global_timer_ns();
     }
   }
 }
@@ -551,6 +569,7 @@ int p2p_land_launch(const void* rows, const int32_t* size_matrix, int32_t* keep_
   a.epoch = epoch;
   a.epoch_counter = static_cast<const unsigned long long*>(replay.epoch_counter);
   a.strict = replay.strict;
+  a.trace = static_cast<unsigned long long*>(replay.trace);
   a.limit_ns = wait_limit_ns;
   a.sizes = size_matrix;
   a.keep = keep_matrix;

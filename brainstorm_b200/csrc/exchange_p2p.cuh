@@ -117,6 +117,10 @@ __device__ __forceinline__ void block_exclusive_scan(int* a, int n, int* s_warp)
 struct P2pReplay {
   void* epoch_counter = nullptr;
   int strict = 0;
+  // six uint64 of %globaltimer (ns) the landing kernel leaves behind: CTA 0 entered, CTA 0
+  // saw every rank ready, the last CTA finished (flags raised), CTA 0 had its plan, the
+  // first and the last CTA left their copy loops.  Null: no trace.
+  void* trace = nullptr;
 };
 int p2p_land_launch(const void* rows, const int32_t* size_matrix, int32_t* keep_matrix,
                     int world_size, int group_size, int my_rank, int layout, int zero_tails,

@@ -10,6 +10,7 @@
 //   516      uint32       abort word of this rank's landing kernel
 //   520      uint64       epoch counter: exchanges this rank has opened (device-side count)
 //   1024     int32        status word of the bounded waits
+//   1088     2 x 8 uint64 timing trace of the last forward / inverse landing kernel
 //   2048     two size boards of kBoardInts int32 each, used alternately
 //   65536    kKept + kKeptReplay size matrices (kBoardInts int32 each) kept for the inverse
 //            exchanges; the last kKeptReplay belong to exchanges issued for replay
@@ -44,6 +45,7 @@ constexpr size_t kCounterOffset = 512;
 constexpr size_t kAbortOffset = 516;
 constexpr size_t kEpochCounter = 520;
 constexpr size_t kStatusOffset = 1024;
+constexpr size_t kTraceOffset = 1088;
 constexpr size_t kBoardOffset = 2048;
 constexpr size_t kBoardInts = (65536 - kBoardOffset) / 8;
 constexpr size_t kKeptOffset = 65536;
@@ -109,10 +111,11 @@ int check_alive(const brt_p2p_ctx* c) {
   return BRT_OK;
 }
 
-P2pReplay replay_of(const brt_p2p_ctx* c, bool strict) {
+P2pReplay replay_of(const brt_p2p_ctx* c, bool strict, int trace_slot = -1) {
   P2pReplay r;
   r.epoch_counter = c->base + kEpochCounter;
   r.strict = strict ? 1 : 0;
+  if (trace_slot >= 0) r.trace = c->base + kTraceOffset + 64 * trace_slot;
   return r;
 }
 
@@ -129,7 +132,10 @@ int land(brt_p2p_ctx* c, const void* rows, const int32_t* matrix, int32_t* keep,
                          stride, (int64_t)c->half_bytes, halves, exchange,
                          c->base + kReadyOffset, c->arrive_flags, c->base + kCounterOffset,
                          c->base + kAbortOffset, c->base + kStatusOffset, c->host_status_dev,
-                         c->wait_ns, replay_of(c, strict), stream);
+                         c->wait_ns,
+                         replay_of(c, strict,
+                                   layout == BRT_P2P_SPARSE_INVERSE || layout == BRT_P2P_SLOTS_BACK),
+                         stream);
 }
 
 int wait_arrivals(brt_p2p_ctx* c, uint64_t exchange, void* stream) {
@@ -215,6 +221,24 @@ BRT_API int brt_p2p_ctx_reset_status(brt_p2p_ctx* c) {
 
 BRT_API uint64_t brt_p2p_ctx_exchanges(const brt_p2p_ctx* c) { return c ? c->exchanges : 0; }
 
+BRT_API int brt_p2p_ctx_trace(brt_p2p_ctx* c, uint64_t* nanoseconds) {
+  clear_error();
+  BRT_REQUIRE(c != nullptr && nanoseconds != nullptr, "null pointers");
+  BRT_CUDA_TRY(cudaDeviceSynchronize());
+  uint64_t t[16];
+  BRT_CUDA_TRY(cudaMemcpy(t, c->base + kTraceOffset, sizeof(t), cudaMemcpyDeviceToHost));
+  for (int k = 0; k < 2; k++) {
+    const uint64_t* s = t + 8 * k;
+    uint64_t* o = nanoseconds + 5 * k;
+    o[0] = s[1] - s[0];                        // waiting for the other ranks
+    o[1] = s[2] - s[1];                        // moving, up to the raised flags
+    o[2] = s[3] - s[1];                        // of which: planning (CTA 0)
+    o[3] = s[4] > s[1] ? s[4] - s[1] : 0;      // the first CTA leaves its copy loop
+    o[4] = s[5] > s[1] ? s[5] - s[1] : 0;      // the last CTA leaves its copy loop
+  }
+  return BRT_OK;
+}
+
 namespace {
 // What the PUSH stage of a forward exchange launches: the landing kernel over rows that are
 // already laid out by destination, or the dispatch that lands its rows itself.
@@ -298,7 +322,7 @@ int forward_begin(brt_p2p_ctx* c, const void* rows, const FusedDispatch* fused,
               matrix, keep, c->world, group_size, c->rank, stride_rows, (int64_t)c->half_bytes,
               halves, x, c->base + kReadyOffset, c->arrive_flags, c->base + kCounterOffset,
               c->base + kAbortOffset, c->base + kStatusOffset, c->host_status_dev, c->wait_ns,
-              replay_of(c, strict), main_stream))
+              replay_of(c, strict, 0), main_stream))
         return rc;
     }
   }

@@ -175,6 +175,13 @@ class PeerArena:
                   ctypes.byref(n_rows))
         return int(out.value), int(n_rows.value)
 
+    def trace(self):
+        """(wait, move, plan, first CTA out, last CTA out) of the last forward landing kernel
+        and the same five of the last inverse one, in microseconds; synchronises the device."""
+        t = (ctypes.c_uint64 * 10)()
+        _lib.call("brt_p2p_ctx_trace", self.ctx, t)
+        return [v / 1e3 for v in t]
+
     def status(self) -> int:
         return int(_lib.query("brt_p2p_ctx_status", self.ctx))
 

@@ -608,6 +608,12 @@ BRT_API int brt_p2p_ctx_set_wait_limit(brt_p2p_ctx* ctx, uint64_t nanoseconds);
 BRT_API int brt_p2p_ctx_status(const brt_p2p_ctx* ctx);
 BRT_API int brt_p2p_ctx_reset_status(brt_p2p_ctx* ctx);
 BRT_API uint64_t brt_p2p_ctx_exchanges(const brt_p2p_ctx* ctx);
+/* Where the last forward and the last inverse landing kernel of this context spent their
+ * time (device clock, after a device synchronisation).  nanoseconds[0..4] for the forward
+ * kernel: waiting for every rank to enter the exchange (skew, not work); from there until the
+ * arrival flags were raised; and, counted from the same instant, when CTA 0 had its plan,
+ * when the first CTA left its copy loop and when the last one did.  [5..9]: the inverse. */
+BRT_API int brt_p2p_ctx_trace(brt_p2p_ctx* ctx, uint64_t* nanoseconds);
 BRT_API int brt_p2p_sparse_forward_begin(brt_p2p_ctx* ctx, const void* rows,
                                          const int32_t* sizes, int group_size,
                                          int64_t grain_bytes, int64_t stride_rows, int layout,
