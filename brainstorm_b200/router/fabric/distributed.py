@@ -4,6 +4,12 @@ Dispatch: local fused dispatch in global-expert order, then the packed variable-
 all-to-all that regroups rows as [local expert][source rank].  Combine: the inverse exchange,
 then the local weighted combine.  Without an initialised process group both exchanges are the
 identity, which is how single-GPU runs use these fabrics.
+
+``device_sizes=True`` (dispatch fabric; not in the reference) keeps the exchange's size tensors
+on the device: no host synchronisation, so a layer built from these fabrics can be captured in
+a CUDA graph inside ``brt_dist.replayable_exchanges()``.  The flow the experts get is then the
+whole landing half seen as rows, of which the first ``loads.sum()`` are theirs, and ``loads``
+is a device tensor.  Peer-memory transport only.
 """
 from typing import List, Tuple, Union
 
@@ -24,8 +30,11 @@ class DistributedFusedDispatchFabric(FusedDispatchFabric):
     def __init__(self, flow_num: int, capacity_padding=False,
                  route_logic: Union[str, List[str]] = "1d",
                  transform: Union[bool, List[bool]] = False, task_locality: bool = False,
-                 **kwargs):
+                 device_sizes: bool = False, **kwargs):
         self.task_locality = task_locality
+        self.device_sizes = device_sizes
+        if device_sizes and task_locality:
+            raise ValueError("task_locality needs the sizes on the host")
         super().__init__(flow_num=flow_num, capacity_padding=capacity_padding,
                          route_logic=route_logic, transform=transform, **kwargs)
 
@@ -36,7 +45,16 @@ class DistributedFusedDispatchFabric(FusedDispatchFabric):
             data, tag_stack, load_stack, extra = to_torch_tensor(in_flows[flow_idx],
                                                                  retrieve_attr=True)
             fused = None
-            if not self.transforms[flow_idx] and self.route_logics[flow_idx] == "1d":
+            plain = not self.transforms[flow_idx] and self.route_logics[flow_idx] == "1d"
+            if self.device_sizes and dist.is_initialized():
+                if plain and getattr(route_indices, c_router._DENSE, None) is not None:
+                    fused = brt_dist.dispatch_group_sparse_a2a_device(
+                        data, route_indices, loads, self.max_path_padding, self.max_path_load)
+                else:
+                    (routed,) = self._route(data, route_indices, loads, score, flow_idx, None)
+                    fused = brt_dist.group_sparse_a2a_device(
+                        routed, loads, self.max_path_padding, self.max_path_load)
+            elif plain:
                 # dispatch and exchange as one kernel over peer memory when that is possible
                 fused = brt_dist.dispatch_group_sparse_a2a(
                     data, route_indices, loads, self.max_path_padding, self.max_path_load)

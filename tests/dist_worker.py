@@ -153,6 +153,27 @@ def main():
     ep = GatherRouter("distributed_fused_combine", {"transform": True})(routed, None, score)
     assert torch.equal(ep.data, local.data), f"rank {rank}: expert-parallel route differs"
 
+    if p2p.arena() is not None and p2p.ZERO_COPY:
+        # the same route with the exchange's sizes left on the device (weighted dispatch takes
+        # the two-op path, the unweighted one the fused kernel)
+        for weighted in (False, True):
+            skw = {"device_sizes": True}
+            ref = GatherRouter("fused_combine", {"transform": not weighted})(
+                ScatterRouter(protocol_type="topk", fabric_type="fused_dispatch",
+                              protocol_kwargs={"top_k": 2},
+                              fabric_kwargs={"transform": weighted})(Annotator([0])(x), score),
+                None, score)
+            routed_d = ScatterRouter(protocol_type="topk",
+                                     fabric_type="distributed_fused_dispatch",
+                                     protocol_kwargs={"top_k": 2},
+                                     fabric_kwargs=dict(skw, transform=weighted))(
+                Annotator([0])(x), score)
+            assert routed_d.load.is_cuda
+            ep_d = GatherRouter("distributed_fused_combine", {"transform": not weighted})(
+                routed_d, None, score)
+            assert torch.equal(ep_d.data, ref.data), \
+                f"rank {rank}: device-sized route differs (weighted dispatch: {weighted})"
+
     # ---- padded-slot fabrics: plain, and with the locality matching (the cells of rank
     # reorder[k] come out on rank k)
     cap = 2 * T // E * 3
