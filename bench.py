@@ -521,6 +521,48 @@ def run_gpu(args):
                    "dispatch_kernel": "dispatch",
                    "combine_kernel": "combine"}.get(dominant, "indices")
 
+    # ---- the two big kernels launched back to back: the events that bracket every launch
+    # above keep the next launch from overlapping the previous kernel's tail and add their
+    # own few microseconds, which is a tenth of a 40 us kernel.  Here ONE pair of events spans
+    # `reps` consecutive launches of the same kernel (a CUDA graph holds them, so the host is
+    # not in the way); each launch moves more bytes than L2 holds.
+    back_to_back = None
+    if not distributed and padded and not args.no_graph:
+        def consecutive(fn, reps=8):
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                fn()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    for _ in range(reps):
+                        fn()
+            torch.cuda.current_stream().wait_stream(side)
+            ts = []
+            for _ in range(8):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                g.replay()
+                b.record()
+                torch.cuda.synchronize()
+                ts.append(a.elapsed_time(b) / reps)
+            return statistics.median(ts[3:])
+
+        try:
+            d_ms = consecutive(lambda: R.dispatch_with_indices_and_loads(
+                x, idx, loads, None, False, None, padded, cap))
+            c_ms = consecutive(lambda: R.combine_with_indices_and_loads(
+                routed, idx, loads, gates, None, padded))
+            back_to_back = {}
+            for n, ms_ in (("dispatch", d_ms), ("combine", c_ms)):
+                gbs = ab[n] / (ms_ * 1e-3) / 1e9
+                back_to_back[n] = {"ms": round(ms_, 5), "achieved_gbs": round(gbs, 1),
+                                   "frac": round(gbs / peak, 4)}
+            back_to_back["timing"] = ("one pair of CUDA events around 8 consecutive launches "
+                                      "of the kernel (a CUDA graph), median of 5, per launch")
+        except Exception as exc:  # noqa: BLE001
+            back_to_back = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+
     # ---- the gate in front of the path: scores -> mask (-> indices), torch ops of the
     # reference's protocol beside the library's single-launch gate
     gate = measure_gate(wl, dev, w, R, padded, caps)
@@ -547,6 +589,7 @@ def run_gpu(args):
                          round(device_kernels[dominant]["achieved_gbs"] / 8000, 4),
                      "whole_op": {"op": dominant_op, **kernels[dominant_op]}},
         "device_kernels": device_kernels,
+        "kernels_back_to_back": back_to_back,
         "gate": gate,
         "kernels": kernels,
         "routing": {"kept_routes": ab["R"], "cells_routed": ab["T_r"], "output_rows": ab["L"]},
