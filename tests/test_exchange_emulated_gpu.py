@@ -382,10 +382,12 @@ def test_wait_runs_out_and_is_reported():
 STRICT = 16
 
 
-def _section(ranks, xs, sizes, group, cols, expert=None):
+def _section(ranks, xs, sizes, group, cols, expert=None, stride=0, fused=None):
     """One replay section on every emulated rank: forward exchange with device-resident
     sizes, an optional per-rank transform of the landed rows, the inverse exchange.  Returns
-    (received sizes per rank, landed rows per rank (clones), returned rows per rank)."""
+    (received sizes per rank, landed rows per rank (clones), returned rows per rank).
+    ``fused`` = (index tensors, dense counts): the forward exchange is the dispatch that lands
+    its rows itself, ``xs`` are then the cells."""
     st = torch.cuda.current_stream().cuda_stream
     world = ranks.world
     grain = cols * 4
@@ -393,15 +395,20 @@ def _section(ranks, xs, sizes, group, cols, expert=None):
         _lib.call("brt_p2p_ctx_replay_begin", c)
     for stage in (POST, PUSH | STRICT, WAIT):
         for r in range(world):
-            _lib.call("brt_p2p_sparse_forward_begin", ranks.ctxs[r], xs[r].data_ptr(),
-                      sizes[r].data_ptr(), group, grain, 0, 1, st, st, stage)
+            if fused is not None:
+                _lib.call("brt_p2p_dispatch_forward_begin", ranks.ctxs[r], xs[r].data_ptr(),
+                          fused[0][r].data_ptr(), sizes[r].data_ptr(), fused[1][r].data_ptr(),
+                          xs[r].size(0), grain, group, stride, st, st, stage)
+            else:
+                _lib.call("brt_p2p_sparse_forward_begin", ranks.ctxs[r], xs[r].data_ptr(),
+                          sizes[r].data_ptr(), group, grain, stride, 1, st, st, stage)
     received, landed, ids = [], [], []
     for r in range(world):
         got = torch.empty((group * world,), dtype=torch.int32, device="cuda")
         out, cap, xid = ctypes.c_void_p(), ctypes.c_int64(), ctypes.c_uint64()
         _lib.call("brt_p2p_forward_device_sizes", ranks.ctxs[r], got.data_ptr(), st,
                   ctypes.byref(out), ctypes.byref(cap), ctypes.byref(xid))
-        assert cap.value == ranks.half // grain
+        assert cap.value == (stride * world * group if stride else ranks.half // grain)
         received.append(got)
         landed.append(ranks.rows_at(out.value, cap.value, cols))
         ids.append(xid.value)
@@ -410,8 +417,9 @@ def _section(ranks, xs, sizes, group, cols, expert=None):
     for stage in (POST, PUSH, WAIT):
         for r in range(world):
             out, n_rows = ctypes.c_void_p(), ctypes.c_int64()
-            _lib.call("brt_p2p_sparse_backward", ranks.ctxs[r], ids[r], group, grain, 0, 0, 0,
-                      sources[r].data_ptr(), st, stage, ctypes.byref(out), ctypes.byref(n_rows))
+            _lib.call("brt_p2p_sparse_backward", ranks.ctxs[r], ids[r], group, grain, stride, 0,
+                      0, sources[r].data_ptr(), st, stage, ctypes.byref(out),
+                      ctypes.byref(n_rows))
             back[r] = ranks.rows_at(out.value, n_rows.value, cols)
     for c in ranks.ctxs:
         _lib.call("brt_p2p_ctx_replay_end", c)
@@ -463,6 +471,79 @@ def test_replay_sections_with_device_resident_sizes(world, group, cols):
                 m = xs_np[r].shape[0]
                 assert np.array_equal(back[r][:m].cpu().numpy(), xs_np[r]), \
                     f"iteration {it}, rank {r}: round trip differs"
+        for c in ranks.ctxs:
+            assert _lib.query("brt_p2p_ctx_status", c) == 0
+    finally:
+        ranks.close()
+
+
+@pytest.mark.parametrize("world,group,cells,cols,mode", [(2, 2, 300, 8, "packed"),
+                                                         (4, 2, 400, 512, "padded"),
+                                                         (8, 4, 700, 16, "capacity")])
+def test_replay_sections_with_the_fused_dispatch(world, group, cells, cols, mode):
+    """The section of a routing step as the distributed fabric issues it with
+    ``device_sizes``: dispatch that lands its rows itself, sizes on the device, inverse
+    exchange; packed buckets, padded buckets (a slot size) and loads padded above the cell
+    counts.  Issued three times with new cells and new picks."""
+    from brainstorm_b200._C import router as R
+
+    dev = torch.device("cuda", 0)
+    E = world * group
+    per_path = max(1, cells * 2 // E)
+    stride = 2 * per_path if mode == "padded" else 0
+    ranks = Ranks(world, half=32 << 20)
+    try:
+        for it in range(3):
+            rng = np.random.default_rng(7000 + 10 * it + world)
+            xs, idxs, loads, counts, xs_np, rows_np, sizes_np = [], [], [], [], [], [], []
+            for r in range(world):
+                mask = oracle.topk_hot_mask(rng.standard_normal((cells, E)).astype(np.float32), 2)
+                x = rng.standard_normal((cells, cols)).astype(np.float32)
+                if mode == "padded":
+                    thr = np.full(E, stride, dtype=np.int32)
+                    m_np, _ = oracle.throttle_hotmask(mask, np.zeros(E, dtype=np.int32), thr)
+                    i_np, l_np = oracle.generate_indices_and_loads(m_np)
+                    i_t, l_t, _ = R.throttle_and_generate_indices(
+                        torch.from_numpy(mask).to(dev),
+                        torch.zeros(E, dtype=torch.int32, device=dev),
+                        torch.from_numpy(thr).to(dev))
+                else:
+                    caps = [per_path // 2 + 1, 2 * per_path, 16 * per_path] \
+                        if mode == "capacity" else None
+                    i_np, l_np = oracle.generate_indices_and_loads(mask, caps, caps is not None)
+                    i_t, l_t = R.generate_indices_and_loads(
+                        torch.from_numpy(mask).to(dev),
+                        None if caps is None else torch.tensor(caps, dtype=torch.int32,
+                                                               device=dev),
+                        caps is not None)
+                (routed,) = oracle.dispatch_with_indices_and_loads(
+                    x, i_np, l_np, max_path_padding=bool(stride), max_path_load=stride)
+                xs_np.append(x)
+                rows_np.append(routed)
+                sizes_np.append(l_np)
+                xs.append(torch.from_numpy(x).to(dev))
+                idxs.append(i_t)
+                loads.append(l_t.contiguous())
+                counts.append(getattr(i_t, R._DENSE))
+            sim = oracle.sim_group_sparse_all_to_all(rows_np, sizes_np, bool(stride), stride)
+            received, landed, back = _section(ranks, xs, loads, group, cols, stride=stride,
+                                              fused=(idxs, counts))
+            torch.cuda.synchronize()
+            for r in range(world):
+                want, want_sizes = sim[r][0], np.asarray(sim[r][1]).reshape(-1)
+                assert np.array_equal(received[r].cpu().numpy(), want_sizes), (it, r)
+                g = landed[r].cpu().numpy()
+                b = back[r].cpu().numpy()
+                if stride:
+                    for k, cnt in enumerate(want_sizes):
+                        assert np.array_equal(g[k * stride:k * stride + cnt],
+                                              want[k * stride:k * stride + cnt]), (it, r, k)
+                    for k, cnt in enumerate(sizes_np[r]):
+                        assert np.array_equal(b[k * stride:k * stride + cnt],
+                                              rows_np[r][k * stride:k * stride + cnt]), (it, r, k)
+                else:
+                    assert np.array_equal(g[:want.shape[0]], want), (it, r)
+                    assert np.array_equal(b[:rows_np[r].shape[0]], rows_np[r]), (it, r)
         for c in ranks.ctxs:
             assert _lib.query("brt_p2p_ctx_status", c) == 0
     finally:
