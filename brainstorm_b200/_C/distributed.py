@@ -29,7 +29,7 @@ def _check_cuda(t: torch.Tensor, name: str):
 
 
 def _stream(device) -> int:
-    return torch.cuda.current_stream(device).cuda_stream
+    return _lib.raw_stream(device)
 
 
 def _world():
@@ -99,7 +99,7 @@ def group_locality_reorder(loads: torch.Tensor, wolrd_size: int, group_size: int
         raise RuntimeError(f"loads must hold world_size^2 * group_size = {W * W * group_size} "
                            f"entries, got {loads.numel()}")
     src = _contig(loads)
-    with torch.cuda.device(loads.device):
+    with _lib.device_guard(loads.device):
         out = torch.empty_like(src)
         idx = torch.empty(W, dtype=torch.int32, device=loads.device)
         _lib.call("brt_group_locality_reorder", src.data_ptr(), int(group_size), W,
@@ -220,7 +220,7 @@ def _asymmetry(in_data, send_sizes, locality_aware, zero_fill=False):
     _check_cuda(send_sizes, "send_sizes")
     _, W = _world()
     group_size = send_sizes.numel() // W
-    with torch.cuda.device(in_data.device):
+    with _lib.device_guard(in_data.device):
         moved = _slots_p2p(_contig(in_data), send_sizes, group_size)
         if moved is not None:
             out, recv_sizes = moved
@@ -249,7 +249,7 @@ def batched_group_asymmetry_all_to_all(in_datas: List[torch.Tensor], send_sizes:
     _check_cuda(send_sizes, "send_sizes")
     _, W = _world()
     group_size = send_sizes.numel() // W
-    with torch.cuda.device(send_sizes.device):
+    with _lib.device_guard(send_sizes.device):
         recv_sizes = _exchange_sizes(send_sizes)
         send_np, recv_np = _host_sizes(send_sizes, recv_sizes)
         outs = []
@@ -271,7 +271,7 @@ def size_known_group_asymmetry_all_to_all(in_data: torch.Tensor, send_sizes: tor
     _check_cuda(in_data, "in_data")
     _, W = _world()
     group_size = send_sizes.numel() // W
-    with torch.cuda.device(in_data.device):
+    with _lib.device_guard(in_data.device):
         x = _contig(in_data)
         n = W * group_size
         tag = getattr(send_sizes, _TAG, None)
@@ -298,7 +298,7 @@ def batched_size_known_group_asymmetry_all_to_all(in_datas: List[torch.Tensor],
     outs = []
     for x in in_datas:
         _check_cuda(x, "in_data")
-        with torch.cuda.device(x.device):
+        with _lib.device_guard(x.device):
             outs.append(_slot_a2a(x, send_np, recv_np, send_sizes.numel() // W, False))
     return outs
 
@@ -360,7 +360,7 @@ def group_sparse_all_to_all(in_data: torch.Tensor, send_sizes: torch.Tensor,
     _check_cuda(send_sizes, "send_sizes")
     rank, W = _world()
     group_size = send_sizes.numel() // W
-    with torch.cuda.device(in_data.device):
+    with _lib.device_guard(in_data.device):
         x = _contig(in_data)
         if _p2p_usable(x, W, group_size) and not (max_path_padding and not max_path_load):
             # The rows leave before the host knows any size: the landing kernel reads the size
@@ -421,7 +421,7 @@ def dispatch_group_sparse_all_to_all(in_data: torch.Tensor, route_indices: torch
             not route_indices.is_contiguous() or (max_path_padding and not max_path_load):
         return None
     group_size = E // W
-    with torch.cuda.device(in_data.device):
+    with _lib.device_guard(in_data.device):
         x = _contig(in_data)
         if not _p2p_usable(x, W, group_size):
             return None
@@ -485,7 +485,7 @@ def group_sparse_all_to_all_device(in_data: torch.Tensor, send_sizes: torch.Tens
     _check_cuda(send_sizes, "send_sizes")
     _, W = _world()
     group_size = send_sizes.numel() // W
-    with torch.cuda.device(in_data.device):
+    with _lib.device_guard(in_data.device):
         x = _contig(in_data)
         if not _p2p_usable(x, W, group_size) or (max_path_padding and not max_path_load):
             raise RuntimeError("this exchange cannot use the peer-memory transport")
@@ -516,7 +516,7 @@ def dispatch_group_sparse_all_to_all_device(in_data: torch.Tensor, route_indices
             not route_indices.is_contiguous() or (max_path_padding and not max_path_load):
         raise RuntimeError("this dispatch cannot be fused with the peer-memory exchange")
     group_size = E // W
-    with torch.cuda.device(in_data.device):
+    with _lib.device_guard(in_data.device):
         x = _contig(in_data)
         if not _p2p_usable(x, W, group_size):
             raise RuntimeError("this exchange cannot use the peer-memory transport")
@@ -542,7 +542,7 @@ def size_known_group_sparse_all_to_all(in_data: torch.Tensor, send_sizes: torch.
     _check_cuda(in_data, "in_data")
     _, W = _world()
     group_size = send_sizes.numel() // W
-    with torch.cuda.device(in_data.device):
+    with _lib.device_guard(in_data.device):
         x = _contig(in_data)
         n = W * group_size
         stride = x.size(0) // n if max_path_padding else 0

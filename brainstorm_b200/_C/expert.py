@@ -48,7 +48,7 @@ def grouped_expert_linear(rows: torch.Tensor, weights: torch.Tensor, loads: torc
     else:
         mpl = 0
     dev = rows.device
-    with torch.cuda.device(dev):
+    with _lib.device_guard(dev):
         x = rows if rows.is_contiguous() else rows.contiguous()
         w = weights if weights.is_contiguous() else weights.contiguous()
         counts = loads if (loads.dtype == torch.int32 and loads.is_contiguous()) \
@@ -57,7 +57,7 @@ def grouped_expert_linear(rows: torch.Tensor, weights: torch.Tensor, loads: torc
         try:
             _lib.call("brt_grouped_expert_gemm", x.data_ptr(), w.data_ptr(), out.data_ptr(),
                       counts.data_ptr(), E, L, mpl, n_in, n_out, int(bool(relu)),
-                      _error_word(dev).data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+                      _error_word(dev).data_ptr(), _lib.raw_stream(dev))
         except _lib.BrtError as exc:
             if exc.status == 4:  # BRT_ERR_UNSUPPORTED: feature counts the tiles do not divide
                 raise NotImplementedError(str(exc)) from None

@@ -32,7 +32,7 @@ def _ptr(t: Optional[torch.Tensor]):
 
 
 def _stream(device) -> int:
-    return torch.cuda.current_stream(device).cuda_stream
+    return _lib.raw_stream(device)
 
 
 def _int32c(t: torch.Tensor, name: str) -> torch.Tensor:
@@ -58,8 +58,7 @@ class _ScratchPool:
         self._bufs = {}
 
     def get(self, purpose: str, device: torch.device, nbytes: int) -> torch.Tensor:
-        stream = torch.cuda.current_stream(device)
-        key = (purpose, device.index, stream.cuda_stream)
+        key = (purpose, device.index, _lib.raw_stream(device))
         buf = self._bufs.pop(key, None)
         if buf is None or buf.numel() < nbytes:
             buf = torch.empty(max(nbytes, 1 << 16), dtype=torch.uint8, device=device)
@@ -114,7 +113,7 @@ def throttle_hotmask(hotmask: torch.Tensor, prefix: torch.Tensor, threshold: tor
     if prefix.dtype != torch.int32 or not prefix.is_contiguous():
         raise RuntimeError("prefix must be a contiguous int32 tensor (it is updated in place)")
     T, E = hotmask.shape
-    with torch.cuda.device(hotmask.device):
+    with _lib.device_guard(hotmask.device):
         out = torch.empty_like(hotmask)
         nbytes = _lib.query("brt_index_scratch_bytes", T, E)
         scratch = _scratch.get("index", hotmask.device, nbytes)
@@ -136,7 +135,7 @@ def generate_indices_and_loads(
     check_index_status()
     hot_mask = _int32c(hot_mask, "hot_mask")
     T, E = hot_mask.shape
-    with torch.cuda.device(hot_mask.device):
+    with _lib.device_guard(hot_mask.device):
         if hot_mask.numel() == 0:
             return (torch.zeros((0, E), dtype=torch.int32, device=hot_mask.device),
                     torch.zeros((E,), dtype=torch.int32, device=hot_mask.device))
@@ -188,7 +187,7 @@ def throttle_and_generate_indices(
         raise RuntimeError("prefix must be a contiguous int32 tensor (it is updated in place)")
     T, E = hot_mask.shape
     dev = hot_mask.device
-    with torch.cuda.device(dev):
+    with _lib.device_guard(dev):
         caps, ncap = None, 0
         if supported_capacities is not None:
             _check_cuda(supported_capacities, "supported_capacities.value()")
@@ -263,7 +262,7 @@ def route_scores(
                                   "of 4 and at most 256 paths")
     T, E = score.shape
     dev = score.device
-    with torch.cuda.device(dev):
+    with _lib.device_guard(dev):
         out = torch.empty((T, E), dtype=torch.int32, device=dev)
         both = torch.empty((2, E), dtype=torch.int32, device=dev)
         loads, counts = both[0], both[1]
@@ -324,7 +323,7 @@ def convert_index_format(origin_indices: torch.Tensor, loads: torch.Tensor, is_t
     _check_cuda(origin_indices, "origin_indices")
     origin = _int32c(origin_indices, "origin_indices")
     T, E = origin.shape
-    with torch.cuda.device(origin.device):
+    with _lib.device_guard(origin.device):
         cuda_loads = loads
         if not loads.is_cuda:
             if is_to_tag:
@@ -355,7 +354,7 @@ def dispatch_with_indices_and_loads(
     _check_cuda(in_data, "in_data")
     _check_cuda(route_indices, "route_indices")
     dev = in_data.device
-    with torch.cuda.device(dev):
+    with _lib.device_guard(dev):
         cell_num = in_data.size(0)
         path_num = route_indices.size(1)
         if cell_num == 0:
@@ -515,7 +514,7 @@ def combine_with_indices_and_loads(
     _check_cuda(in_data, "in_data")
     _check_cuda(route_indices, "route_indices")
     dev = in_data.device
-    with torch.cuda.device(dev):
+    with _lib.device_guard(dev):
         cell_num = route_indices.size(0)
         if cell_num == 0:
             if not is_tag_index:

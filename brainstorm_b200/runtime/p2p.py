@@ -93,7 +93,7 @@ class PeerArena:
         on the current stream and wait for its size matrix only.  Returns (matrix
         [world, world * group] int32, my output rows, whether it fits the landing halves,
         device address of my output, exchange id)."""
-        main = torch.cuda.current_stream().cuda_stream
+        main = _lib.raw_stream()
         _lib.call("brt_p2p_sparse_forward_begin", self.ctx, rows.data_ptr(), sizes.data_ptr(),
                   group_size, grain, stride_rows, layout, main, self.side.cuda_stream, 0)
         return self._forward_sizes(group_size)
@@ -114,7 +114,7 @@ class PeerArena:
         """Dispatch fused with the forward packed exchange: every kept copy of a cell goes
         straight to its row in the destination rank's landing half.  Same results as
         ``sparse_forward`` of the dispatched rows."""
-        main = torch.cuda.current_stream().cuda_stream
+        main = _lib.raw_stream()
         _lib.call("brt_p2p_dispatch_forward_begin", self.ctx, cells.data_ptr(),
                   route_indices.data_ptr(), loads.data_ptr(), counts.data_ptr(), cells.size(0),
                   grain, group_size, stride_rows, main, self.side.cuda_stream, 0)
@@ -135,7 +135,7 @@ class PeerArena:
         received = torch.empty((group_size * self.world,), dtype=torch.int32, device=device)
         out, cap, xid = ctypes.c_void_p(), ctypes.c_int64(), ctypes.c_uint64()
         _lib.call("brt_p2p_forward_device_sizes", self.ctx, received.data_ptr(),
-                  torch.cuda.current_stream().cuda_stream, ctypes.byref(out), ctypes.byref(cap),
+                  _lib.raw_stream(), ctypes.byref(out), ctypes.byref(cap),
                   ctypes.byref(xid))
         return received, int(out.value), int(cap.value), int(xid.value)
 
@@ -146,7 +146,7 @@ class PeerArena:
         """``sparse_forward`` without a host synchronisation.  Returns (rows this rank receives
         as a device tensor [group, world] flattened, device address of my output, the rows
         the output can hold, exchange id)."""
-        main = torch.cuda.current_stream().cuda_stream
+        main = _lib.raw_stream()
         _lib.call("brt_p2p_sparse_forward_begin", self.ctx, rows.data_ptr(), sizes.data_ptr(),
                   group_size, grain, stride_rows, layout, main, main, self._DEVICE_STAGES)
         return self._device_sizes(group_size, rows.device)
@@ -156,7 +156,7 @@ class PeerArena:
                                 grain: int, stride_rows: int):
         """``dispatch_forward`` without a host synchronisation; returns what
         ``sparse_forward_device`` returns."""
-        main = torch.cuda.current_stream().cuda_stream
+        main = _lib.raw_stream()
         _lib.call("brt_p2p_dispatch_forward_begin", self.ctx, cells.data_ptr(),
                   route_indices.data_ptr(), loads.data_ptr(), counts.data_ptr(), cells.size(0),
                   grain, group_size, stride_rows, main, main, self._DEVICE_STAGES)
@@ -171,7 +171,7 @@ class PeerArena:
         out, n_rows = ctypes.c_void_p(), ctypes.c_int64()
         _lib.call("brt_p2p_sparse_backward", self.ctx, exchange_id, group_size, grain,
                   stride_rows, layout, int(zero_tails), rows.data_ptr(),
-                  torch.cuda.current_stream().cuda_stream, 0, ctypes.byref(out),
+                  _lib.raw_stream(), 0, ctypes.byref(out),
                   ctypes.byref(n_rows))
         return int(out.value), int(n_rows.value)
 
