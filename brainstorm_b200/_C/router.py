@@ -248,8 +248,8 @@ def route_scores(
     ``output`` = "mask": (hot_mask, cells per path); "throttled_mask": (hot_mask cut at
     ``throttle_capacity`` on top of ``prefix``, prefix) with ``prefix`` updated in place;
     "seat_indices": (indices, loads) as ``generate_indices_and_loads`` of the hot mask;
-    "throttled_seat_indices": (indices, loads, prefix) of the throttled hot mask
-    (``with_mask`` appends that mask).
+    "throttled_seat_indices": (indices, loads, prefix) of the throttled hot mask.
+    ``with_mask`` (seat-index outputs) appends the 0/1 mask the indices belong to.
     ``with_gates`` appends the picked scores renormalised to sum 1 per cell.  Raises
     ``NotImplementedError`` when the scores do not fit the single-launch kernel; callers then
     route in two steps."""
@@ -268,8 +268,8 @@ def route_scores(
         loads, counts = both[0], both[1]
         seats = output in ("seat_indices", "throttled_seat_indices")
         gates = torch.empty((T, E), dtype=torch.float32, device=dev) if with_gates else None
-        if with_mask and output != "throttled_seat_indices":
-            raise RuntimeError("with_mask goes with output='throttled_seat_indices'")
+        if with_mask and not seats:
+            raise RuntimeError("with_mask goes with the seat-index outputs")
         mask_out = torch.empty((T, E), dtype=torch.int32, device=dev) if with_mask else None
         caps, ncap = None, 0
         if supported_capacities is not None:
@@ -312,8 +312,12 @@ def route_scores(
         if with_mask:
             res += (mask_out,)
         return res
-    second = prefix if output == "throttled_mask" else loads
-    return (out, second, gates) if with_gates else (out, second)
+    res = (out, prefix if output == "throttled_mask" else loads)
+    if with_gates:
+        res += (gates,)
+    if with_mask:
+        res += (mask_out,)
+    return res
 
 
 def convert_index_format(origin_indices: torch.Tensor, loads: torch.Tensor, is_to_tag: bool):

@@ -908,8 +908,8 @@ __device__ __forceinline__ void expand_binary(const TileCtx& x, const TileSmem& 
     } else {
       __stcs(reinterpret_cast<int4*>(out + row * x.path_num + col0 + 4 * q),
              make_int4(v[0], v[1], v[2], v[3]));
-      if constexpr (MODE == Mode::kThrottleSeat) {
-        if (mask_out != nullptr)  // the throttled 0/1 mask itself, for callers that want both
+      if constexpr (MODE == Mode::kThrottleSeat || MODE == Mode::kSeat) {
+        if (mask_out != nullptr)  // the (throttled) 0/1 mask itself, for callers that want both
           __stcs(reinterpret_cast<int4*>(mask_out + row * x.path_num + col0 + 4 * q),
                  make_int4(v[0] != 0, v[1] != 0, v[2] != 0, v[3] != 0));
       }
@@ -958,7 +958,7 @@ __device__ __forceinline__ void expand_tile(const TileCtx& x, const TileSmem& sm
 struct TiledArgs {
   const int* mask;
   int* out;
-  int* mask_out;  // kThrottleSeat only, may be null: the throttled mask beside the indices
+  int* mask_out;  // seat modes of the gated scan, may be null: the 0/1 mask beside the indices
   uint32_t* bits;
   int* tile_sums;
   int* tile_flags;
@@ -1825,8 +1825,9 @@ BRT_API int brt_route_scores(const float* scores, int64_t cell_num, int path_num
     return BRT_OK;
   }
   BRT_REQUIRE(scores != nullptr && out != nullptr, "scores or out is null");
-  BRT_REQUIRE(mask_out == nullptr || output == BRT_ROUTE_THROTTLED_SEAT_INDICES,
-              "mask_out goes with BRT_ROUTE_THROTTLED_SEAT_INDICES only");
+  BRT_REQUIRE(mask_out == nullptr || output == BRT_ROUTE_THROTTLED_SEAT_INDICES ||
+                  output == BRT_ROUTE_SEAT_INDICES,
+              "mask_out goes with the seat-index outputs only");
   if (path_num % 4 != 0 || path_num > 256 || !aligned_to(scores, 16) || !aligned_to(out, 16) ||
       !aligned_to(mask_out, 16) || (gates_out != nullptr && !aligned_to(gates_out, 4)))
     return set_error(BRT_ERR_UNSUPPORTED,

@@ -19,6 +19,10 @@ class ThresholdProtocol(ProtocolBase):
 
     def make_route_decision(self, score: torch.Tensor) -> torch.Tensor:
         if c_router.route_scores_supported(score) and self.residual_path < score.size(1):
+            fused = self._gate_with_indices(score, "threshold", threshold=self.threshold,
+                                            residual_path=self.residual_path)
+            if fused is not None:
+                return fused
             try:  # the library's single-launch gate
                 return c_router.route_scores(score, "threshold", threshold=self.threshold,
                                              residual_path=self.residual_path, output="mask")[0]

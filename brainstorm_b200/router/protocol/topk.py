@@ -18,6 +18,9 @@ class TopKProtocol(ProtocolBase):
 
     def make_route_decision(self, score: torch.Tensor) -> torch.Tensor:
         if c_router.route_scores_supported(score) and 1 <= self.top_k <= score.size(1):
+            fused = self._gate_with_indices(score, "topk", top_k=self.top_k)
+            if fused is not None:
+                return fused
             try:
                 return c_router.route_scores(score, "topk", self.top_k, output="mask")[0]
             except NotImplementedError:  # more scores than one launch takes

@@ -23,6 +23,19 @@ def _dispatch_defaults(dispatch_score: bool) -> Dict[str, Any]:
     return {"flow_num": 1, "route_logic": "1d", "transform": False}
 
 
+class _FabricIndexRules:
+    """(supported_capacities, capacity_padding, path_wise_padding) of a dispatch fabric, read
+    when called (the capacities are a buffer that moves with the module).  A plain object, so
+    that the protocol holding it does not register the fabric as a submodule of its own."""
+
+    def __init__(self, fabric):
+        self.fabric = fabric
+
+    def __call__(self):
+        f = self.fabric
+        return f.supported_capacities, bool(f.capacity_padding), bool(f.path_wise_padding)
+
+
 class _ScoreScatterBase(RouterBase):
     def __init__(self, dispatch_score=False, protocol_type: str = "topk",
                  fabric_type: str = "dispatch", protocol_kwargs: Dict[str, Any] = None,
@@ -38,6 +51,11 @@ class _ScoreScatterBase(RouterBase):
             else {}
         self.fabric_kwargs.update(fabric_kwargs or {})
         self.fabric = make_fabric(fabric_type, self.fabric_kwargs)
+        if hasattr(self.fabric, "capacity_padding") and \
+                hasattr(self.protocol, "index_rules_of"):
+            # the fabric scans the hot mask for seat indices under these rules: a protocol that
+            # runs the library's gate kernel does that scan in the same launch
+            self.protocol.index_rules_of = _FabricIndexRules(self.fabric)
 
     def _route(self, in_flows, score):
         hot_mask = self.protocol(score)

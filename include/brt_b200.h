@@ -223,8 +223,8 @@ typedef enum brt_route_output {
  *            throttle_capacity as in brt_throttle_hotmask (the two THROTTLED outputs)
  *   gates_out optional fp32 [cell_num, path_num]: picked scores divided by their sum
  *            (clamped at FLT_EPSILON), zero elsewhere (protocol/swin_moe.py:193-204)
- *   mask_out optional int32 [cell_num, path_num], BRT_ROUTE_THROTTLED_SEAT_INDICES only: the
- *            throttled hot mask beside its seat indices
+ *   mask_out optional int32 [cell_num, path_num], the two SEAT_INDICES outputs only: the
+ *            (throttled) hot mask beside its seat indices
  *   scratch  brt_index_scratch_bytes(cell_num, path_num) bytes
  *
  * Returns BRT_ERR_UNSUPPORTED (nothing launched) when path_num is not a multiple of 4 or

@@ -232,6 +232,51 @@ def test_swin_moe_gate_hands_its_indices_to_the_fabric(api, cpad):
     assert torch.equal(a.load_stack[-1], b.load_stack[-1])
 
 
+@pytest.mark.parametrize("protocol,pkw", [("topk", {"top_k": 2}), ("threshold", {"threshold": 0.08}),
+                                          ("threshold", {"threshold": 0.3, "residual_path": 1})])
+@pytest.mark.parametrize("rules", [{}, {"supported_capacities": [300, 900, 4000]},
+                                   {"supported_capacities": [300, 900, 4000],
+                                    "capacity_padding": True}])
+def test_scatter_gate_hands_its_indices_to_the_fabric(api, protocol, pkw, rules, monkeypatch):
+    """ScatterRouter with a top-k or threshold protocol: the gate kernel that makes the hot
+    mask also scans it under the fabric's capacity rules, and the fabric runs no index scan
+    of its own; the routed rows equal those of a router whose fabric scans the mask."""
+    from brainstorm_b200._C import router as c_router
+
+    Annotator, ScatterRouter, GatherRouter = api
+    torch.manual_seed(5)
+    T, E = 3000, 8
+    x = torch.randn(T, 32, device="cuda")
+    score = torch.softmax(torch.randn(T, E, device="cuda") * 2, dim=1)
+
+    def make():
+        return ScatterRouter(protocol_type=protocol, fabric_type="fused_dispatch",
+                             protocol_kwargs=pkw, fabric_kwargs=dict(rules)).cuda()
+    fused, plain = make(), make()
+    assert fused.protocol.index_rules_of is not None
+    plain.protocol.index_rules_of = None
+    scans = []
+    real = c_router.generate_indices_and_loads
+    monkeypatch.setattr(c_router, "generate_indices_and_loads",
+                        lambda *a, **k: (scans.append(1), real(*a, **k))[1])
+    a = fused(Annotator([0])(x), score)
+    assert not scans, "the fabric scanned a mask whose indices the gate had already made"
+    b = plain(Annotator([0])(x), score)
+    assert len(scans) == 1
+    assert torch.equal(a.data, b.data)
+    assert torch.equal(a.load_stack[-1], b.load_stack[-1])
+    assert torch.equal(a.tag_stack[-1], b.tag_stack[-1])
+    out_a = GatherRouter(fabric_type="fused_combine", fabric_kwargs={"transform": True})(
+        a, None, score)
+    out_b = GatherRouter(fabric_type="fused_combine", fabric_kwargs={"transform": True})(
+        b, None, score)
+    assert torch.equal(out_a.data, out_b.data)
+    # a copy of the router reads the rules of ITS fabric
+    import copy
+    twin = copy.deepcopy(fused)
+    assert twin.protocol.index_rules_of.fabric is twin.fabric
+
+
 def test_install_as_brt(api):
     import brainstorm_b200
 
