@@ -211,11 +211,19 @@ BRT_API int brt_p2p_ctx_status(const brt_p2p_ctx* c) {
 BRT_API int brt_p2p_ctx_reset_status(brt_p2p_ctx* c) {
   clear_error();
   BRT_REQUIRE(c != nullptr, "null context");
+  // Back to the state of a fresh context: after a wait ran out the ranks may have counted
+  // different numbers of exchanges, so the flags, both exchange counts and the kept matrices
+  // start over.  The flags in this arena are raised by the OTHER ranks: the caller makes sure
+  // (a host barrier on either side of this call) that no rank enters an exchange before every
+  // rank has reset.
   BRT_CUDA_TRY(cudaDeviceSynchronize());
-  BRT_CUDA_TRY(cudaMemset(c->base + kStatusOffset, 0, 4));
-  BRT_CUDA_TRY(cudaMemset(c->base + kCounterOffset, 0, 8));
+  BRT_CUDA_TRY(cudaMemset(c->base, 0, kBoardOffset));
   c->host_status[0] = 0;
   c->pending = 0;
+  c->exchanges = 0;
+  c->replaying = false;
+  c->replay_slots = 0;
+  for (auto& k : c->kept) k = KeptMatrix();
   return BRT_OK;
 }
 

@@ -263,6 +263,18 @@ def setup(group, rank: int, world: int) -> Optional[PeerArena]:
     return None
 
 
+def reset(group=None) -> None:
+    """Collective: bring the arena of every rank back to its initial state after a bounded
+    wait ran out (``check_status`` raised).  Exchanges issued before the reset are lost; CUDA
+    graphs that hold exchanges must be captured again."""
+    if _arena is None:
+        return
+    torch.cuda.synchronize()
+    dist.barrier(group=group)
+    _lib.call("brt_p2p_ctx_reset_status", _arena.ctx)
+    dist.barrier(group=group)
+
+
 def check_status() -> None:
     """Raise if a bounded wait of an earlier exchange ran out.  Reads a word of host memory
     that the kernels write; no device synchronisation."""

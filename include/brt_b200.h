@@ -567,7 +567,11 @@ BRT_API int brt_p2p_dispatch_land(
  *                 not fit a landing half.
  * brt_p2p_ctx_status             BRT_OK, or BRT_ERR_TIMEOUT once a bounded wait of an exchange
  *                 of this context has run out (read from host memory, no synchronisation);
- *                 later exchanges are then refused until brt_p2p_ctx_reset_status.
+ *                 later exchanges are then refused until brt_p2p_ctx_reset_status, which
+ *                 puts the context back into its initial state (flags, exchange counts, kept
+ *                 matrices: after a failed wait the ranks may have counted differently).
+ *                 Every rank resets, with a host barrier before and after, and CUDA graphs
+ *                 captured before the reset are captured again.
  * brt_p2p_ctx_set_wait_limit     the bound of every wait (default 2 s: the largest skew
  *                 between ranks that an exchange tolerates).
  *

@@ -369,12 +369,22 @@ def test_wait_runs_out_and_is_reported():
         with pytest.raises(_lib.BrtError):  # refused until the status is cleared
             _lib.call("brt_p2p_sparse_forward_begin", ranks.ctxs[0], x.data_ptr(),
                       sizes.data_ptr(), 1, 16, 0, 1, st, st, 0)
-        _lib.call("brt_p2p_ctx_reset_status", ranks.ctxs[0])
-        assert _lib.query("brt_p2p_ctx_status", ranks.ctxs[0]) == 0
         # nothing landed in rank 1's arena and the device still answers
         landing = ranks.rows_at(ranks.arenas[1] + ranks.control + ranks.half, 8, 4)  # exchange 1: half 1
         assert float(landing.abs().sum()) == 0.0
         assert float((x * 2).sum()) == 64.0
+        for c in ranks.ctxs:  # every rank resets; then the exchanges work again
+            _lib.call("brt_p2p_ctx_reset_status", c)
+        assert _lib.query("brt_p2p_ctx_status", ranks.ctxs[0]) == 0
+        _lib.call("brt_p2p_ctx_set_wait_limit", ranks.ctxs[0], 2_000_000_000)
+        xs_np, sizes_np = make_inputs(2, 1, 4, 9, 0, seed=77)
+        sim = oracle.sim_group_sparse_all_to_all(xs_np, sizes_np, False, 0)
+        outs, ids, fit = ranks.forward([torch.from_numpy(a).to(dev) for a in xs_np],
+                                       [torch.from_numpy(s).to(dev) for s in sizes_np], 1)
+        assert all(fit)
+        for r in range(2):
+            assert np.array_equal(ranks.rows_at(outs[r][0], outs[r][1], 4).cpu().numpy(),
+                                  sim[r][0])
     finally:
         ranks.close()
 
