@@ -654,6 +654,14 @@ def run_gpu(args):
                 "frac_of_measured_peer_copy": round(gbs / 770.0, 4),
                 "timing": "CUDA events around each launch of the kernel, on its stream; "
                           "bytes = what this rank sends to other ranks in one exchange"}
+            if exchange_trace is not None:
+                # the same launch by the device's own clock, from "every rank has entered the
+                # exchange" to "arrival flags raised" (no launch or event overhead, no skew)
+                move = exchange_trace["rank0_forward"]["move"]
+                if move > 0:
+                    result["roofline"]["by_device_clock"] = {
+                        "move_us": move, "achieved": round(fwd / (move * 1e-6) / 1e9, 1),
+                        "frac": round(fwd / (move * 1e-6) / 1e9 / 900.0, 4)}
         result["a2a"] = {
             "forward_ms": op_ms["a2a_forward"], "backward_ms": op_ms["a2a_backward"],
             "remote_bytes_per_rank_per_direction": a2a_bytes[0],

@@ -207,3 +207,40 @@ def test_workload_generator_is_deterministic():
     assert a["cap"] == 640 and a["mask"].sum().item() == 4096
     c2 = bench.WORKLOADS["cfg2"]
     assert bench.capacity_of(c2) == 2048 and bench.capacity_of(bench.WORKLOADS["cfg3"]) == 4096
+
+
+def test_scatter_router_tells_its_protocol_the_fabric_rules():
+    """The hand-over of seat indices from the gate kernel to the fabric is set up on the host:
+    the router gives its protocol a view of the fabric's capacity rules (which follows a deep
+    copy to the copy's own fabric), and without CUDA scores the protocol routes with torch ops
+    and attaches nothing."""
+    import copy
+
+    import torch
+
+    from brainstorm_b200.router import ScatterRouter
+
+    router = ScatterRouter(protocol_type="topk", fabric_type="fused_dispatch",
+                           protocol_kwargs={"top_k": 2},
+                           fabric_kwargs={"supported_capacities": [4, 8],
+                                          "capacity_padding": True})
+    rules = router.protocol.index_rules_of
+    caps, cpad, pwise = rules()
+    assert caps is router.fabric.supported_capacities and cpad is True and pwise is False
+    twin = copy.deepcopy(router)
+    assert twin.protocol.index_rules_of.fabric is twin.fabric
+    assert "index_rules_of" not in dict(router.protocol.named_modules())
+    assert not any("index_rules_of" in k for k in router.state_dict())
+    mask = router.protocol(torch.rand(6, 4))
+    assert mask.dtype == torch.int32 and int(mask.sum()) == 12
+    assert not hasattr(mask, "_brt_routes")
+
+
+def test_replayable_exchanges_need_the_arena():
+    import pytest
+
+    from brainstorm_b200._C import distributed as C_dist
+
+    with pytest.raises(RuntimeError):
+        with C_dist.replayable_exchanges():
+            pass
