@@ -247,6 +247,7 @@ def run_gpu(args):
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(8)] for _ in range(args.steps)]
     a2a_bytes = [0]
     fused_used = [False]
+    pulled = [False]
 
     def step(i=None):
         rec = (lambda j: ev[i][j].record()) if i is not None else (lambda j: None)
@@ -278,16 +279,28 @@ def run_gpu(args):
             else:
                 recv, out_loads, in_loads = brt_dist.group_sparse_a2a(routed, loads, padded, cap)
             rec(4)
-            routed = brt_dist.size_known_group_sparse_a2a(recv, out_loads, in_loads, padded)
-            rec(5)
             # rows this rank really sends to OTHER ranks (in_loads: my send sizes, [W, G])
             sent = in_loads.reshape(world, -1)
             a2a_bytes[0] = int(sent.sum() - sent[rank].sum()) * d * x.element_size()
             fused_used[0] = fused is not None
+            out = None
+            if args.pull_combine:
+                # inverse exchange and combine as one kernel that pulls the rows from the
+                # peers (an option of the distributed combine fabric): no separate inverse leg
+                rec(5)
+                out = brt_dist.combine_group_sparse_a2a(recv, idx, gates, out_loads, in_loads,
+                                                        padded)
+                routed = recv
+            pulled[0] = out is not None
+            if out is None:
+                routed = brt_dist.size_known_group_sparse_a2a(recv, out_loads, in_loads, padded)
+                rec(5)
+                (out,) = R.combine_with_indices_and_loads(routed, idx, loads, gates, None,
+                                                          padded)
         else:
             rec(4)
             rec(5)
-        (out,) = R.combine_with_indices_and_loads(routed, idx, loads, gates, None, padded)
+            (out,) = R.combine_with_indices_and_loads(routed, idx, loads, gates, None, padded)
         rec(6)
         return out, idx, loads, routed
 
@@ -303,8 +316,13 @@ def run_gpu(args):
         with brt_dist.replayable_exchanges():
             recv, out_loads, in_loads = brt_dist.dispatch_group_sparse_a2a_device(
                 x, idx, loads, padded, cap)
-            routed = brt_dist.size_known_group_sparse_a2a(recv, out_loads, in_loads, padded)
-        (out,) = R.combine_with_indices_and_loads(routed, idx, loads, gates, None, padded)
+            out = brt_dist.combine_group_sparse_a2a(recv, idx, gates, out_loads, in_loads,
+                                                    padded) if args.pull_combine else None
+            routed = recv
+            if out is None:
+                routed = brt_dist.size_known_group_sparse_a2a(recv, out_loads, in_loads, padded)
+        if out is None:
+            (out,) = R.combine_with_indices_and_loads(routed, idx, loads, gates, None, padded)
         return out, idx, loads, routed
 
     def barrier():
@@ -503,7 +521,7 @@ def run_gpu(args):
     for name, t in timed.items():
         if t["launches"] == 0:
             continue
-        if name.startswith("p2p_") or name == "dispatch_land_kernel":
+        if name.startswith("p2p_") or name in ("dispatch_land_kernel", "combine_land_kernel"):
             # exchange kernels: bound by NVLink, not by HBM
             device_kernels[name] = {"launches": t["launches"],
                                     "ms": round(t["total_ms"] / t["launches"], 5)}
@@ -662,11 +680,14 @@ def run_gpu(args):
                     result["roofline"]["by_device_clock"] = {
                         "move_us": move, "achieved": round(fwd / (move * 1e-6) / 1e9, 1),
                         "frac": round(fwd / (move * 1e-6) / 1e9 / 900.0, 4)}
+        # with the combine that pulls its rows from the peers the inverse leg IS the combine
+        back_ms = op_ms["combine"] if pulled[0] else op_ms["a2a_backward"]
         result["a2a"] = {
-            "forward_ms": op_ms["a2a_forward"], "backward_ms": op_ms["a2a_backward"],
+            "forward_ms": op_ms["a2a_forward"], "backward_ms": back_ms,
             "remote_bytes_per_rank_per_direction": a2a_bytes[0],
             "bus_gbs_forward": fwd / (op_ms["a2a_forward"] * 1e-3) / 1e9,
-            "bus_gbs_backward": fwd / (op_ms["a2a_backward"] * 1e-3) / 1e9,
+            "bus_gbs_backward": fwd / (back_ms * 1e-3) / 1e9,
+            "backward_includes_combine": pulled[0],
             "nvlink_peak_gbs_per_direction": 900.0,
             "transport": "peer-memory landing kernels over NVLink"
                          if __import__("brainstorm_b200.runtime.p2p", fromlist=["arena"]).arena()
@@ -755,13 +776,25 @@ def exchange_checks(dev, rank, world, x, mask, gates, caps, cap, padded, R, brt_
         else:
             fused_same = bool(torch.equal(fused[0], two[0]))
         fused_same = fused_same and bool(torch.equal(fused[1], two[1]))
-    verdict = torch.tensor([int(round_trip), int(layout), int(same_as_local), int(fused_same)],
-                           device=dev)
+    # (5) the combine that pulls its rows from the peers equals inverse exchange + combine
+    pull_same, pull_ran = True, False
+    fwd3 = brt_dist.group_sparse_a2a(routed, loads, padded, cap)
+    pulled_out = brt_dist.combine_group_sparse_a2a(fwd3[0], idx, gates, fwd3[1], fwd3[2], padded)
+    if pulled_out is not None:
+        pull_ran = True
+        pull_same = bool(torch.equal(pulled_out, local_out))
+    else:
+        brt_dist.size_known_group_sparse_a2a(fwd3[0], fwd3[1], fwd3[2], padded)
+    verdict = torch.tensor([int(round_trip), int(layout), int(same_as_local), int(fused_same),
+                            int(pull_same)], device=dev)
     dist.all_reduce(verdict, op=dist.ReduceOp.MIN)
     v = verdict.tolist()
     return {"round_trip_bit_exact": bool(v[0]), "forward_layout_matches_reference_walk": bool(v[1]),
             "step_equals_single_rank_step": bool(v[2]),
             "fused_dispatch_exchange_equals_two_steps": bool(v[3]),
+            "fused_exchange_combine_equals_two_steps": bool(v[4]),
+            "fused_exchange_combine": "ran" if pull_ran
+            else "not available on this transport (two steps)",
             "fused_dispatch_exchange": "ran" if fused is not None
             else "not available on this transport (two steps)", "ranks": world,
             "rows_exchanged_per_rank": int(n_rows)}
@@ -1264,6 +1297,10 @@ def main():
     ap.add_argument("--no-fused-exchange", action="store_true",
                     help="at N>1 run dispatch and the forward exchange as two ops instead of the "
                          "one kernel that stores the dispatched rows straight into the peers")
+    ap.add_argument("--pull-combine", action="store_true",
+                    help="at N>1 run the inverse exchange and the combine as the one kernel that "
+                         "pulls the expert outputs from the peers (checked either way; the "
+                         "default, rows pushed back and combined locally, measured faster)")
     ap.add_argument("--no-graph", action="store_true",
                     help="time eager launches instead of a CUDA graph replay")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)

@@ -447,6 +447,72 @@ def dispatch_group_sparse_all_to_all(in_data: torch.Tensor, route_indices: torch
         return [out, recv_t, send_t]
 
 
+def combine_group_sparse_all_to_all(in_data: torch.Tensor, route_indices: torch.Tensor,
+                                    gates, send_sizes: torch.Tensor, recv_sizes: torch.Tensor,
+                                    max_path_padding: bool = False):
+    """``size_known_group_sparse_all_to_all`` followed by ``combine_with_indices_and_loads``
+    (seat indices, no residual), as ONE kernel over peer memory: the sequence of the reference's
+    expert-parallel combine fabric (python/brt/router/fabric/distributed.py:120-158) without the
+    returned buffer in between - the combine of this rank's cells pulls every kept route's row
+    from the arena of the rank that hosts the expert.  ``in_data`` are this rank's expert
+    outputs in the layout the forward exchange landed (its output, changed in place, or a
+    buffer from ``expert_output_buffer``); ``send_sizes`` / ``recv_sizes`` are the second and
+    third output of that forward call.  Returns the combined cells [cells, ...], or ``None``
+    when the call cannot take the fused route (no peer arena, size tensors that name no
+    exchange, expert outputs outside the arena, rows that are not 16-byte multiples); the caller
+    then runs the two ops.  The verdict depends on the program, not on the data.  A single cell
+    is combined like any other number (the reference's combine hands a lone cell's rows back
+    unweighted, router.cc:402-412)."""
+    from . import router as c_router
+
+    _check_cuda(in_data, "in_data")
+    _check_cuda(route_indices, "route_indices")
+    _, W = _world()
+    E = route_indices.size(1)
+    tag = getattr(send_sizes, _TAG, None)
+    if tag is None or tag != getattr(recv_sizes, _TAG, None) or E % W != 0 or \
+            tag[1] != E // W or in_data.dtype not in c_router._DT or in_data.dim() < 2 or \
+            route_indices.dtype != torch.int32 or not route_indices.is_contiguous() or \
+            not in_data.is_contiguous():
+        return None
+    group_size = E // W
+    g, gdt = None, 0
+    if gates is not None:
+        if not gates.is_cuda or gates.dtype not in (torch.float32, in_data.dtype) or \
+                gates.shape != route_indices.shape:
+            return None
+        g = gates if gates.is_contiguous() else gates.contiguous()
+        gdt = c_router._DT[g.dtype]
+    with _lib.device_guard(in_data.device):
+        if not _p2p_usable(in_data, W, group_size):
+            return None
+        arena = p2p.arena()
+        offset = arena.offset_of(in_data)
+        if offset is None or offset % 16 != 0:
+            return None
+        stride = in_data.size(0) // (W * group_size) if max_path_padding else 0
+        out = torch.empty((route_indices.size(0),) + tuple(in_data.shape[1:]),
+                          dtype=in_data.dtype, device=in_data.device)
+        try:
+            arena.combine_backward(tag[0], group_size, _row_bytes(in_data), stride, offset,
+                                   route_indices, g, gdt, c_router._DT[in_data.dtype], out)
+        except _lib.BrtError as exc:
+            if exc.status != 4:  # BRT_ERR_UNSUPPORTED is the same verdict on every rank
+                raise
+            return None
+    return out
+
+
+def expert_output_buffer(rows: int, like: torch.Tensor) -> torch.Tensor:
+    """A buffer of ``rows`` rows like those of ``like`` that the fused combine can pull from:
+    experts that do not work in place write their outputs here (same place on every rank;
+    valid from the forward exchange until the next forward exchange but one)."""
+    arena = p2p.arena()
+    if arena is None:
+        raise RuntimeError("no peer-memory arena")
+    return arena.expert_buffer(rows, like)
+
+
 class replayable_exchanges:
     """``with replayable_exchanges():`` around ``*_device`` exchanges and their inverses makes
     the sequence fit for CUDA graph capture: put the ``with`` inside ``torch.cuda.graph(...)``

@@ -23,7 +23,7 @@ def _error_word(device: torch.device) -> torch.Tensor:
 
 def grouped_expert_linear(rows: torch.Tensor, weights: torch.Tensor, loads: torch.Tensor,
                           max_path_padding: bool = False, max_path_load: int = 0,
-                          relu: bool = False) -> torch.Tensor:
+                          relu: bool = False, out: torch.Tensor = None) -> torch.Tensor:
     """``out[r] = act(rows[r] @ weights[e].T)`` for the first ``loads[e]`` rows of every expert
     ``e`` of a dispatched buffer.
 
@@ -31,7 +31,9 @@ def grouped_expert_linear(rows: torch.Tensor, weights: torch.Tensor, loads: torc
     ``max_path_load`` rows per expert with ``max_path_padding``, else packed), ``weights``
     [E, out, in] bf16, ``loads`` [E] int32 on the device.  Returns [L, out] bf16; rows beyond an
     expert's load are left unwritten (combine never reads them).  ``in`` must be a multiple of
-    64 and ``out`` of 128 (``NotImplementedError`` otherwise)."""
+    64 and ``out`` of 128 (``NotImplementedError`` otherwise).  ``out``: a contiguous [L, out]
+    bf16 tensor to write instead of a new one (e.g. ``expert_output_buffer`` of the
+    expert-parallel exchange, which the fused combine pulls from)."""
     if not rows.is_cuda or not weights.is_cuda or not loads.is_cuda:
         raise RuntimeError("rows, weights and loads must be CUDA tensors")
     if rows.dtype != torch.bfloat16 or weights.dtype != torch.bfloat16:
@@ -53,7 +55,12 @@ def grouped_expert_linear(rows: torch.Tensor, weights: torch.Tensor, loads: torc
         w = weights if weights.is_contiguous() else weights.contiguous()
         counts = loads if (loads.dtype == torch.int32 and loads.is_contiguous()) \
             else loads.to(torch.int32).contiguous()
-        out = torch.empty((L, n_out), dtype=torch.bfloat16, device=dev)
+        if out is None:
+            out = torch.empty((L, n_out), dtype=torch.bfloat16, device=dev)
+        elif out.shape != (L, n_out) or out.dtype != torch.bfloat16 or \
+                not out.is_contiguous() or out.device != dev:
+            raise RuntimeError("out must be a contiguous [L, out_features] bf16 tensor on the "
+                               "device of the rows")
         try:
             _lib.call("brt_grouped_expert_gemm", x.data_ptr(), w.data_ptr(), out.data_ptr(),
                       counts.data_ptr(), E, L, mpl, n_in, n_out, int(bool(relu)),

@@ -90,6 +90,8 @@ SIGNATURES = {
     "brt_p2p_dispatch_land": (_int, [_vp, _vp, _vp, _i64, _i64, _vp, _vp, _int, _int, _int, _i64,
                                      _i64, _vp, _u64, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _vp]),
     "brt_p2p_ctx_trace": (_int, [_vp, _vp]),
+    "brt_p2p_combine_backward": (_int, [_vp, _u64, _int, _i64, _i64, _i64, _vp, _vp, _int, _int,
+                                        _i64, _vp, _vp, _int]),
     "brt_p2p_ctx_replay_begin": (_int, [_vp]),
     "brt_p2p_ctx_replay_end": (_int, [_vp]),
     "brt_p2p_forward_device_sizes": (_int, [_vp, _vp, _vp, _vp, _vp, _vp]),

@@ -277,9 +277,14 @@ dispatch_land_kernel(const __grid_constant__ DispatchLandArgs a) {
       atomicMax(a.trace + 5, now);
     }
   }
-  __threadfence_system();
+  // Ordering the flag after every thread's accesses without a system-scope fence per thread
+  // (or per CTA: those serialise device-wide and cost about 10 us per launch).  The CTA
+  // barrier orders the CTA's accesses before thread 0; its device-scope fence and the counter
+  // update release them to the CTA that finds the counter complete, whose single system-scope
+  // fence precedes the flags: fences are cumulative, so the chain covers every access.
   __syncthreads();
   if (tid == 0) {
+    __threadfence();
     const unsigned int prev = atomicAdd(a.done_counter, 1u);
     if (prev == gridDim.x - 1) {
       *a.done_counter = 0;

@@ -89,9 +89,10 @@ p2p_push_kernel(const char* __restrict__ src, const __grid_constant__ CopyList l
   }
   if (sig.world_size == 0) return;  // plain multi-range copy, nobody to tell
   // arrive: the last CTA to finish raises my flag at every rank
-  __threadfence_system();
+  // (device-scope fence per CTA, one system-scope fence in the last CTA: see p2p_land_kernel)
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence();
     const unsigned int prev = atomicAdd(sig.done_counter, 1u);
     if (prev == gridDim.x - 1) {
       *sig.done_counter = 0;  // ready for the next exchange (stream-ordered)
@@ -330,9 +331,14 @@ p2p_land_kernel(const char* __restrict__ src, const __grid_constant__ LandArgs a
       atomicMax(a.trace + 5, now);
     }
   }
-  __threadfence_system();
+  // Ordering the flag after every thread's accesses without a system-scope fence per thread
+  // (or per CTA: those serialise device-wide and cost about 10 us per launch).  The CTA
+  // barrier orders the CTA's accesses before thread 0; its device-scope fence and the counter
+  // update release them to the CTA that finds the counter complete, whose single system-scope
+  // fence precedes the flags: fences are cumulative, so the chain covers every access.
   __syncthreads();
   if (tid == 0) {
+    __threadfence();
     const unsigned int prev = atomicAdd(a.done_counter, 1u);
     if (prev == gridDim.x - 1) {
       *a.done_counter = 0;  // ready for the next exchange (stream-ordered)
@@ -369,11 +375,12 @@ p2p_post_kernel(const int* __restrict__ values, const __grid_constant__ PostList
   for (int r = 0; r < post.world_size; r++)
     for (int t = threadIdx.x; t < post.n; t += kThreads)
       post.peer_board[r][post.my_rank * post.n + t] = values[t];
-  __threadfence_system();
   __syncthreads();
-  if (threadIdx.x == 0)
+  if (threadIdx.x == 0) {
+    __threadfence_system();  // cumulative over the barrier: the board rows of every thread
     for (int r = 0; r < post.world_size; r++)
       store_release_sys(post.peer_flags[r] + post.my_rank, epoch);
+  }
 }
 
 __global__ void __launch_bounds__(32)

@@ -144,6 +144,17 @@ int p2p_dispatch_land_launch(const void* src_data, const int32_t* route_indices,
                              void* my_done_counter, void* my_abort_word, void* status_word,
                              void* host_status_word, uint64_t wait_limit_ns,
                              const P2pReplay& replay, void* stream);
+// Combine that pulls its rows from the arenas of the ranks hosting the experts (the inverse
+// exchange and the combine in one kernel); `expert_rows[i]` is where rank i's expert output
+// starts, laid out as the forward exchange landed it, `size_matrix` is that exchange's.
+int p2p_combine_land_launch(void* dst_data, const void* gates, int gates_dtype, int dtype,
+                            const int32_t* route_indices, int64_t cell_num, int64_t row_bytes,
+                            const int32_t* size_matrix, int world_size, int group_size,
+                            int my_rank, int64_t stride_rows, const void* const* expert_rows,
+                            uint64_t epoch, const void* my_ready_flags,
+                            void* const* peer_arrive_flag_arrays, void* my_done_counter,
+                            void* my_abort_word, void* status_word, void* host_status_word,
+                            uint64_t wait_limit_ns, const P2pReplay& replay, void* stream);
 // out_loads[j * world + s] = rows rank s sends to my expert j in the exchange whose sizes are
 // on `board`, once every rank's ready flag shows the exchange (bounded wait).
 int p2p_received_sizes_launch(const int32_t* board, int world_size, int group_size, int my_rank,

@@ -499,4 +499,50 @@ BRT_API int brt_p2p_sparse_backward(brt_p2p_ctx* c, uint64_t exchange_id, int gr
   return BRT_OK;
 }
 
+BRT_API int brt_p2p_combine_backward(brt_p2p_ctx* c, uint64_t exchange_id, int group_size,
+                                     int64_t row_bytes, int64_t stride_rows,
+                                     int64_t expert_rows_offset, const int32_t* route_indices,
+                                     const void* gates, int gates_dtype, int dtype,
+                                     int64_t cell_num, void* dst_data, void* main_stream,
+                                     int stages) {
+  clear_error();
+  BRT_REQUIRE(c != nullptr, "null context");
+  BRT_REQUIRE(group_size >= 1 && row_bytes > 0 && row_bytes % 16 == 0 && stride_rows >= 0,
+              "bad bucket geometry");
+  BRT_REQUIRE(expert_rows_offset >= (int64_t)kControlBytes && expert_rows_offset % 16 == 0 &&
+                  (size_t)expert_rows_offset < kControlBytes + 2 * c->half_bytes,
+              "the expert outputs must lie in the landing halves of the arena, at a 16-byte "
+              "aligned offset that is the same on every rank");
+  if (stages == 0) stages = BRT_P2P_STAGE_POST | BRT_P2P_STAGE_PUSH | BRT_P2P_STAGE_WAIT;
+  const KeptMatrix& k = c->kept[exchange_id % kKept];
+  if (exchange_id == 0 || k.id != exchange_id || k.group != group_size)
+    return set_error(BRT_ERR_UNSUPPORTED,
+                     "the size matrix of forward exchange %llu is no longer kept",
+                     (unsigned long long)exchange_id);
+  if (int rc = check_alive(c)) return rc;
+  if (stages & BRT_P2P_STAGE_POST) {
+    BRT_REQUIRE(c->pending == 0, "the sizes of the previous forward exchange were never read");
+    c->exchanges++;
+    // "my expert outputs are complete": everything enqueued before is ordered by the stream
+    if (int rc = p2p_post_launch(nullptr, 0, c->world, c->rank, c->exchanges, nullptr,
+                                 c->ready_flags, replay_of(c, false), main_stream))
+      return rc;
+  }
+  const uint64_t x = c->exchanges;
+  if (stages & BRT_P2P_STAGE_PUSH) {
+    const void* rows_at[kMaxRanks];
+    for (int r = 0; r < c->world; r++) rows_at[r] = c->peer[r] + expert_rows_offset;
+    if (int rc = p2p_combine_land_launch(
+            dst_data, gates, gates_dtype, dtype, route_indices, cell_num, row_bytes,
+            kept_slot(c, k.slot), c->world, group_size, c->rank, stride_rows, rows_at, x,
+            c->base + kReadyOffset, c->arrive_flags, c->base + kCounterOffset,
+            c->base + kAbortOffset, c->base + kStatusOffset, c->host_status_dev, c->wait_ns,
+            replay_of(c, false, 1), main_stream))
+      return rc;
+  }
+  if (stages & BRT_P2P_STAGE_WAIT)
+    if (int rc = wait_arrivals(c, x, main_stream)) return rc;
+  return BRT_OK;
+}
+
 }  // extern "C"

@@ -273,38 +273,6 @@ __global__ void __launch_bounds__(kThreads) dispatch_tag_kernel(const MoveArgs a
 }
 
 // ---------------------------------------------------------------------------------- combine
-// (The packed fp32 instructions of sm_100, mul.rn.f32x2 / add.rn.f32x2, were tried here: the
-// results differed from the scalar sequence in the last bit and the kernel ran slower, so the
-// fold stays scalar.)
-template <int VB, int DT, int GMODE>
-__device__ __forceinline__ void fold_chunk(float (&acc)[Lanes<VB, DT>::N],
-                                           const typename Chunk<VB>::type& row, float g) {
-  using L = Lanes<VB, DT>;
-  float x[L::N];
-  unpack_chunk<VB, DT>(row, x);
-#pragma unroll
-  for (int i = 0; i < L::N; i++) {
-    if constexpr (GMODE != 0) x[i] = __fmul_rn(x[i], g);
-    acc[i] = __fadd_rn(acc[i], x[i]);
-  }
-}
-
-template <int DT, int GMODE>
-__device__ __forceinline__ float gate_at(const void* gates, int64_t at) {
-  if constexpr (GMODE == 1) return static_cast<const float*>(gates)[at];
-  if constexpr (GMODE == 2)
-    return Elem<DT>::to_f32(static_cast<const typename Elem<DT>::type*>(gates)[at]);
-  return 1.f;
-}
-
-// Per-warp staging area: kStages x (route table + kMaxRoutes row pieces of 2 KB).
-struct alignas(16) FoldStage {
-  uint4 rows[kMaxRoutes][kFoldVecs];
-  RouteSlot route[kMaxRoutes];
-  int count;
-  int pad[3];
-};
-
 // GMODE: 0 = no gates, 1 = fp32 gates, 2 = gates stored in the data type.
 // 16-byte rows only (VB == 16).
 template <int DT, int GMODE, int IV>

@@ -11,6 +11,7 @@ a CUDA graph inside ``brt_dist.replayable_exchanges()``.  The flow the experts g
 whole landing half seen as rows, of which the first ``loads.sum()`` are theirs, and ``loads``
 is a device tensor.  Peer-memory transport only.
 """
+import os
 from typing import List, Tuple, Union
 
 import torch
@@ -86,8 +87,13 @@ class DistributedFusedDispatchFabric(FusedDispatchFabric):
 @register_fabric("distributed_fused_combine")
 class DistributedFusedCombineFabric(FusedCombineFabric):
     def __init__(self, flow_num, reduction="add", transform=False, task_locality: bool = False,
-                 **kwargs) -> None:
+                 pull_combine: bool = None, **kwargs) -> None:
         self.task_locality = task_locality
+        # Inverse exchange and combine as ONE kernel that pulls the expert outputs from the
+        # peers (not in the reference).  Off by default: on the NVLink boxes it was measured
+        # on, the two kernels (rows pushed back, then combined locally) finish a little sooner.
+        self.pull_combine = (os.environ.get("BRT_P2P_PULL_COMBINE", "0") == "1"
+                             if pull_combine is None else bool(pull_combine))
         super().__init__(flow_num=flow_num, reduction=reduction, transform=transform, **kwargs)
 
     def combine(self, in_flows: List[GridTensor], residual_flows: List[GridTensor],
@@ -98,10 +104,19 @@ class DistributedFusedCombineFabric(FusedCombineFabric):
             out_loads = popped["in_loads"]
             data, tag_stack, load_stack, extra = to_torch_tensor(flow, retrieve_attr=True)
             residual = residual_flows[idx] if residual_flows is not None else None
-            data = brt_dist.size_known_group_sparse_a2a(data, in_loads, out_loads,
-                                                        self.max_path_padding)
-            (out,) = c_router.combine_with_indices_and_loads(
-                data, route_indices, out_loads, score if self.transform else None, residual,
-                max_path_padding=self.max_path_padding, ever_padded=self.ever_padded)
+            out = None
+            if residual is None and self.pull_combine:
+                # expert outputs that still sit in the arena (experts that work in place, or
+                # that wrote into brt_dist.expert_output_buffer) are pulled by the combine
+                # itself: inverse exchange and combine as one kernel
+                out = brt_dist.combine_group_sparse_a2a(
+                    data, route_indices, score if self.transform else None, in_loads,
+                    out_loads, self.max_path_padding)
+            if out is None:
+                data = brt_dist.size_known_group_sparse_a2a(data, in_loads, out_loads,
+                                                            self.max_path_padding)
+                (out,) = c_router.combine_with_indices_and_loads(
+                    data, route_indices, out_loads, score if self.transform else None, residual,
+                    max_path_padding=self.max_path_padding, ever_padded=self.ever_padded)
             out_flows.append(init_grid_tensor(out, tag_stack, load_stack, extra))
         return out_flows

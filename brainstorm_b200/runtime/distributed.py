@@ -144,6 +144,19 @@ def dispatch_group_sparse_a2a_device(in_data: torch.Tensor, route_indices: torch
                                                           max_path_padding, max_path_load)
 
 
+def combine_group_sparse_a2a(in_data: torch.Tensor, route_indices: torch.Tensor, gates,
+                             in_loads: torch.Tensor, out_loads: torch.Tensor,
+                             max_path_padding=False):
+    """``size_known_group_sparse_a2a`` + weighted combine as one kernel that pulls the expert
+    outputs over NVLink when the peer-memory transport can take it, else ``None`` (the caller
+    runs the two steps)."""
+    if is_nccl_activated():
+        return C_dist.combine_group_sparse_all_to_all(in_data, route_indices, gates, in_loads,
+                                                      out_loads, max_path_padding)
+    return None
+
+
+expert_output_buffer = C_dist.expert_output_buffer
 replayable_exchanges = C_dist.replayable_exchanges
 
 

@@ -162,6 +162,36 @@ class PeerArena:
                   grain, group_size, stride_rows, main, main, self._DEVICE_STAGES)
         return self._device_sizes(group_size, cells.device)
 
+    # ---- the inverse exchange folded into the combine ---------------------------------------
+    def offset_of(self, t: torch.Tensor):
+        """Byte offset of ``t`` inside the landing halves of this arena, or None when it lives
+        elsewhere."""
+        off = t.data_ptr() - self.base
+        nbytes = t.numel() * t.element_size()
+        if off < self.control_bytes or off + nbytes > self.total:
+            return None
+        return off
+
+    def expert_buffer(self, rows: int, like: torch.Tensor) -> torch.Tensor:
+        """``rows`` rows shaped like the rows of ``like`` in the landing half that the next
+        exchange would use: after a forward exchange that is the half its output is NOT in, a
+        place for expert outputs that ``combine_backward`` can pull from.  Every rank gets the
+        same offset."""
+        lo, hi = self._half_of_next_exchange()
+        if rows * _row_bytes(like) > hi - lo:
+            raise RuntimeError("the expert outputs do not fit a landing half")
+        return self.view(lo, rows, like)
+
+    def combine_backward(self, exchange_id: int, group_size: int, grain: int, stride_rows: int,
+                         rows_offset: int, route_indices: torch.Tensor, gates, gates_dtype: int,
+                         dtype: int, out: torch.Tensor) -> None:
+        """Enqueue the combine that pulls the expert outputs (at ``rows_offset`` in every
+        rank's arena, laid out as forward exchange ``exchange_id`` landed them) over NVLink."""
+        _lib.call("brt_p2p_combine_backward", self.ctx, exchange_id, group_size, grain,
+                  stride_rows, rows_offset, route_indices.data_ptr(),
+                  None if gates is None else gates.data_ptr(), gates_dtype, dtype,
+                  route_indices.size(0), out.data_ptr(), _lib.raw_stream(), 0)
+
     def sparse_backward(self, exchange_id: int, group_size: int, grain: int, stride_rows: int,
                         rows: torch.Tensor, layout: int = SPARSE_INVERSE,
                         zero_tails: bool = False):

@@ -636,6 +636,28 @@ BRT_API int brt_p2p_ctx_replay_end(brt_p2p_ctx* ctx);
 BRT_API int brt_p2p_forward_device_sizes(brt_p2p_ctx* ctx, int32_t* received_sizes,
                                          void* stream, void** out_data,
                                          int64_t* capacity_rows, uint64_t* exchange_id);
+/*
+ * The inverse exchange and the weighted combine in ONE kernel (replaces
+ * size_known_group_sparse_all_to_all followed by combine_with_indices_and_loads in
+ * python/brt/router/fabric/distributed.py:120-158): the combine of this rank's cells pulls
+ * every kept route's row straight from the arena of the rank that hosts the expert (16-byte
+ * peer loads), in the layout forward exchange `exchange_id` landed, folds in ascending path
+ * order with the roundings of brt_combine_with_indices_and_loads and writes dst_data
+ * [cell_num, row_bytes] (fully written; a cell without a kept route becomes zero).
+ * `expert_rows_offset`: byte offset, inside the arena, of the first row of the expert outputs;
+ * the same on every rank, inside the landing halves (the landed rows themselves when the
+ * experts work in place, else a buffer the experts wrote).  route_indices and gates as for
+ * brt_combine_with_indices_and_loads (seat indices, no residual); the loads are those of the
+ * forward exchange.  Stages POST | PUSH | WAIT as for the other exchanges: the post says "my
+ * expert outputs are complete", the wait returns once every rank has finished reading this
+ * rank's rows.  BRT_ERR_UNSUPPORTED (nothing enqueued): the matrix is no longer kept.
+ */
+BRT_API int brt_p2p_combine_backward(brt_p2p_ctx* ctx, uint64_t exchange_id, int group_size,
+                                     int64_t row_bytes, int64_t stride_rows,
+                                     int64_t expert_rows_offset, const int32_t* route_indices,
+                                     const void* gates, int gates_dtype, int dtype,
+                                     int64_t cell_num, void* dst_data, void* main_stream,
+                                     int stages);
 BRT_API int brt_p2p_sparse_backward(brt_p2p_ctx* ctx, uint64_t exchange_id, int group_size,
                                     int64_t grain_bytes, int64_t stride_rows, int layout,
                                     int zero_tails, const void* rows, void* main_stream,

@@ -148,10 +148,13 @@ def main():
     local = GatherRouter("fused_combine", {"transform": True})(
         ScatterRouter(protocol_type="topk", fabric_type="fused_dispatch",
                       protocol_kwargs={"top_k": 2})(Annotator([0])(x), score), None, score)
-    routed = ScatterRouter(protocol_type="topk", fabric_type="distributed_fused_dispatch",
-                           protocol_kwargs={"top_k": 2})(Annotator([0])(x), score)
-    ep = GatherRouter("distributed_fused_combine", {"transform": True})(routed, None, score)
-    assert torch.equal(ep.data, local.data), f"rank {rank}: expert-parallel route differs"
+    for pull in (False, True):  # inverse exchange + combine as two kernels, and as one that pulls
+        routed = ScatterRouter(protocol_type="topk", fabric_type="distributed_fused_dispatch",
+                               protocol_kwargs={"top_k": 2})(Annotator([0])(x), score)
+        ep = GatherRouter("distributed_fused_combine",
+                          {"transform": True, "pull_combine": pull})(routed, None, score)
+        assert torch.equal(ep.data, local.data), \
+            f"rank {rank}: expert-parallel route differs (pull_combine={pull})"
 
     if p2p.arena() is not None and p2p.ZERO_COPY:
         # the same route with the exchange's sizes left on the device (weighted dispatch takes
@@ -209,13 +212,18 @@ def main():
         cells = torch.zeros((T, d), device=dev)
         mask = torch.zeros((T, E), dtype=torch.int32, device=dev)
 
-        def step():
+        def step(pull=False):
             idx, loads = R.generate_indices_and_loads(mask)
             with brt_dist.replayable_exchanges():
                 landed, received, sent = brt_dist.dispatch_group_sparse_a2a_device(
                     cells, idx, loads)
-                back = brt_dist.size_known_group_sparse_a2a(landed, received, sent)
-            (y,) = R.combine_with_indices_and_loads(back, idx, loads, None, None)
+                if pull:
+                    y = brt_dist.combine_group_sparse_a2a(landed, idx, None, received, sent)
+                    assert y is not None
+                else:
+                    back = brt_dist.size_known_group_sparse_a2a(landed, received, sent)
+            if not pull:
+                (y,) = R.combine_with_indices_and_loads(back, idx, loads, None, None)
             return y, received, landed
 
         def fill(seed):
@@ -251,6 +259,24 @@ def main():
             torch.cuda.synchronize()
             check(y.clone(), received.clone(), landed[:int(received.sum())].clone(),
                   f"replay {seed}")
+        # the same step with the combine that pulls its rows from the peers, captured too
+        fill(7)
+        step(pull=True)
+        torch.cuda.synchronize()
+        dist.barrier()
+        pull_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(pull_graph):
+            y2, received2, landed2 = step(pull=True)
+        for seed in (8, 9):
+            fill(seed)
+            pull_graph.replay()
+            torch.cuda.synchronize()
+            snap = (y2.clone(), received2.clone(), landed2[:int(received2.sum())].clone())
+            graph.replay()  # the two graphs share the arena: they may alternate
+            torch.cuda.synchronize()
+            assert torch.equal(y, snap[0]), \
+                f"rank {rank}: pull replay {seed} differs from the two ops"
+            check(*snap, f"pull replay {seed}")
         # ordinary exchanges continue after the replays, and another replay after them
         xs, sizes = rank_inputs(rank, W, 2, 8, 20)
         o, ol, il = brt_dist.group_sparse_a2a(torch.from_numpy(xs).to(dev),
@@ -285,9 +311,11 @@ def main():
                     tokens, idx, loads)
                 per_expert = received.view(G, W).sum(dim=1).to(torch.int32)
                 hidden = X.grouped_expert_linear(landed[:bound], w1, per_expert, relu=True)
-                y = X.grouped_expert_linear(hidden, w2, per_expert)
-                back = brt_dist.size_known_group_sparse_a2a(y, received, sent)
-            (out,) = R.combine_with_indices_and_loads(back, idx, loads, gate_w, None)
+                # the experts' outputs go where the combine can pull them from the peers
+                y = X.grouped_expert_linear(hidden, w2, per_expert,
+                                            out=brt_dist.expert_output_buffer(bound, landed))
+                out = brt_dist.combine_group_sparse_a2a(y, idx, gate_w, received, sent)
+                assert out is not None
             return out
 
         def refill(seed):

@@ -602,3 +602,105 @@ def test_replay_section_rules_and_rows_that_do_not_fit():
         assert float((xs[0] * 2).sum()) == 2.0 * xs[0].numel()  # the device still answers
     finally:
         ranks.close()
+
+
+@pytest.mark.parametrize("world,group,cells,cols,k,mode,dtype,gated", [
+    (2, 2, 300, 8, 2, "packed", "f32", True), (4, 2, 257, 8, 2, "packed", "f32", False),
+    (8, 4, 500, 1024, 2, "packed", "bf16", True), (2, 4, 640, 600, 1, "packed", "f32", True),
+    (4, 1, 300, 16, 1, "padded", "f32", True), (8, 2, 400, 520, 2, "padded", "f32", True),
+    (2, 3, 200, 4, 2, "capacity", "f32", True), (4, 4, 900, 16, 3, "capacity", "f32", True),
+    (4, 2, 333, 64, 4, "packed", "bf16", True),
+])
+def test_combine_that_pulls_from_the_peers(world, group, cells, cols, k, mode, dtype, gated):
+    """Inverse exchange and weighted combine as one kernel: the cells come out as from the
+    checker's inverse walk of the exchange followed by its combine, bit for bit (fp32) or
+    within one rounding of the checker's bf16 arithmetic.  The experts multiply the landed rows
+    in place by a factor of their rank; k = 3 and 4 exercise the routes beyond the two staged
+    ones."""
+    from brainstorm_b200._C import router as R
+
+    dev = torch.device("cuda", 0)
+    tdt = torch.float32 if dtype == "f32" else torch.bfloat16
+    E = world * group
+    rng = np.random.default_rng(world * 131 + group * 17 + cells)
+    per_path = max(1, cells * k // E)
+    stride = 2 * per_path if mode == "padded" else 0
+    xs, idxs, loads, counts, gates = [], [], [], [], []
+    idx_np, loads_np, gates_np, rows_np = [], [], [], []
+    for r in range(world):
+        score = rng.standard_normal((cells, E)).astype(np.float32)
+        mask = oracle.topk_hot_mask(score, k)
+        x = rng.standard_normal((cells, cols)).astype(np.float32)
+        if dtype == "bf16":
+            x = oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits(x))
+        if mode == "padded":
+            thr = np.full(E, stride, dtype=np.int32)
+            m_np, _ = oracle.throttle_hotmask(mask, np.zeros(E, dtype=np.int32), thr)
+            i_np, l_np = oracle.generate_indices_and_loads(m_np)
+            i_t, l_t, _ = R.throttle_and_generate_indices(
+                torch.from_numpy(mask).to(dev), torch.zeros(E, dtype=torch.int32, device=dev),
+                torch.from_numpy(thr).to(dev))
+        else:
+            caps = [per_path // 2 + 1, 2 * per_path, 16 * per_path] if mode == "capacity" else None
+            i_np, l_np = oracle.generate_indices_and_loads(mask, caps, caps is not None)
+            i_t, l_t = R.generate_indices_and_loads(
+                torch.from_numpy(mask).to(dev),
+                None if caps is None else torch.tensor(caps, dtype=torch.int32, device=dev),
+                caps is not None)
+        g_np = np.abs(score) + 0.25
+        (routed,) = oracle.dispatch_with_indices_and_loads(
+            x, i_np, l_np, max_path_padding=bool(stride), max_path_load=stride)
+        xs.append(torch.from_numpy(x).to(dev).to(tdt))
+        idxs.append(i_t)
+        loads.append(l_t.contiguous())
+        counts.append(getattr(i_t, R._DENSE))
+        gates.append(torch.from_numpy(g_np).to(dev))
+        idx_np.append(i_np)
+        loads_np.append(l_np)
+        gates_np.append(g_np)
+        rows_np.append(routed)
+    fwd = oracle.sim_group_sparse_all_to_all(rows_np, loads_np, bool(stride), stride)
+    # the experts: every row on rank r is multiplied by r + 2 (exact in bf16 up to one rounding)
+    expert_out = []
+    for r in range(world):
+        y = fwd[r][0] * np.float32(r + 2)
+        if dtype == "bf16":
+            y = oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits(y))
+        expert_out.append(y)
+    back = oracle.sim_size_known_group_sparse_all_to_all(
+        expert_out, [f[1] for f in fwd], loads_np, bool(stride))
+    ranks = Ranks(world, half=32 << 20)
+    st = torch.cuda.current_stream().cuda_stream
+    grain = cols * (4 if dtype == "f32" else 2)
+    dt_code = 0 if dtype == "f32" else 2
+    try:
+        for repeat in range(2):
+            outs = ranks.dispatch_forward(xs, idxs, loads, counts, group, stride)
+            ids = [int(_lib.query("brt_p2p_ctx_exchanges", c)) for c in ranks.ctxs]
+            offsets = []
+            for r in range(world):
+                ptr, n_rows = outs[r]
+                ranks.rows_at(ptr, n_rows, cols, tdt).mul_(r + 2)
+                offsets.append(ptr - ranks.arenas[r])
+            assert len(set(offsets)) == 1
+            results = [torch.full((cells, cols), float("nan"), dtype=tdt, device=dev)
+                       for _ in range(world)]
+            for stage in (POST, PUSH, WAIT):
+                for r in range(world):
+                    _lib.call("brt_p2p_combine_backward", ranks.ctxs[r], ids[r], group, grain,
+                              stride, offsets[r], idxs[r].data_ptr(),
+                              gates[r].data_ptr() if gated else None, 0, dt_code, cells,
+                              results[r].data_ptr(), st, stage)
+            torch.cuda.synchronize()
+            for r in range(world):
+                (want,) = oracle.combine_with_indices_and_loads(
+                    oracle.to_bits(back[r], dtype), idx_np[r], loads_np[r],
+                    gates_np[r] if gated else None, None, bool(stride), dtype=dtype)
+                want = oracle.from_bits(want, dtype)
+                got = results[r].float().cpu().numpy()
+                assert np.array_equal(got, want), \
+                    f"rank {r}: {np.abs(got - want).max()} off the checker's combine"
+        for c in ranks.ctxs:
+            assert _lib.query("brt_p2p_ctx_status", c) == 0
+    finally:
+        ranks.close()
