@@ -52,6 +52,7 @@ struct DispatchLandArgs {
   long long half_bytes;
   unsigned long long epoch, limit_ns;
   unsigned long long* trace;                // see P2pReplay
+  unsigned long long* work_counter;         // see P2pReplay
   const unsigned long long* epoch_counter;  // see p2p::effective_epoch()
   int strict;              // rows that do not fit are reported as an error
   const int* sizes;        // [world][world * group] on my board
@@ -205,11 +206,40 @@ dispatch_land_kernel(const __grid_constant__ DispatchLandArgs a) {
       cp_async_commit();
     };
 
-    const ItemStep step = rows::step_of(warps, a.pieces_per_row);
-    ItemCursor at = rows::cursor_at(warp < items ? warp : 0, a.pieces_per_row);
-    if (warp >= items) at.cell = a.cell_num;
-    ItemCursor ahead = rows::advance(at, step);
-    ItemCursor ahead2 = rows::advance(ahead, step);
+    // The warp's items: a fixed share (every warps-th item), or, with a work counter, runs of
+    // kClaim consecutive items claimed from it, so that a warp whose rows went to a busy link
+    // takes fewer and the CTAs finish together.
+    constexpr int kClaim = 4;
+    int64_t next_static = warp;
+    int64_t claimed = 0;
+    int claimed_left = 0;
+    auto next_item = [&]() -> ItemCursor {
+      int64_t item;
+      if (a.work_counter == nullptr) {
+        item = next_static;
+        next_static += warps;
+      } else {
+        if (claimed_left == 0) {
+          unsigned long long base = 0;
+          if (lane == 0) base = atomicAdd(a.work_counter, (unsigned long long)kClaim);
+          claimed = (int64_t)__shfl_sync(0xffffffffu, base, 0);
+          claimed_left = kClaim;
+        }
+        item = claimed++;
+        claimed_left--;
+      }
+      ItemCursor c;
+      if (item < items) {
+        c = rows::cursor_at(item, a.pieces_per_row);
+      } else {
+        c.cell = a.cell_num;
+        c.piece = 0;
+      }
+      return c;
+    };
+    ItemCursor at = next_item();
+    ItemCursor ahead = next_item();
+    ItemCursor ahead2 = next_item();
     int stage = 0;
     fetch(at);
     issue(my[0], at);
@@ -261,7 +291,7 @@ dispatch_land_kernel(const __grid_constant__ DispatchLandArgs a) {
       __syncwarp();
       at = ahead;
       ahead = ahead2;
-      ahead2 = rows::advance(ahead2, step);
+      ahead2 = next_item();
       stage ^= 1;
     }
     cp_async_wait<0>();
@@ -288,6 +318,7 @@ dispatch_land_kernel(const __grid_constant__ DispatchLandArgs a) {
     const unsigned int prev = atomicAdd(a.done_counter, 1u);
     if (prev == gridDim.x - 1) {
       *a.done_counter = 0;
+      if (a.work_counter != nullptr) *a.work_counter = 0ull;
       const unsigned int aborted = atomicExch(a.abort_word, 0u);
       __threadfence_system();
       if (aborted == 0u)
@@ -381,6 +412,7 @@ int p2p_dispatch_land_launch(const void* src_data, const int32_t* route_indices,
   a.epoch_counter = static_cast<const unsigned long long*>(replay.epoch_counter);
   a.strict = replay.strict;
   a.trace = static_cast<unsigned long long*>(replay.trace);
+  a.work_counter = static_cast<unsigned long long*>(replay.work_counter);
   a.limit_ns = wait_limit_ns;
   a.sizes = size_matrix;
   a.keep = keep_matrix;

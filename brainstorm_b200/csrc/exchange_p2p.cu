@@ -131,6 +131,7 @@ struct LandArgs {
   long long half_bytes;   // capacity of a landing half
   unsigned long long epoch;
   unsigned long long* trace;                // see P2pReplay
+  unsigned long long* work_counter;         // see P2pReplay
   const unsigned long long* epoch_counter;  // see effective_epoch()
   int strict;             // a landing that does not fit is an error (reported), not a verdict
   unsigned long long limit_ns;
@@ -279,9 +280,10 @@ p2p_land_kernel(const char* __restrict__ src, const __grid_constant__ LandArgs a
   if (tracer) a.trace[3] = global_timer_ns();
   const long long total_chunks = go ? s_first[n] : 0;
   const long long run = (total_chunks + kWays - 1) / kWays;
-  for (long long k = blockIdx.x; k < run * kWays; k += gridDim.x) {
+  // one 32 KB chunk of the list, by position k in the interleaved order
+  auto copy_kth = [&](long long k) {
     const long long chunk = (k % kWays) * run + k / kWays;
-    if (chunk >= total_chunks) continue;
+    if (chunk >= total_chunks) return;
     int lo = 0, hi = n - 1;  // last bucket whose first chunk is <= chunk (empty ones skipped)
     while (lo < hi) {
       const int mid = (lo + hi + 1) >> 1;
@@ -294,6 +296,22 @@ p2p_land_kernel(const char* __restrict__ src, const __grid_constant__ LandArgs a
     if (bytes > kChunkBytes) bytes = kChunkBytes;
     copy_chunk(src + (long long)s_src[p] * a.grain + at,
                a.land[dest] + (long long)s_dst[p] * a.grain + at, bytes);
+  };
+  if (a.work_counter == nullptr) {
+    for (long long k = blockIdx.x; k < run * kWays; k += gridDim.x) copy_kth(k);
+  } else {
+    // Chunks are handed out one at a time from a counter: a CTA whose chunks went to a busy
+    // link simply takes fewer.  The claim of the next chunk is in flight during the copy.
+    __shared__ unsigned long long s_claim[2];
+    if (tid == 0) s_claim[0] = atomicAdd(a.work_counter, 1ull);
+    __syncthreads();
+    for (int turn = 0;; turn ^= 1) {
+      const long long k = (long long)s_claim[turn];
+      if (k >= run * kWays) break;
+      if (tid == 0) s_claim[turn ^ 1] = atomicAdd(a.work_counter, 1ull);
+      copy_kth(k);
+      __syncthreads();
+    }
   }
 
   if (move && a.layout >= 2 && a.zero_tails) {
@@ -342,6 +360,7 @@ p2p_land_kernel(const char* __restrict__ src, const __grid_constant__ LandArgs a
     const unsigned int prev = atomicAdd(a.done_counter, 1u);
     if (prev == gridDim.x - 1) {
       *a.done_counter = 0;  // ready for the next exchange (stream-ordered)
+      if (a.work_counter != nullptr) *a.work_counter = 0ull;
       const unsigned int aborted = atomicExch(a.abort_word, 0u);
       __threadfence_system();
       if (aborted == 0u)
@@ -577,6 +596,7 @@ int p2p_land_launch(const void* rows, const int32_t* size_matrix, int32_t* keep_
   a.epoch_counter = static_cast<const unsigned long long*>(replay.epoch_counter);
   a.strict = replay.strict;
   a.trace = static_cast<unsigned long long*>(replay.trace);
+  a.work_counter = static_cast<unsigned long long*>(replay.work_counter);
   a.limit_ns = wait_limit_ns;
   a.sizes = size_matrix;
   a.keep = keep_matrix;

@@ -121,6 +121,10 @@ struct P2pReplay {
   // saw every rank ready, the last CTA finished (flags raised), CTA 0 had its plan, the
   // first and the last CTA left their copy loops.  Null: no trace.
   void* trace = nullptr;
+  // a uint64 in the rank's own arena, zero between launches: the landing kernels hand out
+  // their work items from it (warps and CTAs that finish early take more) instead of
+  // giving every warp a fixed share.  Null: fixed shares.
+  void* work_counter = nullptr;
 };
 int p2p_land_launch(const void* rows, const int32_t* size_matrix, int32_t* keep_matrix,
                     int world_size, int group_size, int my_rank, int layout, int zero_tails,

@@ -9,6 +9,7 @@
 //   512      uint32       completion counter of this rank's landing kernel
 //   516      uint32       abort word of this rank's landing kernel
 //   520      uint64       epoch counter: exchanges this rank has opened (device-side count)
+//   528      uint64       work counter of this rank's landing kernel (zero between launches)
 //   1024     int32        status word of the bounded waits
 //   1088     2 x 8 uint64 timing trace of the last forward / inverse landing kernel
 //   2048     two size boards of kBoardInts int32 each, used alternately
@@ -44,6 +45,7 @@ constexpr size_t kReadyOffset = 256;
 constexpr size_t kCounterOffset = 512;
 constexpr size_t kAbortOffset = 516;
 constexpr size_t kEpochCounter = 520;
+constexpr size_t kWorkCounter = 528;
 constexpr size_t kStatusOffset = 1024;
 constexpr size_t kTraceOffset = 1088;
 constexpr size_t kBoardOffset = 2048;
@@ -116,6 +118,7 @@ P2pReplay replay_of(const brt_p2p_ctx* c, bool strict, int trace_slot = -1) {
   r.epoch_counter = c->base + kEpochCounter;
   r.strict = strict ? 1 : 0;
   if (trace_slot >= 0) r.trace = c->base + kTraceOffset + 64 * trace_slot;
+  r.work_counter = c->base + kWorkCounter;
   return r;
 }
 
