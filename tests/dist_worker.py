@@ -354,6 +354,16 @@ def main():
                 f"rank {rank}: FFN layer differs from the fp32 reference by {err}"
 
     p2p.check_status()
+    if p2p.arena() is not None:
+        # the collective reset (what a job does after a wait ran out): every rank back to its
+        # initial state, then the exchanges work again
+        p2p.reset()
+        assert int(p2p.arena().status()) == 0
+        xs, sizes = rank_inputs(rank, W, 3, 8, 15)
+        o, ol, il = brt_dist.group_sparse_a2a(torch.from_numpy(xs).to(dev),
+                                              torch.from_numpy(sizes).to(dev))
+        assert np.array_equal(brt_dist.size_known_group_sparse_a2a(o, ol, il).cpu().numpy(), xs)
+        p2p.check_status()
     dist.barrier()
     if rank == 0:
         print("DIST_OK", W)
