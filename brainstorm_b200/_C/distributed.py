@@ -528,7 +528,11 @@ class replayable_exchanges:
         return self
 
     def __exit__(self, exc_type, exc, tb):
-        p2p.arena().replay_end()
+        try:
+            p2p.arena().replay_end()
+        except Exception:
+            if exc_type is None:  # otherwise the error that ended the block is the one to show
+                raise
         return False
 
 

@@ -88,6 +88,7 @@ struct brt_p2p_ctx {
   uint64_t pending = 0;
   int pending_slot = 0;
   size_t pending_board = 0;  // byte offset of its size board in every arena
+  bool pending_sizes_on_host = false;  // its SIZES stage was issued
   bool replaying = false;
   uint64_t replay_slots = 0;
   int group = 0, layout = 0;
@@ -282,6 +283,7 @@ int forward_begin(brt_p2p_ctx* c, const void* rows, const FusedDispatch* fused,
     c->pending = c->exchanges;
     c->pending_slot = c->replaying ? kKept + (int)(c->replay_slots++ % kKeptReplay)
                                    : (int)(c->exchanges % kKept);
+    c->pending_sizes_on_host = false;
     c->pending_board = (c->replaying ? kReplayBoardOffset : kBoardOffset) +
                        4 * (c->exchanges & 1) * kBoardInts;
     c->group = group_size;
@@ -316,6 +318,7 @@ int forward_begin(brt_p2p_ctx* c, const void* rows, const FusedDispatch* fused,
                                  side));
     BRT_CUDA_TRY(cudaMemcpyAsync(c->pinned + 1, c->base + board, (size_t)c->world * n * 4,
                                  cudaMemcpyDeviceToHost, side));
+    c->pending_sizes_on_host = true;
   }
   if (stages & BRT_P2P_STAGE_PUSH) {
     int32_t* keep = kept_slot(c, c->pending_slot);
@@ -374,6 +377,9 @@ BRT_API int brt_p2p_sparse_forward_sizes(brt_p2p_ctx* c, void* side_stream,
                   out_data != nullptr && exchange_id != nullptr,
               "null pointers");
   BRT_REQUIRE(c->pending != 0, "no forward exchange in flight");
+  BRT_REQUIRE(c->pending_sizes_on_host,
+              "this exchange was issued without BRT_P2P_STAGE_SIZES: its sizes are on the "
+              "device only (brt_p2p_forward_device_sizes)");
   BRT_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(side_stream)));
   const uint64_t x = c->pending;
   c->pending = 0;

@@ -575,6 +575,19 @@ def test_replay_section_rules_and_rows_that_do_not_fit():
             _lib.call("brt_p2p_sparse_forward_begin", ranks.ctxs[0], xs[0].data_ptr(),
                       sizes[0].data_ptr(), group, cols * 4, 0, 1, st, st, 0)
         _lib.call("brt_p2p_ctx_replay_end", ranks.ctxs[0])  # empty section: fine
+        # sizes that were never sent to the host cannot be read there
+        _lib.call("brt_p2p_sparse_forward_begin", ranks.ctxs[0], xs[0].data_ptr(),
+                  sizes[0].data_ptr(), group, cols * 4, 0, 1, st, st, POST)
+        with pytest.raises(_lib.BrtError):
+            m = ctypes.POINTER(ctypes.c_int32)()
+            n_rows, fits = ctypes.c_int64(), ctypes.c_int()
+            out, xid = ctypes.c_void_p(), ctypes.c_uint64()
+            _lib.call("brt_p2p_sparse_forward_sizes", ranks.ctxs[0], st, ctypes.byref(m),
+                      ctypes.byref(n_rows), ctypes.byref(fits), ctypes.byref(out),
+                      ctypes.byref(xid))
+        torch.cuda.synchronize()
+        for c in ranks.ctxs:  # rank 0 alone posted an exchange: start over
+            _lib.call("brt_p2p_ctx_reset_status", c)
         with pytest.raises(_lib.BrtError):
             _lib.call("brt_p2p_ctx_replay_end", ranks.ctxs[0])  # none open
         # rank 1 would receive 32 rows = 128 KB: nothing moves, and the status says why
