@@ -717,3 +717,95 @@ def test_combine_that_pulls_from_the_peers(world, group, cells, cols, k, mode, d
             assert _lib.query("brt_p2p_ctx_status", c) == 0
     finally:
         ranks.close()
+
+
+@pytest.mark.parametrize("world,group,cells,cols,dtype,gate_kind", [
+    (3, 1, [5, 0, 1], 8, "f32", "f32"),       # a rank without cells, a rank with one; E = 3: narrow index rows
+    (2, 3, [40, 17], 16, "f16", "data"),      # fp16 rows with fp16 gates; E = 6
+    (2, 2, [33, 64], 24, "bf16", "data"),     # bf16 gates
+    (5, 1, [9, 9, 9, 9, 9], 4, "f32", "none"),
+])
+def test_combine_that_pulls_edge_cases(world, group, cells, cols, dtype, gate_kind):
+    """Uneven and empty cell counts per rank, path counts that are not multiples of 4 (one
+    index per lane), gates stored in the data type, no gates.  Packed buckets; the forward
+    exchange is the unfused one (rows dispatched by the checker)."""
+    dev = torch.device("cuda", 0)
+    tdt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[dtype]
+    dt_code = {"f32": 0, "f16": 1, "bf16": 2}[dtype]
+    E = world * group
+    rng = np.random.default_rng(world * 7 + group)
+
+    def rounded(a):
+        return oracle.from_bits(oracle.to_bits(np.ascontiguousarray(a, dtype=np.float32), dtype),
+                                dtype)
+
+    idx_np, loads_np, gates_np, rows_np = [], [], [], []
+    for r in range(world):
+        T = cells[r]
+        mask = oracle.topk_hot_mask(rng.standard_normal((T, E)).astype(np.float32), min(2, E)) \
+            if T else np.zeros((0, E), dtype=np.int32)
+        x = rounded(rng.standard_normal((T, cols)))
+        i_np, l_np = oracle.generate_indices_and_loads(mask) if T else \
+            (np.zeros((0, E), dtype=np.int32), np.zeros(E, dtype=np.int32))
+        (routed,) = oracle.dispatch_with_indices_and_loads(x, i_np, l_np) if T else \
+            (np.zeros((0, cols), dtype=np.float32),)
+        idx_np.append(i_np)
+        loads_np.append(l_np)
+        gates_np.append(rounded(rng.random((T, E)) + 0.5))
+        rows_np.append(routed)
+    fwd = oracle.sim_group_sparse_all_to_all(rows_np, loads_np, False, 0)
+    expert_out = [rounded(fwd[r][0] * np.float32(r + 2)) for r in range(world)]
+    back = oracle.sim_size_known_group_sparse_all_to_all(
+        expert_out, [f[1] for f in fwd], loads_np, False)
+    ranks = Ranks(world)
+    st = torch.cuda.current_stream().cuda_stream
+    grain = cols * (4 if dtype == "f32" else 2)
+    try:
+        xs = [torch.from_numpy(a).to(dev).to(tdt) for a in rows_np]
+        sizes = [torch.from_numpy(l).to(dev) for l in loads_np]
+        idxs = [torch.from_numpy(i).to(dev).contiguous() for i in idx_np]
+        if gate_kind == "none":
+            gates, gdt = [None] * world, 0
+        elif gate_kind == "f32":
+            gates, gdt = [torch.from_numpy(g).to(dev) for g in gates_np], 0
+        else:
+            gates, gdt = [torch.from_numpy(g).to(dev).to(tdt) for g in gates_np], dt_code
+        outs, ids, fit = ranks.forward(xs, sizes, group)
+        assert all(fit)
+        offsets = []
+        for r in range(world):
+            ptr, n_rows, _ = outs[r]
+            if n_rows:
+                ranks.rows_at(ptr, n_rows, cols, tdt).mul_(r + 2)
+            offsets.append(ptr - ranks.arenas[r])
+        results = [torch.full((max(cells[r], 1), cols), float("nan"), dtype=tdt, device=dev)
+                   for r in range(world)]
+        for stage in (POST, PUSH, WAIT):
+            for r in range(world):
+                _lib.call("brt_p2p_combine_backward", ranks.ctxs[r], ids[r], group, grain, 0,
+                          offsets[r], idxs[r].data_ptr() if cells[r] else results[r].data_ptr(),
+                          None if gates[r] is None or not cells[r] else gates[r].data_ptr(),
+                          gdt, dt_code, cells[r], results[r].data_ptr(), st, stage)
+        torch.cuda.synchronize()
+        for r in range(world):
+            T = cells[r]
+            if T == 0:
+                continue
+            # (a single cell is combined like any other number here; the checker mirrors the
+            # reference's shortcut for T == 1, so it is given a second, unrouted cell)
+            i_chk, g_chk = idx_np[r], gates_np[r]
+            if T == 1:
+                i_chk = np.concatenate([i_chk, np.zeros((1, E), dtype=np.int32)])
+                g_chk = np.concatenate([g_chk, np.ones((1, E), dtype=np.float32)])
+            (want,) = oracle.combine_with_indices_and_loads(
+                oracle.to_bits(back[r], dtype), i_chk, loads_np[r],
+                None if gate_kind == "none" else
+                (g_chk if gate_kind == "f32" else oracle.to_bits(g_chk, dtype)),
+                None, False, dtype=dtype, gates_dtype="f32" if gate_kind != "data" else dtype)
+            want = oracle.from_bits(want, dtype)[:T]
+            got = results[r][:T].float().cpu().numpy()
+            assert np.array_equal(got, want), f"rank {r}: {np.abs(got - want).max()}"
+        for c in ranks.ctxs:
+            assert _lib.query("brt_p2p_ctx_status", c) == 0
+    finally:
+        ranks.close()
