@@ -657,6 +657,11 @@ def run_gpu(args):
             plain["round_trip_bit_exact"] and hot["round_trip_bit_exact"]
             and skewed["round_trip_bit_exact"])
         result["locality"] = measure_locality(loads, world, dev, brt_dist)
+        try:
+            result["balanced_placement"] = measure_balanced_placement(
+                dev, rank, world, x, mask, gates, caps, cap, padded, R, brt_dist, args.steps)
+        except Exception as exc:  # noqa: BLE001  (an extra, never the reason a run fails)
+            result["balanced_placement"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:160]}
         fwd = a2a_bytes[0]
         land_name = "dispatch_land_kernel" if fused_used[0] else "p2p_land_forward_kernel"
         land = device_kernels.get(land_name)
@@ -940,6 +945,100 @@ def measure_a2a_cfg4(dev, rank, world, R, brt_dist, local_bias: float, iters: in
                      else "nccl send/recv",
         "loads_rank": loads,
     }
+
+
+def measure_balanced_placement(dev, rank, world, x, mask, gates, caps, cap, padded, R, brt_dist,
+                               steps: int):
+    """The same step with the experts re-placed so that every rank hosts about the same number
+    of routed rows (what a placement search is for: python/brt/runtime/placement.py:139-357
+    searches placements from captured loads).  The exchange is bound by the busiest receiver's
+    link; with popular experts spread over the ranks that receiver is an average one.  Experts
+    are dealt to ranks greedily, most popular first, each rank taking E / W of them; the
+    columns of the hot mask and of the gates are permuted accordingly.  Returns the step time
+    (CUDA graph replay when every rank could capture, else eager) and the busiest receiver's
+    share before and after."""
+    import torch.distributed as dist
+    from brainstorm_b200.runtime import p2p as brt_p2p
+
+    E = mask.size(1)
+    G = E // world
+    if padded:
+        m, _ = R.throttle_hotmask(mask, torch.zeros_like(caps), caps)
+    else:
+        m = mask
+    mine = m.sum(dim=0).to(torch.int64)
+    per_rank = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(per_rank, mine)
+    S = torch.stack(per_rank).cpu()              # [source rank][expert]
+    totals = S.sum(dim=0).tolist()
+
+    def busiest_over_mean(assign):               # assign[p] = expert at position p
+        S_perm = S[:, assign].reshape(world, world, G).sum(dim=2).clone()   # [source][dest]
+        S_perm.fill_diagonal_(0)
+        return float(S_perm.sum(dim=0).max()) / max(float(S_perm.sum(dim=1).float().mean()), 1.0)
+
+    bins, sums = [[] for _ in range(world)], [0] * world
+    for e in sorted(range(E), key=lambda i: -totals[i]):
+        r = min((i for i in range(world) if len(bins[i]) < G), key=lambda i: sums[i])
+        bins[r].append(e)
+        sums[r] += totals[e]
+    assign = [e for b in bins for e in sorted(b)]
+    perm = torch.tensor(assign, dtype=torch.int64, device=dev)
+    mask_b = mask.index_select(1, perm).contiguous()
+    gates_b = gates.index_select(1, perm).contiguous()
+    zeros_e = torch.zeros((E,), dtype=torch.int32, device=dev)
+
+    def step():
+        if padded:
+            idx, loads, _ = R.throttle_and_generate_indices(mask_b, torch.zeros_like(zeros_e),
+                                                            caps, caps)
+        else:
+            idx, loads = R.generate_indices_and_loads(mask_b, caps)
+        with brt_dist.replayable_exchanges():
+            recv, out_loads, in_loads = brt_dist.dispatch_group_sparse_a2a_device(
+                x, idx, loads, padded, cap)
+            back = brt_dist.size_known_group_sparse_a2a(recv, out_loads, in_loads, padded)
+        (out,) = R.combine_with_indices_and_loads(back, idx, loads, gates_b, None, padded)
+        return out
+
+    graph, why = None, ""
+    try:
+        if brt_p2p.arena() is None:
+            raise RuntimeError("no peer-memory arena")
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step()
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                step()
+        torch.cuda.current_stream().wait_stream(side)
+    except Exception as exc:  # noqa: BLE001
+        graph, why = None, f"{type(exc).__name__}: {exc}"[:160]
+    agreed = torch.tensor([1 if graph is not None else 0], device=dev)
+    dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+    if int(agreed.item()) != 1:
+        return {"unavailable": why or "another rank could not capture the step"}
+    for _ in range(3):
+        graph.replay()
+    dist.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        graph.replay()
+    b.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(b) / steps], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return {"ms_per_step": float(t.item()),
+            "busiest_receiver_over_mean": {"block_placement": round(busiest_over_mean(list(range(E))), 3),
+                                           "balanced_placement": round(busiest_over_mean(assign), 3)},
+            "note": "same cells, gates and capacities; experts dealt to ranks most popular "
+                    "first so that every rank receives about the mean (the headline value "
+                    "keeps the block placement of the stated config)"}
 
 
 def measure_locality(loads, world, dev, brt_dist):
