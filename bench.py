@@ -953,8 +953,9 @@ def measure_balanced_placement(dev, rank, world, x, mask, gates, caps, cap, padd
     of routed rows (what a placement search is for: python/brt/runtime/placement.py:139-357
     searches placements from captured loads).  The exchange is bound by the busiest receiver's
     link; with popular experts spread over the ranks that receiver is an average one.  Experts
-    are dealt to ranks greedily, most popular first, each rank taking E / W of them; the
-    columns of the hot mask and of the gates are permuted accordingly.  Returns the step time
+    are dealt to ranks greedily, most popular first, each rank taking E / W of them
+    (``runtime.placement.load_balanced_placement``); the columns of the hot mask and of the
+    gates are permuted accordingly.  Returns the step time
     (CUDA graph replay when every rank could capture, else eager) and the busiest receiver's
     share before and after."""
     import torch.distributed as dist
@@ -977,12 +978,8 @@ def measure_balanced_placement(dev, rank, world, x, mask, gates, caps, cap, padd
         S_perm.fill_diagonal_(0)
         return float(S_perm.sum(dim=0).max()) / max(float(S_perm.sum(dim=1).float().mean()), 1.0)
 
-    bins, sums = [[] for _ in range(world)], [0] * world
-    for e in sorted(range(E), key=lambda i: -totals[i]):
-        r = min((i for i in range(world) if len(bins[i]) < G), key=lambda i: sums[i])
-        bins[r].append(e)
-        sums[r] += totals[e]
-    assign = [e for b in bins for e in sorted(b)]
+    from brainstorm_b200.runtime.placement import load_balanced_placement
+    assign = [e for hosted in load_balanced_placement(totals, world) for e in hosted]
     perm = torch.tensor(assign, dtype=torch.int64, device=dev)
     mask_b = mask.index_select(1, perm).contiguous()
     gates_b = gates.index_select(1, perm).contiguous()

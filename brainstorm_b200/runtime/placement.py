@@ -301,6 +301,29 @@ def search_placement(decision_histories: Sequence[Sequence[np.ndarray]], world_s
 
 
 # ----------------------------------------------------------------------------- applying it
+def load_balanced_placement(expert_loads: Sequence[float], world_size: int) -> List[List[int]]:
+    """Experts dealt to ranks so that every rank hosts about the same load: most loaded expert
+    first, each to the rank with the smallest load so far that still has room (every rank
+    takes ``E / world_size`` experts); experts of a rank in ascending order.  Not in the
+    reference, whose search (python/brt/runtime/placement.py:139-357) minimises the cells that
+    change ranks between two layers; this one evens out what the ranks RECEIVE in one layer,
+    which is what bounds the expert-parallel exchange when some experts are popular.  The
+    result has the form the other helpers take (``placement_to_indices``,
+    ``reorder_gate_rows``)."""
+    E = len(expert_loads)
+    if world_size < 1 or E % world_size != 0:
+        raise ValueError("the experts must divide evenly over the ranks")
+    per_rank = E // world_size
+    bins: List[List[int]] = [[] for _ in range(world_size)]
+    sums = [0.0] * world_size
+    for e in sorted(range(E), key=lambda i: (-float(expert_loads[i]), i)):
+        r = min((i for i in range(world_size) if len(bins[i]) < per_rank),
+                key=lambda i: (sums[i], i))
+        bins[r].append(e)
+        sums[r] += float(expert_loads[e])
+    return [sorted(b) for b in bins]
+
+
 def placement_to_indices(placement: Sequence[Sequence[int]]) -> torch.Tensor:
     """Expert ids in the order the ranks host them (rank 0's experts, then rank 1's, ...): row
     i of a gate reordered with it scores the expert that now has global index i."""

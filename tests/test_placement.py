@@ -3,6 +3,7 @@ search itself against exhaustive enumeration on small problems."""
 import itertools
 
 import numpy as np
+import pytest
 import torch
 
 from brainstorm_b200.runtime import placement as P
@@ -106,3 +107,23 @@ def test_gate_rows_follow_the_experts():
     keys, mine, indices = P.generate_rank_placement(2, 4, expert_keys=[(2, 1), (2, 3)],
                                                     global_expert_num=8)
     assert mine[(2, 3)] == [4, 5] and indices[(2, 1)].tolist() == list(range(8))
+
+
+def test_load_balanced_placement_evens_out_the_ranks():
+    from brainstorm_b200.runtime.placement import load_balanced_placement
+
+    rng = np.random.default_rng(5)
+    for world, per_rank in ((2, 16), (4, 8), (8, 4), (8, 16)):
+        loads = np.exp(rng.standard_normal(world * per_rank))      # a few popular experts
+        placement = load_balanced_placement(loads.tolist(), world)
+        assert sorted(e for hosted in placement for e in hosted) == list(range(world * per_rank))
+        assert all(len(hosted) == per_rank and hosted == sorted(hosted) for hosted in placement)
+        balanced = max(sum(loads[e] for e in hosted) for hosted in placement)
+        block = max(loads[r * per_rank:(r + 1) * per_rank].sum() for r in range(world))
+        mean = loads.sum() / world
+        assert balanced <= block + 1e-9
+        assert balanced <= 1.25 * mean, (world, per_rank, balanced / mean)
+    with pytest.raises(ValueError):
+        load_balanced_placement([1.0, 2.0, 3.0], 2)
+    # ties are broken by index, so every rank computes the same placement
+    assert load_balanced_placement([1.0] * 8, 4) == [[0, 4], [1, 5], [2, 6], [3, 7]]
